@@ -1,0 +1,111 @@
+"""ctypes binding of libhdit_b200.so (declared in include/hdit.h).
+
+The library is the only compute path of this package: if it is missing or a
+call fails, an exception is raised -- there is no eager/PyTorch fallback.
+"""
+import ctypes
+import os
+import threading
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libhdit_b200.so")
+
+HDIT_OK = 0
+HDIT_ERR_BAD_ARG = 1
+HDIT_ERR_SHAPE = 2
+HDIT_ERR_CUDA = 3
+HDIT_ERR_NOT_INITIALISED = 4
+HDIT_ERR_PEER_TIMEOUT = 5
+HDIT_ERR_TOO_LARGE = 6
+
+HDIT_BF16, HDIT_FP16, HDIT_FP32 = 0, 1, 2
+HDIT_MAX_Q_SEG = 2
+HDIT_MAX_KV_SEG = 10
+
+ATTN_FINAL, ATTN_PARTIAL_FIRST, ATTN_PARTIAL_MERGE, ATTN_MERGE_FINAL = 0, 1, 2, 3
+
+
+class HditError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, code, message):
+        super().__init__(f"hdit status {code}: {message}")
+        self.code = code
+
+
+class Seg(ctypes.Structure):
+    _fields_ = [
+        ("ptr", ctypes.c_void_p),
+        ("len", ctypes.c_int64),
+        ("stride_b", ctypes.c_int64),
+        ("stride_s", ctypes.c_int64),
+        ("stride_h", ctypes.c_int64),
+    ]
+
+
+class AttnArgs(ctypes.Structure):
+    _fields_ = [
+        ("dtype", ctypes.c_int32),
+        ("mode", ctypes.c_int32),
+        ("batch", ctypes.c_int32),
+        ("heads", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("n_q_seg", ctypes.c_int32),
+        ("n_kv_seg", ctypes.c_int32),
+        ("softmax_scale", ctypes.c_float),
+        ("q", Seg * HDIT_MAX_Q_SEG),
+        ("k", Seg * HDIT_MAX_KV_SEG),
+        ("v", Seg * HDIT_MAX_KV_SEG),
+        ("out", ctypes.c_void_p),
+        ("out_stride_b", ctypes.c_int64),
+        ("out_stride_s", ctypes.c_int64),
+        ("out_stride_h", ctypes.c_int64),
+        ("lse", ctypes.c_void_p),
+        ("acc_out", ctypes.c_void_p),
+        ("acc_lse", ctypes.c_void_p),
+        ("stream", ctypes.c_void_p),
+    ]
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+def _declare(lib):
+    lib.hdit_version.restype = ctypes.c_int
+    lib.hdit_version.argtypes = []
+    lib.hdit_last_error.restype = ctypes.c_char_p
+    lib.hdit_last_error.argtypes = []
+    lib.hdit_device_status.restype = ctypes.c_int
+    lib.hdit_device_status.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int32), ctypes.c_int]
+    lib.hdit_attn_fwd.restype = ctypes.c_int
+    lib.hdit_attn_fwd.argtypes = [ctypes.POINTER(AttnArgs)]
+
+
+def lib():
+    """The loaded shared library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    raise ImportError(
+                        f"{LIB_PATH} is missing: build it with `python -m hetu_dit_b200.build` "
+                        "(there is no fallback compute path)"
+                    )
+                handle = ctypes.CDLL(LIB_PATH)
+                _declare(handle)
+                _lib = handle
+    return _lib
+
+
+def check(code):
+    if code != HDIT_OK:
+        raise HditError(code, lib().hdit_last_error().decode("utf-8", "replace"))
+
+
+def device_status(device, clear=False):
+    """(code, block, where, iteration) written by the first failed bounded wait, or zeros."""
+    out = (ctypes.c_int32 * 4)()
+    check(lib().hdit_device_status(int(device), out, 1 if clear else 0))
+    return tuple(out)

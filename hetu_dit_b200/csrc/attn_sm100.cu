@@ -1,0 +1,694 @@
+// Joint flash-attention forward for sm_100a.
+//
+// One CTA owns two 128-row Q tiles of one (batch, head) and walks the KV
+// sequence in 128-row blocks:
+//
+//   warp 8      TMA producer   : Q tiles once, then K/V blocks through two rings
+//   warp 9      MMA issuer     : S = Q K^T (tcgen05.mma, smem x smem -> TMEM)
+//                                O += P V  (tcgen05.mma, TMEM x smem -> TMEM)
+//   warps 0-3   softmax group 0: owns Q tile 0, one thread per row
+//   warps 4-7   softmax group 1: owns Q tile 1
+//
+// The two softmax groups ping-pong against the tensor pipe: while group 0
+// exponentiates S0 the MMA warp runs P1 V and the next Q1 K^T, and vice versa.
+// P overwrites S in TMEM as packed 16-bit pairs and is consumed from there.
+// The running maximum is updated lazily (only when it grows by more than 2^8),
+// so O is rescaled in TMEM rarely.
+//
+// TMEM columns: S0/P0 [0,128)  S1/P1 [128,256)  O0 [256,256+D)  O1 [256+D,256+2D).
+//
+// Q and K/V are lists of segments (image tokens, text tokens, ring blocks), each
+// with its own TMA descriptor, so no concatenated copy exists; a tile or block
+// never straddles two segments and ragged tails are masked per block.
+//
+// All waits are bounded; on time-out the CTA records where it gave up in the
+// device status block, drains, frees its TMEM and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include <mutex>
+
+#include "host_common.h"
+#include "ptx_sm100.cuh"
+
+namespace hdit {
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 128;
+constexpr int kNumThreads = 320;
+constexpr int kPanelBytes = 128 * 128;  // 128 rows x 64 16-bit elements, 128B-swizzled
+constexpr uint32_t kSpinLimit = 8u * 1000u * 1000u;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr float kLn2 = 0.69314718055994531f;
+
+enum Where : int {
+  W_PROD_KEMPTY = 1,
+  W_PROD_VEMPTY = 2,
+  W_MMA_QFULL = 3,
+  W_MMA_KFULL = 4,
+  W_MMA_VFULL = 5,
+  W_MMA_PREADY = 6,
+  W_SM_SFULL = 7,
+  W_SM_ODONE = 8,
+};
+
+struct alignas(64) AttnKernelParams {
+  CUtensorMap q_map[HDIT_MAX_Q_SEG];
+  CUtensorMap k_map[HDIT_MAX_KV_SEG];
+  CUtensorMap v_map[HDIT_MAX_KV_SEG];
+  int q_len[HDIT_MAX_Q_SEG];
+  int kv_len[HDIT_MAX_KV_SEG];
+  // 1 if the descriptor's dims are (D, S, H, B) instead of (D, H, S, B)
+  unsigned char q_swap[HDIT_MAX_Q_SEG];
+  unsigned char k_swap[HDIT_MAX_KV_SEG];
+  unsigned char v_swap[HDIT_MAX_KV_SEG];
+  int n_q_seg, n_kv_seg;
+  int batch, heads;
+  int n_tiles_seg0, n_tiles, n_pairs;
+  int n_kv_blocks;
+  int mode;
+  float scale_log2;
+  void* out;
+  long long out_sb, out_ss, out_sh;
+  float* lse;
+  float* acc_out;
+  float* acc_lse;
+  long long sq_total;
+  int32_t* status;
+};
+
+template <int D>
+struct Cfg {
+  static constexpr int kPanels = D / 64;
+  static constexpr int kTileBytes = kPanels * kPanelBytes;
+  static constexpr int kStages = (D == 128) ? 2 : 4;
+  static constexpr int kSmemQ = 2 * kTileBytes;
+  static constexpr int kSmemK = kStages * kTileBytes;
+  static constexpr int kSmemV = kStages * kTileBytes;
+  static constexpr int kNumBars = 2 + 4 * kStages + 6;
+  static constexpr int kSmemBytes = kSmemQ + kSmemK + kSmemV + 1024 /*align*/ + 512 /*barriers etc.*/;
+  static constexpr uint32_t kTmemCols = 512;
+  static constexpr uint32_t kColS = 0;      // + t * 128
+  static constexpr uint32_t kColO = 256;    // + t * D
+};
+
+struct KvCursor {
+  int seg;
+  int row0;
+  __device__ __forceinline__ void advance(const AttnKernelParams& p) {
+    row0 += kBlockN;
+    if (row0 >= p.kv_len[seg]) {
+      ++seg;
+      row0 = 0;
+    }
+  }
+};
+
+__device__ __forceinline__ void tile_coords(const AttnKernelParams& p, int tile, int& seg, int& row0, int& out_row0) {
+  if (tile < p.n_tiles_seg0) {
+    seg = 0;
+    row0 = tile * kBlockM;
+    out_row0 = row0;
+  } else {
+    seg = 1;
+    row0 = (tile - p.n_tiles_seg0) * kBlockM;
+    out_row0 = p.q_len[0] + row0;
+  }
+}
+
+__device__ __forceinline__ void load_tile(const CUtensorMap* map, bool swapped, char* smem, uint64_t* bar, int panels,
+                                          int h, int row0, int b) {
+  for (int pn = 0; pn < panels; ++pn) {
+    if (swapped)
+      tma_load_4d(smem + pn * kPanelBytes, map, bar, pn * 64, row0, h, b);
+    else
+      tma_load_4d(smem + pn * kPanelBytes, map, bar, pn * 64, h, row0, b);
+  }
+}
+
+template <bool FP16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (FP16) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+template <int D, bool FP16>
+__global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_constant__ AttnKernelParams p) {
+  using C = Cfg<D>;
+  extern __shared__ char smem_raw[];
+  char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  char* smem_q = smem;
+  char* smem_k = smem_q + C::kSmemQ;
+  char* smem_v = smem_k + C::kSmemK;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_v + C::kSmemV);
+  uint64_t* q_full = bars;                       // [2]
+  uint64_t* k_full = q_full + 2;                 // [stages]
+  uint64_t* k_empty = k_full + C::kStages;       // [stages]
+  uint64_t* v_full = k_empty + C::kStages;       // [stages]
+  uint64_t* v_empty = v_full + C::kStages;       // [stages]
+  uint64_t* s_full = v_empty + C::kStages;       // [2]
+  uint64_t* p_ready = s_full + 2;                // [2]
+  uint64_t* o_done = p_ready + 2;                // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- work item -------------------------------------------------------
+  int idx = blockIdx.x;
+  const int pair = idx % p.n_pairs;
+  idx /= p.n_pairs;
+  const int h = idx % p.heads;
+  const int b = idx / p.heads;
+  const int tile0 = pair * 2;
+  const bool tile1_valid = (tile0 + 1) < p.n_tiles;
+  const int nblk = p.n_kv_blocks;
+
+  // ---- set-up ----------------------------------------------------------
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_ready[i], 128);
+      mbar_init(&o_done[i], 1);
+    }
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) {
+      for (int s = 0; s < p.n_q_seg; ++s) tma_prefetch_desc(&p.q_map[s]);
+      for (int s = 0; s < p.n_kv_seg; ++s) {
+        tma_prefetch_desc(&p.k_map[s]);
+        tma_prefetch_desc(&p.v_map[s]);
+      }
+      for (int t = 0; t < 2; ++t) {
+        if (t == 1 && !tile1_valid) break;
+        int seg, row0, orow;
+        tile_coords(p, tile0 + t, seg, row0, orow);
+        mbar_expect_tx(&q_full[t], C::kTileBytes);
+        load_tile(&p.q_map[seg], p.q_swap[seg], smem_q + t * C::kTileBytes, &q_full[t], C::kPanels, h, row0, b);
+      }
+      KvCursor cur{0, 0};
+      bool ok = true;
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int st = j % C::kStages;
+        const uint32_t n = static_cast<uint32_t>(j / C::kStages);
+        if (j >= C::kStages) {
+          if (!mbar_wait_bounded(&k_empty[st], (n - 1) & 1, abort_flag, kSpinLimit)) {
+            report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_PROD_KEMPTY, j);
+            ok = false;
+            break;
+          }
+        }
+        mbar_expect_tx(&k_full[st], C::kTileBytes);
+        load_tile(&p.k_map[cur.seg], p.k_swap[cur.seg], smem_k + st * C::kTileBytes, &k_full[st], C::kPanels, h,
+                  cur.row0, b);
+        if (j >= C::kStages) {
+          if (!mbar_wait_bounded(&v_empty[st], (n - 1) & 1, abort_flag, kSpinLimit)) {
+            report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_PROD_VEMPTY, j);
+            ok = false;
+            break;
+          }
+        }
+        mbar_expect_tx(&v_full[st], C::kTileBytes);
+        load_tile(&p.v_map[cur.seg], p.v_swap[cur.seg], smem_v + st * C::kTileBytes, &v_full[st], C::kPanels, h,
+                  cur.row0, b);
+        cur.advance(p);
+      }
+    }
+  } else if (warp == 9) {
+    // ============================ MMA issuer ============================
+    if (lane == 0) {
+      constexpr uint32_t kFmt = FP16 ? 0u : 1u;
+      constexpr uint32_t idesc_qk = make_idesc_f16(kBlockM, kBlockN, kFmt, 0);
+      constexpr uint32_t idesc_pv = make_idesc_f16(kBlockM, D, kFmt, 1);
+      const uint32_t q_addr = smem_u32(smem_q);
+      const uint32_t k_addr = smem_u32(smem_k);
+      const uint32_t v_addr = smem_u32(smem_v);
+      bool ok = true;
+
+      auto issue_qk = [&](int t, int stage) {
+        const uint32_t d_tmem = tmem_base + C::kColS + t * 128;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+          const uint64_t a = make_smem_desc_sw128(q_addr + t * C::kTileBytes + off, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(k_addr + stage * C::kTileBytes + off, 16, 1024);
+          umma_ss(d_tmem, a, bdesc, idesc_qk, kk > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int t, int stage, bool accumulate) {
+        const uint32_t d_tmem = tmem_base + C::kColO + t * D;
+        const uint32_t a_tmem = tmem_base + C::kColS + t * 128;
+#pragma unroll
+        for (int kk = 0; kk < kBlockN / 16; ++kk) {
+          const uint64_t bdesc =
+              make_smem_desc_sw128(v_addr + stage * C::kTileBytes + kk * 2048, kPanelBytes, 1024);
+          umma_ts(d_tmem, a_tmem + kk * 8, bdesc, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+        }
+      };
+      auto wait = [&](uint64_t* bar, uint32_t parity, int where, int iter) {
+        if (!ok) return;
+        if (!mbar_wait_bounded(bar, parity, abort_flag, kSpinLimit)) {
+          report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, where, iter);
+          ok = false;
+        }
+      };
+
+      // prologue: S(t,0) for both tiles
+      wait(&q_full[0], 0, W_MMA_QFULL, 0);
+      wait(&k_full[0], 0, W_MMA_KFULL, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0, 0);
+        tc_commit(&s_full[0]);
+      }
+      if (tile1_valid) {
+        wait(&q_full[1], 0, W_MMA_QFULL, 1);
+        if (ok) {
+          tc_fence_after();
+          issue_qk(1, 0);
+          tc_commit(&s_full[1]);
+        }
+      }
+      if (ok) tc_commit(&k_empty[0]);
+
+      const int last_t = tile1_valid ? 1 : 0;
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int st = j % C::kStages;
+        const uint32_t ph = static_cast<uint32_t>(j / C::kStages) & 1;
+        const int stn = (j + 1) % C::kStages;
+        const uint32_t phn = static_cast<uint32_t>((j + 1) / C::kStages) & 1;
+        for (int t = 0; t <= last_t && ok; ++t) {
+          if (t == 0) wait(&v_full[st], ph, W_MMA_VFULL, j);
+          wait(&p_ready[t], j & 1, W_MMA_PREADY, j * 2 + t);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(t, st, j > 0);
+          if (t == last_t) tc_commit(&v_empty[st]);
+          if (j + 1 < nblk) {
+            if (t == 0) wait(&k_full[stn], phn, W_MMA_KFULL, j + 1);
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(t, stn);
+            tc_commit(&s_full[t]);
+            if (t == last_t) tc_commit(&k_empty[stn]);
+          } else {
+            tc_commit(&o_done[t]);
+          }
+        }
+      }
+    }
+  } else {
+    // ========================= softmax / epilogue =========================
+    const int t = warp >> 2;           // which Q tile this warpgroup owns
+    const int quarter = warp & 3;      // TMEM lane quarter this warp may touch
+    const int row = quarter * 32 + lane;
+    const bool active = (t == 0) || tile1_valid;
+    if (active) {
+      const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+      const uint32_t tm_s = tmem_base + lane_base + C::kColS + t * 128;
+      const uint32_t tm_o = tmem_base + lane_base + C::kColO + t * D;
+      const float scale_log2 = p.scale_log2;
+      float m_run = -INFINITY;
+      float l_run = 0.f;
+      bool ok = true;
+      KvCursor cur{0, 0};
+
+      for (int j = 0; j < nblk; ++j) {
+        // warp-uniform outcome: the tcgen05.ld/st below need the whole warp converged
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&s_full[t], j & 1, abort_flag, kSpinLimit))) {
+          report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_SM_SFULL, j * 2 + t);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t s[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(tm_s + c * 32, s[c]);
+        tc_wait_ld();
+
+        const int valid = min(kBlockN, p.kv_len[cur.seg] - cur.row0);
+        cur.advance(p);
+        if (valid < kBlockN) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i >= valid) s[c][i] = 0xff800000u;  // -inf
+        }
+
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(s[c][i]));
+            mx1 = fmaxf(mx1, __uint_as_float(s[c][i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(s[c][i + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(s[c][i + 3]));
+          }
+        const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+        const float m_new = fmaxf(m_run, m_blk);
+        const bool grow = (m_new - m_run) > kRescaleThreshold;  // true on the first block (m_run = -inf)
+        if (__any_sync(0xffffffffu, grow)) {
+          const float alpha = grow ? ex2_approx(m_run - m_new) : 1.0f;
+          if (grow) m_run = m_new;
+          l_run *= alpha;
+          if (j > 0) {
+            // O(t) is stable here: the commit that raised s_full covered the previous P V.
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(tm_o + c * 32, o);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(tm_o + c * 32, o);
+            }
+          }
+        }
+
+        const float neg_m = -m_run;
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(s[c][i]), scale_log2, neg_m));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(s[c][i + 1]), scale_log2, neg_m));
+            sum0 += p0;
+            sum1 += p1;
+            pk[i >> 1] = pack2<FP16>(p0, p1);
+          }
+          tmem_st16(tm_s + c * 16, pk);
+        }
+        l_run += sum0 + sum1;
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&p_ready[t]);
+      }
+
+      // ------------------------------ epilogue ------------------------------
+      if (ok && !__all_sync(0xffffffffu, mbar_wait_bounded(&o_done[t], 0, abort_flag, kSpinLimit))) {
+        report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_SM_ODONE, t);
+        ok = false;
+      }
+      if (ok) {
+        tc_fence_after();
+        int seg, row0, orow0;
+        tile_coords(p, tile0 + t, seg, row0, orow0);
+        const bool row_valid = (row0 + row) < p.q_len[seg];
+        const long long qpos = orow0 + row;
+        const float blk_lse2 = m_run + log2f(l_run);  // log2 domain
+        float w_blk = 1.0f / l_run;
+        float w_prev = 0.f;
+        float lse_out = blk_lse2 * kLn2;
+        const long long acc_row = ((static_cast<long long>(b) * p.sq_total + qpos) * p.heads + h) * D;
+        const long long lse_idx = (static_cast<long long>(b) * p.heads + h) * p.sq_total + qpos;
+        const bool merge = (p.mode == HDIT_ATTN_PARTIAL_MERGE || p.mode == HDIT_ATTN_MERGE_FINAL);
+        const bool to_acc = (p.mode == HDIT_ATTN_PARTIAL_FIRST || p.mode == HDIT_ATTN_PARTIAL_MERGE);
+        if (merge && row_valid) {
+          const float prev = p.acc_lse[lse_idx];
+          const float blk = blk_lse2 * kLn2;
+          const float mx = fmaxf(prev, blk);
+          const float merged = mx + logf(expf(prev - mx) + expf(blk - mx));
+          w_prev = expf(prev - merged);
+          w_blk = expf(blk - merged) / l_run;
+          lse_out = merged;
+        }
+        if (row_valid) {
+          if (to_acc)
+            p.acc_lse[lse_idx] = lse_out;
+          else if (p.lse != nullptr)
+            p.lse[lse_idx] = lse_out;
+        }
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tm_o + c * 32, o);
+          tc_wait_ld();
+          if (row_valid) {
+            float f[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(o[i]) * w_blk;
+            if (merge) {
+              const float4* prev = reinterpret_cast<const float4*>(p.acc_out + acc_row + c * 32);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float4 v = prev[i];
+                f[4 * i + 0] = fmaf(v.x, w_prev, f[4 * i + 0]);
+                f[4 * i + 1] = fmaf(v.y, w_prev, f[4 * i + 1]);
+                f[4 * i + 2] = fmaf(v.z, w_prev, f[4 * i + 2]);
+                f[4 * i + 3] = fmaf(v.w, w_prev, f[4 * i + 3]);
+              }
+            }
+            if (to_acc) {
+              float4* dst = reinterpret_cast<float4*>(p.acc_out + acc_row + c * 32);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) dst[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+            } else {
+              uint16_t* base = reinterpret_cast<uint16_t*>(p.out) + static_cast<long long>(b) * p.out_sb +
+                               qpos * p.out_ss + static_cast<long long>(h) * p.out_sh + c * 32;
+              uint4* dst = reinterpret_cast<uint4*>(base);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 v;
+                v.x = pack2<FP16>(f[8 * i + 0], f[8 * i + 1]);
+                v.y = pack2<FP16>(f[8 * i + 2], f[8 * i + 3]);
+                v.z = pack2<FP16>(f[8 * i + 4], f[8 * i + 5]);
+                v.w = pack2<FP16>(f[8 * i + 6], f[8 * i + 7]);
+                dst[i] = v;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown ----------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // Let anything this CTA still has in flight (TMA writes, MMAs) land before
+    // its shared memory and TMEM go back to the SM.
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 9) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// Descriptor over a (B, S, H, D) tensor, box = 64 elements x 128 rows of one head.
+int encode_seg(CUtensorMap* map, unsigned char* swapped, const hdit_seg& seg, int dtype, int B, int H, int D) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return set_error(HDIT_ERR_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
+  if (seg.ptr == nullptr || seg.len <= 0) return set_error(HDIT_ERR_BAD_ARG, "segment with null pointer or len <= 0");
+  if ((reinterpret_cast<uintptr_t>(seg.ptr) & 15) != 0)
+    return set_error(HDIT_ERR_SHAPE, "segment pointer not 16-byte aligned");
+  if (seg.stride_s % 8 != 0 || seg.stride_h % 8 != 0 || seg.stride_b % 8 != 0)
+    return set_error(HDIT_ERR_SHAPE, "segment strides must be multiples of 8 elements");
+  if (seg.stride_s < D || (H > 1 && seg.stride_h < D))
+    return set_error(HDIT_ERR_SHAPE, "segment rows overlap (stride < head_dim)");
+  const long long sh = (H > 1) ? seg.stride_h : D;
+  long long sb = seg.stride_b;
+  if (B == 1 || sb <= 0) {
+    // Size-1 batch: any stride addresses the same data; give the descriptor a legal one.
+    const long long span_s = seg.stride_s * seg.len;
+    const long long span_h = sh * H;
+    sb = span_s > span_h ? span_s : span_h;
+  }
+  const bool swap = sh > seg.stride_s;  // keep descriptor strides ascending
+  cuuint64_t dims[4];
+  cuuint64_t strides[3];
+  cuuint32_t box[4];
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  dims[0] = static_cast<cuuint64_t>(D);
+  box[0] = 64;
+  if (!swap) {
+    dims[1] = static_cast<cuuint64_t>(H);
+    dims[2] = static_cast<cuuint64_t>(seg.len);
+    strides[0] = static_cast<cuuint64_t>(sh) * 2;
+    strides[1] = static_cast<cuuint64_t>(seg.stride_s) * 2;
+    box[1] = 1;
+    box[2] = kBlockN;
+  } else {
+    dims[1] = static_cast<cuuint64_t>(seg.len);
+    dims[2] = static_cast<cuuint64_t>(H);
+    strides[0] = static_cast<cuuint64_t>(seg.stride_s) * 2;
+    strides[1] = static_cast<cuuint64_t>(sh) * 2;
+    box[1] = kBlockN;
+    box[2] = 1;
+  }
+  dims[3] = static_cast<cuuint64_t>(B);
+  strides[2] = static_cast<cuuint64_t>(sb) * 2;
+  box[3] = 1;
+  const CUtensorMapDataType dt = (dtype == HDIT_FP16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUresult r = enc(map, dt, 4, const_cast<void*>(seg.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(HDIT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (len=%lld strides=%lld,%lld,%lld)",
+                     static_cast<int>(r), static_cast<long long>(seg.len), static_cast<long long>(seg.stride_b),
+                     static_cast<long long>(seg.stride_s), static_cast<long long>(seg.stride_h));
+  *swapped = swap ? 1 : 0;
+  return HDIT_OK;
+}
+
+template <int D, bool FP16>
+int launch(const AttnKernelParams& kp, int grid, cudaStream_t stream) {
+  auto kernel = attn_fwd_kernel<D, FP16>;
+  // The attribute is per device: set it whenever this thread meets a new device.
+  static thread_local int last_dev = -1;
+  int dev = 0;
+  HDIT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev != last_dev) {
+    HDIT_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
+    last_dev = dev;
+  }
+  kernel<<<grid, kNumThreads, Cfg<D>::kSmemBytes, stream>>>(kp);
+  HDIT_CUDA_OK(cudaGetLastError());
+  return HDIT_OK;
+}
+
+}  // namespace
+}  // namespace hdit
+
+extern "C" int hdit_attn_fwd(const hdit_attn_args* a) {
+  using namespace hdit;
+  if (a == nullptr) return set_error(HDIT_ERR_BAD_ARG, "args is null");
+  if (a->dtype != HDIT_BF16 && a->dtype != HDIT_FP16) return set_error(HDIT_ERR_BAD_ARG, "dtype must be bf16 or fp16");
+  if (a->head_dim != 64 && a->head_dim != 128) return set_error(HDIT_ERR_SHAPE, "head_dim must be 64 or 128");
+  if (a->batch <= 0 || a->heads <= 0) return set_error(HDIT_ERR_BAD_ARG, "batch and heads must be positive");
+  if (a->n_q_seg < 1 || a->n_q_seg > HDIT_MAX_Q_SEG) return set_error(HDIT_ERR_SHAPE, "n_q_seg out of range");
+  if (a->n_kv_seg < 1 || a->n_kv_seg > HDIT_MAX_KV_SEG) return set_error(HDIT_ERR_SHAPE, "n_kv_seg out of range");
+  if (a->mode < HDIT_ATTN_FINAL || a->mode > HDIT_ATTN_MERGE_FINAL) return set_error(HDIT_ERR_BAD_ARG, "unknown mode");
+  const bool needs_acc = a->mode != HDIT_ATTN_FINAL;
+  const bool needs_out = a->mode == HDIT_ATTN_FINAL || a->mode == HDIT_ATTN_MERGE_FINAL;
+  if (needs_acc && (a->acc_out == nullptr || a->acc_lse == nullptr))
+    return set_error(HDIT_ERR_BAD_ARG, "acc_out / acc_lse required for partial and merge modes");
+  if (needs_out) {
+    if (a->out == nullptr) return set_error(HDIT_ERR_BAD_ARG, "out is null");
+    if ((reinterpret_cast<uintptr_t>(a->out) & 15) != 0 || a->out_stride_s % 8 != 0 || a->out_stride_h % 8 != 0 ||
+        a->out_stride_b % 8 != 0)
+      return set_error(HDIT_ERR_SHAPE, "out must be 16-byte aligned with strides multiple of 8 elements");
+  }
+  if (needs_acc && (reinterpret_cast<uintptr_t>(a->acc_out) & 15) != 0)
+    return set_error(HDIT_ERR_SHAPE, "acc_out must be 16-byte aligned");
+
+  AttnKernelParams kp;
+  memset(&kp, 0, sizeof(kp));
+  kp.batch = a->batch;
+  kp.heads = a->heads;
+  kp.mode = a->mode;
+
+  // Drop empty segments so the kernel never sees a zero-length block list.
+  long long sq = 0;
+  int nq = 0;
+  for (int i = 0; i < a->n_q_seg; ++i) {
+    if (a->q[i].len < 0) return set_error(HDIT_ERR_BAD_ARG, "negative q segment length");
+    if (a->q[i].len == 0) continue;
+    if (a->q[i].len > 0x7fffff00LL) return set_error(HDIT_ERR_TOO_LARGE, "q segment too long");
+    const int rc = encode_seg(&kp.q_map[nq], &kp.q_swap[nq], a->q[i], a->dtype, a->batch, a->heads, a->head_dim);
+    if (rc != HDIT_OK) return rc;
+    kp.q_len[nq] = static_cast<int>(a->q[i].len);
+    sq += a->q[i].len;
+    ++nq;
+  }
+  if (nq == 0) return HDIT_OK;  // nothing to compute
+  int nkv = 0;
+  int nblk = 0;
+  for (int i = 0; i < a->n_kv_seg; ++i) {
+    if (a->k[i].len != a->v[i].len) return set_error(HDIT_ERR_SHAPE, "k and v segment lengths differ");
+    if (a->k[i].len < 0) return set_error(HDIT_ERR_BAD_ARG, "negative kv segment length");
+    if (a->k[i].len == 0) continue;
+    if (a->k[i].len > 0x7fffff00LL) return set_error(HDIT_ERR_TOO_LARGE, "kv segment too long");
+    int rc = encode_seg(&kp.k_map[nkv], &kp.k_swap[nkv], a->k[i], a->dtype, a->batch, a->heads, a->head_dim);
+    if (rc != HDIT_OK) return rc;
+    rc = encode_seg(&kp.v_map[nkv], &kp.v_swap[nkv], a->v[i], a->dtype, a->batch, a->heads, a->head_dim);
+    if (rc != HDIT_OK) return rc;
+    kp.kv_len[nkv] = static_cast<int>(a->k[i].len);
+    nblk += static_cast<int>((a->k[i].len + kBlockN - 1) / kBlockN);
+    ++nkv;
+  }
+  if (nkv == 0) return set_error(HDIT_ERR_SHAPE, "attention over an empty key/value sequence");
+  kp.n_q_seg = nq;
+  kp.n_kv_seg = nkv;
+  kp.n_kv_blocks = nblk;
+  kp.n_tiles_seg0 = (kp.q_len[0] + kBlockM - 1) / kBlockM;
+  kp.n_tiles = kp.n_tiles_seg0 + (nq > 1 ? (kp.q_len[1] + kBlockM - 1) / kBlockM : 0);
+  kp.n_pairs = (kp.n_tiles + 1) / 2;
+  kp.sq_total = sq;
+  const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf(static_cast<float>(a->head_dim));
+  kp.scale_log2 = scale * 1.4426950408889634f;
+  kp.out = a->out;
+  kp.out_sb = a->out_stride_b;
+  kp.out_ss = a->out_stride_s;
+  kp.out_sh = a->out_stride_h;
+  kp.lse = a->lse;
+  kp.acc_out = a->acc_out;
+  kp.acc_lse = a->acc_lse;
+  kp.status = device_status_ptr();
+  if (kp.status == nullptr) return HDIT_ERR_CUDA;
+
+  const long long grid = static_cast<long long>(kp.n_pairs) * a->heads * a->batch;
+  if (grid > 0x7fffffffLL) return set_error(HDIT_ERR_TOO_LARGE, "grid too large");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
+  const bool fp16 = a->dtype == HDIT_FP16;
+  if (a->head_dim == 128)
+    return fp16 ? launch<128, true>(kp, static_cast<int>(grid), stream)
+                : launch<128, false>(kp, static_cast<int>(grid), stream);
+  return fp16 ? launch<64, true>(kp, static_cast<int>(grid), stream)
+              : launch<64, false>(kp, static_cast<int>(grid), stream);
+}

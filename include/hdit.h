@@ -1,0 +1,134 @@
+/*
+ * hdit.h -- C ABI of libhdit_b200.so: hand-written sm_100a kernels for the
+ * denoising-stage parallel hot path of Hetu-DiT (USP attention, PipeFusion
+ * patch movement, stale-KV scatter, parameter-slice migration).
+ *
+ * Conventions for every entry point:
+ *   - plain pointers and sizes only; all buffers are caller-owned device memory
+ *     unless a comment says "host";
+ *   - the CUDA stream is passed explicitly as an opaque pointer (cudaStream_t);
+ *     calls are asynchronous with respect to the host;
+ *   - the return value is an hdit_status; 0 means the work was enqueued.
+ *     hdit_last_error() gives a host-side message for the calling thread;
+ *   - no entry point allocates device memory. Kernels report a bounded wait
+ *     that ran out into a small file-scope device array of the library; read
+ *     it with hdit_device_status() (a blocking copy, so synchronise first).
+ *   - kernels never trap or spin for ever: every device-side wait has an
+ *     iteration limit, after which the kernel records where it gave up and
+ *     returns.
+ *
+ * Each declaration cites the reference (PKU-DAIR/Hetu-DiT, paths relative to
+ * its repository root) interface it stands in for.
+ */
+#ifndef HDIT_H_
+#define HDIT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(HDIT_BUILDING) && defined(__GNUC__)
+#define HDIT_API __attribute__((visibility("default")))
+#else
+#define HDIT_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum hdit_status {
+  HDIT_OK = 0,
+  HDIT_ERR_BAD_ARG = 1,        /* null pointer, negative size, unknown enum   */
+  HDIT_ERR_SHAPE = 2,          /* unsupported head_dim / alignment / too many segments */
+  HDIT_ERR_CUDA = 3,           /* a CUDA runtime / driver call failed          */
+  HDIT_ERR_NOT_INITIALISED = 4,
+  HDIT_ERR_PEER_TIMEOUT = 5,   /* a bounded device-side wait ran out           */
+  HDIT_ERR_TOO_LARGE = 6       /* exceeds a documented fixed capacity          */
+} hdit_status;
+
+typedef enum hdit_dtype { HDIT_BF16 = 0, HDIT_FP16 = 1, HDIT_FP32 = 2 } hdit_dtype;
+
+#define HDIT_MAX_Q_SEG 2
+#define HDIT_MAX_KV_SEG 10
+
+/* Library version as major*10000 + minor*100 + patch. */
+HDIT_API int hdit_version(void);
+
+/* Host message describing the last non-zero status returned on this thread. */
+HDIT_API const char* hdit_last_error(void);
+
+/*
+ * Device-side status block: out[0] = code (0 = clean, otherwise an
+ * hdit_status), out[1] = blockIdx.x, out[2] = role / wait identifier,
+ * out[3] = loop iteration. Synchronise the stream first. `clear` != 0 resets it.
+ */
+HDIT_API int hdit_device_status(int device, int32_t out[4], int clear);
+
+/* One sequence segment of a (B, S, H, D) tensor whose last dim is contiguous.
+ * Strides are in elements. `len` is this segment's S. */
+typedef struct hdit_seg {
+  const void* ptr;
+  int64_t len;
+  int64_t stride_b;
+  int64_t stride_s;
+  int64_t stride_h;
+} hdit_seg;
+
+/* How the attention epilogue treats its result. */
+typedef enum hdit_attn_mode {
+  HDIT_ATTN_FINAL = 0,        /* write softmax(QK^T)V in `dtype` to out (+ lse)                  */
+  HDIT_ATTN_PARTIAL_FIRST = 1,/* write fp32 partial result to acc_out, its log-sum-exp to acc_lse */
+  HDIT_ATTN_PARTIAL_MERGE = 2,/* log-sum-exp merge with (acc_out, acc_lse), write both back       */
+  HDIT_ATTN_MERGE_FINAL = 3   /* merge as above, then write `dtype` to out (+ lse)                */
+} hdit_attn_mode;
+
+/*
+ * Joint (text + image/video) flash-attention forward on tcgen05/TMEM tiles fed
+ * by TMA; non-causal, no dropout, fp32 accumulation, online softmax.
+ *
+ * Q is the concatenation of n_q_seg segments along S, K/V of n_kv_seg segments
+ * (e.g. [image; text] for the "rear" joint strategy, [text; image] for "front",
+ * or the KV blocks a ring step contributes); no concatenated copy is ever
+ * materialised. Output rows follow the Q concatenation order.
+ *
+ * Replaces, in the reference:
+ *   flash_attn `_flash_attn_forward` as called by ring_flash_attn_forward
+ *     (hetu_dit/core/parallel/ring/ring_flash_attn.py:76-87),
+ *   the torch.cat of joint K/V around it (:60-71),
+ *   `update_out_and_lse` (:88) via the PARTIAL_* / MERGE_* modes,
+ *   `flash_attn_func` / F.scaled_dot_product_attention in the attention
+ *     processors (hetu_dit/model_executor/diffusion_executor/layers/
+ *     attention_processor.py:592,602,752,772,962,969,1139,1149,1516,1524).
+ *
+ * Requirements: head_dim in {64, 128}; dtype bf16 or fp16; every pointer
+ * 16-byte aligned and every stride a multiple of 8 elements; strides of `out`
+ * as for a (B, Sq, H, D) tensor; lse is (B, H, Sq) fp32 contiguous (may be
+ * NULL in FINAL mode); acc_out is (B, Sq, H, D) fp32 contiguous and acc_lse
+ * (B, H, Sq) fp32 contiguous (PARTIAL and MERGE modes only).
+ */
+typedef struct hdit_attn_args {
+  int32_t dtype;      /* hdit_dtype: HDIT_BF16 or HDIT_FP16 */
+  int32_t mode;       /* hdit_attn_mode */
+  int32_t batch;
+  int32_t heads;
+  int32_t head_dim;
+  int32_t n_q_seg;
+  int32_t n_kv_seg;
+  float softmax_scale; /* <= 0 selects head_dim^-0.5 */
+  hdit_seg q[HDIT_MAX_Q_SEG];
+  hdit_seg k[HDIT_MAX_KV_SEG];
+  hdit_seg v[HDIT_MAX_KV_SEG];
+  void* out;
+  int64_t out_stride_b, out_stride_s, out_stride_h;
+  float* lse;
+  float* acc_out;
+  float* acc_lse;
+  void* stream;
+} hdit_attn_args;
+
+HDIT_API int hdit_attn_fwd(const hdit_attn_args* args);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HDIT_H_ */
