@@ -1,0 +1,578 @@
+"""Generates the golden fixtures in this directory from the reference's own source files.
+
+Run it where the reference checkout is available:
+
+    python tests/golden/make_golden.py --reference /path/to/Hetu-DiT
+
+It never copies reference source into this repository: functions are lifted
+from the reference files at run time (by AST for single functions, by loading
+whole files under stub packages otherwise), executed on CPU, and only their
+inputs and outputs are written out:
+
+  bookkeeping.json   integer bookkeeping (patch metadata, rank groups, slice
+                     ranges, migration plans, TP split table)
+  rope.npz           apply_rotary_emb on seeded inputs
+  usp_<case>.npz     hetuDiT*LongContextAttention / ring attention / KV cache on
+                     CPU `gloo` ranks, fp32
+
+The reference imports packages that are not installed here (diffusers, ray,
+yunchang, flash_attn on CPU). Those imports are satisfied with stubs defined
+below: yunchang's SeqAllToAll4D / RingComm / update_out_and_lse and flash-attn's
+_flash_attn_forward are re-stated from their published behaviour with
+torch.distributed (gloo) and fp32 torch math; everything else executed is the
+reference's code.
+"""
+import argparse
+import ast
+import asyncio
+import importlib.util
+import json
+import logging
+import os
+import sys
+import types
+from itertools import combinations
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+# ----------------------------------------------------------------------------- lifting helpers
+def _find(tree, name, cls=None):
+    body = tree.body
+    if cls is not None:
+        for node in body:
+            if isinstance(node, ast.ClassDef) and node.name == cls:
+                body = node.body
+                break
+        else:
+            raise KeyError(cls)
+    for node in body:
+        if isinstance(node, (ast.FunctionDef, ast.AsyncFunctionDef, ast.ClassDef)) and node.name == name:
+            return node
+    raise KeyError(name)
+
+
+def lift(path, name, cls=None, namespace=None):
+    """Compile one function / class definition out of a reference file into `namespace`."""
+    with open(path) as f:
+        tree = ast.parse(f.read())
+    node = _find(tree, name, cls)
+    mod = ast.Module(body=[node], type_ignores=[])
+    ns = dict(namespace or {})
+    exec(compile(mod, path, "exec"), ns)
+    return ns[name], ns
+
+
+class _NS(types.SimpleNamespace):
+    pass
+
+
+# ----------------------------------------------------------------------------- bookkeeping
+def gen_bookkeeping(ref):
+    from typing import Any, Dict, List, Optional, Tuple, Union
+
+    log = logging.getLogger("golden")
+    out = {}
+
+    # --- patch metadata --------------------------------------------------
+    rs_path = os.path.join(ref, "hetu_dit/core/distributed/runtime_state.py")
+    cases = []
+    for variant, fname in (("image", "_calc_patches_metadata"), ("cogvideox", "_calc_cogvideox_patches_metadata")):
+        for (h, w, vae, patch, npp, sp) in [
+            (1024, 1024, 8, 2, 4, 1), (1024, 1024, 8, 2, 4, 2), (1024, 1024, 8, 2, 4, 4), (1024, 1024, 8, 2, 4, 8),
+            (512, 512, 8, 2, 4, 1), (512, 512, 8, 2, 4, 2), (768, 768, 8, 2, 4, 1), (768, 768, 8, 2, 4, 2),
+            (1536, 1536, 8, 2, 4, 1), (1536, 1536, 8, 2, 4, 2), (1536, 1536, 8, 2, 4, 4), (1024, 1024, 8, 2, 1, 1),
+            (1024, 1024, 8, 2, 2, 2), (1024, 1024, 8, 2, 8, 1), (1024, 1024, 8, 2, 3, 1), (1024, 1024, 8, 2, 5, 2),
+            (1024, 2048, 8, 2, 4, 2), (1152, 896, 8, 2, 4, 1), (1152, 896, 8, 2, 3, 2), (768, 1360, 8, 2, 1, 2),
+            (768, 1360, 8, 2, 2, 4), (768, 1360, 8, 2, 4, 1), (1024, 1024, 16, 1, 4, 2), (720, 1280, 8, 2, 3, 1),
+            (1000, 1000, 8, 2, 4, 1), (1080, 1920, 8, 2, 4, 1),
+        ]:
+            for rank in range(sp):
+                ns = {
+                    "get_sequence_parallel_world_size": lambda sp=sp: sp,
+                    "get_sequence_parallel_rank": lambda rank=rank: rank,
+                    "logger": log,
+                }
+                fn, _ = lift(rs_path, fname, cls="DiTRuntimeState", namespace=ns)
+                self = _NS(
+                    backbone_patch_size=patch, vae_scale_factor=vae, vae_scale_factor_spatial=vae,
+                    vae_scale_factor_temporal=4,
+                    input_config=_NS(height=h, width=w, num_frames=49),
+                    parallel_config=_NS(pp_config=_NS(num_pipeline_patch=npp)),
+                )
+                rec = {"variant": variant, "height": h, "width": w, "vae": vae, "patch": patch,
+                       "num_pipeline_patch": npp, "sp_world": sp, "sp_rank": rank}
+                try:
+                    fn(self)
+                    rec["result"] = {k: getattr(self, k) for k in (
+                        "num_pipeline_patch", "pp_patches_height", "pp_patches_start_idx_local",
+                        "pp_patches_start_end_idx_global", "pp_patches_token_start_idx_local",
+                        "pp_patches_token_start_end_idx_global", "pp_patches_token_num")}
+                except ValueError as e:
+                    rec["error"] = "ValueError"
+                cases.append(rec)
+    out["patches_metadata"] = cases
+
+    # --- rank groups -------------------------------------------------------
+    utils_ns = {}
+    with open(os.path.join(ref, "hetu_dit/core/distributed/utils.py")) as f:
+        exec(compile(f.read(), "utils.py", "exec"), utils_ns)
+    RankGenerator = utils_ns["RankGenerator"]
+    rg_cases = []
+    for (tp, sp, pp, cfg, dp) in [(1, 8, 1, 1, 1), (1, 4, 2, 1, 1), (1, 2, 4, 1, 1), (2, 2, 2, 1, 1), (1, 2, 2, 2, 1),
+                                  (1, 1, 4, 1, 2), (2, 1, 1, 1, 1), (1, 1, 1, 1, 1), (2, 2, 1, 2, 2), (1, 4, 1, 1, 2)]:
+        for off in (0, 8):
+            g = RankGenerator(tp, sp, pp, cfg, dp, "tp-sp-pp-cfg-dp", rank_offset=off)
+            rg_cases.append({"tp": tp, "sp": sp, "pp": pp, "cfg": cfg, "dp": dp, "rank_offset": off,
+                             "groups": {tok: g.get_ranks(tok) for tok in ("tp", "sp", "pp", "cfg", "dp", "tp-sp")}})
+    out["rank_generator"] = rg_cases
+    mo = utils_ns["generate_masked_orthogonal_rank_groups"]
+    out["masked_orthogonal"] = [
+        {"world": 24, "sizes": [2, 3, 4], "mask": m, "groups": mo(24, [2, 3, 4], m)}
+        for m in ([False, True, False], [True, False, True], [True, True, True], [False, False, False])
+    ]
+
+    ps_path = os.path.join(ref, "hetu_dit/core/distributed/parallel_state.py")
+    fake_torch = _NS(distributed=_NS(new_group=lambda ranks, backend=None: list(ranks)))
+    sp_fn, _ = lift(ps_path, "set_seq_parallel_pg", namespace={"torch": fake_torch, "List": List})
+    sp_cases = []
+    for (u, r, ranks) in [(4, 2, list(range(8))), (2, 4, list(range(8))), (8, 1, list(range(8))), (1, 8, list(range(8))),
+                          (2, 2, [0, 3, 4, 7]), (2, 1, [5, 2]), (1, 2, [1, 6]), (2, 2, list(range(8))),
+                          (1, 1, [3]), (4, 1, [7, 1, 3, 5])]:
+        for low in (True, False):
+            world = len(ranks)
+            per_rank = {}
+            for rank in sorted(ranks):
+                upg, rpg = sp_fn(u, r, rank, world, ranks, use_ulysses_low=low)
+                per_rank[str(rank)] = {"ulysses": upg, "ring": rpg}
+            sp_cases.append({"ulysses": u, "ring": r, "ranks": ranks, "use_ulysses_low": low, "per_rank": per_rank})
+    out["seq_parallel_groups"] = sp_cases
+
+    pg_ns = {"combinations": combinations, "np": np, "List": List}
+    comb_fn, _ = lift(ps_path, "_generate_rank_combinations", cls="ParallelGroups", namespace=pg_ns)
+    part_fn, _ = lift(ps_path, "_generate_group_ranks", cls="ParallelGroups", namespace=pg_ns)
+    me = _NS(valid_degrees=[1, 2, 4, 8])
+    out["rank_combinations"] = [{"world": w, "base": b, "result": comb_fn(me, w, b)} for w, b in ((4, 0), (8, 0), (2, 8))]
+    out["group_partitions"] = [{"ranks": rk, "result": part_fn(me, rk)}
+                               for rk in ([0], [0, 1], [0, 1, 2, 3], [1, 3, 5, 7], list(range(8)))]
+
+    # --- slice ranges --------------------------------------------------------
+    u_path = os.path.join(ref, "hetu_dit/utils.py")
+    r2i_round, _ = lift(u_path, "range_to_indices")
+    meta_fn, _ = lift(u_path, "get_gpu_metadata")
+    bc_path = os.path.join(ref, "hetu_dit/model_executor/cache/base_cache.py")
+    r2i_trunc, _ = lift(bc_path, "range_to_indices", cls="BaseBlockCache", namespace={"Tuple": Tuple, "logger": log})
+    ranges = []
+    for world in (1, 2, 3, 4, 8):
+        for rank in range(world):
+            ranges.append((rank / world, rank / world + 1.0 / world))
+            ranges.append((rank * (1.0 / world), rank * (1.0 / world) + 1.0 / world))
+    ranges += [(0.0, 1.0), (0.25, 0.75), (0.5, 0.5), (0.9, 0.3), (0.0, 0.3333), (0.3333, 0.6666), (0.6666, 1.0)]
+    r2i = []
+    for rng in ranges:
+        for total in (0, 1, 7, 24, 38, 57, 1536, 3072, 4096, 6144, 12288, 18432, 333, 1000):
+            r2i.append({"range": list(rng), "total": total, "round": list(r2i_round(rng, total)),
+                        "trunc": list(r2i_trunc(None, rng, total))})
+    out["range_to_indices"] = r2i
+    out["gpu_metadata"] = [
+        {"pp_rank": pr, "pp_world": pw, "tp_rank": tr, "tp_world": tw,
+         "result": {k: list(v) for k, v in meta_fn(pr, pw, tr, tw).items()}}
+        for pw in (1, 2, 3, 4, 8) for pr in range(pw) for tw in (1, 2, 3, 4, 8) for tr in range(tw)
+    ]
+
+    # --- TP split table ------------------------------------------------------
+    tc_path = os.path.join(ref, "hetu_dit/model_executor/cache/transformer_cache.py")
+    choose_fn, _ = lift(tc_path, "choose_tp_split_type", cls="TransformerBlockCache", namespace={"Optional": Optional})
+    det_fn, _ = lift(tc_path, "determine_tp_split_type_by_name", cls="TransformerBlockCache")
+    tself = _NS()
+    tself.determine_tp_split_type_by_name = lambda n: det_fn(tself, n)
+    names = [f"{a}.module.{n}" for a in ("attn", "attn1", "attn2") for n in
+             ("to_q", "to_k", "to_v", "add_k_proj", "add_q_proj", "add_v_proj", "to_add_out", "to_out.0", "to_out.1",
+              "norm_q")]
+    names += ["ff.module.net.0.proj", "ff.module.net.2", "ff_context.module.net.0.proj", "ff_context.module.net.2",
+              "ff.module.net.0", "norm1.linear", "proj_mlp", "proj_out", "attn.to_q", "ff.net.2"]
+    out["tp_split_type"] = [{"name": n, "result": choose_fn(tself, n)} for n in names]
+
+    # --- migration plans -------------------------------------------------------
+    import torch.nn as nn
+    from dataclasses import dataclass, field
+    dc_ns = {"dataclass": dataclass, "field": field, "Optional": Optional, "Tuple": Tuple, "List": List, "nn": nn}
+    NeededPiece, dc_ns2 = lift(bc_path, "NeededPiece", namespace=dc_ns)
+    dc_ns2.pop("__builtins__", None)
+    Plan, _ = lift(bc_path, "DataReconstructionPlan", namespace={**dc_ns, "NeededPiece": NeededPiece})
+
+    class Stop(Exception):
+        pass
+
+    class FakeLinearBlock(nn.Module):
+        """A block whose named_modules() yields Linear layers under the names the reference adjusts."""
+
+        def __init__(self, spec):
+            super().__init__()
+            for path, out_f, in_f, bias in spec:
+                parts = path.split(".")
+                mod = self
+                for p in parts[:-1]:
+                    if not hasattr(mod, p):
+                        mod.add_module(p, nn.Module())
+                    mod = getattr(mod, p)
+                with torch.device("meta"):
+                    mod.add_module(parts[-1], nn.Linear(in_f, out_f, bias=bias))
+
+    def block_spec(kind, dm):
+        if kind == "sd3":
+            return [("attn.module.to_q", dm, dm, True), ("attn.module.to_k", dm, dm, True),
+                    ("attn.module.to_v", dm, dm, True), ("attn.module.add_k_proj", dm, dm, True),
+                    ("attn.module.add_v_proj", dm, dm, True), ("attn.module.add_q_proj", dm, dm, True),
+                    ("attn.module.to_out.0", dm, dm, True), ("attn.module.to_add_out", dm, dm, True),
+                    ("ff.module.net.0.proj", 4 * dm, dm, True), ("ff.module.net.2", dm, 4 * dm, True),
+                    ("ff_context.module.net.0.proj", 4 * dm, dm, True), ("ff_context.module.net.2", dm, 4 * dm, True),
+                    ("norm1.linear", 6 * dm, dm, True)]
+        return [("attn.module.to_q", dm, dm, True), ("attn.module.to_k", dm, dm, False),
+                ("attn.module.to_v", dm, dm, True), ("attn.module.to_out.0", dm, dm, True),
+                ("proj_mlp", 4 * dm, dm, True)]
+
+    adj_fn, _ = lift(bc_path, "_adjust_pipeline_legacy", cls="BaseBlockCache", namespace={
+        "nn": nn, "Optional": Optional, "Dict": Dict, "List": List, "Tuple": Tuple, "logger": log,
+        "get_runtime_state": lambda: _NS(runtime_config=_NS(adjust_strategy="cache")),
+        "DataReconstructionPlan": Plan, "NeededPiece": NeededPiece,
+    })
+
+    plan_cases = []
+    for (kind, dm, nblocks, old_pp, new_pp, cached, target, slice_bias) in [
+        ("sd3", 1536, 4, (0.0, 1.0), (0.0, 1.0), {0: (0.0, 0.5), 1: (0.0, 0.5), 2: (0.0, 0.5), 3: (0.0, 0.5)}, (0.0, 1.0), True),
+        ("sd3", 1536, 4, (0.0, 1.0), (0.0, 1.0), {0: (0.0, 1.0), 1: (0.0, 1.0), 2: (0.0, 1.0), 3: (0.0, 1.0)}, (0.5, 1.0), True),
+        ("sd3", 1536, 4, (0.0, 0.5), (0.5, 1.0), {0: (0.0, 1.0), 1: (0.0, 1.0)}, (0.0, 1.0), True),
+        ("sd3", 1536, 8, (0.0, 0.5), (0.25, 0.75), {0: (0.0, 0.5), 1: (0.0, 0.5), 2: (0.25, 0.5), 3: (0.0, 0.25)}, (0.25, 0.75), True),
+        ("flux1", 3072, 6, (0.0, 1.0), (0.0, 1.0), {i: (0.25, 0.5) for i in range(6)}, (0.0, 1.0), True),
+        ("flux1", 3072, 6, (0.0, 1.0), (0.0, 1.0), {i: (0.25, 0.5) for i in range(6)}, (0.0, 1.0), False),
+        ("flux1", 3072, 3, (0.0, 1.0), (0.0, 1.0), {0: (0.0, 1.0 / 3), 2: (2.0 / 3, 1.0)}, (1.0 / 3, 1.0), True),
+        ("sd3", 1000, 3, (0.0, 1.0), (0.0, 1.0), {0: (0.0, 1.0 / 3), 1: (1.0 / 3, 1.0 / 3 + 1.0 / 3)}, (0.0, 0.5), True),
+    ]:
+        cpu_blocks = [FakeLinearBlock(block_spec(kind, dm)) for _ in range(nblocks)]
+
+        class FakeSelf:
+            def __init__(self):
+                self.cache = {i: (None, tuple(r)) for i, r in cached.items()}
+                self.active_block_indices = sorted(cached.keys())
+
+            def range_to_indices(self, rng, total):
+                return r2i_trunc(self, rng, total)
+
+            def get_total_blocks(self, m):
+                return nblocks
+
+            def get_cpu_block_for_index(self, m, idx):
+                return cpu_blocks[idx]
+
+            def choose_tp_split_type(self, name):
+                return choose_fn(tself, name)
+
+            def __getattr__(self, name):
+                raise Stop(name)
+
+        fs = FakeSelf()
+        old_tp = next(iter(cached.values())) if cached else (0.0, 1.0)
+        try:
+            asyncio.run(adj_fn(fs, None, None, old_pp, new_pp, old_tp, target, slice_bias, None))
+        except Stop:
+            pass
+        pieces = [{k: getattr(p, k) for k in ("uid", "block_index", "layer_path", "tensor_type", "split_dim", "full_size",
+                                              "abs_start_idx", "abs_end_idx", "dest_offset")}
+                  for p in fs.__dict__.get("_last_p2p_all_pieces", [])]
+        plan_cases.append({
+            "kind": kind, "hidden": dm, "num_blocks": nblocks, "new_pp": list(new_pp),
+            "cached": {str(k): list(v) for k, v in cached.items()}, "target_tp": list(target), "slice_bias": slice_bias,
+            "linears": [[n, o, i, b] for n, o, i, b in block_spec(kind, dm)], "pieces": pieces,
+        })
+    out["migration_plans"] = plan_cases
+
+    with open(os.path.join(HERE, "bookkeeping.json"), "w") as f:
+        json.dump(out, f, separators=(",", ":"))
+    print("bookkeeping.json:", {k: len(v) for k, v in out.items()})
+
+
+# ----------------------------------------------------------------------------- RoPE
+def gen_rope(ref):
+    from typing import Tuple, Union
+    path = os.path.join(ref, "hetu_dit/model_executor/diffusion_executor/layers/attention_processor.py")
+    fn, _ = lift(path, "apply_rotary_emb", namespace={"torch": torch, "Union": Union, "Tuple": Tuple})
+    g = torch.Generator().manual_seed(1234)
+    data = {}
+    for i, (B, H, S, D) in enumerate([(1, 2, 37, 64), (2, 3, 16, 128)]):
+        x = torch.randn(B, H, S, D, generator=g)
+        ang = torch.rand(S, D // 2, generator=g) * 6.28
+        cos = torch.cos(ang).repeat_interleave(2, dim=-1)
+        sin = torch.sin(ang).repeat_interleave(2, dim=-1)
+        data[f"x{i}"] = x.numpy()
+        data[f"cos{i}"] = cos.numpy()
+        data[f"sin{i}"] = sin.numpy()
+        data[f"y{i}"] = fn(x, (cos, sin)).numpy()
+        xb = x.to(torch.bfloat16)
+        data[f"yb{i}"] = fn(xb, (cos, sin)).float().numpy()
+    np.savez_compressed(os.path.join(HERE, "rope.npz"), **data)
+    print("rope.npz written")
+
+
+# ----------------------------------------------------------------------------- USP attention on gloo ranks
+def _install_stub_packages(ref, state):
+    """Registers stub third-party modules and loads the reference's attention files under their real names."""
+    import torch.distributed as dist
+
+    def pkg(name):
+        m = types.ModuleType(name)
+        m.__path__ = []
+        sys.modules[name] = m
+        return m
+
+    def load(name, relpath):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(ref, relpath))
+        m = importlib.util.module_from_spec(spec)
+        sys.modules[name] = m
+        spec.loader.exec_module(m)
+        parent, _, leaf = name.rpartition(".")
+        setattr(sys.modules[parent], leaf, m)
+        return m
+
+    # ---- hetu_dit stubs ---------------------------------------------------
+    for n in ("hetu_dit", "hetu_dit.core", "hetu_dit.core.distributed", "hetu_dit.core.resource_manager",
+              "hetu_dit.core.parallel", "hetu_dit.core.parallel.hybrid", "hetu_dit.core.parallel.ring",
+              "hetu_dit.core.parallel.ulysses"):
+        pkg(n)
+    lg = types.ModuleType("hetu_dit.logger")
+    lg.init_logger = lambda name: logging.getLogger(name)
+    sys.modules["hetu_dit.logger"] = lg
+    ps = types.ModuleType("hetu_dit.core.distributed.parallel_state")
+    ps.get_sequence_parallel_world_size = lambda: state.sp_world
+    sys.modules["hetu_dit.core.distributed.parallel_state"] = ps
+    rs = types.ModuleType("hetu_dit.core.distributed.runtime_state")
+    rs.runtime_state_is_initialized = lambda: state.runtime is not None
+    rs.get_runtime_state = lambda: state.runtime
+    sys.modules["hetu_dit.core.distributed.runtime_state"] = rs
+    d = sys.modules["hetu_dit.core.distributed"]
+    d.get_ulysses_parallel_world_size = lambda: state.ulysses
+    d.get_runtime_state = lambda: state.runtime
+    d.runtime_state = rs
+    d.parallel_state = ps
+
+    # ---- yunchang 0.3.5 stubs (published behaviour, gloo transport) ---------
+    class _PG:
+        ULYSSES_PG = None
+        RING_PG = None
+
+    class SeqAllToAll4D:
+        @staticmethod
+        def apply(group, x, scatter_idx, gather_idx):
+            world = dist.get_world_size(group)
+            if world == 1:
+                return x
+            rank = dist.get_rank(group)
+            gathered = [torch.empty_like(x) for _ in range(world)]
+            dist.all_gather(gathered, x.contiguous(), group=group)
+            parts = [torch.chunk(g, world, dim=scatter_idx)[rank] for g in gathered]
+            return torch.cat(parts, dim=gather_idx).contiguous()
+
+    class RingComm:
+        def __init__(self, process_group):
+            self._pg = process_group
+            self.rank = dist.get_rank(process_group)
+            self.world_size = dist.get_world_size(process_group)
+            self._ops, self._reqs = [], None
+            ranks = dist.get_process_group_ranks(process_group)
+            self.send_rank = ranks[(self.rank + 1) % self.world_size]
+            self.recv_rank = ranks[(self.rank - 1) % self.world_size]
+
+        def send_recv(self, to_send, recv_tensor=None):
+            res = torch.empty_like(to_send) if recv_tensor is None else recv_tensor
+            self._ops.append(dist.P2POp(dist.isend, to_send.contiguous(), self.send_rank, group=self._pg))
+            self._ops.append(dist.P2POp(dist.irecv, res, self.recv_rank, group=self._pg))
+            return res
+
+        def commit(self):
+            self._reqs = dist.batch_isend_irecv(self._ops)
+
+        def wait(self):
+            for r in self._reqs:
+                r.wait()
+            self._reqs, self._ops = None, []
+
+    def update_out_and_lse(out, lse, block_out, block_lse, slice_=None):
+        block_out = block_out.to(torch.float32)
+        block_lse = block_lse.transpose(-2, -1).unsqueeze(dim=-1)
+        if out is None:
+            return block_out, block_lse
+        new_lse = lse + torch.log(1 + torch.exp(block_lse - lse))
+        out = torch.exp(lse - new_lse) * out + torch.exp(block_lse - new_lse) * block_out
+        return out, new_lse
+
+    class LongContextAttention(torch.nn.Module):
+        def __init__(self, scatter_idx=2, gather_idx=1, ring_impl_type="basic", use_pack_qkv=False, **kw):
+            super().__init__()
+            self.scatter_idx, self.gather_idx = scatter_idx, gather_idx
+            self.ring_impl_type, self.use_pack_qkv = ring_impl_type, use_pack_qkv
+
+    class UlyssesAttention(torch.nn.Module):
+        pass
+
+    class RingFlashAttnFunc(torch.autograd.Function):
+        pass
+
+    def torch_attn(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, *args, **kwargs):
+        o = torch.nn.functional.scaled_dot_product_attention(
+            q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), dropout_p=0.0, is_causal=False, scale=softmax_scale)
+        return o.transpose(1, 2)
+
+    y = pkg("yunchang")
+    y.LongContextAttention, y.UlyssesAttention = LongContextAttention, UlyssesAttention
+    pkg("yunchang.comm")
+    m = types.ModuleType("yunchang.comm.all_to_all"); m.SeqAllToAll4D = SeqAllToAll4D
+    sys.modules[m.__name__] = m
+    m = types.ModuleType("yunchang.globals"); m.PROCESS_GROUP = _PG
+    sys.modules[m.__name__] = m
+    r = pkg("yunchang.ring")
+    r.zigzag_ring_flash_attn_func = r.stripe_flash_attn_func = None
+    m = types.ModuleType("yunchang.ring.utils"); m.RingComm, m.update_out_and_lse = RingComm, update_out_and_lse
+    sys.modules[m.__name__] = m
+    m = types.ModuleType("yunchang.ring.ring_flash_attn"); m.RingFlashAttnFunc = RingFlashAttnFunc
+    sys.modules[m.__name__] = m
+    pkg("yunchang.ulysses")
+    m = types.ModuleType("yunchang.ulysses.attn_layer"); m.torch_attn = torch_attn
+    sys.modules[m.__name__] = m
+
+    # ---- flash-attn stub: exact fp32 attention, 8-tuple like flash-attn 2.6 -------
+    def _flash_attn_forward(q, k, v, dropout_p, softmax_scale, causal, window_size, softcap, alibi_slopes, return_softmax):
+        assert not causal and dropout_p == 0
+        s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * softmax_scale
+        lse = torch.logsumexp(s, dim=-1)
+        out = torch.einsum("bhqk,bkhd->bqhd", torch.exp(s - lse.unsqueeze(-1)), v.float()).to(q.dtype)
+        return out, q, k, v, out, lse, None, None
+
+    fa = pkg("flash_attn")
+    m = types.ModuleType("flash_attn.flash_attn_interface"); m._flash_attn_forward = _flash_attn_forward
+    sys.modules[m.__name__] = m
+    fa.flash_attn_interface = m
+
+    # ---- the reference's own files ----------------------------------------------
+    cm = load("hetu_dit.core.resource_manager.cache_manager", "hetu_dit/core/resource_manager/cache_manager.py")
+    ring = load("hetu_dit.core.parallel.ring.ring_flash_attn", "hetu_dit/core/parallel/ring/ring_flash_attn.py")
+    sys.modules["hetu_dit.core.parallel.ring"].ring_flash_attn_func = ring.ring_flash_attn_func
+    load("hetu_dit.core.parallel.hybrid.utils", "hetu_dit/core/parallel/hybrid/utils.py")
+    hyb = load("hetu_dit.core.parallel.hybrid.attn_layer", "hetu_dit/core/parallel/hybrid/attn_layer.py")
+    return _PG, cm, ring, hyb
+
+
+USP_CASES = {
+    # name: (world, ulysses, ring, class, joint_strategy, S_loc, S_txt, H, D, kv_cache)
+    "plain_u2": (2, 2, 1, "hetuDiTLongContextAttention", "none", 40, 0, 4, 64, False),
+    "flux_front_u2": (2, 2, 1, "hetuDiTFluxLongContextAttention", "front", 40, 24, 4, 64, False),
+    "joint_rear_u2r2": (4, 2, 2, "hetuDiTJointLongContextAttention", "rear", 24, 13, 4, 64, False),
+    "joint_front_r2": (2, 1, 2, "hetuDiTJointLongContextAttention", "front", 33, 9, 2, 128, False),
+    "joint_rear_u4": (4, 4, 1, "hetuDiTJointLongContextAttention", "rear", 16, 7, 8, 64, False),
+    "joint_rear_r4": (4, 1, 4, "hetuDiTJointLongContextAttention", "rear", 20, 5, 2, 64, False),
+    "kvcache_rear_u2": (2, 2, 1, "hetuDiTJointLongContextAttention", "rear", 32, 11, 4, 64, True),
+}
+
+
+def _usp_worker(rank, world, ref, name, port, outdir):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    _, U, R, cls_name, strategy, S_loc, S_txt, H, D, kv_cache = USP_CASES[name]
+    state = _NS(sp_world=U * R, ulysses=U, runtime=None)
+    PG, cm, ring_mod, hyb = _install_stub_packages(ref, state)
+    # Ulysses groups: consecutive ranks; ring groups: stride U (parallel_state.py:679-712).
+    for i in range(R):
+        g = dist.new_group(list(range(i * U, (i + 1) * U)), backend="gloo")
+        if rank // U == i:
+            PG.ULYSSES_PG = g
+    for i in range(U):
+        g = dist.new_group(list(range(i, U * R, U)), backend="gloo")
+        if rank % U == i:
+            PG.RING_PG = g
+
+    gen = torch.Generator().manual_seed(1000 + sum(map(ord, name)))
+    B = 1
+    P = U * R
+    full = {k: torch.randn(B, S_loc * P, H, D, generator=gen) for k in ("q", "k", "v")}
+    joint = {k: torch.randn(B, S_txt, H, D, generator=gen) for k in ("jq", "jk", "jv")} if S_txt else {}
+    sl = slice(rank * S_loc, (rank + 1) * S_loc)
+    q, k, v = (full[n][:, sl].contiguous() for n in ("q", "k", "v"))
+    layer = getattr(hyb, cls_name)()
+    kwargs = {}
+    if strategy != "none":
+        kwargs = dict(joint_tensor_query=joint["jq"], joint_tensor_key=joint["jk"], joint_tensor_value=joint["jv"],
+                      joint_strategy=strategy)
+    save = {}
+    if not kv_cache:
+        out = layer(None, q, k, v, **kwargs)
+        save["out"] = out.numpy()
+    else:
+        # PipeFusion + SP: a warm-up (whole image) call fills the stale-KV buffer, then one patch call reuses it.
+        n_patch = 2
+        tok = S_loc // n_patch
+        rt = _NS(num_pipeline_patch=n_patch, patch_mode=False, pipeline_patch_idx=0,
+                 pp_patches_token_num=[tok] * n_patch,
+                 pp_patches_token_start_idx_local=[i * tok for i in range(n_patch + 1)])
+        state.runtime = rt
+        attn_obj = object()
+        cm.get_cache_manager().register_cache_entry(attn_obj, "attn", "sequence_parallel_attn_cache")
+        out0 = layer(attn_obj, q, k, v, **kwargs)
+        save["out_warmup"] = out0.numpy()
+        # new activations for patch 1 only
+        fresh = {n: torch.randn(B, tok * P, H, D, generator=gen) for n in ("q", "k", "v")}
+        psl = slice(rank * tok, (rank + 1) * tok)
+        rt.patch_mode, rt.pipeline_patch_idx = True, 1
+        out1 = layer(attn_obj, fresh["q"][:, psl].contiguous(), fresh["k"][:, psl].contiguous(),
+                     fresh["v"][:, psl].contiguous(), **kwargs)
+        save["out_patch1"] = out1.numpy()
+        if rank == 0:
+            for n in ("q", "k", "v"):
+                save[f"fresh_{n}"] = fresh[n].numpy()
+    np.savez_compressed(os.path.join(outdir, f"rank{rank}.npz"), **save)
+    if rank == 0:
+        inputs = {n: t.numpy() for n, t in {**full, **joint}.items()}
+        np.savez_compressed(os.path.join(outdir, "inputs.npz"), **inputs)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def gen_usp(ref):
+    import tempfile
+    import torch.multiprocessing as mp
+    port = 29611
+    for name, spec in USP_CASES.items():
+        world = spec[0]
+        with tempfile.TemporaryDirectory() as tmp:
+            mp.spawn(_usp_worker, args=(world, ref, name, port, tmp), nprocs=world, join=True)
+            port += 1
+            merged = {}
+            with np.load(os.path.join(tmp, "inputs.npz")) as f:
+                merged.update({k: f[k] for k in f.files})
+            for r in range(world):
+                with np.load(os.path.join(tmp, f"rank{r}.npz")) as f:
+                    for k in f.files:
+                        merged[k if k.startswith("fresh_") else f"{k}_rank{r}"] = f[k]
+            merged["spec"] = np.array(json.dumps({
+                "world": world, "ulysses": spec[1], "ring": spec[2], "cls": spec[3], "joint_strategy": spec[4],
+                "s_loc": spec[5], "s_txt": spec[6], "heads": spec[7], "head_dim": spec[8], "kv_cache": spec[9]}))
+            np.savez_compressed(os.path.join(HERE, f"usp_{name}.npz"), **merged)
+            print(f"usp_{name}.npz written")
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only", default="")
+    a = ap.parse_args()
+    logging.basicConfig(level=logging.ERROR)
+    torch.set_num_threads(2)
+    if a.only in ("", "bookkeeping"):
+        gen_bookkeeping(a.reference)
+    if a.only in ("", "rope"):
+        gen_rope(a.reference)
+    if a.only in ("", "usp"):
+        gen_usp(a.reference)
