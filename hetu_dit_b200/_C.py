@@ -67,6 +67,57 @@ class AttnArgs(ctypes.Structure):
     ]
 
 
+class CopyPiece(ctypes.Structure):
+    _fields_ = [
+        ("src", ctypes.c_void_p),
+        ("dst", ctypes.c_void_p),
+        ("n_outer", ctypes.c_int64),
+        ("src_outer_pitch", ctypes.c_int64),
+        ("dst_outer_pitch", ctypes.c_int64),
+        ("rows", ctypes.c_int64),
+        ("src_pitch", ctypes.c_int64),
+        ("dst_pitch", ctypes.c_int64),
+        ("row_bytes", ctypes.c_int64),
+    ]
+
+
+class NormRopeTensor(ctypes.Structure):
+    _fields_ = [
+        ("x", ctypes.c_void_p),
+        ("x_stride_b", ctypes.c_int64),
+        ("x_stride_s", ctypes.c_int64),
+        ("x_stride_h", ctypes.c_int64),
+        ("norm_weight", ctypes.c_void_p),
+        ("do_norm", ctypes.c_int32),
+        ("do_rope", ctypes.c_int32),
+        ("dst", ctypes.c_void_p * 8),
+        ("dst_stride_b", ctypes.c_int64),
+        ("dst_stride_s", ctypes.c_int64),
+        ("dst_stride_h", ctypes.c_int64),
+        ("dst_seq_offset", ctypes.c_int64),
+    ]
+
+
+class NormRopeArgs(ctypes.Structure):
+    _fields_ = [
+        ("dtype", ctypes.c_int32),
+        ("batch", ctypes.c_int32),
+        ("seq", ctypes.c_int32),
+        ("heads", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("n_tensors", ctypes.c_int32),
+        ("n_dst", ctypes.c_int32),
+        ("eps", ctypes.c_float),
+        ("cos", ctypes.c_void_p),
+        ("sin", ctypes.c_void_p),
+        ("rope_rows", ctypes.c_int64),
+        ("rope_seq_start", ctypes.c_int64),
+        ("rope_row0", ctypes.c_int64),
+        ("t", NormRopeTensor * 3),
+        ("stream", ctypes.c_void_p),
+    ]
+
+
 _lib = None
 _lock = threading.Lock()
 
@@ -80,6 +131,13 @@ def _declare(lib):
     lib.hdit_device_status.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int32), ctypes.c_int]
     lib.hdit_attn_fwd.restype = ctypes.c_int
     lib.hdit_attn_fwd.argtypes = [ctypes.POINTER(AttnArgs)]
+    lib.hdit_copy_pieces.restype = ctypes.c_int
+    lib.hdit_copy_pieces.argtypes = [ctypes.POINTER(CopyPiece), ctypes.c_int64, ctypes.c_void_p]
+    lib.hdit_kv_scatter.restype = ctypes.c_int
+    lib.hdit_kv_scatter.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int64] * 7 + [
+        ctypes.c_void_p]
+    lib.hdit_qk_norm_rope.restype = ctypes.c_int
+    lib.hdit_qk_norm_rope.argtypes = [ctypes.POINTER(NormRopeArgs)]
 
 
 def lib():

@@ -1,0 +1,230 @@
+// Fused per-head RMSNorm + rotary embedding + (optional) Ulysses head scatter.
+//
+// One pass over Q, K (and V, copy only) of a layer: each thread owns 8
+// consecutive elements (16 bytes) of one (token, head) row, the row's threads
+// reduce the sum of squares with shuffles, and the result is written either in
+// place, to a plain destination, or head-sliced into up to 8 destination
+// buffers (one per Ulysses peer, mapped peer memory included) at a sequence
+// offset -- which turns the head->sequence all-to-all into the epilogue of this
+// kernel. HBM-bound: 2 bytes read + 2 bytes written per element plus the
+// L2-resident cos/sin rows.
+//
+// Rounding follows the reference's eager sequence so results agree to the
+// last bit wherever the fp32 reduction order does: normalise in fp32, round to
+// the 16-bit type, multiply by the 16-bit weight and round, rotate in fp32 with
+// separately rounded products, round once more.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "host_common.h"
+
+namespace hdit {
+namespace {
+
+constexpr int kMaxDst = 8;
+constexpr int kMaxTensors = 3;
+
+struct NormRopeTensor {
+  const void* x;
+  long long xs_b, xs_s, xs_h;
+  const void* weight;  // 16-bit (D) or null
+  int do_norm;
+  int do_rope;
+  void* dst[kMaxDst];
+  long long ds_b, ds_s, ds_h;
+  long long dst_seq_offset;
+};
+
+struct NormRopeParams {
+  NormRopeTensor t[kMaxTensors];
+  int n_tensors;
+  int batch, seq, heads;
+  int n_dst;           // heads are split evenly over n_dst destinations
+  float eps;
+  const float* cos_tab;  // (rope_rows, D) fp32
+  const float* sin_tab;
+  long long rope_seq_start;  // tokens below this index are not rotated
+  long long rope_row0;       // table row of token rope_seq_start
+};
+
+template <bool FP16>
+__device__ __forceinline__ float to_f(uint16_t v) {
+  if constexpr (FP16)
+    return __half2float(__ushort_as_half(v));
+  else
+    return __bfloat162float(__ushort_as_bfloat16(v));
+}
+template <bool FP16>
+__device__ __forceinline__ uint16_t from_f(float f) {
+  if constexpr (FP16)
+    return __half_as_ushort(__float2half_rn(f));
+  else
+    return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+
+template <int D, bool FP16>
+__global__ void __launch_bounds__(512) norm_rope_kernel(const __grid_constant__ NormRopeParams p) {
+  constexpr int TPR = D / 8;  // threads per (token, head) row
+  const NormRopeTensor& t = p.t[blockIdx.y];
+  const int rows_per_iter = blockDim.x / TPR;
+  const int part = threadIdx.x % TPR;
+  const int row_in_blk = threadIdx.x / TPR;
+  const int heads_per_dst = p.heads / p.n_dst;
+  const long long n_tok = static_cast<long long>(p.batch) * p.seq;
+
+  for (long long tok = blockIdx.x; tok < n_tok; tok += gridDim.x) {
+    const int b = static_cast<int>(tok / p.seq);
+    const int s = static_cast<int>(tok - static_cast<long long>(b) * p.seq);
+    const bool rotate = t.do_rope && s >= p.rope_seq_start;
+    float cs[8], sn[8];
+    if (rotate) {
+      const long long trow = (s - p.rope_seq_start + p.rope_row0) * D + part * 8;
+      const float4 c0 = *reinterpret_cast<const float4*>(p.cos_tab + trow);
+      const float4 c1 = *reinterpret_cast<const float4*>(p.cos_tab + trow + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(p.sin_tab + trow);
+      const float4 s1 = *reinterpret_cast<const float4*>(p.sin_tab + trow + 4);
+      cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    }
+    // All threads of a warp run the same number of iterations (heads is padded up), so the
+    // shuffles below are always executed by full warps.
+    for (int h0 = 0; h0 < p.heads; h0 += rows_per_iter) {
+      const int h = h0 + row_in_blk;
+      const bool live = h < p.heads;
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (live) {
+        const uint16_t* src = static_cast<const uint16_t*>(t.x) + b * t.xs_b + s * t.xs_s + h * t.xs_h + part * 8;
+        raw = *reinterpret_cast<const uint4*>(src);
+      }
+      const uint16_t* e = reinterpret_cast<const uint16_t*>(&raw);
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = to_f<FP16>(e[i]);
+
+      if (t.do_norm) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+#pragma unroll
+        for (int off = TPR / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        const float rstd = rsqrtf(ss * (1.0f / D) + p.eps);
+        if (t.weight != nullptr) {
+          const uint4 wraw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(t.weight) + part * 8);
+          const uint16_t* w = reinterpret_cast<const uint16_t*>(&wraw);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float y = to_f<FP16>(from_f<FP16>(__fmul_rn(f[i], rstd)));
+            f[i] = to_f<FP16>(from_f<FP16>(__fmul_rn(y, to_f<FP16>(w[i]))));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = to_f<FP16>(from_f<FP16>(__fmul_rn(f[i], rstd)));
+        }
+      }
+      if (rotate) {
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          const float a = f[i], c = f[i + 1];
+          f[i] = __fadd_rn(__fmul_rn(a, cs[i]), __fmul_rn(-c, sn[i]));
+          f[i + 1] = __fadd_rn(__fmul_rn(c, cs[i + 1]), __fmul_rn(a, sn[i + 1]));
+        }
+      }
+      if (live) {
+        uint4 outv;
+        uint16_t* o = reinterpret_cast<uint16_t*>(&outv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = from_f<FP16>(f[i]);
+        const int d_idx = h / heads_per_dst;
+        const int hh = h - d_idx * heads_per_dst;
+        uint16_t* dst = static_cast<uint16_t*>(t.dst[d_idx]) + b * t.ds_b + (s + t.dst_seq_offset) * t.ds_s +
+                        hh * t.ds_h + part * 8;
+        *reinterpret_cast<uint4*>(dst) = outv;
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace hdit
+
+extern "C" int hdit_qk_norm_rope(const hdit_norm_rope_args* a) {
+  using namespace hdit;
+  if (a == nullptr) return set_error(HDIT_ERR_BAD_ARG, "args is null");
+  if (a->dtype != HDIT_BF16 && a->dtype != HDIT_FP16) return set_error(HDIT_ERR_BAD_ARG, "dtype must be bf16 or fp16");
+  if (a->head_dim != 64 && a->head_dim != 128) return set_error(HDIT_ERR_SHAPE, "head_dim must be 64 or 128");
+  if (a->n_tensors < 1 || a->n_tensors > kMaxTensors) return set_error(HDIT_ERR_SHAPE, "n_tensors must be 1..3");
+  if (a->n_dst < 1 || a->n_dst > kMaxDst || a->heads % a->n_dst != 0)
+    return set_error(HDIT_ERR_SHAPE, "heads (%d) must split evenly over n_dst (%d) <= 8", a->heads, a->n_dst);
+  if (a->batch < 0 || a->seq < 0 || a->heads <= 0) return set_error(HDIT_ERR_BAD_ARG, "negative size");
+  if (static_cast<long long>(a->batch) * a->seq == 0) return HDIT_OK;
+  NormRopeParams p;
+  memset(&p, 0, sizeof(p));
+  bool any_rope = false;
+  for (int i = 0; i < a->n_tensors; ++i) {
+    const hdit_norm_rope_tensor& s = a->t[i];
+    NormRopeTensor& d = p.t[i];
+    if (s.x == nullptr) return set_error(HDIT_ERR_BAD_ARG, "tensor %d: x is null", i);
+    if ((reinterpret_cast<uintptr_t>(s.x) & 15) || (s.x_stride_b % 8) || (s.x_stride_s % 8) || (s.x_stride_h % 8))
+      return set_error(HDIT_ERR_SHAPE, "tensor %d: x must be 16-byte aligned with strides multiple of 8", i);
+    if ((s.dst_stride_b % 8) || (s.dst_stride_s % 8) || (s.dst_stride_h % 8))
+      return set_error(HDIT_ERR_SHAPE, "tensor %d: dst strides must be multiples of 8", i);
+    if (s.norm_weight != nullptr && (reinterpret_cast<uintptr_t>(s.norm_weight) & 15))
+      return set_error(HDIT_ERR_SHAPE, "tensor %d: norm weight must be 16-byte aligned", i);
+    d.x = s.x;
+    d.xs_b = s.x_stride_b;
+    d.xs_s = s.x_stride_s;
+    d.xs_h = s.x_stride_h;
+    d.weight = s.norm_weight;
+    d.do_norm = s.do_norm;
+    d.do_rope = s.do_rope;
+    any_rope |= s.do_rope != 0;
+    for (int j = 0; j < a->n_dst; ++j) {
+      if (s.dst[j] == nullptr || (reinterpret_cast<uintptr_t>(s.dst[j]) & 15))
+        return set_error(HDIT_ERR_BAD_ARG, "tensor %d: dst[%d] null or misaligned", i, j);
+      d.dst[j] = s.dst[j];
+    }
+    d.ds_b = s.dst_stride_b;
+    d.ds_s = s.dst_stride_s;
+    d.ds_h = s.dst_stride_h;
+    d.dst_seq_offset = s.dst_seq_offset;
+  }
+  if (any_rope) {
+    if (a->cos == nullptr || a->sin == nullptr) return set_error(HDIT_ERR_BAD_ARG, "rope requested without cos/sin tables");
+    if ((reinterpret_cast<uintptr_t>(a->cos) & 15) || (reinterpret_cast<uintptr_t>(a->sin) & 15))
+      return set_error(HDIT_ERR_SHAPE, "cos/sin tables must be 16-byte aligned");
+    if (a->rope_seq_start < 0 || a->rope_row0 < 0 ||
+        (a->seq > a->rope_seq_start && a->rope_row0 + (a->seq - a->rope_seq_start) > a->rope_rows))
+      return set_error(HDIT_ERR_SHAPE, "rope table of %lld rows does not cover tokens [%lld, %d)",
+                       (long long)a->rope_rows, (long long)a->rope_seq_start, a->seq);
+  }
+  p.n_tensors = a->n_tensors;
+  p.batch = a->batch;
+  p.seq = a->seq;
+  p.heads = a->heads;
+  p.n_dst = a->n_dst;
+  p.eps = a->eps;
+  p.cos_tab = a->cos;
+  p.sin_tab = a->sin;
+  p.rope_seq_start = a->rope_seq_start;
+  p.rope_row0 = a->rope_row0;
+
+  const int tpr = a->head_dim / 8;
+  int threads = a->heads * tpr;
+  threads = (threads + 31) / 32 * 32;
+  if (threads > 512) threads = 512;
+  const long long n_tok = static_cast<long long>(a->batch) * a->seq;
+  const long long cap = 148LL * 8;
+  dim3 grid(static_cast<unsigned>(n_tok < cap ? n_tok : cap), static_cast<unsigned>(a->n_tensors));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
+  const bool fp16 = a->dtype == HDIT_FP16;
+  if (a->head_dim == 128) {
+    if (fp16) norm_rope_kernel<128, true><<<grid, threads, 0, st>>>(p);
+    else norm_rope_kernel<128, false><<<grid, threads, 0, st>>>(p);
+  } else {
+    if (fp16) norm_rope_kernel<64, true><<<grid, threads, 0, st>>>(p);
+    else norm_rope_kernel<64, false><<<grid, threads, 0, st>>>(p);
+  }
+  HDIT_CUDA_OK(cudaGetLastError());
+  return HDIT_OK;
+}

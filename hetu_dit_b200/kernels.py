@@ -93,3 +93,119 @@ def attn_fwd(
     if not writes_out:
         return None
     return (out, lse) if return_lse else out
+
+
+def copy_pieces(pieces, device):
+    """Moves a list of (src_ptr, dst_ptr, n_outer, src_outer_pitch, dst_outer_pitch, rows, src_pitch,
+    dst_pitch, row_bytes) boxes (all byte units) on `device`'s current stream."""
+    n = len(pieces)
+    if n == 0:
+        return
+    arr = (_C.CopyPiece * n)()
+    for i, pc in enumerate(pieces):
+        (arr[i].src, arr[i].dst, arr[i].n_outer, arr[i].src_outer_pitch, arr[i].dst_outer_pitch, arr[i].rows,
+         arr[i].src_pitch, arr[i].dst_pitch, arr[i].row_bytes) = pc
+    with torch.cuda.device(device):
+        _C.check(_C.lib().hdit_copy_pieces(arr, n, _stream_ptr(device)))
+
+
+def copy_2d(dst, src):
+    """dst[...] = src[...] for two same-shape views whose last dim is contiguous and whose leading dims
+    collapse to at most (outer, rows); used for patch hand-off and slice copies."""
+    if dst.shape != src.shape or dst.dtype != src.dtype:
+        raise ValueError("shape / dtype mismatch")
+    if dst.numel() == 0:
+        return
+    es = src.element_size()
+    pieces = [(s.data_ptr(), d.data_ptr(), o, sop * es, dop * es, r, sp * es, dp * es, rb * es)
+              for (s, d, o, sop, dop, r, sp, dp, rb) in _collapse(src, dst)]
+    copy_pieces(pieces, src.device if src.is_cuda else dst.device)
+
+
+def _collapse(src, dst):
+    """Splits a same-shape (src, dst) view pair into 3-level boxes (element units)."""
+    shape = list(src.shape)
+    ss, ds = list(src.stride()), list(dst.stride())
+    # drop size-1 dims, merge dims that are contiguous in both tensors
+    dims = [(n, a, b) for n, a, b in zip(shape, ss, ds) if n != 1]
+    if not dims:
+        return [(src, dst, 1, 0, 0, 1, 0, 0, 1)]
+    merged = [dims[-1]]
+    for n, a, b in reversed(dims[:-1]):
+        n0, a0, b0 = merged[0]
+        if a == a0 * n0 and b == b0 * n0:
+            merged[0] = (n * n0, a0, b0)
+        else:
+            merged.insert(0, (n, a, b))
+    if merged[-1][1] != 1 or merged[-1][2] != 1:
+        raise ValueError("innermost dimension must be contiguous in both tensors")
+    row = merged[-1][0]
+    lead = merged[:-1]
+    if len(lead) == 0:
+        return [(src, dst, 1, 0, 0, 1, 0, 0, row)]
+    if len(lead) == 1:
+        return [(src, dst, 1, 0, 0, lead[0][0], lead[0][1], lead[0][2], row)]
+    if len(lead) == 2:
+        return [(src, dst, lead[0][0], lead[0][1], lead[0][2], lead[1][0], lead[1][1], lead[1][2], row)]
+    # more than two leading levels: peel the outermost
+    out = []
+    for i in range(shape[0]):
+        out.extend(_collapse(src[i], dst[i]))
+    return out
+
+
+def kv_scatter(kv_cache, new_k, new_v, token_start):
+    """kv_cache: (B, S, 2*R) stale buffer in the [K || V] layout; new_k / new_v: (B, n, R)-shaped views
+    (any trailing dims, rows contiguous). Writes rows [token_start, token_start + n)."""
+    B, S = kv_cache.shape[0], kv_cache.shape[1]
+    nk = new_k.reshape(B, new_k.shape[1], -1) if new_k.dim() != 3 else new_k
+    nv = new_v.reshape(B, new_v.shape[1], -1) if new_v.dim() != 3 else new_v
+    n, R = nk.shape[1], nk.shape[2]
+    if kv_cache.shape[2] != 2 * R or not kv_cache.is_contiguous():
+        raise ValueError("kv_cache must be contiguous (B, S, 2*row)")
+    if nk.stride(2) != 1 or nv.stride(2) != 1 or nk.stride() != nv.stride():
+        raise ValueError("new_k / new_v rows must be contiguous and share strides")
+    es = kv_cache.element_size()
+    with torch.cuda.device(kv_cache.device):
+        _C.check(_C.lib().hdit_kv_scatter(kv_cache.data_ptr(), nk.data_ptr(), nv.data_ptr(), B, S, int(token_start), n,
+                                          R * es, nk.stride(1) * es, nk.stride(0) * es, _stream_ptr(kv_cache.device)))
+
+
+def qk_norm_rope(tensors, *, eps=1e-6, cos=None, sin=None, rope_seq_start=0, rope_row0=0, dsts=None,
+                 dst_seq_offset=0):
+    """Fused RMSNorm + RoPE (+ head scatter) over up to three (B, S, H, D) tensors.
+
+    tensors: list of (x, norm_weight or None, do_norm, do_rope). dsts: None for in-place, or a list (one
+    entry per tensor) of lists of destination tensors (B, S_dst, H/n_dst, D); all tensors share n_dst.
+    """
+    x0 = tensors[0][0]
+    B, S, H, D = x0.shape
+    a = _C.NormRopeArgs()
+    a.dtype = _DTYPE_CODE[x0.dtype]
+    a.batch, a.seq, a.heads, a.head_dim = B, S, H, D
+    a.n_tensors = len(tensors)
+    a.eps = eps
+    if cos is not None:
+        if cos.dtype != torch.float32 or sin.dtype != torch.float32 or not cos.is_contiguous() or not sin.is_contiguous():
+            raise TypeError("cos / sin must be contiguous fp32 (rows, D) tables")
+        a.cos, a.sin, a.rope_rows = cos.data_ptr(), sin.data_ptr(), cos.shape[0]
+    a.rope_seq_start, a.rope_row0 = int(rope_seq_start), int(rope_row0)
+    n_dst = 1 if dsts is None else len(dsts[0])
+    a.n_dst = n_dst
+    for i, (x, w, do_norm, do_rope) in enumerate(tensors):
+        if tuple(x.shape) != (B, S, H, D) or x.stride(3) != 1:
+            raise ValueError("all tensors must be (B, S, H, D) with contiguous D")
+        t = a.t[i]
+        t.x = x.data_ptr()
+        t.x_stride_b, t.x_stride_s, t.x_stride_h = x.stride(0), x.stride(1), x.stride(2)
+        t.norm_weight = w.data_ptr() if w is not None else None
+        t.do_norm, t.do_rope = int(bool(do_norm)), int(bool(do_rope))
+        outs = [x] if dsts is None else dsts[i]
+        for j, o in enumerate(outs):
+            t.dst[j] = o.data_ptr()
+        o0 = outs[0]
+        t.dst_stride_b, t.dst_stride_s, t.dst_stride_h = o0.stride(0), o0.stride(1), o0.stride(2)
+        t.dst_seq_offset = int(dst_seq_offset)
+    a.stream = _stream_ptr(x0.device)
+    with torch.cuda.device(x0.device):
+        _C.check(_C.lib().hdit_qk_norm_rope(ctypes.byref(a)))

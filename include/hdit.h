@@ -128,6 +128,98 @@ typedef struct hdit_attn_args {
 
 HDIT_API int hdit_attn_fwd(const hdit_attn_args* args);
 
+/*
+ * One strided box to move: n_outer x rows x row_bytes, with independent source and
+ * destination pitches (all in bytes). src and dst may live on different GPUs of one
+ * NVSwitch domain when the pointer is a mapped peer address.
+ */
+typedef struct hdit_copy_piece {
+  const void* src;
+  void* dst;
+  int64_t n_outer, src_outer_pitch, dst_outer_pitch;
+  int64_t rows, src_pitch, dst_pitch;
+  int64_t row_bytes;
+} hdit_copy_piece;
+
+/*
+ * Moves `n` pieces (host array) with one vectorised, coalesced copy kernel per 40
+ * pieces; the piece table travels in kernel parameter space.
+ *
+ * Replaces, in the reference, the data plane of parameter-slice migration: the
+ * NIXL/UCX WRITE built from per-piece descriptors in
+ * hetu_dit/core/distributed/nixl_manager.py:186-252 (destination side) and
+ * hetu_dit/worker/worker.py:2336-2406 (source side), where a row-split piece is one
+ * contiguous span and a column-split piece is one descriptor per weight row (here:
+ * one piece with rows = out_features); and the pinned-buffer slice copies of the CPU
+ * back-fill, hetu_dit/model_executor/cache/base_cache.py:907-996. It also carries
+ * the PipeFusion patch hand-off that the reference does with NCCL isend/irecv,
+ * hetu_dit/core/distributed/group_coordinator.py:982-1002.
+ */
+HDIT_API int hdit_copy_pieces(const hdit_copy_piece* pieces, int64_t n, void* stream);
+
+/*
+ * Stale-KV scatter: writes the fresh K and V rows of one PipeFusion patch into the
+ * per-layer stale buffer, whose layout is the reference's [K || V] concatenation on
+ * the last dim: (batch, cache_tokens, 2 * row_bytes). new_k / new_v hold n_tokens rows
+ * of row_bytes each, new_token_pitch / new_batch_pitch bytes apart.
+ *
+ * Replaces torch.cat([k, v], -1) + kv_cache[:, start:end] = new_kv + torch.chunk in
+ * CacheManager.update_and_get_kv_cache / _update_kv_in_dim
+ * (hetu_dit/core/resource_manager/cache_manager.py:88-90,113,134-148,186-205,208-231).
+ */
+HDIT_API int hdit_kv_scatter(void* kv_cache, const void* new_k, const void* new_v, int64_t batch,
+                             int64_t cache_tokens, int64_t token_start, int64_t n_tokens, int64_t row_bytes,
+                             int64_t new_token_pitch, int64_t new_batch_pitch, void* stream);
+
+/* One tensor handled by hdit_qk_norm_rope: (B, S, H, D) in, the same logical tensor out. */
+typedef struct hdit_norm_rope_tensor {
+  const void* x;
+  int64_t x_stride_b, x_stride_s, x_stride_h;   /* elements; D contiguous */
+  const void* norm_weight;                      /* (D) in `dtype`, or NULL for a weightless norm */
+  int32_t do_norm;                              /* 0 = skip RMSNorm */
+  int32_t do_rope;                              /* 0 = skip rotary embedding */
+  void* dst[8];                                 /* n_dst destinations; dst[j] receives heads [j*H/n_dst, (j+1)*H/n_dst) */
+  int64_t dst_stride_b, dst_stride_s, dst_stride_h;
+  int64_t dst_seq_offset;                       /* token s lands at row s + dst_seq_offset of the destination */
+} hdit_norm_rope_tensor;
+
+/*
+ * Fused per-head RMSNorm + rotary embedding for up to three tensors of one layer (Q, K
+ * and, copy only, V), written in place, to a plain destination, or head-sliced into
+ * n_dst buffers at a sequence offset. With the buffers of the Ulysses peers as
+ * destinations this is the head->sequence all-to-all done as peer stores from the
+ * QKV-projection epilogue.
+ *
+ * Replaces, in the reference:
+ *   attn.norm_q / norm_k / norm_added_q / norm_added_k calls
+ *     (hetu_dit/model_executor/diffusion_executor/layers/attention_processor.py:
+ *      552-555, 859-862, 881-888, 1069-1072, 1404-1407, 1452-1455),
+ *   apply_rotary_emb, use_real=True, use_real_unbind_dim=-1 (:68-120; call sites
+ *     :903-905, :1075-1082, :1410-1434),
+ *   SeqAllToAll4D.apply(ulysses_pg, x, scatter_idx=2, gather_idx=1)
+ *     (hetu_dit/core/parallel/hybrid/attn_layer.py:102-110, 234-242, 355-363).
+ *
+ * cos / sin are (rope_rows, D) fp32 tables; token s >= rope_seq_start uses table row
+ * (s - rope_seq_start + rope_row0); earlier tokens (e.g. the text prefix of CogVideoX /
+ * HunyuanVideo) are not rotated. eps is the RMSNorm epsilon.
+ */
+typedef struct hdit_norm_rope_args {
+  int32_t dtype;
+  int32_t batch, seq, heads, head_dim;
+  int32_t n_tensors;
+  int32_t n_dst;
+  float eps;
+  const float* cos;
+  const float* sin;
+  int64_t rope_rows;
+  int64_t rope_seq_start;
+  int64_t rope_row0;
+  hdit_norm_rope_tensor t[3];
+  void* stream;
+} hdit_norm_rope_args;
+
+HDIT_API int hdit_qk_norm_rope(const hdit_norm_rope_args* args);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,181 @@
+"""GPU parity of the tcgen05 attention kernel (through the C ABI) against the CPU oracle.
+
+Acceptance for 16-bit activations: cosine similarity >= 0.9999 and
+max |got - want| / max |want| <= 2e-2 per output block.
+"""
+import pytest
+import torch
+
+from oracle import attention as oa
+
+pytestmark = pytest.mark.gpu
+
+COS_MIN = 0.9999
+MAX_REL = 2e-2
+LSE_ATOL = 2e-3
+
+
+def _mk(shape, dtype, gen, transposed=False):
+    B, S, H, D = shape
+    if transposed:
+        return torch.randn(B, H, S, D, generator=gen, dtype=torch.float32).to(dtype).transpose(1, 2)
+    return torch.randn(B, S, H, D, generator=gen, dtype=torch.float32).to(dtype)
+
+
+def _check(out, lse, qs, ks, vs, scale=None):
+    q, k, v = (torch.cat(x, 1) for x in (qs, ks, vs))
+    want, want_lse = oa.attention_with_lse(q, k, v, scale)
+    cos, rel = oa.cosine_and_max_rel(out.cpu(), want)
+    assert cos >= COS_MIN and rel <= MAX_REL, (cos, rel)
+    if lse is not None:
+        assert (lse.cpu() - want_lse).abs().max().item() <= LSE_ATOL
+
+
+def _run(qs, ks, vs, **kw):
+    from hetu_dit_b200 import _C, kernels
+    dev = torch.device("cuda:0")
+    out, lse = kernels.attn_fwd([t.to(dev) for t in qs], [t.to(dev) for t in ks], [t.to(dev) for t in vs],
+                                return_lse=True, **kw)
+    torch.cuda.synchronize()
+    assert _C.device_status(0, clear=True)[0] == 0
+    return out, lse
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("sq,skv", [(1, 1), (63, 65), (64, 64), (65, 127), (127, 129), (128, 128), (129, 63),
+                                    (300, 500), (256, 1024), (513, 257)])
+def test_single_segment(D, sq, skv):
+    gen = torch.Generator().manual_seed(sq * 1000 + skv + D)
+    q, k, v = _mk((2, sq, 3, D), torch.bfloat16, gen), _mk((2, skv, 3, D), torch.bfloat16, gen), _mk(
+        (2, skv, 3, D), torch.bfloat16, gen)
+    out, lse = _run([q], [k], [v])
+    _check(out, lse, [q], [k], [v])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D", [64, 128])
+def test_joint_segments(D, dtype):
+    """[image; text] ("rear") and [text; image] ("front") without a concatenated copy."""
+    gen = torch.Generator().manual_seed(7 + D)
+    img = [_mk((1, 333, 4, D), dtype, gen) for _ in range(3)]
+    txt = [_mk((1, 77, 4, D), dtype, gen) for _ in range(3)]
+    for order in ((img, txt), (txt, img)):
+        qs, ks, vs = [order[0][0], order[1][0]], [order[0][1], order[1][1]], [order[0][2], order[1][2]]
+        out, lse = _run(qs, ks, vs)
+        _check(out, lse, qs, ks, vs)
+
+
+def test_transposed_layout_and_scale():
+    gen = torch.Generator().manual_seed(11)
+    q, k, v = (_mk((2, 200, 4, 128), torch.bfloat16, gen, transposed=True) for _ in range(3))
+    out, lse = _run([q], [k], [v], softmax_scale=0.05)
+    _check(out, lse, [q], [k], [v], scale=0.05)
+
+
+def test_many_kv_segments():
+    gen = torch.Generator().manual_seed(12)
+    q = _mk((1, 150, 2, 64), torch.bfloat16, gen)
+    lens = [5, 128, 129, 1, 64, 200, 33, 17, 256, 90]
+    ks = [_mk((1, n, 2, 64), torch.bfloat16, gen) for n in lens]
+    vs = [_mk((1, n, 2, 64), torch.bfloat16, gen) for n in lens]
+    out, lse = _run([q], ks, vs)
+    _check(out, lse, [q], ks, vs)
+
+
+def test_large_score_range():
+    """Scores far apart exercise the lazy running-max rescale of O in TMEM."""
+    gen = torch.Generator().manual_seed(13)
+    q = _mk((1, 128, 1, 64), torch.bfloat16, gen) * 4
+    k = _mk((1, 1024, 1, 64), torch.bfloat16, gen)
+    k[:, 512:] *= 6  # later blocks carry much larger scores
+    v = _mk((1, 1024, 1, 64), torch.bfloat16, gen)
+    out, lse = _run([q], [k], [v])
+    _check(out, lse, [q], [k], [v])
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_partial_and_merge_modes(D):
+    """Ring-style accumulation: PARTIAL_FIRST, PARTIAL_MERGE, MERGE_FINAL over KV blocks == one shot."""
+    from hetu_dit_b200 import _C, kernels
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(14 + D)
+    q = _mk((2, 190, 3, D), torch.bfloat16, gen).to(dev)
+    blocks = [(_mk((2, n, 3, D), torch.bfloat16, gen).to(dev), _mk((2, n, 3, D), torch.bfloat16, gen).to(dev))
+              for n in (200, 77, 300)]
+    acc = torch.empty(2, 190, 3, D, dtype=torch.float32, device=dev)
+    acc_lse = torch.empty(2, 3, 190, dtype=torch.float32, device=dev)
+    kernels.attn_fwd([q], [blocks[0][0]], [blocks[0][1]], mode=_C.ATTN_PARTIAL_FIRST, acc_out=acc, acc_lse=acc_lse)
+    kernels.attn_fwd([q], [blocks[1][0]], [blocks[1][1]], mode=_C.ATTN_PARTIAL_MERGE, acc_out=acc, acc_lse=acc_lse)
+    out, lse = kernels.attn_fwd([q], [blocks[2][0]], [blocks[2][1]], mode=_C.ATTN_MERGE_FINAL, acc_out=acc,
+                                acc_lse=acc_lse, return_lse=True)
+    torch.cuda.synchronize()
+    assert _C.device_status(0, clear=True)[0] == 0
+    _check(out, lse, [q.cpu()], [b[0].cpu() for b in blocks], [b[1].cpu() for b in blocks])
+
+
+@pytest.mark.parametrize("name,H,D,s_img,s_txt,order", [
+    ("sd3-medium", 24, 64, 4096, 333, "rear"),
+    ("flux.1-dev", 24, 128, 4096, 512, "front"),
+])
+def test_baseline_image_shapes(name, H, D, s_img, s_txt, order):
+    gen = torch.Generator().manual_seed(15)
+    img = [_mk((1, s_img, H, D), torch.bfloat16, gen) for _ in range(3)]
+    txt = [_mk((1, s_txt, H, D), torch.bfloat16, gen) for _ in range(3)]
+    a, b = (img, txt) if order == "rear" else (txt, img)
+    qs, ks, vs = [a[0], b[0]], [a[1], b[1]], [a[2], b[2]]
+    out, lse = _run(qs, ks, vs)
+    # the CPU oracle on every head would take minutes; check 4 heads fully
+    hs = [0, 7, 13, H - 1]
+    _check(out[:, :, hs], lse[:, hs], [t[:, :, hs] for t in qs], [t[:, :, hs] for t in ks], [t[:, :, hs] for t in vs])
+
+
+@pytest.mark.parametrize("name,H,D,s_vid,s_txt", [
+    ("cogvideox-1.5-5b", 48, 64, 44880, 224),
+    ("hunyuanvideo u4", 6, 128, 118800, 256),
+])
+def test_video_shapes_properties(name, H, D, s_vid, s_txt):
+    """Full-size video sequences: the oracle checks a slice of rows; size-independent
+    properties cover the rest (softmax rows sum to one; block merge equals one shot)."""
+    from hetu_dit_b200 import _C, kernels
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(16)
+    Hs = 2  # two heads of the full-length sequence keep the test to a few seconds
+    q = _mk((1, 640, Hs, D), torch.bfloat16, gen).to(dev)
+    k = _mk((1, s_vid, Hs, D), torch.bfloat16, gen).to(dev)
+    v = _mk((1, s_vid, Hs, D), torch.bfloat16, gen).to(dev)
+    tk = _mk((1, s_txt, Hs, D), torch.bfloat16, gen).to(dev)
+    tv = _mk((1, s_txt, Hs, D), torch.bfloat16, gen).to(dev)
+    out, lse = kernels.attn_fwd([q], [tk, k], [tv, v], return_lse=True)
+    torch.cuda.synchronize()
+    assert _C.device_status(0, clear=True)[0] == 0
+    _check(out[:, :128], lse[:, :, :128], [q[:, :128].cpu()], [tk.cpu(), k.cpu()], [tv.cpu(), v.cpu()])
+    # V = 1 -> every output element is 1 (rows of P sum to one)
+    ones_v, ones_t = torch.ones_like(v), torch.ones_like(tv)
+    o1 = kernels.attn_fwd([q], [tk, k], [ones_t, ones_v])
+    assert (o1.float() - 1).abs().max().item() <= 1e-2
+    # two halves merged by log-sum-exp == one shot
+    half = s_vid // 2
+    acc = torch.empty(1, 640, Hs, D, dtype=torch.float32, device=dev)
+    acc_lse = torch.empty(1, Hs, 640, dtype=torch.float32, device=dev)
+    kernels.attn_fwd([q], [tk, k[:, :half]], [tv, v[:, :half]], mode=_C.ATTN_PARTIAL_FIRST, acc_out=acc, acc_lse=acc_lse)
+    o2, lse2 = kernels.attn_fwd([q], [k[:, half:]], [v[:, half:]], mode=_C.ATTN_MERGE_FINAL, acc_out=acc,
+                                acc_lse=acc_lse, return_lse=True)
+    torch.cuda.synchronize()
+    cos, rel = oa.cosine_and_max_rel(o2, out)
+    assert cos >= COS_MIN and rel <= MAX_REL
+    assert (lse2 - lse).abs().max().item() <= LSE_ATOL
+
+
+def test_argument_errors():
+    from hetu_dit_b200 import _C, kernels
+    dev = torch.device("cuda:0")
+    q = torch.zeros(1, 8, 2, 96, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(_C.HditError) as e:
+        kernels.attn_fwd([q], [q], [q])
+    assert e.value.code == _C.HDIT_ERR_SHAPE
+    q = torch.zeros(1, 8, 2, 64, dtype=torch.bfloat16, device=dev)
+    empty = torch.zeros(1, 0, 2, 64, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(_C.HditError):
+        kernels.attn_fwd([q], [empty], [empty])
+    with pytest.raises(TypeError):
+        kernels.attn_fwd([q.float()], [q.float()], [q.float()])

@@ -1,0 +1,133 @@
+"""GPU parity of the movement kernels (C ABI) against the CPU oracle: bit-exact for byte movement."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention as oa
+from oracle import bookkeeping as ob
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.mark.parametrize("shift,cols", [(0, 64), (8, 64), (4, 30), (2, 31), (1, 33)])
+def test_copy_pieces_alignments(shift, cols):
+    """Every vector width (16/8/4/2/1 bytes) moves exactly the requested bytes and nothing else."""
+    from hetu_dit_b200 import kernels
+    gen = torch.Generator().manual_seed(shift * 100 + cols)
+    src = torch.randint(0, 255, (5, 37, 256), dtype=torch.uint8, generator=gen).to(DEV)
+    dst = torch.zeros(5, 64, 300, dtype=torch.uint8, device=DEV)
+    want = dst.clone()
+    sv = src[:, 3:30, shift:shift + cols]
+    kernels.copy_pieces([(sv.data_ptr(), dst[:, 10:37, shift:shift + cols].data_ptr(), 5, 37 * 256, 64 * 300, 27, 256,
+                          300, cols)], torch.device(DEV))
+    want[:, 10:37, shift:shift + cols] = sv
+    torch.cuda.synchronize()
+    assert torch.equal(dst, want)
+
+
+def test_copy_many_pieces_and_empty():
+    from hetu_dit_b200 import kernels
+    src = torch.arange(100 * 1024, dtype=torch.int32, device=DEV).reshape(100, 1024)
+    dst = torch.zeros_like(src)
+    pieces = [(src[i].data_ptr(), dst[99 - i].data_ptr(), 1, 0, 0, 1, 0, 0, 4096) for i in range(100)]
+    pieces.append((src.data_ptr(), dst.data_ptr(), 1, 0, 0, 0, 0, 0, 4096))  # zero rows: ignored
+    kernels.copy_pieces(pieces, torch.device(DEV))
+    kernels.copy_pieces([], torch.device(DEV))
+    torch.cuda.synchronize()
+    assert torch.equal(dst, src.flip(0))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_kv_scatter_matches_cache_update(dtype):
+    """PipeFusion stale-KV scatter for every patch of an SD3-shaped layer, bit for bit."""
+    from hetu_dit_b200 import kernels
+    B, H, D = 2, 24, 64
+    meta = ob.calc_patches_metadata(512, 512, 8, 2, 4, 1, 0)
+    tok = meta["pp_patches_token_start_idx_local"]
+    S = tok[-1]
+    gen = torch.Generator().manual_seed(3)
+    cache_cpu = torch.randn(B, S, 2 * H * D, generator=gen).to(dtype)
+    cache = cache_cpu.clone().to(DEV)
+    for p in range(meta["num_pipeline_patch"]):
+        n = tok[p + 1] - tok[p]
+        k = torch.randn(B, n, H * D, generator=gen).to(dtype)
+        v = torch.randn(B, n, H * D, generator=gen).to(dtype)
+        want = oa.kv_cache_update(cache_cpu, torch.cat([k, v], -1), True, meta["num_pipeline_patch"], p, tok)
+        kernels.kv_scatter(cache, k.to(DEV), v.to(DEV), tok[p])
+        torch.cuda.synchronize()
+        assert torch.equal(cache.cpu(), want)
+        kc, vc = torch.chunk(cache, 2, dim=-1)
+        assert torch.equal(kc[:, tok[p]:tok[p + 1]].cpu(), k) and torch.equal(vc[:, tok[p]:tok[p + 1]].cpu(), v)
+
+
+def test_kv_scatter_range_error():
+    from hetu_dit_b200 import _C, kernels
+    cache = torch.zeros(1, 16, 128, dtype=torch.bfloat16, device=DEV)
+    k = torch.zeros(1, 8, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(_C.HditError) as e:
+        kernels.kv_scatter(cache, k, k, 12)
+    assert e.value.code == _C.HDIT_ERR_SHAPE
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_norm_rope_matches_oracle(D, dtype):
+    from hetu_dit_b200 import kernels
+    gen = torch.Generator().manual_seed(D)
+    B, S, H, S_txt = 2, 75, 5, 11
+    q = torch.randn(B, S, H, D, generator=gen).to(dtype)
+    k = torch.randn(B, S, H, D, generator=gen).to(dtype)
+    wq = (1 + 0.1 * torch.randn(D, generator=gen)).to(dtype)
+    wk = (1 + 0.1 * torch.randn(D, generator=gen)).to(dtype)
+    ang = torch.rand(S - S_txt, D // 2, generator=gen) * 6.28
+    cos = torch.cos(ang).repeat_interleave(2, -1).contiguous()
+    sin = torch.sin(ang).repeat_interleave(2, -1).contiguous()
+
+    def want(x, w):
+        y = oa.rms_norm(x, w, 1e-6)
+        rot = oa.apply_rotary_emb(y[:, S_txt:].transpose(1, 2), cos, sin).transpose(1, 2)
+        return torch.cat([y[:, :S_txt], rot], 1)
+
+    qd, kd = q.to(DEV), k.to(DEV)
+    kernels.qk_norm_rope([(qd, wq.to(DEV), True, True), (kd, wk.to(DEV), True, True)], eps=1e-6, cos=cos.to(DEV),
+                         sin=sin.to(DEV), rope_seq_start=S_txt)
+    torch.cuda.synchronize()
+    for got, ref in ((qd, want(q, wq)), (kd, want(k, wk))):
+        # same rounding sequence as the reference; only the fp32 reduction order may differ -> 1 ulp
+        tol = 2 ** -7 if dtype == torch.bfloat16 else 2 ** -10
+        diff = (got.cpu().float() - ref.float()).abs()
+        assert (diff <= tol * ref.float().abs().clamp_min(1.0)).all()
+        assert (diff == 0).float().mean().item() > 0.99
+
+
+def test_rope_golden(golden_dir):
+    """apply_rotary_emb outputs recorded from the reference function."""
+    from hetu_dit_b200 import kernels
+    with np.load(os.path.join(golden_dir, "rope.npz")) as f:
+        for i in range(2):
+            x = torch.from_numpy(f[f"x{i}"]).to(torch.bfloat16)  # (B, H, S, D)
+            cos, sin = torch.from_numpy(f[f"cos{i}"]).to(DEV), torch.from_numpy(f[f"sin{i}"]).to(DEV)
+            xd = x.transpose(1, 2).contiguous().to(DEV)
+            kernels.qk_norm_rope([(xd, None, False, True)], cos=cos, sin=sin)
+            torch.cuda.synchronize()
+            assert torch.equal(xd.transpose(1, 2).cpu().float(), torch.from_numpy(f[f"yb{i}"]))
+
+
+def test_norm_rope_head_scatter():
+    """Head-sliced destinations at a sequence offset == the Ulysses all-to-all layout."""
+    from hetu_dit_b200 import kernels
+    gen = torch.Generator().manual_seed(9)
+    B, S, H, D, U = 1, 40, 8, 64, 4
+    x = torch.randn(B, S, H, D, generator=gen).to(torch.bfloat16)
+    w = torch.ones(D, dtype=torch.bfloat16)
+    dsts = [torch.zeros(B, 3 * S, H // U, D, dtype=torch.bfloat16, device=DEV) for _ in range(U)]
+    kernels.qk_norm_rope([(x.to(DEV), w.to(DEV), True, False)], dsts=[dsts], dst_seq_offset=S)
+    torch.cuda.synchronize()
+    y = oa.rms_norm(x, w, 1e-6)
+    for u in range(U):
+        got = dsts[u].cpu()
+        assert torch.equal(got[:, S:2 * S], y[:, :, u * 2:(u + 1) * 2])
+        assert got[:, :S].abs().sum() == 0 and got[:, 2 * S:].abs().sum() == 0
