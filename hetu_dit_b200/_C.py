@@ -138,6 +138,23 @@ def _declare(lib):
         ctypes.c_void_p]
     lib.hdit_qk_norm_rope.restype = ctypes.c_int
     lib.hdit_qk_norm_rope.argtypes = [ctypes.POINTER(NormRopeArgs)]
+    lib.hdit_heap_alloc.restype = ctypes.c_int
+    lib.hdit_heap_alloc.argtypes = [ctypes.c_int64, ctypes.POINTER(ctypes.c_void_p)]
+    lib.hdit_heap_free.restype = ctypes.c_int
+    lib.hdit_heap_free.argtypes = [ctypes.c_void_p]
+    lib.hdit_ipc_export.restype = ctypes.c_int
+    lib.hdit_ipc_export.argtypes = [ctypes.c_void_p, ctypes.c_char_p]
+    lib.hdit_ipc_open.restype = ctypes.c_int
+    lib.hdit_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+    lib.hdit_ipc_close.restype = ctypes.c_int
+    lib.hdit_ipc_close.argtypes = [ctypes.c_void_p]
+    lib.hdit_peer_barrier.restype = ctypes.c_int
+    lib.hdit_peer_barrier.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
+                                      ctypes.c_int, ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p]
+    lib.hdit_peer_signal.restype = ctypes.c_int
+    lib.hdit_peer_signal.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
+    lib.hdit_peer_wait.restype = ctypes.c_int
+    lib.hdit_peer_wait.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p]
 
 
 def lib():

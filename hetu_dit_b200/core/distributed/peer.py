@@ -1,0 +1,194 @@
+"""Symmetric peer heap of one NVSwitch domain and the groups built on it.
+
+Every rank (one process per GPU) owns one heap allocated by the C library and
+maps every other rank's heap once through CUDA IPC. A buffer that peers write
+into, or read from, is carved from the heap at the same offset on every rank of
+the communicating group, so `peer_ptr(rank, offset)` is all a kernel needs. This
+replaces the reference's pool of NCCL communicators for every rank subset
+(hetu_dit/core/distributed/parallel_state.py:1126-1510): activating a plan only
+selects which ranks' base pointers are used.
+"""
+import ctypes
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+
+from ... import _C
+
+FLAG_BYTES = 64 * 1024          # head of the heap: int32 counters
+MAX_RANKS_PER_NODE = 8
+_BARRIER_SLOTS = 256 * MAX_RANKS_PER_NODE  # one row of 8 counters per rank subset (bit mask of members)
+_P2P_BASE = _BARRIER_SLOTS      # then 8 x 8 x 16 point-to-point sequence counters
+DEFAULT_MAX_SPINS = 20_000_000  # about two seconds of polling
+
+
+class _RawCuda:
+    """Minimal __cuda_array_interface__ carrier so torch can view heap memory."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class PeerHeap:
+    def __init__(self, nbytes: int, rank: int, world_size: int, device: torch.device,
+                 all_gather_bytes: Optional[Callable[[bytes], List[bytes]]] = None):
+        """all_gather_bytes(my_handle) -> every rank's handle in rank order (any host channel,
+        e.g. torch.distributed.all_gather_object); None for a single rank."""
+        if nbytes <= FLAG_BYTES:
+            raise ValueError("heap too small")
+        self.nbytes = int(nbytes)
+        self.rank, self.world_size, self.device = rank, world_size, torch.device(device)
+        self._cursor = FLAG_BYTES
+        self._named: Dict[str, tuple] = {}
+        self._epochs: Dict[int, int] = {}
+        self._p2p_seq: Dict[tuple, int] = {}
+        lib = _C.lib()
+        with torch.cuda.device(self.device):
+            base = ctypes.c_void_p()
+            _C.check(lib.hdit_heap_alloc(self.nbytes, ctypes.byref(base)))
+            self.base = base.value
+            self.peer_base: List[Optional[int]] = [None] * world_size
+            self.peer_base[rank] = self.base
+            if world_size > 1:
+                if all_gather_bytes is None:
+                    raise ValueError("a multi-rank heap needs a host channel to exchange IPC handles")
+                handle = ctypes.create_string_buffer(64)
+                _C.check(lib.hdit_ipc_export(self.base, handle))
+                handles = all_gather_bytes(handle.raw)
+                for r, h in enumerate(handles):
+                    if r == rank:
+                        continue
+                    p = ctypes.c_void_p()
+                    _C.check(lib.hdit_ipc_open(ctypes.create_string_buffer(h, 64), ctypes.byref(p)))
+                    self.peer_base[r] = p.value
+        self._bytes = torch.as_tensor(_RawCuda(self.base, self.nbytes), device=self.device)
+
+    # ------------------------------------------------------------------ allocation
+    def reset(self):
+        """Forget every buffer (plan switch). Ranks of a new group then allocate from the same offset."""
+        self._cursor = FLAG_BYTES
+        self._named.clear()
+
+    def alloc(self, shape: Sequence[int], dtype: torch.dtype, name: Optional[str] = None):
+        """(tensor, offset): a zero-copy view of `shape` at a 256-byte aligned heap offset. A `name`
+        makes the buffer persistent: asking again with the same name, shape and dtype returns it."""
+        shape = tuple(int(s) for s in shape)
+        if name is not None and name in self._named:
+            t, off = self._named[name]
+            if tuple(t.shape) == shape and t.dtype == dtype:
+                return t, off
+            raise ValueError(f"heap buffer {name!r} exists with shape {tuple(t.shape)}, asked for {shape}")
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        off = (self._cursor + 255) // 256 * 256
+        if off + nbytes > self.nbytes:
+            raise MemoryError(f"peer heap exhausted: need {nbytes} bytes at offset {off} of {self.nbytes}")
+        self._cursor = off + nbytes
+        t = self._bytes[off:off + nbytes].view(dtype).view(shape)
+        if name is not None:
+            self._named[name] = (t, off)
+        return t, off
+
+    def offset_of(self, t: torch.Tensor) -> int:
+        off = t.data_ptr() - self.base
+        if off < 0 or off >= self.nbytes:
+            raise ValueError("tensor does not live in the peer heap")
+        return off
+
+    def peer_ptr(self, rank: int, offset: int) -> int:
+        base = self.peer_base[rank]
+        if base is None:
+            raise RuntimeError(f"rank {rank} is not mapped")
+        return base + offset
+
+    # ------------------------------------------------------------------ flags
+    def _flag_ptr(self, rank: int, index: int) -> int:
+        return self.peer_ptr(rank, index * 4)
+
+    def barrier(self, ranks: Sequence[int], max_spins: int = DEFAULT_MAX_SPINS):
+        """Stream-ordered barrier among `ranks` (global ranks of this node, this rank included)."""
+        ranks = list(ranks)
+        n = len(ranks)
+        if n == 1:
+            return
+        me = ranks.index(self.rank)
+        mask = 0
+        for r in ranks:
+            mask |= 1 << (r % MAX_RANKS_PER_NODE)
+        epoch = self._epochs.get(mask, 0) + 1
+        self._epochs[mask] = epoch
+        peer_slots = (ctypes.c_void_p * n)()
+        my_slots = (ctypes.c_void_p * n)()
+        for i, r in enumerate(ranks):
+            if i == me:
+                continue
+            peer_slots[i] = self._flag_ptr(r, mask * MAX_RANKS_PER_NODE + me)      # in r's heap, row of this group
+            my_slots[i] = self._flag_ptr(self.rank, mask * MAX_RANKS_PER_NODE + i)  # in my heap, written by r
+        with torch.cuda.device(self.device):
+            stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+            _C.check(_C.lib().hdit_peer_barrier(peer_slots, my_slots, n, me, epoch, max_spins, stream))
+
+    def p2p_flag_index(self, src: int, dst: int, channel: int) -> int:
+        return _P2P_BASE + ((src % 8) * 8 + (dst % 8)) * 16 + channel
+
+    def signal(self, dst: int, channel: int):
+        """Bump the (me -> dst, channel) sequence counter in dst's heap after all earlier stream work."""
+        key = (self.rank, dst, channel)
+        seq = self._p2p_seq.get(key, 0) + 1
+        self._p2p_seq[key] = seq
+        with torch.cuda.device(self.device):
+            stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+            _C.check(_C.lib().hdit_peer_signal(self._flag_ptr(dst, self.p2p_flag_index(self.rank, dst, channel)), seq,
+                                               stream))
+        return seq
+
+    def wait(self, src: int, channel: int, max_spins: int = DEFAULT_MAX_SPINS):
+        """Hold the stream until the next (src -> me, channel) message has been signalled."""
+        key = (src, self.rank, channel)
+        seq = self._p2p_seq.get(key, 0) + 1
+        self._p2p_seq[key] = seq
+        with torch.cuda.device(self.device):
+            stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+            _C.check(_C.lib().hdit_peer_wait(self._flag_ptr(self.rank, self.p2p_flag_index(src, self.rank, channel)),
+                                             seq, max_spins, src * 16 + channel, stream))
+        return seq
+
+    def check(self):
+        """Synchronise and raise if a bounded device-side wait ran out since the last check."""
+        torch.cuda.synchronize(self.device)
+        code, blk, where, it = _C.device_status(self.device.index or 0, clear=True)
+        if code != 0:
+            raise _C.HditError(code, f"device-side wait timed out (where={where}, detail={it}, block={blk})")
+
+
+class PeerGroup:
+    """An ordered set of global ranks sharing the heap; the stand-in for a torch ProcessGroup
+    handed to the attention operators (ULYSSES_PG / RING_PG) and coordinators."""
+
+    def __init__(self, ranks: Sequence[int], my_global_rank: int, heap: Optional[PeerHeap]):
+        self.ranks = list(ranks)
+        self.world_size = len(self.ranks)
+        self.rank_in_group = self.ranks.index(my_global_rank) if my_global_rank in self.ranks else -1
+        self.global_rank = my_global_rank
+        self.heap = heap
+
+    @property
+    def rank(self):
+        return self.rank_in_group
+
+    def barrier(self, max_spins: int = DEFAULT_MAX_SPINS):
+        if self.world_size > 1:
+            if self.heap is None:
+                raise RuntimeError("a multi-rank group needs the peer heap")
+            self.heap.barrier(self.ranks, max_spins)
+
+    def next_rank(self):
+        return self.ranks[(self.rank_in_group + 1) % self.world_size]
+
+    def prev_rank(self):
+        return self.ranks[(self.rank_in_group - 1) % self.world_size]
+
+    def __repr__(self):
+        return f"PeerGroup(ranks={self.ranks}, rank={self.rank_in_group})"

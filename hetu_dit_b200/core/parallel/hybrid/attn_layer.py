@@ -1,0 +1,175 @@
+"""USP long-context attention: Ulysses head<->sequence exchange around ring attention.
+
+Interface of the reference's hetu_dit/core/parallel/hybrid/attn_layer.py:
+hetuDiTLongContextAttention (:17-139), hetuDiTJointLongContextAttention
+(:142-274), hetuDiTFluxLongContextAttention (:277-395); same constructor
+arguments, same forward keyword arguments, same output row order.
+
+Data movement differs from the reference by design. Its four NCCL all-to-alls
+per layer (yunchang SeqAllToAll4D) become peer stores: one kernel writes the
+head slice every Ulysses peer needs straight into that peer's gathered buffer
+in the node's peer heap (Q, K and V in one launch), a flag barrier orders it
+against the consumers, the tcgen05 attention kernel runs on the gathered
+tensors (joint text K/V as an extra segment, never concatenated), and the
+context rows are stored back into their owners' output buffers the same way.
+"""
+from typing import Optional
+
+import torch
+from torch import Tensor
+
+from .... import kernels
+from ...distributed import parallel_state as ps
+from ...distributed.peer import PeerGroup
+from .utils import RING_IMPL_DICT
+
+_SUPPORTED_JOINT = ["none", "front", "rear"]
+
+
+class _UlyssesExchange:
+    """The two all-to-alls of one attention call over the peer heap."""
+
+    def __init__(self, group: PeerGroup):
+        self.group = group
+        self.heap = group.heap
+        if group.world_size > 1 and self.heap is None:
+            raise RuntimeError("Ulysses attention across ranks needs the peer heap")
+
+    def gather_heads(self, tensors, tags):
+        """SeqAllToAll4D(scatter_idx=2, gather_idx=1) for several (B, S_loc, H, D) tensors at once:
+        rank r ends up with (B, U*S_loc, H/U, D) holding head slice r of every rank's tokens, in
+        group-rank order. Tensors with different S_loc go in separate launches."""
+        g, U, me = self.group, self.group.world_size, self.group.rank_in_group
+        outs = []
+        by_len = {}
+        for t, tag in zip(tensors, tags):
+            B, S, H, D = t.shape
+            if H % U != 0:
+                raise RuntimeError(f"{H} heads are not divisible by the Ulysses degree {U}")
+            buf, off = self.heap.alloc((B, U * S, H // U, D), t.dtype, name=f"usp_{tag}_{(B, S, H, D)}_{t.dtype}")
+            outs.append(buf)
+            ptrs = [self.heap.peer_ptr(r, off) for r in g.ranks]
+            by_len.setdefault(S, []).append((t, kernels.RawDst(ptrs, buf.stride()[:3])))
+        for S, items in by_len.items():
+            for i in range(0, len(items), 3):
+                chunk = items[i:i + 3]
+                kernels.qk_norm_rope([(t, None, False, False) for t, _ in chunk], dsts=[d for _, d in chunk],
+                                     dst_seq_offset=me * S)
+        g.barrier()
+        return outs
+
+    def scatter_sequence(self, ctx: Tensor, tag: str) -> Tensor:
+        """SeqAllToAll4D(scatter_idx=1, gather_idx=2): (B, U*S_loc, H/U, D) -> (B, S_loc, H, D)."""
+        g, U, me = self.group, self.group.world_size, self.group.rank_in_group
+        B, S_tot, Hl, D = ctx.shape
+        S = S_tot // U
+        out, off = self.heap.alloc((B, S, Hl * U, D), ctx.dtype, name=f"usp_{tag}_{(B, S, Hl * U, D)}_{ctx.dtype}")
+        es = ctx.element_size()
+        pieces = []
+        for p, r in enumerate(g.ranks):
+            src = ctx[:, p * S:(p + 1) * S]
+            dst = self.heap.peer_ptr(r, off) + me * Hl * D * es
+            pieces.append((src.data_ptr(), dst, B, ctx.stride(0) * es, out.stride(0) * es, S, ctx.stride(1) * es,
+                           out.stride(1) * es, Hl * D * es))
+        kernels.copy_pieces(pieces, ctx.device)
+        g.barrier()
+        # Hand back a private copy: the heap buffer is overwritten by the next layer's exchange.
+        return out.clone()
+
+
+class hetuDiTLongContextAttention(torch.nn.Module):
+    ring_impl_type_supported_kv_cache = ["basic"]
+
+    def __init__(self, scatter_idx: int = 2, gather_idx: int = 1, ring_impl_type: str = "basic",
+                 use_pack_qkv: bool = False, use_kv_cache: bool = False) -> None:
+        super().__init__()
+        if scatter_idx != 2 or gather_idx != 1:
+            raise ValueError("only the (B, S, H, D) layout with scatter_idx=2, gather_idx=1 is supported")
+        self.scatter_idx, self.gather_idx = scatter_idx, gather_idx
+        self.ring_impl_type = ring_impl_type
+        self.use_pack_qkv = use_pack_qkv
+        self.use_kv_cache = use_kv_cache
+        if use_kv_cache and ring_impl_type not in self.ring_impl_type_supported_kv_cache:
+            raise RuntimeError(f"ring_impl_type: {ring_impl_type} do not support SP kv cache.")
+        if ring_impl_type not in RING_IMPL_DICT:
+            raise RuntimeError(f"ring_impl_type: {ring_impl_type} is not available")
+        self.ring_attn_fn = RING_IMPL_DICT[ring_impl_type]
+        self.ring_pg: Optional[PeerGroup] = None
+        self.ulysses_pg: Optional[PeerGroup] = None
+
+    # -- shared body -----------------------------------------------------------------------------
+    def _bind_groups(self):
+        # groups are re-read on every call so a plan switch takes effect without re-creating
+        # the operator (hybrid/attn_layer.py:88-90)
+        self.use_kv_cache = ps.get_sequence_parallel_world_size() > 1
+        self.ring_pg = ps.PROCESS_GROUP.RING_PG
+        self.ulysses_pg = ps.PROCESS_GROUP.ULYSSES_PG
+
+    def _run(self, attn, query, key, value, joint_k, joint_v, joint_strategy, dropout_p, softmax_scale, causal,
+             window_size, alibi_slopes, deterministic, return_attn_probs):
+        U = 1 if self.ulysses_pg is None else self.ulysses_pg.world_size
+        if U > 1:
+            r = self.ulysses_pg.rank_in_group
+            if joint_k is not None:
+                hpr = joint_k.shape[-2] // U
+                joint_k = joint_k[..., hpr * r:hpr * (r + 1), :]
+                joint_v = joint_v[..., hpr * r:hpr * (r + 1), :]
+            xchg = _UlyssesExchange(self.ulysses_pg)
+            query, key, value = xchg.gather_heads([query, key, value], ["q", "k", "v"])
+        out = self.ring_attn_fn(query, key, value, dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal,
+                                window_size=window_size, alibi_slopes=alibi_slopes, deterministic=deterministic,
+                                return_attn_probs=return_attn_probs, group=self.ring_pg,
+                                attn_layer=attn if self.use_kv_cache else None, joint_tensor_key=joint_k,
+                                joint_tensor_value=joint_v, joint_strategy=joint_strategy)
+        context = out[0] if isinstance(out, tuple) else out
+        if U > 1:
+            context = xchg.scatter_sequence(context, "o")
+        return context
+
+    @torch.compiler.disable
+    def forward(self, attn, query: Tensor, key: Tensor, value: Tensor, *, joint_tensor_query=None,
+                joint_tensor_key=None, joint_tensor_value=None, dropout_p=0.0, softmax_scale=None, causal=False,
+                window_size=(-1, -1), alibi_slopes=None, deterministic=False, return_attn_probs=False,
+                joint_strategy="none") -> Tensor:
+        """3 x (B, S/P, H, D) -> (B, S/P, H, D)."""
+        self._bind_groups()
+        return self._run(attn, query, key, value, None, None, "none", dropout_p, softmax_scale, causal, window_size,
+                         alibi_slopes, deterministic, return_attn_probs)
+
+
+class hetuDiTJointLongContextAttention(hetuDiTLongContextAttention):
+    @torch.compiler.disable
+    def forward(self, attn, query: Tensor, key: Tensor, value: Tensor, *, joint_tensor_query, joint_tensor_key,
+                joint_tensor_value, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
+                alibi_slopes=None, deterministic=False, return_attn_probs=False, joint_strategy="rear"):
+        """Joint text+image attention; output rows are [local; joint] ("rear") or [joint; local] ("front")."""
+        self._bind_groups()
+        if joint_strategy not in _SUPPORTED_JOINT:
+            raise ValueError(
+                f"joint_strategy: {joint_strategy} not supprted. supported joint strategy: {_SUPPORTED_JOINT}")
+        elif joint_strategy != "none" and joint_tensor_query is None:
+            raise ValueError("joint_tensor_query must not be None when joint_strategy is not None")
+        elif joint_strategy == "rear":
+            query = torch.cat([query, joint_tensor_query], dim=1)
+        elif joint_strategy == "front":
+            query = torch.cat([joint_tensor_query, query], dim=1)
+        return self._run(attn, query, key, value, joint_tensor_key, joint_tensor_value, joint_strategy, dropout_p,
+                         softmax_scale, causal, window_size, alibi_slopes, deterministic, return_attn_probs)
+
+
+class hetuDiTFluxLongContextAttention(hetuDiTLongContextAttention):
+    @torch.compiler.disable
+    def forward(self, attn, query: Tensor, key: Tensor, value: Tensor, *, joint_tensor_query, joint_tensor_key,
+                joint_tensor_value, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
+                alibi_slopes=None, deterministic=False, return_attn_probs=False, joint_strategy="front"):
+        """Flux: text tokens always lead (hybrid/attn_layer.py:327)."""
+        self._bind_groups()
+        query = torch.cat([joint_tensor_query, query], dim=1)
+        return self._run(attn, query, key, value, joint_tensor_key, joint_tensor_value, "front", dropout_p,
+                         softmax_scale, causal, window_size, alibi_slopes, deterministic, return_attn_probs)
+
+
+# names used by the xDiT lineage of this operator
+xFuserLongContextAttention = hetuDiTLongContextAttention
+xFuserJointLongContextAttention = hetuDiTJointLongContextAttention
+xFuserFluxLongContextAttention = hetuDiTFluxLongContextAttention

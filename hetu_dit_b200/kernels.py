@@ -7,6 +7,39 @@ from . import _C
 
 _DTYPE_CODE = {torch.bfloat16: _C.HDIT_BF16, torch.float16: _C.HDIT_FP16}
 
+# Launch accounting for benchmarks: how many kernels of this library were enqueued, and
+# (optionally) CUDA-event pairs around every attention launch on its own stream.
+_launches = 0
+_attn_timing = False
+_attn_events = []
+
+
+def reset_counters():
+    global _launches
+    _launches = 0
+    _attn_events.clear()
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def enable_attn_timing(on: bool):
+    global _attn_timing
+    _attn_timing = bool(on)
+
+
+def attn_timing_summary():
+    """Mean device time of the attention launches recorded since reset_counters() (synchronises)."""
+    torch.cuda.synchronize()
+    ms = [a.elapsed_time(b) for a, b in _attn_events]
+    return {"count": len(ms), "mean_ms": (sum(ms) / len(ms)) if ms else None, "min_ms": min(ms) if ms else None}
+
+
+def _count(n=1):
+    global _launches
+    _launches += n
+
 
 def _stream_ptr(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
@@ -89,7 +122,15 @@ def attn_fwd(
         a.acc_lse = acc_lse.data_ptr()
     a.stream = _stream_ptr(q0.device)
     with torch.cuda.device(q0.device):
-        _C.check(_C.lib().hdit_attn_fwd(ctypes.byref(a)))
+        if _attn_timing:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _C.check(_C.lib().hdit_attn_fwd(ctypes.byref(a)))
+            e1.record()
+            _attn_events.append((e0, e1))
+        else:
+            _C.check(_C.lib().hdit_attn_fwd(ctypes.byref(a)))
+    _count()
     if not writes_out:
         return None
     return (out, lse) if return_lse else out
@@ -107,6 +148,7 @@ def copy_pieces(pieces, device):
          arr[i].src_pitch, arr[i].dst_pitch, arr[i].row_bytes) = pc
     with torch.cuda.device(device):
         _C.check(_C.lib().hdit_copy_pieces(arr, n, _stream_ptr(device)))
+    _count((n + 39) // 40)
 
 
 def copy_2d(dst, src):
@@ -169,6 +211,17 @@ def kv_scatter(kv_cache, new_k, new_v, token_start):
     with torch.cuda.device(kv_cache.device):
         _C.check(_C.lib().hdit_kv_scatter(kv_cache.data_ptr(), nk.data_ptr(), nv.data_ptr(), B, S, int(token_start), n,
                                           R * es, nk.stride(1) * es, nk.stride(0) * es, _stream_ptr(kv_cache.device)))
+    _count()
+
+
+class RawDst:
+    """Destinations given as raw device addresses (e.g. mapped peer memory) plus (b, s, h) strides in elements."""
+
+    def __init__(self, ptrs, strides):
+        self.ptrs, self.strides = list(ptrs), tuple(int(x) for x in strides)
+
+    def __len__(self):
+        return len(self.ptrs)
 
 
 def qk_norm_rope(tensors, *, eps=1e-6, cos=None, sin=None, rope_seq_start=0, rope_row0=0, dsts=None,
@@ -201,11 +254,17 @@ def qk_norm_rope(tensors, *, eps=1e-6, cos=None, sin=None, rope_seq_start=0, rop
         t.norm_weight = w.data_ptr() if w is not None else None
         t.do_norm, t.do_rope = int(bool(do_norm)), int(bool(do_rope))
         outs = [x] if dsts is None else dsts[i]
-        for j, o in enumerate(outs):
-            t.dst[j] = o.data_ptr()
-        o0 = outs[0]
-        t.dst_stride_b, t.dst_stride_s, t.dst_stride_h = o0.stride(0), o0.stride(1), o0.stride(2)
+        if isinstance(outs, RawDst):
+            for j, ptr in enumerate(outs.ptrs):
+                t.dst[j] = ptr
+            t.dst_stride_b, t.dst_stride_s, t.dst_stride_h = outs.strides
+        else:
+            for j, o in enumerate(outs):
+                t.dst[j] = o.data_ptr()
+            o0 = outs[0]
+            t.dst_stride_b, t.dst_stride_s, t.dst_stride_h = o0.stride(0), o0.stride(1), o0.stride(2)
         t.dst_seq_offset = int(dst_seq_offset)
     a.stream = _stream_ptr(x0.device)
     with torch.cuda.device(x0.device):
         _C.check(_C.lib().hdit_qk_norm_rope(ctypes.byref(a)))
+    _count()

@@ -1,0 +1,126 @@
+"""Attention processors of the -shaped DiT blocks.
+
+They play the role of the reference's hetuDiTJointAttnProcessor2_0 (SD3,
+hetu_dit/model_executor/diffusion_executor/layers/attention_processor.py:632-793)
+and hetuDiTFluxAttnProcessor2_0 (:797-987): QKV (+ added QKV) projections,
+per-head QK-RMSNorm, rotary embedding, PipeFusion stale-KV update, then either
+the single-GPU attention kernel or the USP operator, and the split back into
+image and text streams.
+
+What is fused here and eager in the reference: norm + RoPE run as one in-place
+kernel over Q and K (the reference round-trips fp32 copies, :68-120); text and
+image parts are never concatenated -- they are passed to the attention kernel
+as segments; the stale-KV buffer is updated by one scatter kernel.
+"""
+import torch
+
+from ... import kernels
+from ...core.distributed import parallel_state as ps
+from ...core.parallel import hetuDiTFluxLongContextAttention, hetuDiTJointLongContextAttention
+from ...core.resource_manager.cache_manager import get_cache_manager
+
+
+def _heads(x, attn):
+    B, S, _ = x.shape
+    return x.view(B, S, attn.heads, attn.head_dim)
+
+
+def _norm_rope(attn, q, k, wq, wk, rope, row0):
+    """In-place QK-RMSNorm and RoPE over (B, S, H, D) views; `row0` is the table row of token 0."""
+    do_norm = wq is not None
+    if not do_norm and rope is None:
+        return
+    cos, sin = rope if rope is not None else (None, None)
+    kernels.qk_norm_rope([(q, wq.weight if do_norm else None, do_norm, rope is not None),
+                          (k, wk.weight if do_norm else None, do_norm, rope is not None)],
+                         eps=wq.eps if do_norm else 1e-6, cos=cos, sin=sin, rope_seq_start=0, rope_row0=row0)
+
+
+class JointAttnProcessor:
+    """Double-stream (text + image) attention. joint_strategy "rear" = [image; text] (SD3 order,
+    attention_processor.py:742-744), "front" = [text; image] (Flux order, :895-897)."""
+
+    def __init__(self):
+        self.hybrid_seq_parallel_attn = None
+        self._hybrid_world = 0
+
+    def _operator(self, strategy):
+        world = ps.get_sequence_parallel_world_size()
+        if self.hybrid_seq_parallel_attn is None or self._hybrid_world != world:
+            cls = hetuDiTFluxLongContextAttention if strategy == "front" else hetuDiTJointLongContextAttention
+            self.hybrid_seq_parallel_attn = cls(use_kv_cache=True)
+            self._hybrid_world = world
+        return self.hybrid_seq_parallel_attn
+
+    def __call__(self, attn, hidden_states, encoder_hidden_states=None, image_rotary_emb=None, text_len=None,
+                 token_offset: int = 0):
+        strategy = "front" if image_rotary_emb is not None else "rear"
+        B, S_img, _ = hidden_states.shape
+        S_txt = encoder_hidden_states.shape[1]
+        q, k, v = (_heads(p(hidden_states), attn) for p in (attn.to_q, attn.to_k, attn.to_v))
+        tq, tk, tv = (_heads(p(encoder_hidden_states), attn) for p in (attn.add_q_proj, attn.add_k_proj, attn.add_v_proj))
+        _norm_rope(attn, q, k, attn.norm_q, attn.norm_k, image_rotary_emb, S_txt + token_offset)
+        _norm_rope(attn, tq, tk, attn.norm_added_q, attn.norm_added_k, image_rotary_emb, 0)
+
+        if ps.get_sequence_parallel_world_size() > 1:
+            out = self._operator(strategy)(attn, q, k, v, dropout_p=0.0, causal=False, joint_tensor_query=tq,
+                                           joint_tensor_key=tk, joint_tensor_value=tv, joint_strategy=strategy)
+        else:
+            k, v = get_cache_manager().update_and_get_kv_cache(new_kv=[k, v], layer=attn, slice_dim=1,
+                                                               layer_type="attn") if _cached(attn) else (k, v)
+            if strategy == "rear":
+                out = kernels.attn_fwd([q, tq], [k, tk], [v, tv])
+            else:
+                out = kernels.attn_fwd([tq, q], [tk, k], [tv, v])
+        out = out.reshape(B, out.shape[1], attn.heads * attn.head_dim)
+        if strategy == "rear":
+            img, txt = out[:, :S_img], out[:, S_img:]
+        else:
+            txt, img = out[:, :S_txt], out[:, S_txt:]
+        return attn.to_out[0](img), attn.to_add_out(txt)
+
+
+class SingleAttnProcessor:
+    """Single-stream attention over the [text; image] sequence (Flux single blocks,
+    attention_processor.py:898-901 for the text/image split under SP)."""
+
+    def __init__(self):
+        self.hybrid_seq_parallel_attn = None
+        self._hybrid_world = 0
+
+    def __call__(self, attn, hidden_states, encoder_hidden_states=None, image_rotary_emb=None, text_len=None,
+                 token_offset: int = 0):
+        B, S, _ = hidden_states.shape
+        q, k, v = (_heads(p(hidden_states), attn) for p in (attn.to_q, attn.to_k, attn.to_v))
+        S_txt = int(text_len or 0)
+        if token_offset == 0:
+            _norm_rope(attn, q, k, attn.norm_q, attn.norm_k, image_rotary_emb, 0)
+        else:
+            _norm_rope(attn, q[:, :S_txt], k[:, :S_txt], attn.norm_q, attn.norm_k, image_rotary_emb, 0)
+            _norm_rope(attn, q[:, S_txt:], k[:, S_txt:], attn.norm_q, attn.norm_k, image_rotary_emb, S_txt + token_offset)
+        if ps.get_sequence_parallel_world_size() > 1:
+            world = ps.get_sequence_parallel_world_size()
+            if self.hybrid_seq_parallel_attn is None or self._hybrid_world != world:
+                self.hybrid_seq_parallel_attn = hetuDiTFluxLongContextAttention(use_kv_cache=True)
+                self._hybrid_world = world
+            out = self.hybrid_seq_parallel_attn(attn, q[:, S_txt:], k[:, S_txt:], v[:, S_txt:], dropout_p=0.0,
+                                                causal=False, joint_tensor_query=q[:, :S_txt],
+                                                joint_tensor_key=k[:, :S_txt], joint_tensor_value=v[:, :S_txt],
+                                                joint_strategy="front")
+        elif _cached(attn) and S_txt:
+            ki, vi = get_cache_manager().update_and_get_kv_cache(new_kv=[k[:, S_txt:], v[:, S_txt:]], layer=attn,
+                                                                 slice_dim=1, layer_type="attn")
+            out = kernels.attn_fwd([q], [k[:, :S_txt], ki], [v[:, :S_txt], vi])
+        else:
+            out = kernels.attn_fwd([q], [k], [v])
+        return out.reshape(B, out.shape[1], attn.heads * attn.head_dim)
+
+
+def _cached(attn) -> bool:
+    return ("attn", attn) in get_cache_manager().cache
+
+
+# names of the reference's processors that these stand in for
+hetuDiTJointAttnProcessor2_0 = JointAttnProcessor
+hetuDiTFluxAttnProcessor2_0 = JointAttnProcessor
+hetuDiTFluxSingleAttnProcessor2_0 = SingleAttnProcessor

@@ -1,0 +1,300 @@
+"""SD3-medium-shaped and Flux.1-dev-shaped MMDiT denoisers with seeded random weights.
+
+The reference takes its block definitions from diffusers (absent here) and wraps
+them (hetu_dit/model_executor/diffusion_executor/models/transformers/
+transformer_sd3.py:29-198, transformer_flux.py:30-221). These classes restate
+the architecture from its published shape -- joint (double-stream) blocks with
+adaLN-Zero modulation, optional single-stream blocks, per-head QK RMSNorm,
+3-axis rotary embedding for the Flux shape -- so that one denoising step has the
+reference model's tensor shapes, FLOPs and memory traffic. Module names follow
+the reference's wrapped layout (`attn.module.to_q`, `ff.module.net.0.proj`,
+...) because parameter-slice migration addresses Linear layers by those names
+(hetu_dit/model_executor/cache/transformer_cache.py:113-154).
+
+GEMMs, LayerNorm and GELU run through torch (cuBLAS / ATen); QK-norm, RoPE,
+the K/V cache and attention run through this package's kernels.
+"""
+import math
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..layers.attention_processor import JointAttnProcessor, SingleAttnProcessor
+
+
+@dataclass
+class DiTShape:
+    name: str
+    n_double: int
+    n_single: int
+    hidden: int
+    heads: int
+    head_dim: int
+    token_in: int          # features of one latent token after patchify
+    text_dim: int
+    pooled_dim: int
+    qk_norm: bool
+    rope_axes: Optional[Tuple[int, int, int]]
+    guidance_embed: bool
+    latent_channels: int = 16
+    patch: int = 2
+
+    @property
+    def n_blocks(self):
+        return self.n_double + self.n_single
+
+
+SD3_MEDIUM = DiTShape("sd3-medium", 24, 0, 1536, 24, 64, 64, 4096, 2048, False, None, False)
+FLUX_DEV = DiTShape("flux.1-dev", 19, 38, 3072, 24, 128, 64, 4096, 768, True, (16, 56, 56), True)
+
+
+def timestep_embedding(t: torch.Tensor, dim: int = 256, max_period: float = 10000.0) -> torch.Tensor:
+    half = dim // 2
+    freqs = torch.exp(-math.log(max_period) * torch.arange(half, dtype=torch.float32, device=t.device) / half)
+    args = t.float()[:, None] * freqs[None]
+    return torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
+
+
+class _MLPEmbed(nn.Module):
+    def __init__(self, in_dim, hidden):
+        super().__init__()
+        self.linear_1 = nn.Linear(in_dim, hidden)
+        self.linear_2 = nn.Linear(hidden, hidden)
+
+    def forward(self, x):
+        return self.linear_2(F.silu(self.linear_1(x)))
+
+
+class _Wrapped(nn.Module):
+    """The reference wraps diffusers layers as `<wrapper>.module`; names in the block cache depend on it."""
+
+    def __init__(self, module: nn.Module):
+        super().__init__()
+        self.module = module
+
+    def forward(self, *a, **kw):
+        return self.module(*a, **kw)
+
+
+class _GELUProj(nn.Module):
+    def __init__(self, d_in, d_out):
+        super().__init__()
+        self.proj = nn.Linear(d_in, d_out)
+
+    def forward(self, x):
+        return F.gelu(self.proj(x), approximate="tanh")
+
+
+class FeedForward(nn.Module):
+    def __init__(self, dim, mult=4):
+        super().__init__()
+        self.net = nn.ModuleList([_GELUProj(dim, dim * mult), nn.Identity(), nn.Linear(dim * mult, dim)])
+
+    def forward(self, x):
+        for m in self.net:
+            x = m(x)
+        return x
+
+
+class RMSNormWeight(nn.Module):
+    """Holds the per-head RMSNorm weight; the normalisation itself is fused into the QK kernel."""
+
+    def __init__(self, dim, eps=1e-6):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.eps = eps
+
+
+class Attention(nn.Module):
+    def __init__(self, shape: DiTShape, joint: bool, out_proj: bool = True):
+        super().__init__()
+        d = shape.hidden
+        self.heads, self.head_dim = shape.heads, shape.head_dim
+        self.to_q, self.to_k, self.to_v = nn.Linear(d, d), nn.Linear(d, d), nn.Linear(d, d)
+        self.norm_q = RMSNormWeight(shape.head_dim) if shape.qk_norm else None
+        self.norm_k = RMSNormWeight(shape.head_dim) if shape.qk_norm else None
+        self.to_out = nn.ModuleList([nn.Linear(d, d), nn.Identity()]) if out_proj else None
+        if joint:
+            self.add_q_proj, self.add_k_proj, self.add_v_proj = nn.Linear(d, d), nn.Linear(d, d), nn.Linear(d, d)
+            self.norm_added_q = RMSNormWeight(shape.head_dim) if shape.qk_norm else None
+            self.norm_added_k = RMSNormWeight(shape.head_dim) if shape.qk_norm else None
+            self.to_add_out = nn.Linear(d, d)
+        self.processor = JointAttnProcessor() if joint else SingleAttnProcessor()
+
+    def forward(self, hidden_states, encoder_hidden_states=None, image_rotary_emb=None, text_len=None,
+                token_offset=0):
+        return self.processor(self, hidden_states, encoder_hidden_states=encoder_hidden_states,
+                              image_rotary_emb=image_rotary_emb, text_len=text_len, token_offset=token_offset)
+
+
+def _modulate(x, shift, scale):
+    return x * (1 + scale[:, None]) + shift[:, None]
+
+
+class JointBlock(nn.Module):
+    """Double-stream block: image and text streams with their own weights, one joint attention."""
+
+    def __init__(self, shape: DiTShape):
+        super().__init__()
+        d = shape.hidden
+        self.norm1 = nn.Module()
+        self.norm1.linear = nn.Linear(d, 6 * d)
+        self.norm1_context = nn.Module()
+        self.norm1_context.linear = nn.Linear(d, 6 * d)
+        self.attn = _Wrapped(Attention(shape, joint=True))
+        self.ff = _Wrapped(FeedForward(d))
+        self.ff_context = _Wrapped(FeedForward(d))
+        self.d = d
+
+    def forward(self, hidden, context, temb, rope, token_offset=0):
+        d = self.d
+        mod = self.norm1.linear(F.silu(temb)).chunk(6, dim=-1)
+        cmod = self.norm1_context.linear(F.silu(temb)).chunk(6, dim=-1)
+        h = _modulate(F.layer_norm(hidden, (d,), eps=1e-6), mod[0], mod[1])
+        c = _modulate(F.layer_norm(context, (d,), eps=1e-6), cmod[0], cmod[1])
+        a_img, a_txt = self.attn(h, encoder_hidden_states=c, image_rotary_emb=rope, token_offset=token_offset)
+        hidden = hidden + mod[2][:, None] * a_img
+        h = _modulate(F.layer_norm(hidden, (d,), eps=1e-6), mod[3], mod[4])
+        hidden = hidden + mod[5][:, None] * self.ff(h)
+        context = context + cmod[2][:, None] * a_txt
+        c = _modulate(F.layer_norm(context, (d,), eps=1e-6), cmod[3], cmod[4])
+        context = context + cmod[5][:, None] * self.ff_context(c)
+        return hidden, context
+
+
+class SingleBlock(nn.Module):
+    """Single-stream block over [text; image]: attention and MLP in parallel, one output projection."""
+
+    def __init__(self, shape: DiTShape):
+        super().__init__()
+        d = shape.hidden
+        self.norm = nn.Module()
+        self.norm.linear = nn.Linear(d, 3 * d)
+        self.proj_mlp = nn.Linear(d, 4 * d)
+        self.attn = _Wrapped(Attention(shape, joint=False, out_proj=False))
+        self.proj_out = nn.Linear(5 * d, d)
+        self.d = d
+
+    def forward(self, x, temb, rope, text_len, token_offset=0):
+        shift, scale, gate = self.norm.linear(F.silu(temb)).chunk(3, dim=-1)
+        h = _modulate(F.layer_norm(x, (self.d,), eps=1e-6), shift, scale)
+        mlp = F.gelu(self.proj_mlp(h), approximate="tanh")
+        a = self.attn(h, image_rotary_emb=rope, text_len=text_len, token_offset=token_offset)
+        return x + gate[:, None] * self.proj_out(torch.cat([a, mlp], dim=-1))
+
+
+def rope_tables(ids: torch.Tensor, axes, theta: float = 10000.0):
+    """cos / sin tables (S, D) for integer position ids (S, 3); each axis owns axes[i] dims, pairs share a frequency."""
+    cos, sin = [], []
+    for i, dim in enumerate(axes):
+        freqs = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float64, device=ids.device) / dim))
+        ang = ids[:, i].double()[:, None] * freqs[None]
+        cos.append(torch.cos(ang).repeat_interleave(2, dim=-1))
+        sin.append(torch.sin(ang).repeat_interleave(2, dim=-1))
+    return torch.cat(cos, -1).float().contiguous(), torch.cat(sin, -1).float().contiguous()
+
+
+class ShapedDiT(nn.Module):
+    def __init__(self, shape: DiTShape):
+        super().__init__()
+        self.shape = shape
+        d = shape.hidden
+        self.x_embedder = nn.Linear(shape.token_in, d)
+        self.context_embedder = nn.Linear(shape.text_dim, d)
+        self.time_embed = _MLPEmbed(256, d)
+        self.pooled_embed = _MLPEmbed(shape.pooled_dim, d)
+        self.guidance_embed = _MLPEmbed(256, d) if shape.guidance_embed else None
+        self.transformer_blocks = nn.ModuleList([JointBlock(shape) for _ in range(shape.n_double)])
+        self.single_transformer_blocks = nn.ModuleList([SingleBlock(shape) for _ in range(shape.n_single)])
+        self.norm_out = nn.Module()
+        self.norm_out.linear = nn.Linear(d, 2 * d)
+        self.proj_out = nn.Linear(d, shape.token_in)
+        if shape.rope_axes is None:
+            self.pos_embed_max = 192  # learned-position stand-in: sin-cos table cropped to the latent grid
+        self._rope_cache = {}
+
+    @torch.no_grad()
+    def init_weights(self, seed: int = 0, std: float = 0.02):
+        """Weights ~ N(0, std), biases 0, norm weights 1, from a seeded generator on the parameters' device."""
+        gen = torch.Generator(device=self.x_embedder.weight.device).manual_seed(seed)
+        for name, p in self.named_parameters():
+            if name.endswith("bias"):
+                p.zero_()
+            elif p.dim() == 1:
+                p.fill_(1.0)
+            else:
+                p.copy_(torch.randn(p.shape, generator=gen, device=p.device, dtype=torch.float32) * std)
+        return self
+
+    def _rope(self, text_len, grid_h, grid_w, device):
+        key = (text_len, grid_h, grid_w, str(device))
+        if key not in self._rope_cache:
+            ids = torch.zeros(text_len + grid_h * grid_w, 3, device=device)
+            yy, xx = torch.meshgrid(torch.arange(grid_h, device=device), torch.arange(grid_w, device=device),
+                                    indexing="ij")
+            ids[text_len:, 1] = yy.flatten()
+            ids[text_len:, 2] = xx.flatten()
+            self._rope_cache[key] = rope_tables(ids, self.shape.rope_axes)
+        return self._rope_cache[key]
+
+    def _sincos_pos(self, grid_h, grid_w, device, dtype):
+        key = ("pos", grid_h, grid_w, str(device), dtype)
+        if key not in self._rope_cache:
+            d = self.shape.hidden
+            yy, xx = torch.meshgrid(torch.arange(grid_h, device=device, dtype=torch.float32),
+                                    torch.arange(grid_w, device=device, dtype=torch.float32), indexing="ij")
+            omega = 1.0 / (10000 ** (torch.arange(d // 4, device=device, dtype=torch.float32) / (d // 4)))
+            parts = []
+            for g in (yy, xx):
+                a = g.flatten()[:, None] * omega[None]
+                parts += [torch.sin(a), torch.cos(a)]
+            self._rope_cache[key] = torch.cat(parts, dim=-1).to(dtype)[None]
+        return self._rope_cache[key]
+
+    def forward(self, latent_tokens, text_embeds, pooled, timestep, guidance=None, grid=None, token_offset: int = 0,
+                full_grid: Optional[Tuple[int, int]] = None):
+        """latent_tokens (B, S_img, token_in); text_embeds (B, S_txt, text_dim); pooled (B, pooled_dim);
+        timestep, guidance (B,). Returns the predicted noise (B, S_img, token_in).
+
+        Under sequence parallelism a rank passes its contiguous band of latent rows: `grid` is the
+        band's (rows, cols), `full_grid` the whole latent grid and `token_offset` the index of the
+        band's first token, which selects the band's rows of the rotary / position tables."""
+        shp = self.shape
+        B, S_img, _ = latent_tokens.shape
+        S_txt = text_embeds.shape[1]
+        if grid is None:
+            side = int(math.isqrt(S_img))
+            grid = (side, S_img // side)
+        dtype = latent_tokens.dtype
+        temb = self.time_embed(timestep_embedding(timestep * 1000.0).to(dtype)) + self.pooled_embed(pooled)
+        if self.guidance_embed is not None:
+            g = guidance if guidance is not None else torch.ones_like(timestep)
+            temb = temb + self.guidance_embed(timestep_embedding(g * 1000.0).to(dtype))
+        hidden = self.x_embedder(latent_tokens)
+        context = self.context_embedder(text_embeds)
+        fg = full_grid or grid
+        rope = None
+        if shp.rope_axes is not None:
+            rope = self._rope(S_txt, fg[0], fg[1], latent_tokens.device)
+        else:
+            pos = self._sincos_pos(fg[0], fg[1], latent_tokens.device, dtype)
+            hidden = hidden + pos[:, token_offset:token_offset + S_img]
+        for blk in self.transformer_blocks:
+            hidden, context = blk(hidden, context, temb, rope, token_offset)
+        if len(self.single_transformer_blocks):
+            x = torch.cat([context, hidden], dim=1)
+            for blk in self.single_transformer_blocks:
+                x = blk(x, temb, rope, S_txt, token_offset)
+            hidden = x[:, S_txt:]
+        shift, scale = self.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
+        hidden = _modulate(F.layer_norm(hidden, (shp.hidden,), eps=1e-6), shift, scale)
+        return self.proj_out(hidden)
+
+    def flops_per_step(self, s_img: int, s_txt: int, batch: int = 1) -> float:
+        """Algorithmic FLOPs of one step: 4*S^2*Dm attention + 2*12*Dm^2*S linear per block."""
+        S = s_img + s_txt
+        d = self.shape.hidden
+        return batch * self.shape.n_blocks * (4.0 * S * S * d + 24.0 * d * d * S)

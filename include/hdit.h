@@ -220,6 +220,53 @@ typedef struct hdit_norm_rope_args {
 
 HDIT_API int hdit_qk_norm_rope(const hdit_norm_rope_args* args);
 
+/* ------------------------------------------------------------------------------------------
+ * Peer memory within one NVSwitch domain (one process per GPU).
+ *
+ * The reference keeps a pool of NCCL communicators for every rank subset
+ * (hetu_dit/core/distributed/parallel_state.py:1126-1510) and moves activations with NCCL
+ * all-to-all / isend / irecv and weights with NIXL. Here every rank owns one symmetric heap
+ * that all peers map once; "switching a plan" is choosing which peers' base pointers a kernel
+ * receives. The functions below are set-up (they may allocate and synchronise) except the
+ * flag kernels.
+ * ------------------------------------------------------------------------------------------ */
+
+/* cudaMalloc + zero a heap of `bytes` on the current device (set-up time only). */
+HDIT_API int hdit_heap_alloc(int64_t bytes, void** out);
+HDIT_API int hdit_heap_free(void* ptr);
+
+/* CUDA IPC handle (64 bytes) of a heap, to be sent to the peers over any host channel. */
+HDIT_API int hdit_ipc_export(void* ptr, unsigned char handle[64]);
+/* Maps a peer's heap into this process; the returned pointer is valid in kernels of the
+ * current device. */
+HDIT_API int hdit_ipc_open(const unsigned char handle[64], void** out);
+HDIT_API int hdit_ipc_close(void* ptr);
+
+/*
+ * Barrier among n <= 8 ranks on `stream`: rank `me` stores `epoch` (release, system scope) to
+ * peer_slots[p] in every peer's heap, then polls my_slots[p] in its own heap until it holds at
+ * least `epoch`. Everything enqueued on the stream before the call (peer stores included) is
+ * visible to the peers' work enqueued after their matching call. Epochs must grow by one per
+ * barrier on every rank. After `max_spins` polls without an answer the kernel records
+ * HDIT_ERR_PEER_TIMEOUT (where = 100, iteration = silent peer) and returns.
+ *
+ * Stands in for the synchronisation implied by the reference's NCCL collectives
+ * (SeqAllToAll4D, hybrid/attn_layer.py:102-110,134-136; RingComm.wait, ring_flash_attn.py:91).
+ */
+HDIT_API int hdit_peer_barrier(int32_t* const* peer_slots, const int32_t* const* my_slots, int n, int me,
+                               int32_t epoch, int64_t max_spins, void* stream);
+
+/*
+ * One-way flag: hdit_peer_signal publishes `value` to a flag in a peer's heap after all earlier
+ * work of `stream`; hdit_peer_wait holds `stream` until a flag in the own heap reaches `value`
+ * (bounded as above; where = 101, iteration = tag). Together with hdit_copy_pieces into the
+ * peer's receive slot they replace PipelineGroupCoordinator.pipeline_isend / pipeline_recv /
+ * get_pipeline_recv_data (hetu_dit/core/distributed/group_coordinator.py:931-1002) without the
+ * shape handshake of :848-929 (shapes follow from the patch bookkeeping).
+ */
+HDIT_API int hdit_peer_signal(int32_t* flag, int32_t value, void* stream);
+HDIT_API int hdit_peer_wait(const int32_t* flag, int32_t value, int64_t max_spins, int32_t tag, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,170 @@
+"""CPU oracle: one denoising step of the SD3-/Flux-shaped MMDiT in plain fp32 torch.
+
+TEST INFRASTRUCTURE ONLY. Nothing under hetu_dit_b200/ may import this module.
+
+It consumes the state_dict of hetu_dit_b200.model_executor.models.shaped_dit.
+ShapedDiT and recomputes the step with F.linear, F.layer_norm, oracle.attention.
+rms_norm / apply_rotary_emb and F.scaled_dot_product_attention -- the path the
+reference's processors take without flash-attn or a GPU
+(hetu_dit/model_executor/diffusion_executor/layers/attention_processor.py:
+759-783 for the joint blocks, :969-979 for the Flux blocks; selection in
+hetu_dit/envs.py:81-104). Token order follows the reference: [image; text] for
+the SD3 shape (:742-744), [text; image] for the Flux shape (:895-897).
+Also the timed CPU baseline of bench.py.
+"""
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import attention as oa
+
+
+def _lin(sd, prefix, x):
+    return F.linear(x, sd[prefix + ".weight"].float(), sd[prefix + ".bias"].float())
+
+
+def _timestep_embedding(t, dim=256, max_period=10000.0):
+    half = dim // 2
+    freqs = torch.exp(-math.log(max_period) * torch.arange(half, dtype=torch.float32) / half)
+    args = t.float()[:, None] * freqs[None]
+    return torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
+
+
+def _mlp_embed(sd, prefix, x):
+    return _lin(sd, prefix + ".linear_2", F.silu(_lin(sd, prefix + ".linear_1", x)))
+
+
+def _mod(x, shift, scale):
+    return x * (1 + scale[:, None]) + shift[:, None]
+
+
+def _ff(sd, prefix, x):
+    return _lin(sd, prefix + ".module.net.2", F.gelu(_lin(sd, prefix + ".module.net.0.proj", x), approximate="tanh"))
+
+
+def _heads(x, H, D):
+    return x.view(x.shape[0], x.shape[1], H, D)
+
+
+def _qk(sd, prefix, x, H, D, norm_name, rope, row0, eps=1e-6):
+    """projection -> heads -> RMSNorm -> RoPE; x (B, S, H*D) -> (B, S, H, D)."""
+    y = _heads(x, H, D)
+    w = sd.get(prefix + "." + norm_name + ".weight")
+    if w is not None:
+        y = oa.rms_norm(y, w.float(), eps)
+    if rope is not None:
+        cos, sin = rope
+        S = y.shape[1]
+        y = oa.apply_rotary_emb(y.transpose(1, 2), cos[row0:row0 + S], sin[row0:row0 + S]).transpose(1, 2)
+    return y
+
+
+def joint_block(sd, p, hidden, context, temb, rope, H, D, order):
+    d = hidden.shape[-1]
+    mod = _lin(sd, p + ".norm1.linear", F.silu(temb)).chunk(6, dim=-1)
+    cmod = _lin(sd, p + ".norm1_context.linear", F.silu(temb)).chunk(6, dim=-1)
+    h = _mod(F.layer_norm(hidden, (d,), eps=1e-6), mod[0], mod[1])
+    c = _mod(F.layer_norm(context, (d,), eps=1e-6), cmod[0], cmod[1])
+    a = p + ".attn.module"
+    S_txt, S_img = c.shape[1], h.shape[1]
+    q = _qk(sd, a, _lin(sd, a + ".to_q", h), H, D, "norm_q", rope, S_txt)
+    k = _qk(sd, a, _lin(sd, a + ".to_k", h), H, D, "norm_k", rope, S_txt)
+    v = _heads(_lin(sd, a + ".to_v", h), H, D)
+    tq = _qk(sd, a, _lin(sd, a + ".add_q_proj", c), H, D, "norm_added_q", rope, 0)
+    tk = _qk(sd, a, _lin(sd, a + ".add_k_proj", c), H, D, "norm_added_k", rope, 0)
+    tv = _heads(_lin(sd, a + ".add_v_proj", c), H, D)
+    if order == "rear":
+        o = oa.sdpa(torch.cat([q, tq], 1), torch.cat([k, tk], 1), torch.cat([v, tv], 1))
+        img, txt = o[:, :S_img], o[:, S_img:]
+    else:
+        o = oa.sdpa(torch.cat([tq, q], 1), torch.cat([tk, k], 1), torch.cat([tv, v], 1))
+        txt, img = o[:, :S_txt], o[:, S_txt:]
+    img = _lin(sd, a + ".to_out.0", img.reshape(img.shape[0], S_img, d))
+    txt = _lin(sd, a + ".to_add_out", txt.reshape(txt.shape[0], S_txt, d))
+    hidden = hidden + mod[2][:, None] * img
+    hidden = hidden + mod[5][:, None] * _ff(sd, p + ".ff", _mod(F.layer_norm(hidden, (d,), eps=1e-6), mod[3], mod[4]))
+    context = context + cmod[2][:, None] * txt
+    context = context + cmod[5][:, None] * _ff(sd, p + ".ff_context",
+                                               _mod(F.layer_norm(context, (d,), eps=1e-6), cmod[3], cmod[4]))
+    return hidden, context
+
+
+def single_block(sd, p, x, temb, rope, H, D):
+    d = x.shape[-1]
+    shift, scale, gate = _lin(sd, p + ".norm.linear", F.silu(temb)).chunk(3, dim=-1)
+    h = _mod(F.layer_norm(x, (d,), eps=1e-6), shift, scale)
+    mlp = F.gelu(_lin(sd, p + ".proj_mlp", h), approximate="tanh")
+    a = p + ".attn.module"
+    q = _qk(sd, a, _lin(sd, a + ".to_q", h), H, D, "norm_q", rope, 0)
+    k = _qk(sd, a, _lin(sd, a + ".to_k", h), H, D, "norm_k", rope, 0)
+    v = _heads(_lin(sd, a + ".to_v", h), H, D)
+    o = oa.sdpa(q, k, v).reshape(x.shape[0], x.shape[1], d)
+    return x + gate[:, None] * _lin(sd, p + ".proj_out", torch.cat([o, mlp], dim=-1))
+
+
+def rope_tables(ids, axes, theta=10000.0):
+    cos, sin = [], []
+    for i, dim in enumerate(axes):
+        freqs = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))
+        ang = ids[:, i].double()[:, None] * freqs[None]
+        cos.append(torch.cos(ang).repeat_interleave(2, dim=-1))
+        sin.append(torch.sin(ang).repeat_interleave(2, dim=-1))
+    return torch.cat(cos, -1).float(), torch.cat(sin, -1).float()
+
+
+def sincos_pos(grid_h, grid_w, d):
+    yy, xx = torch.meshgrid(torch.arange(grid_h, dtype=torch.float32), torch.arange(grid_w, dtype=torch.float32),
+                            indexing="ij")
+    omega = 1.0 / (10000 ** (torch.arange(d // 4, dtype=torch.float32) / (d // 4)))
+    parts = []
+    for g in (yy, xx):
+        a = g.flatten()[:, None] * omega[None]
+        parts += [torch.sin(a), torch.cos(a)]
+    return torch.cat(parts, dim=-1)[None]
+
+
+def denoise_step(sd, shape, latent_tokens, text_embeds, pooled, timestep, guidance=None, grid=None, max_blocks=None):
+    """One full step in fp32. `shape` is the DiTShape record; `sd` maps parameter names to tensors."""
+    sd = {k: v.float() for k, v in sd.items()}
+    x, txt, pooled = latent_tokens.float(), text_embeds.float(), pooled.float()
+    B, S_img, _ = x.shape
+    S_txt = txt.shape[1]
+    if grid is None:
+        side = int(math.isqrt(S_img))
+        grid = (side, S_img // side)
+    H, D, d = shape.heads, shape.head_dim, shape.hidden
+    temb = _mlp_embed(sd, "time_embed", _timestep_embedding(timestep * 1000.0)) + _mlp_embed(sd, "pooled_embed", pooled)
+    if shape.guidance_embed:
+        g = guidance if guidance is not None else torch.ones_like(timestep)
+        temb = temb + _mlp_embed(sd, "guidance_embed", _timestep_embedding(g * 1000.0))
+    hidden = _lin(sd, "x_embedder", x)
+    context = _lin(sd, "context_embedder", txt)
+    rope = None
+    if shape.rope_axes is not None:
+        ids = torch.zeros(S_txt + S_img, 3)
+        yy, xx = torch.meshgrid(torch.arange(grid[0]), torch.arange(grid[1]), indexing="ij")
+        ids[S_txt:, 1] = yy.flatten()
+        ids[S_txt:, 2] = xx.flatten()
+        rope = rope_tables(ids, shape.rope_axes)
+        order = "front"
+    else:
+        hidden = hidden + sincos_pos(grid[0], grid[1], d)
+        order = "rear"
+    n = 0
+    for i in range(shape.n_double):
+        if max_blocks is not None and n >= max_blocks:
+            break
+        hidden, context = joint_block(sd, f"transformer_blocks.{i}", hidden, context, temb, rope, H, D, order)
+        n += 1
+    if shape.n_single:
+        xs = torch.cat([context, hidden], dim=1)
+        for i in range(shape.n_single):
+            if max_blocks is not None and n >= max_blocks:
+                break
+            xs = single_block(sd, f"single_transformer_blocks.{i}", xs, temb, rope, H, D)
+            n += 1
+        hidden = xs[:, S_txt:]
+    shift, scale = _lin(sd, "norm_out.linear", F.silu(temb)).chunk(2, dim=-1)
+    hidden = _mod(F.layer_norm(hidden, (d,), eps=1e-6), shift, scale)
+    return _lin(sd, "proj_out", hidden)

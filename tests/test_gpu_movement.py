@@ -96,10 +96,12 @@ def test_norm_rope_matches_oracle(D, dtype):
                          sin=sin.to(DEV), rope_seq_start=S_txt)
     torch.cuda.synchronize()
     for got, ref in ((qd, want(q, wq)), (kd, want(k, wk))):
-        # same rounding sequence as the reference; only the fp32 reduction order may differ -> 1 ulp
-        tol = 2 ** -7 if dtype == torch.bfloat16 else 2 ** -10
+        # Same rounding sequence as the reference; only the fp32 reduction order of the variance may
+        # differ, which can move an intermediate by one unit in the last place before the rotation
+        # mixes two such values: bound = 2 ulp of the largest magnitude.
+        ulp = 2 ** -8 if dtype == torch.bfloat16 else 2 ** -11
         diff = (got.cpu().float() - ref.float()).abs()
-        assert (diff <= tol * ref.float().abs().clamp_min(1.0)).all()
+        assert diff.max().item() <= 2 * ulp * ref.float().abs().max().item()
         assert (diff == 0).float().mean().item() > 0.99
 
 
