@@ -1,0 +1,157 @@
+"""Worker body of the multi-GPU parity tests: one process per GPU, ranks exchange IPC handles over gloo."""
+import json
+import os
+import sys
+import traceback
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+COS_MIN, MAX_REL = 0.9999, 2e-2
+
+
+def _setup(rank, world, port, heap_bytes=256 << 20):
+    import torch.distributed as dist
+    from hetu_dit_b200.core.distributed import parallel_state as ps
+    from hetu_dit_b200.core.distributed.peer import PeerHeap
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dev = torch.device(f"cuda:{rank}")
+    torch.cuda.set_device(dev)
+
+    def gather(b):
+        out = [None] * world
+        dist.all_gather_object(out, b)
+        return out
+
+    heap = PeerHeap(heap_bytes, rank, world, dev, gather)
+    ps.init_distributed_environment(rank, world, heap)
+    return dist, ps, heap, dev
+
+
+def _close(got, want, what):
+    from oracle import attention as oa
+    cos, rel = oa.cosine_and_max_rel(got.float().cpu(), want)
+    assert cos >= COS_MIN and rel <= MAX_REL, f"{what}: cosine {cos} max_rel {rel}"
+
+
+def usp_case(rank, world, port, fixture, errq):
+    """Runs one tests/golden/usp_*.npz case with the product operators and compares with the recorded outputs."""
+    try:
+        dist, ps, heap, dev = _setup(rank, world, port)
+        from hetu_dit_b200.core import parallel as P
+        from hetu_dit_b200.core.distributed.runtime_state import ModelGeometry, initialize_runtime_state, reset_runtime_state
+        from hetu_dit_b200.core.resource_manager.cache_manager import get_cache_manager
+        from hetu_dit_b200.config import EngineConfig
+        with np.load(fixture) as f:
+            d = {k: f[k] for k in f.files}
+        spec = json.loads(str(d.pop("spec")))
+        assert spec["world"] == world
+        t = {k: torch.from_numpy(v) for k, v in d.items()}
+        U, R, S = spec["ulysses"], spec["ring"], spec["s_loc"]
+        ps.initialize_model_parallel(sequence_parallel_degree=U * R, ulysses_degree=U, ring_degree=R)
+        bf = torch.bfloat16
+
+        def loc(x, n):
+            return x[:, rank * n:(rank + 1) * n].to(dev, bf).contiguous()
+
+        layer = getattr(P, spec["cls"])()
+        kw = {}
+        if spec["joint_strategy"] != "none":
+            kw = dict(joint_tensor_query=t["jq"].to(dev, bf), joint_tensor_key=t["jk"].to(dev, bf),
+                      joint_tensor_value=t["jv"].to(dev, bf), joint_strategy=spec["joint_strategy"])
+        if not spec["kv_cache"]:
+            for _ in range(2):  # twice: buffers and flags are re-used across layers
+                out = layer(None, loc(t["q"], S), loc(t["k"], S), loc(t["v"], S), **kw)
+            heap.check()
+            _close(out, t[f"out_rank{rank}"], f"rank {rank}")
+        else:
+            cfg = EngineConfig()
+            cfg.parallel_config.sp_config.ulysses_degree, cfg.parallel_config.sp_config.ring_degree = U, R
+            cfg.parallel_config.pp_config.num_pipeline_patch = 2
+            rt = initialize_runtime_state(ModelGeometry(spec["heads"], spec["head_dim"]), cfg)
+            tok = S // 2
+            rt.num_pipeline_patch = 2
+            rt.pp_patches_token_num = [tok, tok]
+            rt.pp_patches_token_start_idx_local = [0, tok, 2 * tok]
+            attn_obj = object()
+            get_cache_manager().register_cache_entry(attn_obj, "attn", "sequence_parallel_attn_cache")
+            rt.set_patched_mode(False)
+            out0 = layer(attn_obj, loc(t["q"], S), loc(t["k"], S), loc(t["v"], S), **kw)
+            heap.check()
+            _close(out0, t[f"out_warmup_rank{rank}"], f"warm-up rank {rank}")
+            rt.set_patched_mode(True)
+            rt.pipeline_patch_idx = 1
+            out1 = layer(attn_obj, loc(t["fresh_q"], tok), loc(t["fresh_k"], tok), loc(t["fresh_v"], tok), **kw)
+            heap.check()
+            _close(out1, t[f"out_patch1_rank{rank}"], f"patch rank {rank}")
+            reset_runtime_state()
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errq.put(f"rank {rank}:\n{traceback.format_exc()}")
+        raise
+
+
+def pipefusion_case(rank, world, port, errq):
+    """Ring of stages passes patches around twice; payloads must arrive bit-exact and in FIFO order."""
+    try:
+        dist, ps, heap, dev = _setup(rank, world, port)
+        ps.initialize_model_parallel(pipeline_parallel_degree=world)
+        pp = ps.get_pp_group()
+        pp.set_config(torch.bfloat16)
+        gen = torch.Generator().manual_seed(77)
+        shapes = [(2, 96, 1536), (2, 96, 1536), (2, 64, 1536), (2, 333, 1536)]
+        names = [("latent", 0), ("latent", 1), ("latent", 2), ("encoder_hidden_states", 0)]
+        payload = [[torch.randn(s, generator=gen).bfloat16() for s in shapes] for _ in range(3)]  # 3 rounds
+        prev_idx = (rank - 1) % world
+        for rnd in range(3):
+            for (name, idx), src in zip(names, payload[rnd]):
+                # every stage sends its own variant so a misrouted message is detected
+                pp.pipeline_isend((src + rank).to(dev), name=name, segment_idx=idx)
+            for (name, idx) in names:
+                pp.add_pipeline_recv_task(idx, name)
+            for (name, idx), src in zip(names, payload[rnd]):
+                pp.recv_next()
+                got = pp.get_pipeline_recv_data(idx=idx, name=name)
+                heap.check()
+                assert torch.equal(got.cpu(), src + prev_idx), f"rank {rank} round {rnd} {name}[{idx}]"
+            ps.get_world_group().barrier()
+        heap.check()
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errq.put(f"rank {rank}:\n{traceback.format_exc()}")
+        raise
+
+
+def barrier_timeout_case(rank, world, port, errq):
+    """A rank that never joins a barrier: the others' bounded wait runs out and reports the silent peer."""
+    try:
+        dist, ps, heap, dev = _setup(rank, world, port)
+        from hetu_dit_b200 import _C
+        ps.initialize_model_parallel(sequence_parallel_degree=world, ulysses_degree=world)
+        g = ps.get_world_group()
+        g.barrier()
+        heap.check()
+        if rank != world - 1:
+            g.barrier(max_spins=20000)  # the last rank stays away (host-side failure)
+            try:
+                heap.check()
+                raise AssertionError("expected a peer timeout")
+            except _C.HditError as e:
+                assert e.code == _C.HDIT_ERR_PEER_TIMEOUT and f"detail={world - 1}" in str(e), str(e)
+            # the context is still usable afterwards
+            x = torch.ones(8, device=dev) * 2
+            assert x.sum().item() == 16
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errq.put(f"rank {rank}:\n{traceback.format_exc()}")
+        raise
