@@ -192,6 +192,7 @@ def run_gpu(args):
 
     shape = FLUX_DEV
     model = ShapedDiT(shape).to(device=dev, dtype=torch.bfloat16).init_weights(seed=0, std=0.02)
+    model.register_cache()
     host = {k: v.pin_memory() for k, v in _inputs(shape).items()}
     s_loc = S_IMG // world
     rows_loc = GRID[0] // world
@@ -300,6 +301,43 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_kernel_case(args):
+    """Small single-kernel cases for profiler captures: `attn:<batch>` runs the attention kernel alone at
+    the Flux shape (4608 tokens, 24 x 128 heads), `copy:<MiB>` the strided copy kernel."""
+    from hetu_dit_b200 import kernels
+    kind, _, arg = args.kernel_case.partition(":")
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if kind == "attn":
+        B = int(arg or 1)
+        q, k, v = (torch.randn(B, S_IMG + S_TXT, 24, 128, device=dev, dtype=torch.bfloat16) for _ in range(3))
+        fn = lambda: kernels.attn_fwd([q], [k], [v])
+        work = 4.0 * B * (S_IMG + S_TXT) ** 2 * 24 * 128
+        unit = "TFLOP/s"
+    elif kind == "copy":
+        n = int(arg or 512) << 20
+        a = torch.empty(n, dtype=torch.uint8, device=dev)
+        b = torch.empty(n, dtype=torch.uint8, device=dev)
+        fn = lambda: kernels.copy_pieces([(a.data_ptr(), b.data_ptr(), 1, 0, 0, 1, 0, 0, n)], dev)
+        work = 2.0 * n / 1e-3 / 1e12 * 1e-3  # bytes moved (read + write) expressed so work/ms/1e9 -> TB/s
+        work = 2.0 * n
+        unit = "GB/s"
+    else:
+        raise SystemExit(f"unknown kernel case {args.kernel_case}")
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    rate = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    print(json.dumps({"kernel_case": args.kernel_case, "ms_per_launch": ms, "rate": rate, "unit": unit}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -307,8 +345,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-case", default="", help="profiling aid: attn:<batch> or copy:<MiB>")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.kernel_case:
+        run_kernel_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)

@@ -229,6 +229,17 @@ class ShapedDiT(nn.Module):
                 p.copy_(torch.randn(p.shape, generator=gen, device=p.device, dtype=torch.float32) * std)
         return self
 
+    def register_cache(self):
+        """One stale-KV entry per attention layer: the plain cache when the plan has no sequence
+        parallelism, the sequence-parallel one otherwise (what the reference's _register_cache does,
+        hetu_dit/model_executor/diffusion_executor/models/base_model.py:162-178). Call after a plan switch."""
+        from ...core.distributed import parallel_state as ps
+        from ...core.resource_manager.cache_manager import get_cache_manager
+        kind = "sequence_parallel_attn_cache" if ps.get_sequence_parallel_world_size() > 1 else "naive_cache"
+        for m in self.modules():
+            if isinstance(m, Attention):
+                get_cache_manager().register_cache_entry(m, "attn", kind)
+
     def _rope(self, text_len, grid_h, grid_w, device):
         key = (text_len, grid_h, grid_w, str(device))
         if key not in self._rope_cache:
