@@ -267,11 +267,14 @@ def run_gpu(args):
     s_q_gathered = s_q * world if world > 1 else tokens
     attn_flops = 4.0 * s_q_gathered * tokens * heads_loc * shape.head_dim
     achieved = attn_flops / (attn_ms["mean_ms"] * 1e-3) / 1e12 if attn_ms["mean_ms"] else None
+    # DRAM bytes of one launch at this shape, from the committed ncu summary (single-GPU shape only)
     traffic = None
-    prof = os.path.join(ROOT, "profiles", "attn_fwd_flux_shape.json")
+    prof = os.path.join(ROOT, "profiles", "attn_fwd_kernel_flux_shape.txt")
     if os.path.exists(prof) and world == 1:
         with open(prof) as f:
-            traffic = json.load(f).get("dram_bytes_per_launch")
+            for ln in f:
+                if ln.startswith("dram_bytes_per_launch:"):
+                    traffic = int(ln.split(":")[1])
     line = {
         "metric": METRIC, "value": tokens / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",

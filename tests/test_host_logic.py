@@ -1,0 +1,239 @@
+"""CPU tests of the host-side mirror: bookkeeping against the reference-generated fixtures, library exports,
+argument checking, and the multi-rank protocol logic on `gloo` ranks."""
+import ctypes
+import json
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def book(golden_dir):
+    with open(os.path.join(golden_dir, "bookkeeping.json")) as f:
+        return json.load(f)
+
+
+def test_library_exports_every_declared_symbol():
+    """The C-ABI library loads without a GPU and exports everything include/hdit.h declares."""
+    from hetu_dit_b200 import _C
+    lib = ctypes.CDLL(_C.LIB_PATH)
+    with open(os.path.join(ROOT, "include", "hdit.h")) as f:
+        header = f.read()
+    names = re.findall(r"HDIT_API\s+[\w\s\*]+?\b(hdit_\w+)\s*\(", header)
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared but not exported"
+    assert _C.lib().hdit_version() >= 100
+
+
+def test_ctypes_structs_match_header_layout():
+    from hetu_dit_b200 import _C
+    assert ctypes.sizeof(_C.Seg) == 40
+    assert ctypes.sizeof(_C.CopyPiece) == 72
+    assert ctypes.sizeof(_C.AttnArgs) == 32 + 40 * 22 + 8 + 24 + 32
+
+
+def test_no_cpu_path():
+    from hetu_dit_b200 import kernels
+    q = torch.zeros(1, 8, 2, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        kernels.attn_fwd([q], [q], [q])
+
+
+def test_argument_checks_without_gpu():
+    """Bad arguments are rejected on the host before any CUDA call."""
+    from hetu_dit_b200 import _C
+    a = _C.AttnArgs()
+    a.dtype, a.head_dim, a.batch, a.heads, a.n_q_seg, a.n_kv_seg = _C.HDIT_BF16, 96, 1, 1, 1, 1
+    assert _C.lib().hdit_attn_fwd(ctypes.byref(a)) == _C.HDIT_ERR_SHAPE
+    a.head_dim, a.n_kv_seg = 64, 11
+    assert _C.lib().hdit_attn_fwd(ctypes.byref(a)) == _C.HDIT_ERR_SHAPE
+    assert b"n_kv_seg" in _C.lib().hdit_last_error()
+    assert _C.lib().hdit_attn_fwd(None) == _C.HDIT_ERR_BAD_ARG
+    assert _C.lib().hdit_copy_pieces(None, 3, None) == _C.HDIT_ERR_BAD_ARG
+    assert _C.lib().hdit_kv_scatter(None, None, None, 1, 1, 0, 1, 2, 2, 2, None) == _C.HDIT_ERR_BAD_ARG
+
+
+def test_patch_metadata_matches_reference(book):
+    from hetu_dit_b200.core.distributed.runtime_state import split_patches
+    keys = ("num_pipeline_patch", "pp_patches_height", "pp_patches_start_idx_local", "pp_patches_start_end_idx_global",
+            "pp_patches_token_start_idx_local", "pp_patches_token_start_end_idx_global", "pp_patches_token_num")
+    for c in book["patches_metadata"]:
+        args = (c["height"] // c["vae"], c["width"] // c["vae"], c["patch"], c["num_pipeline_patch"], c["sp_world"],
+                c["sp_rank"])
+        strict = c["variant"] == "image"
+        if "error" in c:
+            with pytest.raises(ValueError):
+                split_patches(*args, strict_last_patch=strict)
+        else:
+            assert dict(zip(keys, split_patches(*args, strict_last_patch=strict))) == c["result"], c
+
+
+def test_runtime_state_object(book):
+    from hetu_dit_b200.config import EngineConfig
+    from hetu_dit_b200.core.distributed import parallel_state as ps
+    from hetu_dit_b200.core.distributed.runtime_state import ModelGeometry, initialize_runtime_state, reset_runtime_state
+    ps.destroy_model_parallel()
+    cfg = EngineConfig()
+    cfg.parallel_config.pp_config.num_pipeline_patch = 4
+    rt = initialize_runtime_state(ModelGeometry(24, 64), cfg)
+    rt.set_input_parameters(height=1024, width=1024, batch_size=1, num_inference_steps=20)
+    want = next(c for c in book["patches_metadata"] if c["variant"] == "image" and c["height"] == 1024 and
+                c["width"] == 1024 and c["num_pipeline_patch"] == 4 and c["sp_world"] == 1)
+    assert rt.patches_metadata() == want["result"]
+    rt.set_patched_mode(True)
+    seen = []
+    for _ in range(6):
+        seen.append(rt.pipeline_patch_idx)
+        rt.next_patch()
+    assert seen == [0, 1, 2, 3, 0, 1]
+    rt.set_patched_mode(False)
+    rt.next_patch()
+    assert rt.pipeline_patch_idx == 0
+    with pytest.raises(RuntimeError):
+        bad = EngineConfig()
+        bad.parallel_config.sp_config.ulysses_degree = 5
+        initialize_runtime_state(ModelGeometry(24, 64), bad)
+    reset_runtime_state()
+
+
+def test_rank_generator_matches_reference(book):
+    from hetu_dit_b200.core.distributed.utils import RankGenerator, generate_masked_orthogonal_rank_groups
+    for c in book["rank_generator"]:
+        g = RankGenerator(c["tp"], c["sp"], c["pp"], c["cfg"], c["dp"], "tp-sp-pp-cfg-dp", rank_offset=c["rank_offset"])
+        for tok, groups in c["groups"].items():
+            assert g.get_ranks(tok) == groups
+    for c in book["masked_orthogonal"]:
+        assert generate_masked_orthogonal_rank_groups(c["world"], c["sizes"], c["mask"]) == c["groups"]
+    with pytest.raises(RuntimeError):
+        RankGenerator(2, 1, 1, 1, 1, "sp-pp")
+
+
+def test_seq_parallel_groups_match_reference(book):
+    from hetu_dit_b200.core.distributed.parallel_state import set_seq_parallel_pg
+    for c in book["seq_parallel_groups"]:
+        for rank, groups in c["per_rank"].items():
+            u, r = set_seq_parallel_pg(c["ulysses"], c["ring"], int(rank), len(c["ranks"]), c["ranks"],
+                                       use_ulysses_low=c["use_ulysses_low"])
+            assert u.ranks == groups["ulysses"] and r.ranks == groups["ring"], c
+
+
+def test_comm_pool_enumeration_matches_reference(book):
+    from hetu_dit_b200.core.distributed.parallel_state import ParallelGroups
+    pg = ParallelGroups(0, 1)
+    for c in book["rank_combinations"]:
+        assert pg._generate_rank_combinations(c["world"], c["base"]) == c["result"]
+    for c in book["group_partitions"]:
+        assert pg._generate_group_ranks(c["ranks"]) == c["result"]
+
+
+def test_plan_activation_on_rank_subset():
+    """A U2 x R2 plan placed on ranks {1, 3, 4, 6} of an 8-rank node, seen from every member."""
+    from hetu_dit_b200.core.distributed import parallel_state as ps
+    members = [1, 3, 4, 6]
+    for me in members:
+        pg = ps.ParallelGroups(me, 8)
+        pg.activate_plan(members, ulysses=2, ring=2)
+        sp = pg.group("sp")
+        assert sp.ranks == members and sp.rank_in_group == members.index(me)
+        i = members.index(me)
+        assert sp.ulysses_group.ranks == ([1, 3] if i < 2 else [4, 6])
+        assert sp.ring_group.ranks == ([1, 4] if i % 2 == 0 else [3, 6])
+        assert ps.PROCESS_GROUP.ULYSSES_PG is sp.ulysses_group and ps.PROCESS_GROUP.RING_PG is sp.ring_group
+        assert pg.group("pp").ranks == [me] and pg.group("tp").world_size == 1
+    pg = ps.ParallelGroups(5, 8)
+    pg.activate_plan(range(8), ulysses=2, pp=4)  # tp-sp-pp order: sp pairs are consecutive, pp stride 2
+    assert pg.group("sp").ranks == [4, 5] and pg.group("pp").ranks == [1, 3, 5, 7]
+    with pytest.raises(ValueError):
+        pg.activate_plan(range(8), ulysses=3)
+    with pytest.raises(ValueError):
+        pg.activate_plan([0, 1], ulysses=2)  # rank 5 is not a member
+    ps.destroy_model_parallel()
+
+
+def test_cache_manager_contract():
+    from hetu_dit_b200.core.resource_manager.cache_manager import CacheManager
+    cm = CacheManager()
+    with pytest.raises(ValueError):
+        cm.register_cache_entry(object(), "mlp")
+    with pytest.raises(ValueError):
+        cm.register_cache_entry(object(), "attn", "other")
+    layer = object()
+    cm.register_cache_entry(layer, "attn")
+    k, v = torch.zeros(1, 4, 8), torch.ones(1, 4, 8)
+    # no runtime state -> nothing cached, the fresh tensors come back (no GPU needed)
+    from hetu_dit_b200.core.distributed.runtime_state import reset_runtime_state
+    reset_runtime_state()
+    rk, rv = cm.update_and_get_kv_cache([k, v], layer)
+    assert rk is k and rv is v
+    cm._reset_cache()
+    assert cm.cache == {}
+
+
+def test_operator_argument_errors():
+    from hetu_dit_b200.core.distributed import parallel_state as ps
+    from hetu_dit_b200.core.parallel import hetuDiTJointLongContextAttention, hetuDiTLongContextAttention
+    from hetu_dit_b200.core.parallel.ring import ring_flash_attn_func
+    ps.destroy_model_parallel()
+    with pytest.raises(RuntimeError):
+        hetuDiTLongContextAttention(ring_impl_type="zigzag", use_kv_cache=True)
+    op = hetuDiTJointLongContextAttention()
+    q = torch.zeros(1, 8, 2, 64)
+    with pytest.raises(ValueError):
+        op(None, q, q, q, joint_tensor_query=q, joint_tensor_key=q, joint_tensor_value=q, joint_strategy="middle")
+    with pytest.raises(ValueError):
+        op(None, q, q, q, joint_tensor_query=None, joint_tensor_key=q, joint_tensor_value=q, joint_strategy="rear")
+    with pytest.raises(ValueError):
+        ring_flash_attn_func(q, q, q, joint_strategy="rear")
+    with pytest.raises(AssertionError):
+        ring_flash_attn_func(q, q, q, alibi_slopes=torch.zeros(2))
+
+
+def _gloo_worker(rank, world, port, errq):
+    import traceback
+    try:
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from hetu_dit_b200.core.distributed import parallel_state as ps
+        from hetu_dit_b200.core.distributed.runtime_state import split_patches
+        # every rank derives the same plan from the same inputs, with no collective on the data path
+        ps.init_distributed_environment(rank, world, None)
+        ps.initialize_model_parallel(sequence_parallel_degree=world, ulysses_degree=world)
+        mine = (ps.get_sp_group().ranks, ps.get_ulysses_parallel_rank(), ps.get_sequence_parallel_world_size())
+        seen = [None] * world
+        dist.all_gather_object(seen, mine)
+        assert all(s[0] == list(range(world)) and s[2] == world for s in seen)
+        assert sorted(s[1] for s in seen) == list(range(world))
+        # SP ranks own disjoint token ranges of every patch that tile the image
+        meta = split_patches(128, 128, 2, 4, world, rank)
+        allm = [None] * world
+        dist.all_gather_object(allm, meta[5])
+        covered = sorted(tuple(r) for m in allm for r in m)
+        assert covered[0][0] == 0 and covered[-1][1] == 4096
+        assert all(covered[i][1] == covered[i + 1][0] for i in range(len(covered) - 1))
+        # a multi-rank group without a peer heap cannot move data and says so
+        with pytest.raises(RuntimeError):
+            ps.get_sp_group().barrier()
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errq.put(traceback.format_exc())
+        raise
+
+
+def test_two_rank_host_protocol_on_gloo():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    try:
+        mp.spawn(_gloo_worker, args=(2, 29641, errq), nprocs=2, join=True)
+    except Exception:
+        msgs = []
+        while not errq.empty():
+            msgs.append(errq.get())
+        pytest.fail("\n".join(msgs) or "gloo worker failed")
