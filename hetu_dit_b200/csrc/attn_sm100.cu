@@ -692,3 +692,94 @@ extern "C" int hdit_attn_fwd(const hdit_attn_args* a) {
   return fp16 ? launch<64, true>(kp, static_cast<int>(grid), stream)
               : launch<64, false>(kp, static_cast<int>(grid), stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Two-pass attention whose fp32 running result lives in a static device array.
+//
+// Some hosts of this library cannot allocate device memory around a call: a serving process whose HBM
+// is wholly reserved by its own pool (so a raw cudaMalloc fails or fragments it), or a denoising loop
+// that must not take the device-wide synchronisation cudaMalloc / cudaFree imply. For them the
+// partial-result buffers of the PARTIAL_FIRST -> MERGE_FINAL sequence are carved out of the array
+// below instead of being passed in. Every GPU that loads the library holds these 32.5 MiB until exit.
+namespace hdit {
+namespace {
+
+constexpr size_t kStaticAccFloats = size_t(8) << 20;    // fp32 partial output, 32 MiB
+constexpr size_t kStaticLseFloats = size_t(128) << 10;  // fp32 log-sum-exp, 512 KiB
+static __device__ __align__(256) float g_static_attn_scratch[kStaticAccFloats + kStaticLseFloats];
+
+// Host code must not hand the symbol itself to a kernel: on the host the name is only a stand-in.
+// Its device address is looked up once per device, with that device current.
+float* g_static_scratch_addr[64] = {nullptr};
+std::mutex g_static_scratch_mutex;
+
+int static_scratch_for_current_device(float** out) {
+  int dev = 0;
+  HDIT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(HDIT_ERR_CUDA, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    HDIT_CUDA_OK(cudaGetSymbolAddress(&p, g_static_attn_scratch));
+    g_static_scratch_addr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_scratch_addr[dev];
+  return HDIT_OK;
+}
+
+}  // namespace
+}  // namespace hdit
+
+extern "C" int hdit_attn_fwd_split_static(const hdit_attn_args* a, int32_t first_pass_kv_segs) {
+  using namespace hdit;
+  if (a == nullptr) return set_error(HDIT_ERR_BAD_ARG, "args is null");
+  if (a->mode != HDIT_ATTN_FINAL) return set_error(HDIT_ERR_BAD_ARG, "mode must be HDIT_ATTN_FINAL");
+  if (a->n_kv_seg < 2 || a->n_kv_seg > HDIT_MAX_KV_SEG || first_pass_kv_segs < 1 || first_pass_kv_segs >= a->n_kv_seg)
+    return set_error(HDIT_ERR_BAD_ARG, "need 1 <= first_pass_kv_segs (%d) < n_kv_seg (%d)", first_pass_kv_segs,
+                     a->n_kv_seg);
+  if (a->n_q_seg < 1 || a->n_q_seg > HDIT_MAX_Q_SEG || a->batch <= 0 || a->heads <= 0 || a->head_dim <= 0)
+    return set_error(HDIT_ERR_BAD_ARG, "bad batch / heads / head_dim / n_q_seg");
+  long long sq = 0;
+  for (int i = 0; i < a->n_q_seg; ++i) {
+    if (a->q[i].len < 0) return set_error(HDIT_ERR_BAD_ARG, "negative q segment length");
+    sq += a->q[i].len;
+  }
+  long long kv_first = 0, kv_second = 0;
+  for (int i = 0; i < a->n_kv_seg; ++i) {
+    if (a->k[i].len < 0) return set_error(HDIT_ERR_BAD_ARG, "negative kv segment length");
+    (i < first_pass_kv_segs ? kv_first : kv_second) += a->k[i].len;
+  }
+  if (sq == 0) return HDIT_OK;
+  if (kv_first == 0 || kv_second == 0) return hdit_attn_fwd(a);  // one side is empty: a single pass is the answer
+  const unsigned long long acc_need = 1ull * a->batch * sq * a->heads * a->head_dim;
+  const unsigned long long lse_need = 1ull * a->batch * a->heads * sq;
+  if (acc_need > kStaticAccFloats || lse_need > kStaticLseFloats)
+    return set_error(HDIT_ERR_TOO_LARGE,
+                     "static scratch too small: batch*Sq*heads*head_dim = %llu (max %llu), batch*heads*Sq = %llu "
+                     "(max %llu); use hdit_attn_fwd with caller-provided acc_out / acc_lse instead",
+                     acc_need, (unsigned long long)kStaticAccFloats, lse_need, (unsigned long long)kStaticLseFloats);
+  float* scratch = nullptr;
+  const int rc = static_scratch_for_current_device(&scratch);
+  if (rc != HDIT_OK) return rc;
+
+  hdit_attn_args first = *a;
+  first.mode = HDIT_ATTN_PARTIAL_FIRST;
+  first.n_kv_seg = first_pass_kv_segs;
+  first.out = nullptr;
+  first.lse = nullptr;
+  first.acc_out = scratch;
+  first.acc_lse = scratch + kStaticAccFloats;
+  const int rc1 = hdit_attn_fwd(&first);
+  if (rc1 != HDIT_OK) return rc1;
+
+  hdit_attn_args second = *a;
+  second.mode = HDIT_ATTN_MERGE_FINAL;
+  second.n_kv_seg = a->n_kv_seg - first_pass_kv_segs;
+  for (int i = 0; i < second.n_kv_seg; ++i) {
+    second.k[i] = a->k[first_pass_kv_segs + i];
+    second.v[i] = a->v[first_pass_kv_segs + i];
+  }
+  second.acc_out = scratch;
+  second.acc_lse = scratch + kStaticAccFloats;
+  return hdit_attn_fwd(&second);
+}

@@ -267,6 +267,28 @@ HDIT_API int hdit_peer_barrier(int32_t* const* peer_slots, const int32_t* const*
 HDIT_API int hdit_peer_signal(int32_t* flag, int32_t value, void* stream);
 HDIT_API int hdit_peer_wait(const int32_t* flag, int32_t value, int64_t max_spins, int32_t tag, void* stream);
 
+/*
+ * hdit_attn_fwd in two launches without any caller-provided or freshly allocated scratch.
+ * (No counterpart in the reference: it exists for hosts that cannot allocate device memory
+ * around the call -- e.g. a serving process whose HBM is entirely owned by its own pool, or a
+ * denoising loop that must not incur the device-wide synchronisation of cudaMalloc/cudaFree.)
+ *
+ * KV segments [0, first_pass_kv_segs) are attended first, the rest second; the second launch merges
+ * by log-sum-exp and writes `out` (+ `lse`), so the result equals hdit_attn_fwd(mode = FINAL) over
+ * all segments. This is the ring-attention pattern: the local KV block first, the blocks pulled from
+ * peers afterwards. args->mode must be HDIT_ATTN_FINAL; acc_out / acc_lse are ignored.
+ *
+ * The fp32 partial result between the launches lives in a file-scope device array of the library
+ * (32 MiB + 512 KiB, held by every GPU that loads the library until exit). Limits:
+ * batch * Sq * heads * head_dim <= 8 Mi elements and batch * heads * Sq <= 128 Ki; larger problems
+ * get HDIT_ERR_TOO_LARGE. The function calls no cudaMalloc / cudaFree or allocating library routine.
+ * The first call on a device looks the array's device address up (cudaGetSymbolAddress); make that
+ * first call outside any stream capture. All calls on a device share the one array: two calls that
+ * overlap on the GPU (different streams) race; calls on one stream are safe. Nothing in the array has
+ * to start at zero -- the first launch overwrites every row the second one reads.
+ */
+HDIT_API int hdit_attn_fwd_split_static(const hdit_attn_args* args, int32_t first_pass_kv_segs);
+
 #ifdef __cplusplus
 }
 #endif
