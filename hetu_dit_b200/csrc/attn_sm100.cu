@@ -6,6 +6,10 @@
 //   warp 8      TMA producer   : Q tiles once, then K/V blocks through two rings
 //   warp 9      MMA issuer     : S = Q K^T (tcgen05.mma, smem x smem -> TMEM)
 //                                O += P V  (tcgen05.mma, TMEM x smem -> TMEM)
+//   warps 10-11 idle           : complete the third warpgroup so registers can be handed over
+//                                (setmaxnreg: 72 per thread there, 216 for the softmax threads;
+//                                72 + 2 * 216 = 3 * 168, the pool the CTA was launched with --
+//                                asking for more would block in setmaxnreg.inc for ever)
 //   warps 0-3   softmax group 0: owns Q tile 0, one thread per row
 //   warps 4-7   softmax group 1: owns Q tile 1
 //
@@ -39,7 +43,7 @@ namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
-constexpr int kNumThreads = 320;
+constexpr int kNumThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding the TMA and MMA warps
 constexpr int kPanelBytes = 128 * 128;  // 128 rows x 64 16-bit elements, 128B-swizzled
 constexpr uint32_t kSpinLimit = 8u * 1000u * 1000u;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
@@ -130,6 +134,12 @@ __device__ __forceinline__ void load_tile(const CUtensorMap* map, bool swapped, 
   }
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <bool FP16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if constexpr (FP16) {
@@ -201,6 +211,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Register hand-over between warpgroups: a softmax thread keeps a whole 128-column row of S.
+  // Each warpgroup changes its budget at the top of its own branch so the allocation of the code
+  // below it is known.
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == 8) {
     // =========================== TMA producer ===========================
     if (lane == 0) {
@@ -255,24 +270,29 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       const uint32_t v_addr = smem_u32(smem_v);
       bool ok = true;
 
+      // Descriptors differ from a per-tile base only in the start-address field (low word, units of
+      // 16 bytes), so a k-step costs one 32-bit add instead of a rebuilt 64-bit descriptor.
+      const uint64_t q_desc0 = make_smem_desc_sw128(q_addr, 16, 1024);
+      const uint64_t k_desc0 = make_smem_desc_sw128(k_addr, 16, 1024);
+      const uint64_t v_desc0 = make_smem_desc_sw128(v_addr, kPanelBytes, 1024);
       auto issue_qk = [&](int t, int stage) {
         const uint32_t d_tmem = tmem_base + C::kColS + t * 128;
+        const uint64_t a0 = q_desc0 + static_cast<uint32_t>((t * C::kTileBytes) >> 4);
+        const uint64_t b0 = k_desc0 + static_cast<uint32_t>((stage * C::kTileBytes) >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-          const uint64_t a = make_smem_desc_sw128(q_addr + t * C::kTileBytes + off, 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(k_addr + stage * C::kTileBytes + off, 16, 1024);
-          umma_ss(d_tmem, a, bdesc, idesc_qk, kk > 0 ? 1u : 0u);
+          const uint32_t off = ((kk >> 2) * kPanelBytes + (kk & 3) * 32) >> 4;
+          umma_ss(d_tmem, a0 + off, b0 + off, idesc_qk, kk > 0 ? 1u : 0u);
         }
       };
       auto issue_pv = [&](int t, int stage, bool accumulate) {
         const uint32_t d_tmem = tmem_base + C::kColO + t * D;
         const uint32_t a_tmem = tmem_base + C::kColS + t * 128;
+        const uint64_t b0 = v_desc0 + static_cast<uint32_t>((stage * C::kTileBytes) >> 4);
 #pragma unroll
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
-          const uint64_t bdesc =
-              make_smem_desc_sw128(v_addr + stage * C::kTileBytes + kk * 2048, kPanelBytes, 1024);
-          umma_ts(d_tmem, a_tmem + kk * 8, bdesc, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+          umma_ts(d_tmem, a_tmem + kk * 8, b0 + static_cast<uint32_t>((kk * 2048) >> 4), idesc_pv,
+                  (accumulate || kk > 0) ? 1u : 0u);
         }
       };
       auto wait = [&](uint64_t* bar, uint32_t parity, int where, int iter) {
@@ -327,7 +347,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         }
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ========================= softmax / epilogue =========================
     const int t = warp >> 2;           // which Q tile this warpgroup owns
     const int quarter = warp & 3;      // TMEM lane quarter this warp may touch
@@ -370,11 +392,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            mx0 = fmaxf(mx0, __uint_as_float(s[c][i]));
-            mx1 = fmaxf(mx1, __uint_as_float(s[c][i + 1]));
-            mx2 = fmaxf(mx2, __uint_as_float(s[c][i + 2]));
-            mx3 = fmaxf(mx3, __uint_as_float(s[c][i + 3]));
+          for (int i = 0; i < 32; i += 8) {
+            mx0 = max3(mx0, __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+            mx1 = max3(mx1, __uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3]));
+            mx2 = max3(mx2, __uint_as_float(s[c][i + 4]), __uint_as_float(s[c][i + 5]));
+            mx3 = max3(mx3, __uint_as_float(s[c][i + 6]), __uint_as_float(s[c][i + 7]));
           }
         const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
         const float m_new = fmaxf(m_run, m_blk);
@@ -397,21 +419,29 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
           }
         }
 
-        const float neg_m = -m_run;
-        float sum0 = 0.f, sum1 = 0.f;
+        // p = 2^(s * scale - m): packed fp32x2 FMA and add halve the issue slots of the row loop
+        const float2 scale2 = make_float2(scale_log2, scale_log2);
+        const float2 neg_m2 = make_float2(-m_run, -m_run);
+        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(s[c][i]), scale_log2, neg_m));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(s[c][i + 1]), scale_log2, neg_m));
-            sum0 += p0;
-            sum1 += p1;
-            pk[i >> 1] = pack2<FP16>(p0, p1);
+          for (int i = 0; i < 32; i += 4) {
+            const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), scale2,
+                                         neg_m2);
+            const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3])),
+                                         scale2, neg_m2);
+            const float2 p0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
+            const float2 p1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
+            acc0 = __fadd2_rn(acc0, p0);
+            acc1 = __fadd2_rn(acc1, p1);
+            pk[i >> 1] = pack2<FP16>(p0.x, p0.y);
+            pk[(i >> 1) + 1] = pack2<FP16>(p1.x, p1.y);
           }
           tmem_st16(tm_s + c * 16, pk);
         }
+        const float sum0 = acc0.x + acc0.y, sum1 = acc1.x + acc1.y;
         l_run += sum0 + sum1;
         tc_wait_st();
         tc_fence_before();
