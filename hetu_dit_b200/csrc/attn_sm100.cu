@@ -47,7 +47,6 @@ constexpr int kNumThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding 
 constexpr int kPanelBytes = 128 * 128;  // 128 rows x 64 16-bit elements, 128B-swizzled
 constexpr uint32_t kSpinLimit = 8u * 1000u * 1000u;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-constexpr int kPolyEvery = 0;  // > 0: in every kPolyEvery-th group of 4 scores, 2 use the polynomial exp2 (measured: no gain yet)
 constexpr float kLn2 = 0.69314718055994531f;
 
 enum Where : int {
@@ -141,32 +140,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
-// 2^x for two values on the FMA pipe (x <= 8 here, clamped below at -127): split x into floor and
-// fraction with a round-down magic-number add, evaluate a cubic for 2^fraction (relative error
-// < 1e-4, far below the 16-bit rounding of P) and add the integer part into the exponent field.
-// Running a share of the exponentials here relieves the MUFU unit, whose 16 results per clock per
-// SM otherwise cap the softmax at the tensor pipe's pace.
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-  x.x = fmaxf(x.x, -127.0f);
-  x.y = fmaxf(x.y, -127.0f);
-  const float2 magic = make_float2(12582912.0f, 12582912.0f);  // 1.5 * 2^23
-  unsigned long long xi = *reinterpret_cast<unsigned long long*>(&x);
-  unsigned long long mi = *reinterpret_cast<const unsigned long long*>(&magic);
-  unsigned long long ti;
-  asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(ti) : "l"(xi), "l"(mi));
-  const float2 t = *reinterpret_cast<float2*>(&ti);
-  const float2 n = __fadd2_rn(t, make_float2(-12582912.0f, -12582912.0f));
-  const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
-  float2 p = __ffma2_rn(f, make_float2(0.077119089663028717f, 0.077119089663028717f),
-                        make_float2(0.227564394474029541f, 0.227564394474029541f));
-  p = __ffma2_rn(p, f, make_float2(0.695146143436431885f, 0.695146143436431885f));
-  p = __ffma2_rn(p, f, make_float2(1.0f, 1.0f));
-  float2 r;
-  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
-  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
-  return r;
-}
-
 template <bool FP16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if constexpr (FP16) {
@@ -193,8 +166,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
   uint64_t* v_full = k_empty + C::kStages;       // [stages]
   uint64_t* v_empty = v_full + C::kStages;       // [stages]
   uint64_t* s_full = v_empty + C::kStages;       // [2]
-  uint64_t* p_ready = s_full + 2;                // [2][4]: one per 32-column chunk of P
-  uint64_t* o_done = p_ready + 8;                // [2]
+  uint64_t* p_ready = s_full + 2;                // [2]
+  uint64_t* o_done = p_ready + 2;                // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -217,7 +190,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&s_full[i], 1);
-      for (int c = 0; c < 4; ++c) mbar_init(&p_ready[i * 4 + c], 128);
+      mbar_init(&p_ready[i], 128);
       mbar_init(&o_done[i], 1);
     }
     for (int i = 0; i < C::kStages; ++i) {
@@ -312,13 +285,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
           umma_ss(d_tmem, a0 + off, b0 + off, idesc_qk, kk > 0 ? 1u : 0u);
         }
       };
-      // O += P V for the kv rows of one 32-column chunk of P (two k-steps of 16)
-      auto issue_pv_chunk = [&](int t, int stage, int c, bool accumulate) {
+      auto issue_pv = [&](int t, int stage, bool accumulate) {
         const uint32_t d_tmem = tmem_base + C::kColO + t * D;
         const uint32_t a_tmem = tmem_base + C::kColS + t * 128;
         const uint64_t b0 = v_desc0 + static_cast<uint32_t>((stage * C::kTileBytes) >> 4);
 #pragma unroll
-        for (int kk = 2 * c; kk < 2 * c + 2; ++kk) {
+        for (int kk = 0; kk < kBlockN / 16; ++kk) {
           umma_ts(d_tmem, a_tmem + kk * 8, b0 + static_cast<uint32_t>((kk * 2048) >> 4), idesc_pv,
                   (accumulate || kk > 0) ? 1u : 0u);
         }
@@ -357,16 +329,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         const uint32_t phn = static_cast<uint32_t>((j + 1) / C::kStages) & 1;
         for (int t = 0; t <= last_t && ok; ++t) {
           if (t == 0) wait(&v_full[st], ph, W_MMA_VFULL, j);
-          // P arrives in four chunks: the first P V k-steps run while the softmax group is still
-          // exponentiating the rest of the row
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            wait(&p_ready[t * 4 + c], j & 1, W_MMA_PREADY, j * 2 + t);
-            if (!ok) break;
-            tc_fence_after();
-            issue_pv_chunk(t, st, c, j > 0);
-          }
+          wait(&p_ready[t], j & 1, W_MMA_PREADY, j * 2 + t);
           if (!ok) break;
+          tc_fence_after();
+          issue_pv(t, st, j > 0);
           if (t == last_t) tc_commit(&v_empty[st]);
           if (j + 1 < nblk) {
             if (t == 0) wait(&k_full[stn], phn, W_MMA_KFULL, j + 1);
@@ -467,28 +433,19 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
             const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3])),
                                          scale2, neg_m2);
             const float2 p0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
-            // one pair in kPolyEvery goes through the FMA-pipe exponential
-            const float2 p1 = (kPolyEvery > 0 && ((i >> 2) % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1)
-                                  ? exp2_poly2(x1)
-                                  : make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
+            const float2 p1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
             acc0 = __fadd2_rn(acc0, p0);
             acc1 = __fadd2_rn(acc1, p1);
             pk[i >> 1] = pack2<FP16>(p0.x, p0.y);
             pk[(i >> 1) + 1] = pack2<FP16>(p1.x, p1.y);
           }
-          // publish the previous chunk only now: its tcgen05.st has had this chunk's arithmetic to land
-          if (c > 0) {
-            tc_wait_st();
-            tc_fence_before();
-            mbar_arrive(&p_ready[t * 4 + c - 1]);
-          }
           tmem_st16(tm_s + c * 16, pk);
         }
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(&p_ready[t * 4 + 3]);
         const float sum0 = acc0.x + acc0.y, sum1 = acc1.x + acc1.y;
         l_run += sum0 + sum1;
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&p_ready[t]);
       }
 
       // ------------------------------ epilogue ------------------------------
