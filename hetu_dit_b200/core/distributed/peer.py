@@ -192,3 +192,58 @@ class PeerGroup:
 
     def __repr__(self):
         return f"PeerGroup(ranks={self.ranks}, rank={self.rank_in_group})"
+
+
+class ParamArena:
+    """Peer-mapped memory for model parameters that other ranks may pull during a plan switch.
+
+    Unlike the activation heap it survives plan switches, so it has a first-fit free list instead of a
+    bump pointer. Offsets are private to the owning rank; a peer learns them from the owner's block
+    directory and turns them into addresses with peer_ptr()."""
+
+    def __init__(self, nbytes: int, rank: int, world_size: int, device, all_gather_bytes=None):
+        self.heap = PeerHeap(nbytes + FLAG_BYTES, rank, world_size, device, all_gather_bytes)
+        self.rank = rank
+        self._free = [(FLAG_BYTES, nbytes)]  # (offset, size), sorted by offset
+        self._used = {}                      # offset -> size
+
+    def alloc(self, shape, dtype) -> torch.Tensor:
+        shape = tuple(int(s) for s in shape)
+        n = 1
+        for s in shape:
+            n *= s
+        size = max(256, (n * torch.empty((), dtype=dtype).element_size() + 255) // 256 * 256)
+        for i, (off, avail) in enumerate(self._free):
+            if avail >= size:
+                if avail == size:
+                    self._free.pop(i)
+                else:
+                    self._free[i] = (off + size, avail - size)
+                self._used[off] = size
+                nbytes = n * torch.empty((), dtype=dtype).element_size()
+                return self.heap._bytes[off:off + nbytes].view(dtype).view(shape)
+        raise MemoryError(f"parameter arena exhausted ({size} bytes requested)")
+
+    def free(self, t: torch.Tensor):
+        off = t.data_ptr() - self.heap.base
+        size = self._used.pop(off, None)
+        if size is None:
+            return
+        self._free.append((off, size))
+        self._free.sort()
+        merged = []
+        for o, s in self._free:
+            if merged and merged[-1][0] + merged[-1][1] == o:
+                merged[-1] = (merged[-1][0], merged[-1][1] + s)
+            else:
+                merged.append((o, s))
+        self._free = merged
+
+    def offset_of(self, t: torch.Tensor) -> int:
+        return t.data_ptr() - self.heap.base
+
+    def peer_ptr(self, rank: int, offset: int) -> int:
+        return self.heap.peer_ptr(rank, offset)
+
+    def bytes_in_use(self) -> int:
+        return sum(self._used.values())

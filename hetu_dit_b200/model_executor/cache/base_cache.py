@@ -58,12 +58,14 @@ def _resolve(module: nn.Module, path: str) -> nn.Module:
 class BaseBlockCache:
     """LRU cache of GPU-resident transformer blocks, each tagged with the TP range its split Linears hold."""
 
-    def __init__(self, max_num_cached_blocks: int = 1 << 30, device: Optional[torch.device] = None, allocator=None):
+    def __init__(self, max_num_cached_blocks: int = 1 << 30, device: Optional[torch.device] = None, allocator=None,
+                 deallocator=None):
         self.max_num_cached_blocks = max_num_cached_blocks
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         # allocator(shape, dtype) -> tensor: where migrated parameters live (peer-mapped memory when peers must
         # be able to pull them); default: ordinary device memory.
         self.allocator = allocator or (lambda shape, dtype: torch.empty(shape, dtype=dtype, device=self.device))
+        self.deallocator = deallocator  # deallocator(tensor): gives evicted parameters back to the arena
         self.cache: "OrderedDict[int, Tuple[nn.Module, Tuple[float, float]]]" = OrderedDict()
         self.active_block_indices: List[int] = []
         self._last_p2p_preplans: Dict[int, DataReconstructionPlan] = {}
@@ -291,7 +293,15 @@ class BaseBlockCache:
         return boxes
 
     # ---- LRU ---------------------------------------------------------------------------------------------
+    def _release(self, block: Optional[nn.Module]):
+        if block is not None and self.deallocator is not None:
+            for prm in block.parameters():
+                self.deallocator(prm.data)
+
     def _add_or_update(self, idx: int, block: nn.Module, tp_range: Tuple[float, float]):
+        old = self.cache.get(idx)
+        if old is not None and old[0] is not block:
+            self._release(old[0])
         self.cache[idx] = (block, tuple(tp_range))
         self.cache.move_to_end(idx)
 
@@ -301,7 +311,7 @@ class BaseBlockCache:
             victim = next((i for i in self.cache if i not in keep), None)
             if victim is None:
                 break
-            del self.cache[victim]
+            self._release(self.cache.pop(victim)[0])
 
     # ---- the plan switch -----------------------------------------------------------------------------------
     def adjust_pipeline(self, transformer: nn.Module, cpu_full_transformer: nn.Module, old_pp_range, new_pp_range,

@@ -1,0 +1,240 @@
+"""Denoising stage of the SD3-shaped model with PipeFusion: warm-up steps on the whole image, then
+the patch pipeline with stale K/V.
+
+Plays the role of the reference's SD3 pipeline wrapper
+(hetu_dit/model_executor/pipelines/pipeline_stable_diffusion_3.py: diffusion_stage :665-900,
+_sync_pipeline :1352-1467, _init_async_pipeline :1469-1511, _async_pipeline :1515-1678,
+_backbone_forward :1680-1717) and of its transformer wrapper
+(models/transformers/transformer_sd3.py:95-198, stage split base_transformer.py:65-148).
+
+The schedule is the reference's: stage s owns a contiguous slice of the blocks; a patch travels
+stage to stage, the last stage applies classifier-free guidance and the scheduler step and sends
+the new latent patch back to the first stage; the text stream of a step is computed together with
+patch 0 and re-used by the other patches. Hand-offs go through the peer-heap coordinator
+(group_coordinator.py here): one copy kernel + one flag store per message, no shape handshake per
+message, no host synchronisation in steady state. Latents are token-major (B, tokens, 64) -- the
+patchified form -- so a pipeline patch is a contiguous token range.
+"""
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from ...core.distributed import parallel_state as ps
+from ...core.distributed.runtime_state import get_runtime_state
+from ..models.shaped_dit import ShapedDiT, _modulate, timestep_embedding
+
+
+def flow_match_sigmas(num_steps: int, shift: float = 3.0, device=None) -> torch.Tensor:
+    """Shifted linear sigma schedule of a flow-matching Euler scheduler, num_steps + 1 values ending at 0."""
+    s = torch.linspace(1.0, 1.0 / num_steps, num_steps, dtype=torch.float64)
+    s = shift * s / (1 + (shift - 1) * s)
+    return torch.cat([s, torch.zeros(1, dtype=torch.float64)]).float().to(device)
+
+
+def stage_block_range(total_blocks: int, pp_rank: int, pp_world: int,
+                      attn_layer_num_for_pp: Optional[List[int]] = None) -> Tuple[int, int]:
+    """Blocks [lo, hi) of one stage: explicit per-stage counts, else ceil(total / stages) per stage."""
+    if attn_layer_num_for_pp is not None:
+        assert sum(attn_layer_num_for_pp) == total_blocks, (
+            "Sum of attn_layer_num_for_pp should be equal to the number of all the transformer blocks")
+        return sum(attn_layer_num_for_pp[:pp_rank]), sum(attn_layer_num_for_pp[:pp_rank + 1])
+    per = (total_blocks + pp_world - 1) // pp_world
+    return pp_rank * per, min((pp_rank + 1) * per, total_blocks)
+
+
+class SD3ShapedPipeline:
+    def __init__(self, model: ShapedDiT, guidance_scale: float = 5.0, grid: Tuple[int, int] = (128, 128)):
+        self.model = model
+        self.shape = model.shape
+        self.guidance_scale = guidance_scale
+        self.grid = grid
+        self.encoder_hidden_states_cache = {}
+        self.sigmas = None
+        # True when model.transformer_blocks already holds only this stage's blocks (the worker's block
+        # cache placed them); False when the model is whole and the stage's slice is taken here.
+        self.stage_sliced = False
+
+    # ------------------------------------------------------------------ one stage of the backbone
+    def _stage_blocks(self):
+        blocks = self.model.transformer_blocks
+        if self.stage_sliced:
+            return list(enumerate(blocks))
+        rt = get_runtime_state()
+        lo, hi = stage_block_range(len(blocks), ps.get_pipeline_parallel_rank(), ps.get_pipeline_parallel_world_size(),
+                                   rt.parallel_config.pp_config.attn_layer_num_for_pp)
+        return [(i, blocks[i]) for i in range(lo, hi)]
+
+    def _transformer(self, hidden_states, encoder_hidden_states, pooled, timestep):
+        """Stage forward. First stage: latent tokens in, embeddings applied. Last stage: noise tokens out."""
+        m, rt = self.model, get_runtime_state()
+        d = self.shape.hidden
+        dtype = hidden_states.dtype
+        temb = m.time_embed(timestep_embedding(timestep * 1000.0).to(dtype)) + m.pooled_embed(pooled)
+        if ps.is_pipeline_first_stage():
+            n = hidden_states.shape[1]
+            tok0 = rt.pp_patches_token_start_idx_local[rt.pipeline_patch_idx] if rt.patch_mode else 0
+            pos = m._sincos_pos(self.grid[0], self.grid[1], hidden_states.device, dtype)
+            hidden_states = m.x_embedder(hidden_states) + pos[:, tok0:tok0 + n]
+            encoder_hidden_states = m.context_embedder(encoder_hidden_states)
+        for i, block in self._stage_blocks():
+            if rt.patch_mode and rt.pipeline_patch_idx == 0:
+                self.encoder_hidden_states_cache[i] = encoder_hidden_states
+                hidden_states, encoder_hidden_states = block(hidden_states, encoder_hidden_states, temb, None)
+            elif rt.patch_mode:
+                hidden_states, _ = block(hidden_states, self.encoder_hidden_states_cache[i], temb, None)
+            else:
+                hidden_states, encoder_hidden_states = block(hidden_states, encoder_hidden_states, temb, None)
+        if ps.is_pipeline_last_stage():
+            shift, scale = m.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
+            hidden_states = m.proj_out(_modulate(F.layer_norm(hidden_states, (d,), eps=1e-6), shift, scale))
+        return hidden_states, encoder_hidden_states
+
+    def _backbone_forward(self, latents, encoder_hidden_states, pooled, t):
+        if ps.is_pipeline_first_stage():
+            latents = torch.cat([latents] * 2)  # unconditional + conditional through one batch
+        timestep = t.expand(latents.shape[0])
+        noise_pred, encoder_hidden_states = self._transformer(latents, encoder_hidden_states, pooled, timestep)
+        if ps.is_pipeline_last_stage():
+            uncond, text = noise_pred.chunk(2)
+            latents = uncond + self.guidance_scale * (text - uncond)
+        else:
+            latents = noise_pred
+        return latents, encoder_hidden_states
+
+    def _scheduler_step(self, noise_pred, last_latents, i):
+        """Flow-matching Euler step in fp32; the step index is the caller's, so it advances once per
+        step however many patches the step has (the reference gates its scheduler's step counter on the
+        last patch, scheduling_flow_match_euler_discrete.py:119-124)."""
+        dt = self.sigmas[i + 1] - self.sigmas[i]
+        return (last_latents.float() + dt * noise_pred.float()).to(last_latents.dtype)
+
+    # ------------------------------------------------------------------ warm-up: whole image per step
+    def _sync_pipeline(self, latents, prompt_embeds, pooled, steps: List[int], sync_only: bool = False):
+        rt = get_runtime_state()
+        rt.set_patched_mode(False)
+        pp_world = ps.get_pipeline_parallel_world_size()
+        first, last = ps.is_pipeline_first_stage(), ps.is_pipeline_last_stage()
+        pp = ps.get_pp_group() if pp_world > 1 else None
+        encoder_hidden_states = None
+        for k, i in enumerate(steps):
+            if last:
+                last_timestep_latents = latents
+            if pp_world == 1 or (first and k == 0):
+                pass
+            else:
+                latents = pp.pipeline_recv()
+                if not first:
+                    encoder_hidden_states = pp.pipeline_recv(0, "encoder_hidden_states")
+            latents, encoder_hidden_states = self._backbone_forward(
+                latents, prompt_embeds if first else encoder_hidden_states, pooled, self.sigmas[i:i + 1])
+            if last:
+                latents = self._scheduler_step(latents, last_timestep_latents, i)
+            if sync_only and last and k == len(steps) - 1:
+                pass
+            elif pp_world > 1:
+                pp.pipeline_send(latents)
+                if not last:
+                    pp.pipeline_send(encoder_hidden_states, name="encoder_hidden_states")
+        return latents
+
+    # ------------------------------------------------------------------ patch pipeline
+    def _init_async_pipeline(self, num_timesteps: int, latents, num_pipeline_warmup_steps: int):
+        rt = get_runtime_state()
+        rt.set_patched_mode(True)
+        pp_world = ps.get_pipeline_parallel_world_size()
+        first, last = ps.is_pipeline_first_stage(), ps.is_pipeline_last_stage()
+        tokens = rt.pp_patches_token_num
+        if pp_world == 1:
+            return list(latents.split(tokens, dim=1))
+        pp = ps.get_pp_group()
+        if first:
+            # the latents the last stage produced at the end of warm-up
+            latents = pp.pipeline_recv() if num_pipeline_warmup_steps > 0 else latents
+            patch_latents = list(latents.split(tokens, dim=1))
+        elif last:
+            patch_latents = list(latents.split(tokens, dim=1))
+        else:
+            patch_latents = [None] * rt.num_pipeline_patch
+        recv_timesteps = num_timesteps - 1 if first else num_timesteps
+        for _ in range(recv_timesteps):
+            if not first:
+                pp.add_pipeline_recv_task(0, "encoder_hidden_states")
+            for patch_idx in range(rt.num_pipeline_patch):
+                pp.add_pipeline_recv_task(patch_idx)
+        return patch_latents
+
+    def _async_pipeline(self, latents, prompt_embeds, pooled, steps: List[int]):
+        if len(steps) == 0:
+            return latents
+        rt = get_runtime_state()
+        pp_world = ps.get_pipeline_parallel_world_size()
+        first, last = ps.is_pipeline_first_stage(), ps.is_pipeline_last_stage()
+        pp = ps.get_pp_group() if pp_world > 1 else None
+        patch_latents = self._init_async_pipeline(len(steps), latents, rt.runtime_config.warmup_steps)
+        n_patch = rt.num_pipeline_patch
+        last_patch_latents = [None] * n_patch if last else None
+        last_encoder_hidden_states = None
+        first_async_recv = True
+        for k, i in enumerate(steps):
+            for p in range(n_patch):
+                if last:
+                    last_patch_latents[p] = patch_latents[p]
+                if pp_world == 1 or (first and k == 0):
+                    pass
+                else:
+                    if first_async_recv:
+                        if not first and p == 0:
+                            pp.recv_next()
+                        pp.recv_next()
+                        first_async_recv = False
+                    if not first and p == 0:
+                        # private copy: the text stream serves every patch of this step, while the
+                        # sender may refill the inbox slot as soon as patch 0 has gone round the ring
+                        last_encoder_hidden_states = pp.get_pipeline_recv_data(
+                            idx=p, name="encoder_hidden_states").clone()
+                    patch_latents[p] = pp.get_pipeline_recv_data(idx=p)
+                patch_latents[p], next_encoder_hidden_states = self._backbone_forward(
+                    patch_latents[p], prompt_embeds if first else last_encoder_hidden_states, pooled,
+                    self.sigmas[i:i + 1])
+                if last:
+                    patch_latents[p] = self._scheduler_step(patch_latents[p], last_patch_latents[p], i)
+                    if pp_world > 1 and k != len(steps) - 1:
+                        pp.pipeline_isend(patch_latents[p], segment_idx=p)
+                elif pp_world > 1:
+                    if p == 0:
+                        pp.pipeline_isend(next_encoder_hidden_states, name="encoder_hidden_states")
+                    pp.pipeline_isend(patch_latents[p], segment_idx=p)
+                if pp_world == 1 or (first and k == 0):
+                    pass
+                elif k == len(steps) - 1 and p == n_patch - 1:
+                    pass
+                elif first:
+                    pp.recv_next()
+                else:
+                    if p == n_patch - 1:
+                        pp.recv_next()
+                    pp.recv_next()
+                rt.next_patch()
+        return torch.cat(patch_latents, dim=1) if last else None
+
+    # ------------------------------------------------------------------ entry point
+    @torch.no_grad()
+    def diffusion_stage(self, latents, prompt_embeds, pooled, num_inference_steps: int):
+        """latents (1, S, 64); prompt_embeds (2, S_txt, text_dim) = [negative, positive]; pooled (2, pooled_dim).
+        Returns the denoised latents on the last pipeline stage (None elsewhere)."""
+        rt = get_runtime_state()
+        self.sigmas = flow_match_sigmas(num_inference_steps, device=latents.device)
+        self.encoder_hidden_states_cache = {}
+        warmup = min(rt.runtime_config.warmup_steps, num_inference_steps)
+        steps = list(range(num_inference_steps))
+        patched = rt.num_pipeline_patch > 1 and num_inference_steps > warmup
+        if patched:
+            latents = self._sync_pipeline(latents, prompt_embeds, pooled, steps[:warmup])
+            latents = self._async_pipeline(latents, prompt_embeds, pooled, steps[warmup:])
+        else:
+            latents = self._sync_pipeline(latents, prompt_embeds, pooled, steps, sync_only=True)
+            if not ps.is_pipeline_last_stage():
+                latents = None
+        rt.set_patched_mode(False)
+        return latents

@@ -1,0 +1,89 @@
+"""CPU oracle: PipeFusion denoising of the SD3-shaped model (warm-up steps, then the patch pipeline
+with stale K/V), fp32, one process.
+
+TEST INFRASTRUCTURE ONLY. Nothing under hetu_dit_b200/ may import this module.
+
+Restates the schedule of the reference's SD3 pipeline
+(hetu_dit/model_executor/pipelines/pipeline_stable_diffusion_3.py: _sync_pipeline :1352-1467,
+_async_pipeline :1515-1678, _backbone_forward with classifier-free guidance :1680-1717) and of its
+transformer wrapper (models/transformers/transformer_sd3.py:95-198: positional embedding only on
+the first stage, the text stream of a step computed with patch 0 and re-used by the other patches
+:131-146). A layer's stale-KV buffer is touched only by the stage that owns the layer and patches
+visit stages in order, so running (step, patch, layer) in sequence on one process produces exactly
+the values the pipelined execution does, for any number of stages.
+"""
+import torch
+import torch.nn.functional as F
+
+from . import shaped_dit as osd
+
+
+def flow_match_sigmas(num_steps, shift=3.0):
+    """Sigma schedule of a flow-matching Euler scheduler: shifted linear from 1 to 0 (num_steps + 1 values)."""
+    s = torch.linspace(1.0, 1.0 / num_steps, num_steps, dtype=torch.float64)
+    s = shift * s / (1 + (shift - 1) * s)
+    return torch.cat([s, torch.zeros(1, dtype=torch.float64)]).float()
+
+
+def denoise(sd, shape, latents, prompt_embeds, pooled, num_steps, guidance_scale, num_patch_tokens, warmup_steps, grid):
+    """latents (1, S, token_in); prompt_embeds (2, S_txt, text_dim) = [uncond, cond]; pooled (2, pooled_dim).
+    num_patch_tokens: tokens per pipeline patch (pp_patches_token_num). Returns the final latents, fp32."""
+    sd = {k: v.float() for k, v in sd.items()}
+    H, D, d = shape.heads, shape.head_dim, shape.hidden
+    sig = flow_match_sigmas(num_steps)
+    x = latents.float()
+    S = x.shape[1]
+    pos = osd.sincos_pos(grid[0], grid[1], d)
+    n_layers = shape.n_double
+    kv = [None] * n_layers            # per layer stale (K, V) of the image tokens, (2, S, H, D)
+    text_cache = [None] * n_layers    # per layer text stream input of the current step
+    starts = [0]
+    for n in num_patch_tokens:
+        starts.append(starts[-1] + n)
+
+    def temb_of(i):
+        t = sig[i].expand(2)
+        return osd._mlp_embed(sd, "time_embed", osd._timestep_embedding(t * 1000.0)) + osd._mlp_embed(
+            sd, "pooled_embed", pooled.float())
+
+    def backbone(tokens, i, patch):
+        """tokens (1, n, token_in) -> guided noise prediction (1, n, token_in)."""
+        temb = temb_of(i)
+        lo = 0 if patch is None else starts[patch]
+        n = tokens.shape[1]
+        hidden = osd._lin(sd, "x_embedder", torch.cat([tokens, tokens])) + pos[:, lo:lo + n]
+        context = osd._lin(sd, "context_embedder", prompt_embeds.float())
+        for l in range(n_layers):
+            def hook(k, v, l=l):
+                if patch is None:
+                    kv[l] = (k.clone(), v.clone())
+                else:
+                    kv[l][0][:, lo:lo + n] = k
+                    kv[l][1][:, lo:lo + n] = v
+                return kv[l]
+            if patch is None:
+                hidden, context = osd.joint_block(sd, f"transformer_blocks.{l}", hidden, context, temb, None, H, D,
+                                                  "rear", kv_hook=hook)
+            elif patch == 0:
+                text_cache[l] = context
+                hidden, context = osd.joint_block(sd, f"transformer_blocks.{l}", hidden, context, temb, None, H, D,
+                                                  "rear", kv_hook=hook)
+            else:
+                hidden, _ = osd.joint_block(sd, f"transformer_blocks.{l}", hidden, text_cache[l], temb, None, H, D,
+                                            "rear", kv_hook=hook)
+        shift, scale = osd._lin(sd, "norm_out.linear", F.silu(temb)).chunk(2, dim=-1)
+        out = osd._lin(sd, "proj_out", osd._mod(F.layer_norm(hidden, (d,), eps=1e-6), shift, scale))
+        uncond, cond = out.chunk(2)
+        return uncond + guidance_scale * (cond - uncond)
+
+    for i in range(num_steps):
+        dt = sig[i + 1] - sig[i]
+        if i < warmup_steps or len(num_patch_tokens) == 1:
+            x = x + dt * backbone(x, i, None)
+        else:
+            new = []
+            for p in range(len(num_patch_tokens)):
+                xp = x[:, starts[p]:starts[p + 1]]
+                new.append(xp + dt * backbone(xp, i, p))
+            x = torch.cat(new, dim=1)
+    return x

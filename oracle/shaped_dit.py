@@ -60,7 +60,9 @@ def _qk(sd, prefix, x, H, D, norm_name, rope, row0, eps=1e-6):
     return y
 
 
-def joint_block(sd, p, hidden, context, temb, rope, H, D, order):
+def joint_block(sd, p, hidden, context, temb, rope, H, D, order, kv_hook=None, row0=None):
+    """kv_hook(k_img, v_img) -> (k_all, v_all): PipeFusion's stale-KV cache for the image tokens
+    (attention_processor.py:702-707); row0: rotary table row of the first image token."""
     d = hidden.shape[-1]
     mod = _lin(sd, p + ".norm1.linear", F.silu(temb)).chunk(6, dim=-1)
     cmod = _lin(sd, p + ".norm1_context.linear", F.silu(temb)).chunk(6, dim=-1)
@@ -68,9 +70,12 @@ def joint_block(sd, p, hidden, context, temb, rope, H, D, order):
     c = _mod(F.layer_norm(context, (d,), eps=1e-6), cmod[0], cmod[1])
     a = p + ".attn.module"
     S_txt, S_img = c.shape[1], h.shape[1]
-    q = _qk(sd, a, _lin(sd, a + ".to_q", h), H, D, "norm_q", rope, S_txt)
-    k = _qk(sd, a, _lin(sd, a + ".to_k", h), H, D, "norm_k", rope, S_txt)
+    r0 = S_txt if row0 is None else row0
+    q = _qk(sd, a, _lin(sd, a + ".to_q", h), H, D, "norm_q", rope, r0)
+    k = _qk(sd, a, _lin(sd, a + ".to_k", h), H, D, "norm_k", rope, r0)
     v = _heads(_lin(sd, a + ".to_v", h), H, D)
+    if kv_hook is not None:
+        k, v = kv_hook(k, v)
     tq = _qk(sd, a, _lin(sd, a + ".add_q_proj", c), H, D, "norm_added_q", rope, 0)
     tk = _qk(sd, a, _lin(sd, a + ".add_k_proj", c), H, D, "norm_added_k", rope, 0)
     tv = _heads(_lin(sd, a + ".add_v_proj", c), H, D)
