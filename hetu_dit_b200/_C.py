@@ -140,6 +140,11 @@ def _declare(lib):
         ctypes.c_void_p]
     lib.hdit_qk_norm_rope.restype = ctypes.c_int
     lib.hdit_qk_norm_rope.argtypes = [ctypes.POINTER(NormRopeArgs)]
+    lib.hdit_ln_modulate.restype = ctypes.c_int
+    lib.hdit_ln_modulate.argtypes = [ctypes.c_int32] + [ctypes.c_void_p] * 4 + [ctypes.c_int64] * 6 + [
+        ctypes.c_float, ctypes.c_void_p]
+    lib.hdit_gate_residual.restype = ctypes.c_int
+    lib.hdit_gate_residual.argtypes = [ctypes.c_int32] + [ctypes.c_void_p] * 4 + [ctypes.c_int64] * 7 + [ctypes.c_void_p]
     lib.hdit_heap_alloc.restype = ctypes.c_int
     lib.hdit_heap_alloc.argtypes = [ctypes.c_int64, ctypes.POINTER(ctypes.c_void_p)]
     lib.hdit_heap_free.restype = ctypes.c_int

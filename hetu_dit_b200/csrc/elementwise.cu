@@ -1,0 +1,205 @@
+// adaLN-Zero glue of the DiT blocks as two HBM-bound kernels:
+//   ln_modulate  : out = LayerNorm(x) * (1 + scale[b]) + shift[b]      (no affine, biased variance)
+//   gate_residual: out = x + gate[b] * y
+// Each replaces a chain of eager kernels (layer_norm, mul, add, add / mul, add) that re-reads and
+// re-writes the (B, S, Dm) activation once per link; here every element is read once and written once,
+// with fp32 arithmetic in between. One CTA normalises one token row held in registers (16-byte loads,
+// consecutive threads on consecutive 16-byte chunks).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "host_common.h"
+
+namespace hdit {
+namespace {
+
+constexpr int kLnThreads = 256;
+constexpr int kMaxChunks = 4;  // 8-element chunks per thread -> rows of up to 8192 elements
+
+template <bool FP16>
+__device__ __forceinline__ float ew_to_f(uint16_t v) {
+  if constexpr (FP16) return __half2float(__ushort_as_half(v));
+  else return __bfloat162float(__ushort_as_bfloat16(v));
+}
+template <bool FP16>
+__device__ __forceinline__ uint16_t ew_from_f(float f) {
+  if constexpr (FP16) return __half_as_ushort(__float2half_rn(f));
+  else return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < kLnThreads / 32) ? red[lane] : 0.f;
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return __shfl_sync(0xffffffffu, t, 0);
+}
+
+template <bool FP16>
+__global__ void __launch_bounds__(kLnThreads) ln_modulate_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ shift,
+                                                                const uint16_t* __restrict__ scale, uint16_t* __restrict__ out,
+                                                                long long rows, int dim, long long rows_per_batch,
+                                                                long long x_row_stride, long long out_row_stride,
+                                                                long long mod_batch_stride, float eps) {
+  __shared__ float red[kLnThreads / 32];
+  const int n_chunks = dim / 8;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const long long b = row / rows_per_batch;
+    const uint16_t* xr = x + row * x_row_stride;
+    float v[kMaxChunks][8];
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c) {
+      const int chunk = threadIdx.x + c * kLnThreads;
+      if (chunk < n_chunks) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(xr + chunk * 8);
+        const uint16_t* e = reinterpret_cast<const uint16_t*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          v[c][i] = ew_to_f<FP16>(e[i]);
+          s += v[c][i];
+        }
+      }
+    }
+    const float mean = block_sum(s, red) / dim;
+    float q = 0.f;
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c) {
+      const int chunk = threadIdx.x + c * kLnThreads;
+      if (chunk < n_chunks) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float d = v[c][i] - mean;
+          q = fmaf(d, d, q);
+        }
+      }
+    }
+    const float rstd = rsqrtf(block_sum(q, red) / dim + eps);
+    uint16_t* orow = out + row * out_row_stride;
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c) {
+      const int chunk = threadIdx.x + c * kLnThreads;
+      if (chunk < n_chunks) {
+        const uint4 sh = *reinterpret_cast<const uint4*>(shift + b * mod_batch_stride + chunk * 8);
+        const uint4 sc = *reinterpret_cast<const uint4*>(scale + b * mod_batch_stride + chunk * 8);
+        const uint16_t* she = reinterpret_cast<const uint16_t*>(&sh);
+        const uint16_t* sce = reinterpret_cast<const uint16_t*>(&sc);
+        uint4 o;
+        uint16_t* oe = reinterpret_cast<uint16_t*>(&o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          oe[i] = ew_from_f<FP16>(fmaf((v[c][i] - mean) * rstd, 1.0f + ew_to_f<FP16>(sce[i]), ew_to_f<FP16>(she[i])));
+        *reinterpret_cast<uint4*>(orow + chunk * 8) = o;
+      }
+    }
+  }
+}
+
+template <bool FP16>
+__global__ void __launch_bounds__(256) gate_residual_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate,
+                                                           const uint16_t* __restrict__ y, uint16_t* __restrict__ out,
+                                                           long long rows, int dim, long long rows_per_batch,
+                                                           long long x_row_stride, long long y_row_stride,
+                                                           long long out_row_stride, long long gate_batch_stride) {
+  const int chunks_per_row = dim / 8;
+  const long long total = rows * chunks_per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    // 32-bit division when the index fits (the host caps rows * dim / 8 there for the common shapes)
+    const long long row = (total <= 0xffffffffLL) ? static_cast<long long>(static_cast<unsigned>(i) / static_cast<unsigned>(chunks_per_row))
+                                                  : i / chunks_per_row;
+    const int chunk = static_cast<int>(i - row * chunks_per_row);
+    const long long b = (rows <= 0xffffffffLL && rows_per_batch <= 0xffffffffLL)
+                            ? static_cast<long long>(static_cast<unsigned>(row) / static_cast<unsigned>(rows_per_batch))
+                            : row / rows_per_batch;
+    const uint4 xv = *reinterpret_cast<const uint4*>(x + row * x_row_stride + chunk * 8);
+    const uint4 yv = *reinterpret_cast<const uint4*>(y + row * y_row_stride + chunk * 8);
+    const uint4 gv = *reinterpret_cast<const uint4*>(gate + b * gate_batch_stride + chunk * 8);
+    const uint16_t* xe = reinterpret_cast<const uint16_t*>(&xv);
+    const uint16_t* ye = reinterpret_cast<const uint16_t*>(&yv);
+    const uint16_t* ge = reinterpret_cast<const uint16_t*>(&gv);
+    uint4 o;
+    uint16_t* oe = reinterpret_cast<uint16_t*>(&o);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      oe[k] = ew_from_f<FP16>(fmaf(ew_to_f<FP16>(ge[k]), ew_to_f<FP16>(ye[k]), ew_to_f<FP16>(xe[k])));
+    *reinterpret_cast<uint4*>(out + row * out_row_stride + chunk * 8) = o;
+  }
+}
+
+int check_common(int dtype, int64_t rows, int64_t dim, int64_t rows_per_batch) {
+  if (dtype != HDIT_BF16 && dtype != HDIT_FP16) return set_error(HDIT_ERR_BAD_ARG, "dtype must be bf16 or fp16");
+  if (rows < 0 || dim <= 0 || rows_per_batch <= 0) return set_error(HDIT_ERR_BAD_ARG, "bad sizes");
+  if (dim % 8 != 0 || dim > 8 * kLnThreads * kMaxChunks)
+    return set_error(HDIT_ERR_SHAPE, "row length must be a multiple of 8 and at most %d", 8 * kLnThreads * kMaxChunks);
+  return HDIT_OK;
+}
+
+bool misaligned(const void* p, int64_t stride) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0 || stride % 8 != 0; }
+
+}  // namespace
+}  // namespace hdit
+
+extern "C" int hdit_ln_modulate(int32_t dtype, const void* x, const void* shift, const void* scale, void* out,
+                                int64_t rows, int64_t dim, int64_t rows_per_batch, int64_t x_row_stride,
+                                int64_t out_row_stride, int64_t mod_batch_stride, float eps, void* stream) {
+  using namespace hdit;
+  const int rc = check_common(dtype, rows, dim, rows_per_batch);
+  if (rc != HDIT_OK) return rc;
+  if (rows == 0) return HDIT_OK;
+  if (x == nullptr || shift == nullptr || scale == nullptr || out == nullptr) return set_error(HDIT_ERR_BAD_ARG, "null pointer");
+  if (misaligned(x, x_row_stride) || misaligned(out, out_row_stride) || misaligned(shift, mod_batch_stride) ||
+      misaligned(scale, mod_batch_stride))
+    return set_error(HDIT_ERR_SHAPE, "pointers must be 16-byte aligned and strides multiples of 8 elements");
+  const unsigned grid = static_cast<unsigned>(rows < 148LL * 16 ? rows : 148LL * 16);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  auto xp = static_cast<const uint16_t*>(x);
+  auto sh = static_cast<const uint16_t*>(shift);
+  auto sc = static_cast<const uint16_t*>(scale);
+  auto op = static_cast<uint16_t*>(out);
+  if (dtype == HDIT_FP16)
+    ln_modulate_kernel<true><<<grid, kLnThreads, 0, st>>>(xp, sh, sc, op, rows, static_cast<int>(dim), rows_per_batch,
+                                                          x_row_stride, out_row_stride, mod_batch_stride, eps);
+  else
+    ln_modulate_kernel<false><<<grid, kLnThreads, 0, st>>>(xp, sh, sc, op, rows, static_cast<int>(dim), rows_per_batch,
+                                                           x_row_stride, out_row_stride, mod_batch_stride, eps);
+  HDIT_CUDA_OK(cudaGetLastError());
+  return HDIT_OK;
+}
+
+extern "C" int hdit_gate_residual(int32_t dtype, const void* x, const void* gate, const void* y, void* out, int64_t rows,
+                                  int64_t dim, int64_t rows_per_batch, int64_t x_row_stride, int64_t y_row_stride,
+                                  int64_t out_row_stride, int64_t gate_batch_stride, void* stream) {
+  using namespace hdit;
+  const int rc = check_common(dtype, rows, dim, rows_per_batch);
+  if (rc != HDIT_OK) return rc;
+  if (rows == 0) return HDIT_OK;
+  if (x == nullptr || gate == nullptr || y == nullptr || out == nullptr) return set_error(HDIT_ERR_BAD_ARG, "null pointer");
+  if (misaligned(x, x_row_stride) || misaligned(y, y_row_stride) || misaligned(out, out_row_stride) ||
+      misaligned(gate, gate_batch_stride))
+    return set_error(HDIT_ERR_SHAPE, "pointers must be 16-byte aligned and strides multiples of 8 elements");
+  const long long total = rows * (dim / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  auto xp = static_cast<const uint16_t*>(x);
+  auto gp = static_cast<const uint16_t*>(gate);
+  auto yp = static_cast<const uint16_t*>(y);
+  auto op = static_cast<uint16_t*>(out);
+  if (dtype == HDIT_FP16)
+    gate_residual_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        xp, gp, yp, op, rows, static_cast<int>(dim), rows_per_batch, x_row_stride, y_row_stride, out_row_stride,
+        gate_batch_stride);
+  else
+    gate_residual_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        xp, gp, yp, op, rows, static_cast<int>(dim), rows_per_batch, x_row_stride, y_row_stride, out_row_stride,
+        gate_batch_stride);
+  HDIT_CUDA_OK(cudaGetLastError());
+  return HDIT_OK;
+}

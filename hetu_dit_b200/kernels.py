@@ -268,3 +268,42 @@ def qk_norm_rope(tensors, *, eps=1e-6, cos=None, sin=None, rope_seq_start=0, rop
     with torch.cuda.device(x0.device):
         _C.check(_C.lib().hdit_qk_norm_rope(ctypes.byref(a)))
     _count()
+
+
+def _rows_view(x):
+    """(B, S, Dm) tensor -> (rows, dim, rows_per_batch, row_stride); rows must be evenly strided."""
+    B, S, Dm = x.shape
+    if x.stride(2) != 1 or (B > 1 and x.stride(0) != S * x.stride(1)):
+        raise ValueError("expected a (B, S, Dm) tensor with contiguous last dim and evenly strided rows")
+    return B * S, Dm, S, x.stride(1)
+
+
+def ln_modulate(x, shift, scale, eps=1e-6, out=None):
+    """LayerNorm(x) * (1 + scale[:, None]) + shift[:, None] for x (B, S, Dm), shift / scale (B, Dm) views."""
+    rows, dim, rpb, xs = _rows_view(x)
+    if out is None:
+        out = torch.empty((x.shape[0], x.shape[1], dim), dtype=x.dtype, device=x.device)
+    if shift.stride(-1) != 1 or scale.stride(-1) != 1 or shift.stride(0) != scale.stride(0):
+        raise ValueError("shift / scale must be (B, Dm) views with contiguous last dim and equal batch stride")
+    with torch.cuda.device(x.device):
+        _C.check(_C.lib().hdit_ln_modulate(_DTYPE_CODE[x.dtype], x.data_ptr(), shift.data_ptr(), scale.data_ptr(),
+                                           out.data_ptr(), rows, dim, rpb, xs, out.stride(1), shift.stride(0), eps,
+                                           _stream_ptr(x.device)))
+    _count()
+    return out
+
+
+def gate_residual(x, gate, y, out=None):
+    """x + gate[:, None] * y for x, y (B, S, Dm) and gate a (B, Dm) view."""
+    rows, dim, rpb, xs = _rows_view(x)
+    rows_y, dim_y, _, ys = _rows_view(y)
+    if (rows_y, dim_y) != (rows, dim):
+        raise ValueError("x and y differ in shape")
+    if out is None:
+        out = torch.empty((x.shape[0], x.shape[1], dim), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _C.check(_C.lib().hdit_gate_residual(_DTYPE_CODE[x.dtype], x.data_ptr(), gate.data_ptr(), y.data_ptr(),
+                                             out.data_ptr(), rows, dim, rpb, xs, ys, out.stride(1), gate.stride(0),
+                                             _stream_ptr(x.device)))
+    _count()
+    return out

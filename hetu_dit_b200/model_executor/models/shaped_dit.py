@@ -22,6 +22,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ... import kernels
 from ..layers.attention_processor import JointAttnProcessor, SingleAttnProcessor
 
 
@@ -153,15 +154,14 @@ class JointBlock(nn.Module):
         d = self.d
         mod = self.norm1.linear(F.silu(temb)).chunk(6, dim=-1)
         cmod = self.norm1_context.linear(F.silu(temb)).chunk(6, dim=-1)
-        h = _modulate(F.layer_norm(hidden, (d,), eps=1e-6), mod[0], mod[1])
-        c = _modulate(F.layer_norm(context, (d,), eps=1e-6), cmod[0], cmod[1])
+        # LayerNorm + modulation and gate + residual are one fused pass each (csrc/elementwise.cu)
+        h = kernels.ln_modulate(hidden, mod[0], mod[1])
+        c = kernels.ln_modulate(context, cmod[0], cmod[1])
         a_img, a_txt = self.attn(h, encoder_hidden_states=c, image_rotary_emb=rope, token_offset=token_offset)
-        hidden = hidden + mod[2][:, None] * a_img
-        h = _modulate(F.layer_norm(hidden, (d,), eps=1e-6), mod[3], mod[4])
-        hidden = hidden + mod[5][:, None] * self.ff(h)
-        context = context + cmod[2][:, None] * a_txt
-        c = _modulate(F.layer_norm(context, (d,), eps=1e-6), cmod[3], cmod[4])
-        context = context + cmod[5][:, None] * self.ff_context(c)
+        hidden = kernels.gate_residual(hidden, mod[2], a_img)
+        hidden = kernels.gate_residual(hidden, mod[5], self.ff(kernels.ln_modulate(hidden, mod[3], mod[4])))
+        context = kernels.gate_residual(context, cmod[2], a_txt)
+        context = kernels.gate_residual(context, cmod[5], self.ff_context(kernels.ln_modulate(context, cmod[3], cmod[4])))
         return hidden, context
 
 
@@ -180,10 +180,10 @@ class SingleBlock(nn.Module):
 
     def forward(self, x, temb, rope, text_len, token_offset=0):
         shift, scale, gate = self.norm.linear(F.silu(temb)).chunk(3, dim=-1)
-        h = _modulate(F.layer_norm(x, (self.d,), eps=1e-6), shift, scale)
+        h = kernels.ln_modulate(x, shift, scale)
         mlp = F.gelu(self.proj_mlp(h), approximate="tanh")
         a = self.attn(h, image_rotary_emb=rope, text_len=text_len, token_offset=token_offset)
-        return x + gate[:, None] * self.proj_out(torch.cat([a, mlp], dim=-1))
+        return kernels.gate_residual(x, gate, self.proj_out(torch.cat([a, mlp], dim=-1)))
 
 
 def rope_tables(ids: torch.Tensor, axes, theta: float = 10000.0):
@@ -301,8 +301,7 @@ class ShapedDiT(nn.Module):
                 x = blk(x, temb, rope, S_txt, token_offset)
             hidden = x[:, S_txt:]
         shift, scale = self.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
-        hidden = _modulate(F.layer_norm(hidden, (shp.hidden,), eps=1e-6), shift, scale)
-        return self.proj_out(hidden)
+        return self.proj_out(kernels.ln_modulate(hidden.contiguous(), shift, scale))
 
     def flops_per_step(self, s_img: int, s_txt: int, batch: int = 1) -> float:
         """Algorithmic FLOPs of one step: 4*S^2*Dm attention + 2*12*Dm^2*S linear per block."""

@@ -289,6 +289,26 @@ HDIT_API int hdit_peer_wait(const int32_t* flag, int32_t value, int64_t max_spin
  */
 HDIT_API int hdit_attn_fwd_split_static(const hdit_attn_args* args, int32_t first_pass_kv_segs);
 
+/*
+ * adaLN-Zero glue around the attention and MLP sub-layers of a DiT block, one pass each.
+ *   hdit_ln_modulate  : out[r, :] = LayerNorm(x[r, :]) * (1 + scale[b, :]) + shift[b, :]
+ *   hdit_gate_residual: out[r, :] = x[r, :] + gate[b, :] * y[r, :]
+ * with b = r / rows_per_batch, LayerNorm without affine parameters (biased variance, `eps`), fp32
+ * arithmetic, 16-bit storage. Strides in elements; `dim` a multiple of 8, at most 8192.
+ *
+ * The reference inherits these steps from the diffusers block definitions it wraps (norm1 / norm1_context
+ * modulation and the gated residuals around hetuDiTAttentionWrapper.forward,
+ * hetu_dit/model_executor/diffusion_executor/layers/attention_processor.py:207-449, and
+ * hetuDiTFeedForwardWrapper.forward, layers/feedforward.py:73-78), where they run as chains of eager
+ * elementwise kernels.
+ */
+HDIT_API int hdit_ln_modulate(int32_t dtype, const void* x, const void* shift, const void* scale, void* out,
+                              int64_t rows, int64_t dim, int64_t rows_per_batch, int64_t x_row_stride,
+                              int64_t out_row_stride, int64_t mod_batch_stride, float eps, void* stream);
+HDIT_API int hdit_gate_residual(int32_t dtype, const void* x, const void* gate, const void* y, void* out,
+                                int64_t rows, int64_t dim, int64_t rows_per_batch, int64_t x_row_stride,
+                                int64_t y_row_stride, int64_t out_row_stride, int64_t gate_batch_stride, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -133,3 +133,25 @@ def test_norm_rope_head_scatter():
         got = dsts[u].cpu()
         assert torch.equal(got[:, S:2 * S], y[:, :, u * 2:(u + 1) * 2])
         assert got[:, :S].abs().sum() == 0 and got[:, 2 * S:].abs().sum() == 0
+
+
+@pytest.mark.parametrize("dim", [256, 1536, 3072])
+def test_ln_modulate_and_gate_residual(dim):
+    from hetu_dit_b200 import kernels
+    gen = torch.Generator().manual_seed(dim)
+    B, S = 2, 37
+    x = torch.randn(B, S, dim, generator=gen).bfloat16()
+    y = torch.randn(B, S, dim, generator=gen).bfloat16()
+    mod = (0.3 * torch.randn(B, 3 * dim, generator=gen)).bfloat16()
+    shift, scale, gate = mod.chunk(3, dim=-1)
+    xd, yd, md = x.to(DEV), y.to(DEV), mod.to(DEV)
+    sh, sc, ga = md.chunk(3, dim=-1)
+    got = kernels.ln_modulate(xd, sh, sc)
+    want = torch.nn.functional.layer_norm(x.float(), (dim,), eps=1e-6) * (1 + scale.float()[:, None]) + shift.float()[:, None]
+    assert (got.cpu().float() - want).abs().max().item() <= 2 ** -7 * want.abs().max().item()
+    got = kernels.gate_residual(xd, ga, yd)
+    want = x.float() + gate.float()[:, None] * y.float()
+    assert torch.equal(got.cpu(), want.bfloat16())
+    # strided rows (a slice of a longer sequence) work too
+    got = kernels.gate_residual(xd[:, 5:20], ga, yd[:, 5:20])
+    assert torch.equal(got.cpu(), want[:, 5:20].bfloat16())
