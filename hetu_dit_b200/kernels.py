@@ -270,19 +270,27 @@ def qk_norm_rope(tensors, *, eps=1e-6, cos=None, sin=None, rope_seq_start=0, rop
     _count()
 
 
+def _even_rows(x):
+    return x.stride(2) == 1 and (x.shape[0] == 1 or x.stride(0) == x.shape[1] * x.stride(1))
+
+
 def _rows_view(x):
     """(B, S, Dm) tensor -> (rows, dim, rows_per_batch, row_stride); rows must be evenly strided."""
     B, S, Dm = x.shape
-    if x.stride(2) != 1 or (B > 1 and x.stride(0) != S * x.stride(1)):
+    if not _even_rows(x):
         raise ValueError("expected a (B, S, Dm) tensor with contiguous last dim and evenly strided rows")
     return B * S, Dm, S, x.stride(1)
 
 
 def ln_modulate(x, shift, scale, eps=1e-6, out=None):
     """LayerNorm(x) * (1 + scale[:, None]) + shift[:, None] for x (B, S, Dm), shift / scale (B, Dm) views."""
-    rows, dim, rpb, xs = _rows_view(x)
     if out is None:
-        out = torch.empty((x.shape[0], x.shape[1], dim), dtype=x.dtype, device=x.device)
+        out = torch.empty(tuple(x.shape), dtype=x.dtype, device=x.device)
+    if x.shape[0] > 1 and not _even_rows(x):  # e.g. a token slice of a batch: one launch per batch element
+        for b in range(x.shape[0]):
+            ln_modulate(x[b:b + 1], shift[b:b + 1], scale[b:b + 1], eps, out[b:b + 1])
+        return out
+    rows, dim, rpb, xs = _rows_view(x)
     if shift.stride(-1) != 1 or scale.stride(-1) != 1 or shift.stride(0) != scale.stride(0):
         raise ValueError("shift / scale must be (B, Dm) views with contiguous last dim and equal batch stride")
     with torch.cuda.device(x.device):
@@ -295,12 +303,16 @@ def ln_modulate(x, shift, scale, eps=1e-6, out=None):
 
 def gate_residual(x, gate, y, out=None):
     """x + gate[:, None] * y for x, y (B, S, Dm) and gate a (B, Dm) view."""
-    rows, dim, rpb, xs = _rows_view(x)
-    rows_y, dim_y, _, ys = _rows_view(y)
-    if (rows_y, dim_y) != (rows, dim):
+    if x.shape != y.shape:
         raise ValueError("x and y differ in shape")
     if out is None:
-        out = torch.empty((x.shape[0], x.shape[1], dim), dtype=x.dtype, device=x.device)
+        out = torch.empty(tuple(x.shape), dtype=x.dtype, device=x.device)
+    if x.shape[0] > 1 and not (_even_rows(x) and _even_rows(y)):
+        for b in range(x.shape[0]):
+            gate_residual(x[b:b + 1], gate[b:b + 1], y[b:b + 1], out[b:b + 1])
+        return out
+    rows, dim, rpb, xs = _rows_view(x)
+    _, _, _, ys = _rows_view(y)
     with torch.cuda.device(x.device):
         _C.check(_C.lib().hdit_gate_residual(_DTYPE_CODE[x.dtype], x.data_ptr(), gate.data_ptr(), y.data_ptr(),
                                              out.data_ptr(), rows, dim, rpb, xs, ys, out.stride(1), gate.stride(0),
