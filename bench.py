@@ -262,9 +262,8 @@ def run_gpu(args):
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = out_host.numel() * out_host.element_size()
     # dominant kernel of this repo: the attention kernel (one launch per block, 57 per step)
-    s_q = S_TXT + s_loc if world > 1 else tokens
     heads_loc = shape.heads // world
-    s_q_gathered = s_q * world if world > 1 else tokens
+    s_q_gathered = tokens  # replicated text queries are attended once per head slice, not once per rank
     attn_flops = 4.0 * s_q_gathered * tokens * heads_loc * shape.head_dim
     achieved = attn_flops / (attn_ms["mean_ms"] * 1e-3) / 1e12 if attn_ms["mean_ms"] else None
     # DRAM bytes of one launch at this shape, from the committed ncu summary (single-GPU shape only)

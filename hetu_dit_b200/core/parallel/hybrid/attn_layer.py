@@ -58,19 +58,33 @@ class _UlyssesExchange:
         g.barrier()
         return outs
 
-    def scatter_sequence(self, ctx: Tensor, tag: str) -> Tensor:
-        """SeqAllToAll4D(scatter_idx=1, gather_idx=2): (B, U*S_loc, H/U, D) -> (B, S_loc, H, D)."""
+    def scatter_sequence(self, ctx: Tensor, tag: str, joint_len: int = 0, joint_front: bool = True) -> Tensor:
+        """SeqAllToAll4D(scatter_idx=1, gather_idx=2): (B, U*S_loc, H/U, D) -> (B, S_loc, H, D).
+
+        With joint_len > 0 the context also carries `joint_len` rows of the replicated joint (text)
+        queries, computed once per head slice: those rows go to *every* peer, the image rows of source
+        rank p go to p. The result is (B, joint_len + S_loc, H, D) in [joint; local] ("front") or
+        [local; joint] order."""
         g, U, me = self.group, self.group.world_size, self.group.rank_in_group
         B, S_tot, Hl, D = ctx.shape
-        S = S_tot // U
-        out, off = self.heap.alloc((B, S, Hl * U, D), ctx.dtype, name=f"usp_{tag}_{(B, S, Hl * U, D)}_{ctx.dtype}")
+        S = (S_tot - joint_len) // U
+        rows = S + joint_len
+        out, off = self.heap.alloc((B, rows, Hl * U, D), ctx.dtype, name=f"usp_{tag}_{(B, rows, Hl * U, D)}_{ctx.dtype}")
         es = ctx.element_size()
+        img0_src = joint_len if joint_front else 0      # first image row in ctx
+        img0_dst = joint_len if joint_front else 0      # first image row in out
+        jnt_src = 0 if joint_front else U * S
+        jnt_dst = 0 if joint_front else S
         pieces = []
         for p, r in enumerate(g.ranks):
-            src = ctx[:, p * S:(p + 1) * S]
-            dst = self.heap.peer_ptr(r, off) + me * Hl * D * es
-            pieces.append((src.data_ptr(), dst, B, ctx.stride(0) * es, out.stride(0) * es, S, ctx.stride(1) * es,
-                           out.stride(1) * es, Hl * D * es))
+            base = self.heap.peer_ptr(r, off) + me * Hl * D * es
+            src = ctx[:, img0_src + p * S:img0_src + (p + 1) * S]
+            pieces.append((src.data_ptr(), base + img0_dst * out.stride(1) * es, B, ctx.stride(0) * es,
+                           out.stride(0) * es, S, ctx.stride(1) * es, out.stride(1) * es, Hl * D * es))
+            if joint_len:
+                jsrc = ctx[:, jnt_src:jnt_src + joint_len]
+                pieces.append((jsrc.data_ptr(), base + jnt_dst * out.stride(1) * es, B, ctx.stride(0) * es,
+                               out.stride(0) * es, joint_len, ctx.stride(1) * es, out.stride(1) * es, Hl * D * es))
         kernels.copy_pieces(pieces, ctx.device)
         g.barrier()
         # Hand back a private copy: the heap buffer is overwritten by the next layer's exchange.
@@ -106,7 +120,10 @@ class hetuDiTLongContextAttention(torch.nn.Module):
         self.ulysses_pg = ps.PROCESS_GROUP.ULYSSES_PG
 
     def _run(self, attn, query, key, value, joint_k, joint_v, joint_strategy, dropout_p, softmax_scale, causal,
-             window_size, alibi_slopes, deterministic, return_attn_probs):
+             window_size, alibi_slopes, deterministic, return_attn_probs, joint_q=None):
+        """joint_q stays its own query segment. The reference concatenates it into every rank's query before
+        the all-to-all, so each Ulysses rank attends U identical copies of the text queries; here the
+        replicated rows are attended once per head slice and their context rows are sent to all peers."""
         U = 1 if self.ulysses_pg is None else self.ulysses_pg.world_size
         if U > 1:
             r = self.ulysses_pg.rank_in_group
@@ -114,16 +131,19 @@ class hetuDiTLongContextAttention(torch.nn.Module):
                 hpr = joint_k.shape[-2] // U
                 joint_k = joint_k[..., hpr * r:hpr * (r + 1), :]
                 joint_v = joint_v[..., hpr * r:hpr * (r + 1), :]
+                if joint_q is not None:
+                    joint_q = joint_q[..., hpr * r:hpr * (r + 1), :]
             xchg = _UlyssesExchange(self.ulysses_pg)
             query, key, value = xchg.gather_heads([query, key, value], ["q", "k", "v"])
         out = self.ring_attn_fn(query, key, value, dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal,
                                 window_size=window_size, alibi_slopes=alibi_slopes, deterministic=deterministic,
                                 return_attn_probs=return_attn_probs, group=self.ring_pg,
                                 attn_layer=attn if self.use_kv_cache else None, joint_tensor_key=joint_k,
-                                joint_tensor_value=joint_v, joint_strategy=joint_strategy)
+                                joint_tensor_value=joint_v, joint_strategy=joint_strategy, joint_tensor_query=joint_q)
         context = out[0] if isinstance(out, tuple) else out
         if U > 1:
-            context = xchg.scatter_sequence(context, "o")
+            context = xchg.scatter_sequence(context, "o", joint_len=0 if joint_q is None else joint_q.shape[1],
+                                            joint_front=joint_strategy == "front")
         return context
 
     @torch.compiler.disable
@@ -149,12 +169,9 @@ class hetuDiTJointLongContextAttention(hetuDiTLongContextAttention):
                 f"joint_strategy: {joint_strategy} not supprted. supported joint strategy: {_SUPPORTED_JOINT}")
         elif joint_strategy != "none" and joint_tensor_query is None:
             raise ValueError("joint_tensor_query must not be None when joint_strategy is not None")
-        elif joint_strategy == "rear":
-            query = torch.cat([query, joint_tensor_query], dim=1)
-        elif joint_strategy == "front":
-            query = torch.cat([joint_tensor_query, query], dim=1)
         return self._run(attn, query, key, value, joint_tensor_key, joint_tensor_value, joint_strategy, dropout_p,
-                         softmax_scale, causal, window_size, alibi_slopes, deterministic, return_attn_probs)
+                         softmax_scale, causal, window_size, alibi_slopes, deterministic, return_attn_probs,
+                         joint_q=joint_tensor_query if joint_strategy != "none" else None)
 
 
 class hetuDiTFluxLongContextAttention(hetuDiTLongContextAttention):
@@ -164,9 +181,9 @@ class hetuDiTFluxLongContextAttention(hetuDiTLongContextAttention):
                 alibi_slopes=None, deterministic=False, return_attn_probs=False, joint_strategy="front"):
         """Flux: text tokens always lead (hybrid/attn_layer.py:327)."""
         self._bind_groups()
-        query = torch.cat([joint_tensor_query, query], dim=1)
         return self._run(attn, query, key, value, joint_tensor_key, joint_tensor_value, "front", dropout_p,
-                         softmax_scale, causal, window_size, alibi_slopes, deterministic, return_attn_probs)
+                         softmax_scale, causal, window_size, alibi_slopes, deterministic, return_attn_probs,
+                         joint_q=joint_tensor_query)
 
 
 # names used by the xDiT lineage of this operator

@@ -51,8 +51,12 @@ def _publish(heap, t: torch.Tensor, tag: str) -> torch.Tensor:
 def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                             softmax_scale, dropout_p=0, causal=True, window_size=(-1, -1), alibi_slopes=None,
                             deterministic=False, attn_layer=None, joint_tensor_key=None, joint_tensor_value=None,
-                            joint_strategy="none"):
-    """(out in q.dtype, lse (B, H, Sq) fp32) for this rank's queries against the whole ring's K/V."""
+                            joint_strategy="none", joint_tensor_query=None):
+    """(out in q.dtype, lse (B, H, Sq) fp32) for this rank's queries against the whole ring's K/V.
+
+    joint_tensor_query (not in the reference's signature): joint queries kept as their own segment
+    instead of being concatenated into `q` by the caller; output rows are [joint; q] for "front" and
+    [q; joint] for "rear", exactly as if they had been concatenated."""
     if joint_strategy not in _SUPPORTED_JOINT:
         raise ValueError(
             f"joint_strategy: {joint_strategy} not supprted. supported joint strategy: {_SUPPORTED_JOINT}")
@@ -67,13 +71,16 @@ def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor,
 
     world = 1 if process_group is None else process_group.world_size
     front = [joint_tensor_key], [joint_tensor_value]
+    q_segs = [q]
+    if joint_tensor_query is not None:
+        q_segs = [joint_tensor_query, q] if joint_strategy == "front" else [q, joint_tensor_query]
     if world == 1:
         ks, vs = [k], [v]
         if joint_strategy == "rear":
             ks, vs = [k, joint_tensor_key], [v, joint_tensor_value]
         elif joint_strategy == "front":
             ks, vs = [joint_tensor_key, k], [joint_tensor_value, v]
-        return kernels.attn_fwd([q], ks, vs, softmax_scale=softmax_scale, return_lse=True)
+        return kernels.attn_fwd(q_segs, ks, vs, softmax_scale=softmax_scale, return_lse=True)
 
     heap = process_group.heap
     if heap is None:
@@ -104,20 +111,21 @@ def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor,
         pulled = torch.cuda.Event()
         pulled.record(side)
 
-    sq = q.shape[1]
+    sq = sum(t.shape[1] for t in q_segs)
     acc = torch.empty((B, sq, H, D), dtype=torch.float32, device=dev)
     acc_lse = torch.empty((B, H, sq), dtype=torch.float32, device=dev)
     ks, vs = [k_pub], [v_pub]
     if joint_strategy == "front":
         ks, vs = front[0] + ks, front[1] + vs
-    kernels.attn_fwd([q], ks, vs, softmax_scale=softmax_scale, mode=_C.ATTN_PARTIAL_FIRST, acc_out=acc, acc_lse=acc_lse)
+    kernels.attn_fwd(q_segs, ks, vs, softmax_scale=softmax_scale, mode=_C.ATTN_PARTIAL_FIRST, acc_out=acc,
+                     acc_lse=acc_lse)
 
     torch.cuda.current_stream(dev).wait_event(pulled)
     ks = [stage[0, i] for i in range(world - 1)]
     vs = [stage[1, i] for i in range(world - 1)]
     if joint_strategy == "rear":
         ks, vs = ks + [joint_tensor_key], vs + [joint_tensor_value]
-    out, lse = kernels.attn_fwd([q], ks, vs, softmax_scale=softmax_scale, mode=_C.ATTN_MERGE_FINAL, acc_out=acc,
+    out, lse = kernels.attn_fwd(q_segs, ks, vs, softmax_scale=softmax_scale, mode=_C.ATTN_MERGE_FINAL, acc_out=acc,
                                 acc_lse=acc_lse, return_lse=True)
     process_group.barrier()  # peers have finished pulling this rank's block
     return out, lse
@@ -125,7 +133,7 @@ def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor,
 
 def ring_flash_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
                          alibi_slopes=None, deterministic=False, return_attn_probs=False, group=None, attn_layer=None,
-                         joint_tensor_key=None, joint_tensor_value=None, joint_strategy="none"):
+                         joint_tensor_key=None, joint_tensor_value=None, joint_strategy="none", joint_tensor_query=None):
     """Forward only (inference): returns out, or (out, lse, None) when return_attn_probs is set."""
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** (-0.5)
@@ -133,5 +141,6 @@ def ring_flash_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=Fals
     out, lse = ring_flash_attn_forward(group, q, k, v, softmax_scale=softmax_scale, dropout_p=dropout_p, causal=causal,
                                        window_size=window_size, alibi_slopes=alibi_slopes, deterministic=False,
                                        attn_layer=attn_layer, joint_tensor_key=joint_tensor_key,
-                                       joint_tensor_value=joint_tensor_value, joint_strategy=joint_strategy)
+                                       joint_tensor_value=joint_tensor_value, joint_strategy=joint_strategy,
+                                       joint_tensor_query=joint_tensor_query)
     return out if not return_attn_probs else (out, lse, None)
