@@ -157,7 +157,7 @@ def _declare(lib):
     lib.hdit_ipc_close.argtypes = [ctypes.c_void_p]
     lib.hdit_peer_barrier.restype = ctypes.c_int
     lib.hdit_peer_barrier.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
-                                      ctypes.c_int, ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p]
+                                      ctypes.c_int, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
     lib.hdit_peer_signal.restype = ctypes.c_int
     lib.hdit_peer_signal.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
     lib.hdit_peer_wait.restype = ctypes.c_int

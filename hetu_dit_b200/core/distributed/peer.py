@@ -19,6 +19,7 @@ FLAG_BYTES = 64 * 1024          # head of the heap: int32 counters
 MAX_RANKS_PER_NODE = 8
 _BARRIER_SLOTS = 256 * MAX_RANKS_PER_NODE  # one row of 8 counters per rank subset (bit mask of members)
 _P2P_BASE = _BARRIER_SLOTS      # then 8 x 8 x 16 point-to-point sequence counters
+_EPOCH_BASE = _P2P_BASE + 8 * 8 * 16  # then one barrier epoch counter per rank subset (device-side)
 DEFAULT_MAX_SPINS = 20_000_000  # about two seconds of polling
 
 
@@ -117,8 +118,9 @@ class PeerHeap:
         mask = 0
         for r in ranks:
             mask |= 1 << (r % MAX_RANKS_PER_NODE)
-        epoch = self._epochs.get(mask, 0) + 1
-        self._epochs[mask] = epoch
+        # the epoch lives in this rank's heap and is advanced by the barrier kernel itself, so the
+        # call can be captured in a CUDA graph and replayed
+        counter = self._flag_ptr(self.rank, _EPOCH_BASE + mask)
         peer_slots = (ctypes.c_void_p * n)()
         my_slots = (ctypes.c_void_p * n)()
         for i, r in enumerate(ranks):
@@ -128,7 +130,7 @@ class PeerHeap:
             my_slots[i] = self._flag_ptr(self.rank, mask * MAX_RANKS_PER_NODE + i)  # in my heap, written by r
         with torch.cuda.device(self.device):
             stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-            _C.check(_C.lib().hdit_peer_barrier(peer_slots, my_slots, n, me, epoch, max_spins, stream))
+            _C.check(_C.lib().hdit_peer_barrier(peer_slots, my_slots, n, me, 0, counter, max_spins, stream))
 
     def p2p_flag_index(self, src: int, dst: int, channel: int) -> int:
         return _P2P_BASE + ((src % 8) * 8 + (dst % 8)) * 16 + channel

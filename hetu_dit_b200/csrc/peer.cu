@@ -36,6 +36,7 @@ struct BarrierParams {
   int n;
   int me;
   int32_t epoch;
+  int32_t* epoch_counter;  // when set: the epoch is read from (and advanced in) device memory
   unsigned max_spins;
   int32_t* status;
 };
@@ -45,14 +46,24 @@ __global__ void peer_barrier_kernel(const __grid_constant__ BarrierParams p) {
   const int lane = threadIdx.x;
   __shared__ int abort_flag;
   if (lane == 0) abort_flag = 0;
+  // A counter in device memory keeps the barrier replayable from a CUDA graph: every execution
+  // advances the epoch by itself instead of carrying a value baked in at capture time.
+  int32_t epoch = p.epoch;
+  if (p.epoch_counter != nullptr) {
+    if (lane == 0) {
+      epoch = *p.epoch_counter + 1;
+      *p.epoch_counter = epoch;
+    }
+    epoch = __shfl_sync(0xffffffffu, epoch, 0);
+  }
   __syncwarp();
   if (lane < p.n && lane != p.me) {
     __threadfence_system();
-    st_release_sys(p.peer_slot[lane], p.epoch);
+    st_release_sys(p.peer_slot[lane], epoch);
     bool seen = false;
     for (unsigned i = 0; i < p.max_spins; ++i) {
       // counters only grow; ">=" also accepts a peer that is already one barrier ahead
-      if (ld_acquire_sys(p.my_slot[lane]) - p.epoch >= 0) {
+      if (ld_acquire_sys(p.my_slot[lane]) - epoch >= 0) {
         seen = true;
         break;
       }
@@ -139,7 +150,7 @@ extern "C" int hdit_ipc_close(void* ptr) {
 }
 
 extern "C" int hdit_peer_barrier(int32_t* const* peer_slots, const int32_t* const* my_slots, int n, int me,
-                                 int32_t epoch, int64_t max_spins, void* stream) {
+                                 int32_t epoch, int32_t* epoch_counter, int64_t max_spins, void* stream) {
   using namespace hdit;
   if (n < 1 || n > kMaxPeers || me < 0 || me >= n) return set_error(HDIT_ERR_BAD_ARG, "bad group size or index");
   if (n == 1) return HDIT_OK;
@@ -155,6 +166,7 @@ extern "C" int hdit_peer_barrier(int32_t* const* peer_slots, const int32_t* cons
   p.n = n;
   p.me = me;
   p.epoch = epoch;
+  p.epoch_counter = epoch_counter;
   p.max_spins = static_cast<unsigned>(max_spins > 0 ? (max_spins > 0xffffffffLL ? 0xffffffffLL : max_spins) : 1);
   p.status = device_status_ptr();
   if (p.status == nullptr) return HDIT_ERR_CUDA;

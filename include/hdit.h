@@ -247,14 +247,16 @@ HDIT_API int hdit_ipc_close(void* ptr);
  * peer_slots[p] in every peer's heap, then polls my_slots[p] in its own heap until it holds at
  * least `epoch`. Everything enqueued on the stream before the call (peer stores included) is
  * visible to the peers' work enqueued after their matching call. Epochs must grow by one per
- * barrier on every rank. After `max_spins` polls without an answer the kernel records
+ * barrier on every rank. With `epoch_counter` (a device int32 of this rank, e.g. in its heap) the
+ * kernel takes the epoch from that counter and advances it itself, which keeps a captured CUDA
+ * graph containing the barrier replayable; `epoch` is then ignored. After `max_spins` polls without an answer the kernel records
  * HDIT_ERR_PEER_TIMEOUT (where = 100, iteration = silent peer) and returns.
  *
  * Stands in for the synchronisation implied by the reference's NCCL collectives
  * (SeqAllToAll4D, hybrid/attn_layer.py:102-110,134-136; RingComm.wait, ring_flash_attn.py:91).
  */
 HDIT_API int hdit_peer_barrier(int32_t* const* peer_slots, const int32_t* const* my_slots, int n, int me,
-                               int32_t epoch, int64_t max_spins, void* stream);
+                               int32_t epoch, int32_t* epoch_counter, int64_t max_spins, void* stream);
 
 /*
  * One-way flag: hdit_peer_signal publishes `value` to a flag in a peer's heap after all earlier
