@@ -373,6 +373,86 @@ def run_kernel_case(args):
     print(json.dumps({"kernel_case": args.kernel_case, "ms_per_launch": ms, "rate": rate, "unit": unit}), flush=True)
 
 
+USP_CASES = {
+    # name: (heads, head_dim, image/video tokens, text tokens, joint strategy, {world: (ulysses, ring)})
+    "flux": (24, 128, 4096, 512, "front", {2: (2, 1), 4: (4, 1), 8: (8, 1)}),
+    "cogvideox": (48, 64, 44880, 224, "front", {2: (1, 2), 4: (1, 4), 8: (1, 8)}),
+    "hunyuan": (24, 128, 118800, 256, "rear", {8: (4, 2), 4: (2, 2), 2: (2, 1)}),
+}
+
+
+def run_usp_case(args):
+    """Operator-level timing of one USP attention layer at a BASELINE config's shape under torchrun:
+    `usp:<flux|cogvideox|hunyuan>`. Prints ms per layer (max over ranks), TFLOP/s per GPU, and the share of
+    the layer that is not attention compute (exchange, barriers, copies)."""
+    import torch.distributed as dist
+    from hetu_dit_b200 import _C, kernels
+    from hetu_dit_b200.core import parallel as P
+    from hetu_dit_b200.core.distributed import parallel_state as ps
+    from hetu_dit_b200.core.distributed.peer import PeerHeap
+    name = args.kernel_case.split(":")[1]
+    H, D, s_img, s_txt, strategy, plans = USP_CASES[name]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    dev = torch.device(f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}")
+    torch.cuda.set_device(dev)
+    U, R = plans[world]
+    dist.init_process_group("nccl", device_id=dev)
+
+    def gather(b):
+        out = [None] * world
+        dist.all_gather_object(out, b)
+        return out
+
+    s_loc = s_img // world
+    kv_bytes = 2 * s_img * H * D * 2 // max(U, 1)
+    heap = PeerHeap(max(1 << 30, 6 * kv_bytes), rank, world, dev, gather)
+    ps.init_distributed_environment(rank, world, heap)
+    ps.initialize_model_parallel(sequence_parallel_degree=world, ulysses_degree=U, ring_degree=R)
+    torch.manual_seed(rank)
+    q, k, v = (torch.randn(1, s_loc, H, D, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    jq, jk, jv = (torch.randn(1, s_txt, H, D, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    layer = P.hetuDiTJointLongContextAttention()
+
+    def op():
+        return layer(None, q, k, v, joint_tensor_query=jq, joint_tensor_key=jk, joint_tensor_value=jv,
+                     joint_strategy=strategy)
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    for _ in range(3):
+        op()
+    ms_layer = timed(op, args.steps)
+    # compute only: the same attention work on local copies, no exchange
+    Hl = H // U
+    s_q = s_img // R + s_txt
+    qg = torch.randn(1, s_q, Hl, D, device=dev, dtype=torch.bfloat16)
+    kg = torch.randn(1, s_img + s_txt, Hl, D, device=dev, dtype=torch.bfloat16)
+    vg = torch.randn_like(kg)
+    for _ in range(3):
+        kernels.attn_fwd([qg], [kg], [vg])
+    ms_compute = timed(lambda: kernels.attn_fwd([qg], [kg], [vg]), args.steps)
+    heap.check()
+    if rank == 0:
+        flops = 4.0 * s_q * (s_img + s_txt) * Hl * D
+        print(json.dumps({"usp_case": name, "n_gpus": world, "ulysses": U, "ring": R, "ms_per_layer": ms_layer,
+                          "ms_attention_only": ms_compute, "tflops_per_gpu": flops / (ms_layer * 1e-3) / 1e12,
+                          "exposed_non_compute_frac": max(0.0, 1 - ms_compute / ms_layer)}), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -383,7 +463,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a captured CUDA graph")
     ap.add_argument("--kernel-case", default="", help="profiling aid: attn:<batch> or copy:<MiB>")
     args = ap.parse_args()
-    if args.kernel_case:
+    if args.kernel_case.startswith("usp:"):
+        run_usp_case(args)
+    elif args.kernel_case:
         run_kernel_case(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -215,139 +215,139 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
   // Each warpgroup changes its budget at the top of its own branch so the allocation of the code
   // below it is known.
   if (warp >= 8) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-  if (warp == 8) {
-    // =========================== TMA producer ===========================
-    if (lane == 0) {
-      for (int s = 0; s < p.n_q_seg; ++s) tma_prefetch_desc(&p.q_map[s]);
-      for (int s = 0; s < p.n_kv_seg; ++s) {
-        tma_prefetch_desc(&p.k_map[s]);
-        tma_prefetch_desc(&p.v_map[s]);
-      }
-      for (int t = 0; t < 2; ++t) {
-        if (t == 1 && !tile1_valid) break;
-        int seg, row0, orow;
-        tile_coords(p, tile0 + t, seg, row0, orow);
-        mbar_expect_tx(&q_full[t], C::kTileBytes);
-        load_tile(&p.q_map[seg], p.q_swap[seg], smem_q + t * C::kTileBytes, &q_full[t], C::kPanels, h, row0, b);
-      }
-      KvCursor cur{0, 0};
-      bool ok = true;
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int st = j % C::kStages;
-        const uint32_t n = static_cast<uint32_t>(j / C::kStages);
-        if (j >= C::kStages) {
-          if (!mbar_wait_bounded(&k_empty[st], (n - 1) & 1, abort_flag, kSpinLimit)) {
-            report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_PROD_KEMPTY, j);
-            ok = false;
-            break;
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    if (warp == 8) {
+      // =========================== TMA producer ===========================
+      if (lane == 0) {
+        for (int s = 0; s < p.n_q_seg; ++s) tma_prefetch_desc(&p.q_map[s]);
+        for (int s = 0; s < p.n_kv_seg; ++s) {
+          tma_prefetch_desc(&p.k_map[s]);
+          tma_prefetch_desc(&p.v_map[s]);
+        }
+        for (int t = 0; t < 2; ++t) {
+          if (t == 1 && !tile1_valid) break;
+          int seg, row0, orow;
+          tile_coords(p, tile0 + t, seg, row0, orow);
+          mbar_expect_tx(&q_full[t], C::kTileBytes);
+          load_tile(&p.q_map[seg], p.q_swap[seg], smem_q + t * C::kTileBytes, &q_full[t], C::kPanels, h, row0, b);
+        }
+        KvCursor cur{0, 0};
+        bool ok = true;
+        for (int j = 0; j < nblk && ok; ++j) {
+          const int st = j % C::kStages;
+          const uint32_t n = static_cast<uint32_t>(j / C::kStages);
+          if (j >= C::kStages) {
+            if (!mbar_wait_bounded(&k_empty[st], (n - 1) & 1, abort_flag, kSpinLimit)) {
+              report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_PROD_KEMPTY, j);
+              ok = false;
+              break;
+            }
           }
-        }
-        mbar_expect_tx(&k_full[st], C::kTileBytes);
-        load_tile(&p.k_map[cur.seg], p.k_swap[cur.seg], smem_k + st * C::kTileBytes, &k_full[st], C::kPanels, h,
-                  cur.row0, b);
-        if (j >= C::kStages) {
-          if (!mbar_wait_bounded(&v_empty[st], (n - 1) & 1, abort_flag, kSpinLimit)) {
-            report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_PROD_VEMPTY, j);
-            ok = false;
-            break;
+          mbar_expect_tx(&k_full[st], C::kTileBytes);
+          load_tile(&p.k_map[cur.seg], p.k_swap[cur.seg], smem_k + st * C::kTileBytes, &k_full[st], C::kPanels, h,
+                    cur.row0, b);
+          if (j >= C::kStages) {
+            if (!mbar_wait_bounded(&v_empty[st], (n - 1) & 1, abort_flag, kSpinLimit)) {
+              report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_PROD_VEMPTY, j);
+              ok = false;
+              break;
+            }
           }
+          mbar_expect_tx(&v_full[st], C::kTileBytes);
+          load_tile(&p.v_map[cur.seg], p.v_swap[cur.seg], smem_v + st * C::kTileBytes, &v_full[st], C::kPanels, h,
+                    cur.row0, b);
+          cur.advance(p);
         }
-        mbar_expect_tx(&v_full[st], C::kTileBytes);
-        load_tile(&p.v_map[cur.seg], p.v_swap[cur.seg], smem_v + st * C::kTileBytes, &v_full[st], C::kPanels, h,
-                  cur.row0, b);
-        cur.advance(p);
       }
-    }
-  } else if (warp == 9) {
-    // ============================ MMA issuer ============================
-    if (lane == 0) {
-      constexpr uint32_t kFmt = FP16 ? 0u : 1u;
-      constexpr uint32_t idesc_qk = make_idesc_f16(kBlockM, kBlockN, kFmt, 0);
-      constexpr uint32_t idesc_pv = make_idesc_f16(kBlockM, D, kFmt, 1);
-      const uint32_t q_addr = smem_u32(smem_q);
-      const uint32_t k_addr = smem_u32(smem_k);
-      const uint32_t v_addr = smem_u32(smem_v);
-      bool ok = true;
+    } else if (warp == 9) {
+      // ============================ MMA issuer ============================
+      if (lane == 0) {
+        constexpr uint32_t kFmt = FP16 ? 0u : 1u;
+        constexpr uint32_t idesc_qk = make_idesc_f16(kBlockM, kBlockN, kFmt, 0);
+        constexpr uint32_t idesc_pv = make_idesc_f16(kBlockM, D, kFmt, 1);
+        const uint32_t q_addr = smem_u32(smem_q);
+        const uint32_t k_addr = smem_u32(smem_k);
+        const uint32_t v_addr = smem_u32(smem_v);
+        bool ok = true;
 
-      // Descriptors differ from a per-tile base only in the start-address field (low word, units of
-      // 16 bytes), so a k-step costs one 32-bit add instead of a rebuilt 64-bit descriptor.
-      const uint64_t q_desc0 = make_smem_desc_sw128(q_addr, 16, 1024);
-      const uint64_t k_desc0 = make_smem_desc_sw128(k_addr, 16, 1024);
-      const uint64_t v_desc0 = make_smem_desc_sw128(v_addr, kPanelBytes, 1024);
-      auto issue_qk = [&](int t, int stage) {
-        const uint32_t d_tmem = tmem_base + C::kColS + t * 128;
-        const uint64_t a0 = q_desc0 + static_cast<uint32_t>((t * C::kTileBytes) >> 4);
-        const uint64_t b0 = k_desc0 + static_cast<uint32_t>((stage * C::kTileBytes) >> 4);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = ((kk >> 2) * kPanelBytes + (kk & 3) * 32) >> 4;
-          umma_ss(d_tmem, a0 + off, b0 + off, idesc_qk, kk > 0 ? 1u : 0u);
-        }
-      };
-      auto issue_pv = [&](int t, int stage, bool accumulate) {
-        const uint32_t d_tmem = tmem_base + C::kColO + t * D;
-        const uint32_t a_tmem = tmem_base + C::kColS + t * 128;
-        const uint64_t b0 = v_desc0 + static_cast<uint32_t>((stage * C::kTileBytes) >> 4);
-#pragma unroll
-        for (int kk = 0; kk < kBlockN / 16; ++kk) {
-          umma_ts(d_tmem, a_tmem + kk * 8, b0 + static_cast<uint32_t>((kk * 2048) >> 4), idesc_pv,
-                  (accumulate || kk > 0) ? 1u : 0u);
-        }
-      };
-      auto wait = [&](uint64_t* bar, uint32_t parity, int where, int iter) {
-        if (!ok) return;
-        if (!mbar_wait_bounded(bar, parity, abort_flag, kSpinLimit)) {
-          report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, where, iter);
-          ok = false;
-        }
-      };
+        // Descriptors differ from a per-tile base only in the start-address field (low word, units of
+        // 16 bytes), so a k-step costs one 32-bit add instead of a rebuilt 64-bit descriptor.
+        const uint64_t q_desc0 = make_smem_desc_sw128(q_addr, 16, 1024);
+        const uint64_t k_desc0 = make_smem_desc_sw128(k_addr, 16, 1024);
+        const uint64_t v_desc0 = make_smem_desc_sw128(v_addr, kPanelBytes, 1024);
+        auto issue_qk = [&](int t, int stage) {
+          const uint32_t d_tmem = tmem_base + C::kColS + t * 128;
+          const uint64_t a0 = q_desc0 + static_cast<uint32_t>((t * C::kTileBytes) >> 4);
+          const uint64_t b0 = k_desc0 + static_cast<uint32_t>((stage * C::kTileBytes) >> 4);
+  #pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = ((kk >> 2) * kPanelBytes + (kk & 3) * 32) >> 4;
+            umma_ss(d_tmem, a0 + off, b0 + off, idesc_qk, kk > 0 ? 1u : 0u);
+          }
+        };
+        auto issue_pv = [&](int t, int stage, bool accumulate) {
+          const uint32_t d_tmem = tmem_base + C::kColO + t * D;
+          const uint32_t a_tmem = tmem_base + C::kColS + t * 128;
+          const uint64_t b0 = v_desc0 + static_cast<uint32_t>((stage * C::kTileBytes) >> 4);
+  #pragma unroll
+          for (int kk = 0; kk < kBlockN / 16; ++kk) {
+            umma_ts(d_tmem, a_tmem + kk * 8, b0 + static_cast<uint32_t>((kk * 2048) >> 4), idesc_pv,
+                    (accumulate || kk > 0) ? 1u : 0u);
+          }
+        };
+        auto wait = [&](uint64_t* bar, uint32_t parity, int where, int iter) {
+          if (!ok) return;
+          if (!mbar_wait_bounded(bar, parity, abort_flag, kSpinLimit)) {
+            report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, where, iter);
+            ok = false;
+          }
+        };
 
-      // prologue: S(t,0) for both tiles
-      wait(&q_full[0], 0, W_MMA_QFULL, 0);
-      wait(&k_full[0], 0, W_MMA_KFULL, 0);
-      if (ok) {
-        tc_fence_after();
-        issue_qk(0, 0);
-        tc_commit(&s_full[0]);
-      }
-      if (tile1_valid) {
-        wait(&q_full[1], 0, W_MMA_QFULL, 1);
+        // prologue: S(t,0) for both tiles
+        wait(&q_full[0], 0, W_MMA_QFULL, 0);
+        wait(&k_full[0], 0, W_MMA_KFULL, 0);
         if (ok) {
           tc_fence_after();
-          issue_qk(1, 0);
-          tc_commit(&s_full[1]);
+          issue_qk(0, 0);
+          tc_commit(&s_full[0]);
         }
-      }
-      if (ok) tc_commit(&k_empty[0]);
+        if (tile1_valid) {
+          wait(&q_full[1], 0, W_MMA_QFULL, 1);
+          if (ok) {
+            tc_fence_after();
+            issue_qk(1, 0);
+            tc_commit(&s_full[1]);
+          }
+        }
+        if (ok) tc_commit(&k_empty[0]);
 
-      const int last_t = tile1_valid ? 1 : 0;
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int st = j % C::kStages;
-        const uint32_t ph = static_cast<uint32_t>(j / C::kStages) & 1;
-        const int stn = (j + 1) % C::kStages;
-        const uint32_t phn = static_cast<uint32_t>((j + 1) / C::kStages) & 1;
-        for (int t = 0; t <= last_t && ok; ++t) {
-          if (t == 0) wait(&v_full[st], ph, W_MMA_VFULL, j);
-          wait(&p_ready[t], j & 1, W_MMA_PREADY, j * 2 + t);
-          if (!ok) break;
-          tc_fence_after();
-          issue_pv(t, st, j > 0);
-          if (t == last_t) tc_commit(&v_empty[st]);
-          if (j + 1 < nblk) {
-            if (t == 0) wait(&k_full[stn], phn, W_MMA_KFULL, j + 1);
+        const int last_t = tile1_valid ? 1 : 0;
+        for (int j = 0; j < nblk && ok; ++j) {
+          const int st = j % C::kStages;
+          const uint32_t ph = static_cast<uint32_t>(j / C::kStages) & 1;
+          const int stn = (j + 1) % C::kStages;
+          const uint32_t phn = static_cast<uint32_t>((j + 1) / C::kStages) & 1;
+          for (int t = 0; t <= last_t && ok; ++t) {
+            if (t == 0) wait(&v_full[st], ph, W_MMA_VFULL, j);
+            wait(&p_ready[t], j & 1, W_MMA_PREADY, j * 2 + t);
             if (!ok) break;
             tc_fence_after();
-            issue_qk(t, stn);
-            tc_commit(&s_full[t]);
-            if (t == last_t) tc_commit(&k_empty[stn]);
-          } else {
-            tc_commit(&o_done[t]);
+            issue_pv(t, st, j > 0);
+            if (t == last_t) tc_commit(&v_empty[st]);
+            if (j + 1 < nblk) {
+              if (t == 0) wait(&k_full[stn], phn, W_MMA_KFULL, j + 1);
+              if (!ok) break;
+              tc_fence_after();
+              issue_qk(t, stn);
+              tc_commit(&s_full[t]);
+              if (t == last_t) tc_commit(&k_empty[stn]);
+            } else {
+              tc_commit(&o_done[t]);
+            }
           }
         }
       }
     }
-  }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ========================= softmax / epilogue =========================
