@@ -69,7 +69,13 @@ class _UlyssesExchange:
         B, S_tot, Hl, D = ctx.shape
         S = (S_tot - joint_len) // U
         rows = S + joint_len
-        out, off = self.heap.alloc((B, rows, Hl * U, D), ctx.dtype, name=f"usp_{tag}_{(B, rows, Hl * U, D)}_{ctx.dtype}")
+        # Two buffers used alternately: a peer writes this rank's buffer for layer L+1 only after the
+        # barrier that follows layer L+1's head exchange, which this rank enters after it has enqueued
+        # (on the same stream) everything that reads layer L's result; alternating adds one more layer
+        # of slack for a caller that keeps the returned view a little longer.
+        parity = _UlyssesExchange._parity = 1 - getattr(_UlyssesExchange, "_parity", 0)
+        out, off = self.heap.alloc((B, rows, Hl * U, D), ctx.dtype,
+                                   name=f"usp_{tag}{parity}_{(B, rows, Hl * U, D)}_{ctx.dtype}")
         es = ctx.element_size()
         img0_src = joint_len if joint_front else 0      # first image row in ctx
         img0_dst = joint_len if joint_front else 0      # first image row in out
@@ -87,8 +93,7 @@ class _UlyssesExchange:
                                out.stride(0) * es, joint_len, ctx.stride(1) * es, out.stride(1) * es, Hl * D * es))
         kernels.copy_pieces(pieces, ctx.device)
         g.barrier()
-        # Hand back a private copy: the heap buffer is overwritten by the next layer's exchange.
-        return out.clone()
+        return out
 
 
 class hetuDiTLongContextAttention(torch.nn.Module):
