@@ -8,8 +8,8 @@ flash-attn once per step and merges partial results with eager fp32 kernels.
 Here every rank's K/V block lives in the node's peer heap, so a rank *pulls* the
 R-1 remote blocks into local staging memory with one coalesced copy kernel each
 (on a side stream, crossing NVLink exactly once) while the tensor cores work on
-the block before it; every launch after the first merges its block into the fp32
-running result by log-sum-exp in its epilogue. Joint (text) K/V
+the local block; the remaining blocks are then consumed by a single launch whose
+epilogue merges with the first partial result by log-sum-exp. Joint (text) K/V
 joins the block list at the position the reference's step index implies:
 first for "front", last for "rear". Attention is invariant to the order in
 which KV blocks are visited, so results agree with the reference's rotation.
@@ -98,20 +98,18 @@ def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor,
     stage = _staging[key]
     nbytes = k_pub.numel() * k_pub.element_size()
 
-    # pull the R-1 remote blocks on the side stream, in the order the ring would deliver them; one
-    # event per block lets attention start on block s while block s+1 is still crossing NVLink
+    # pull the R-1 remote blocks on the side stream, in the order the ring would deliver them
     side = _side_stream(dev)
     side.wait_stream(torch.cuda.current_stream(dev))
-    pulled = []
     with torch.cuda.stream(side):
+        pieces = []
         for step in range(1, world):
             src = process_group.ranks[(me - step) % world]
-            kernels.copy_pieces([(heap.peer_ptr(src, k_off), stage[0, step - 1].data_ptr(), 1, 0, 0, 1, 0, 0, nbytes),
-                                 (heap.peer_ptr(src, v_off), stage[1, step - 1].data_ptr(), 1, 0, 0, 1, 0, 0, nbytes)],
-                                dev)
-            ev = torch.cuda.Event()
-            ev.record(side)
-            pulled.append(ev)
+            pieces.append((heap.peer_ptr(src, k_off), stage[0, step - 1].data_ptr(), 1, 0, 0, 1, 0, 0, nbytes))
+            pieces.append((heap.peer_ptr(src, v_off), stage[1, step - 1].data_ptr(), 1, 0, 0, 1, 0, 0, nbytes))
+        kernels.copy_pieces(pieces, dev)
+        pulled = torch.cuda.Event()
+        pulled.record(side)
 
     sq = sum(t.shape[1] for t in q_segs)
     acc = torch.empty((B, sq, H, D), dtype=torch.float32, device=dev)
@@ -121,18 +119,14 @@ def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor,
         ks, vs = front[0] + ks, front[1] + vs
     kernels.attn_fwd(q_segs, ks, vs, softmax_scale=softmax_scale, mode=_C.ATTN_PARTIAL_FIRST, acc_out=acc,
                      acc_lse=acc_lse)
-    out = lse = None
-    for step in range(1, world):
-        torch.cuda.current_stream(dev).wait_event(pulled[step - 1])
-        ks, vs = [stage[0, step - 1]], [stage[1, step - 1]]
-        if step == world - 1:
-            if joint_strategy == "rear":
-                ks, vs = ks + [joint_tensor_key], vs + [joint_tensor_value]
-            out, lse = kernels.attn_fwd(q_segs, ks, vs, softmax_scale=softmax_scale, mode=_C.ATTN_MERGE_FINAL,
-                                        acc_out=acc, acc_lse=acc_lse, return_lse=True)
-        else:
-            kernels.attn_fwd(q_segs, ks, vs, softmax_scale=softmax_scale, mode=_C.ATTN_PARTIAL_MERGE, acc_out=acc,
-                             acc_lse=acc_lse)
+
+    torch.cuda.current_stream(dev).wait_event(pulled)
+    ks = [stage[0, i] for i in range(world - 1)]
+    vs = [stage[1, i] for i in range(world - 1)]
+    if joint_strategy == "rear":
+        ks, vs = ks + [joint_tensor_key], vs + [joint_tensor_value]
+    out, lse = kernels.attn_fwd(q_segs, ks, vs, softmax_scale=softmax_scale, mode=_C.ATTN_MERGE_FINAL, acc_out=acc,
+                                acc_lse=acc_lse, return_lse=True)
     process_group.barrier()  # peers have finished pulling this rank's block
     return out, lse
 
