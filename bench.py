@@ -363,6 +363,25 @@ def run_kernel_case(args):
         work = 2.0 * n / 1e-3 / 1e12 * 1e-3  # bytes moved (read + write) expressed so work/ms/1e9 -> TB/s
         work = 2.0 * n
         unit = "GB/s"
+    elif kind == "normrope":
+        B = int(arg or 8)
+        S = S_IMG + S_TXT
+        q, k = (torch.randn(B, S, 24, 128, device=dev, dtype=torch.bfloat16) for _ in range(2))
+        w = torch.ones(128, device=dev, dtype=torch.bfloat16)
+        ang = torch.rand(S, 64, device=dev) * 6.28
+        cos, sin = torch.cos(ang).repeat_interleave(2, -1).contiguous(), torch.sin(ang).repeat_interleave(2, -1).contiguous()
+        fn = lambda: kernels.qk_norm_rope([(q, w, True, True), (k, w, True, True)], cos=cos, sin=sin)
+        work = 2.0 * 2 * q.numel() * 2  # q and k, read + written once, 2 bytes each
+        unit = "GB/s"
+    elif kind == "lnmod":
+        B = int(arg or 16)
+        x = torch.randn(B, S_IMG + S_TXT, 3072, device=dev, dtype=torch.bfloat16)
+        mod = torch.randn(B, 2 * 3072, device=dev, dtype=torch.bfloat16)
+        sh, sc = mod.chunk(2, dim=-1)
+        out = torch.empty_like(x)
+        fn = lambda: kernels.ln_modulate(x, sh, sc, out=out)
+        work = 2.0 * x.numel() * 2
+        unit = "GB/s"
     else:
         raise SystemExit(f"unknown kernel case {args.kernel_case}")
     for _ in range(3):
