@@ -382,6 +382,15 @@ def run_kernel_case(args):
         fn = lambda: kernels.ln_modulate(x, sh, sc, out=out)
         work = 2.0 * x.numel() * 2
         unit = "GB/s"
+    elif kind == "gate":
+        B = int(arg or 16)
+        x = torch.randn(B, S_IMG + S_TXT, 3072, device=dev, dtype=torch.bfloat16)
+        y = torch.randn_like(x)
+        gate = torch.randn(B, 3072, device=dev, dtype=torch.bfloat16)
+        out = torch.empty_like(x)
+        fn = lambda: kernels.gate_residual(x, gate, y, out=out)
+        work = 3.0 * x.numel() * 2
+        unit = "GB/s"
     else:
         raise SystemExit(f"unknown kernel case {args.kernel_case}")
     for _ in range(3):

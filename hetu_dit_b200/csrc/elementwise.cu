@@ -14,8 +14,8 @@
 namespace hdit {
 namespace {
 
-constexpr int kLnThreads = 256;
-constexpr int kMaxChunks = 4;  // 8-element chunks per thread -> rows of up to 8192 elements
+constexpr int kLnThreads = 128;
+constexpr int kMaxChunks = 8;  // 8-element chunks per thread -> rows of up to 8192 elements
 
 template <bool FP16>
 __device__ __forceinline__ float ew_to_f(uint16_t v) {
@@ -28,62 +28,65 @@ __device__ __forceinline__ uint16_t ew_from_f(float f) {
   else return __bfloat16_as_ushort(__float2bfloat16_rn(f));
 }
 
-__device__ __forceinline__ float block_sum(float v, float* red) {
+// Sum of two values over the CTA with one shared-memory round trip.
+__device__ __forceinline__ float2 block_sum2(float a, float b, float2* red) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // the previous row's readers are done with `red`
+  if (lane == 0) red[warp] = make_float2(a, b);
   __syncthreads();
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float t = (lane < kLnThreads / 32) ? red[lane] : 0.f;
+  float2 t = make_float2(0.f, 0.f);
 #pragma unroll
-  for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-  return __shfl_sync(0xffffffffu, t, 0);
+  for (int w = 0; w < kLnThreads / 32; ++w) {
+    t.x += red[w].x;
+    t.y += red[w].y;
+  }
+  return t;
 }
 
-template <bool FP16>
+template <bool FP16, int NCH>
 __global__ void __launch_bounds__(kLnThreads) ln_modulate_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ shift,
                                                                 const uint16_t* __restrict__ scale, uint16_t* __restrict__ out,
                                                                 long long rows, int dim, long long rows_per_batch,
                                                                 long long x_row_stride, long long out_row_stride,
                                                                 long long mod_batch_stride, float eps) {
-  __shared__ float red[kLnThreads / 32];
+  __shared__ float2 red[kLnThreads / 32];
   const int n_chunks = dim / 8;
   for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
     const long long b = row / rows_per_batch;
     const uint16_t* xr = x + row * x_row_stride;
-    float v[kMaxChunks][8];
-    float s = 0.f;
+    uint4 raw[NCH];
 #pragma unroll
-    for (int c = 0; c < kMaxChunks; ++c) {
+    for (int c = 0; c < NCH; ++c) {
+      const int chunk = threadIdx.x + c * kLnThreads;
+      if (chunk < n_chunks) raw[c] = *reinterpret_cast<const uint4*>(xr + chunk * 8);
+    }
+    float v[NCH][8];
+    float s = 0.f, q = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
       const int chunk = threadIdx.x + c * kLnThreads;
       if (chunk < n_chunks) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(xr + chunk * 8);
-        const uint16_t* e = reinterpret_cast<const uint16_t*>(&raw);
+        const uint16_t* e = reinterpret_cast<const uint16_t*>(&raw[c]);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           v[c][i] = ew_to_f<FP16>(e[i]);
           s += v[c][i];
+          q = fmaf(v[c][i], v[c][i], q);
         }
       }
     }
-    const float mean = block_sum(s, red) / dim;
-    float q = 0.f;
-#pragma unroll
-    for (int c = 0; c < kMaxChunks; ++c) {
-      const int chunk = threadIdx.x + c * kLnThreads;
-      if (chunk < n_chunks) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float d = v[c][i] - mean;
-          q = fmaf(d, d, q);
-        }
-      }
-    }
-    const float rstd = rsqrtf(block_sum(q, red) / dim + eps);
+    // one reduction for both moments: var = E[x^2] - mean^2 in fp32 (activations here are O(1..100))
+    const float2 tot = block_sum2(s, q, red);
+    const float mean = tot.x / dim;
+    const float rstd = rsqrtf(fmaxf(tot.y / dim - mean * mean, 0.f) + eps);
     uint16_t* orow = out + row * out_row_stride;
 #pragma unroll
-    for (int c = 0; c < kMaxChunks; ++c) {
+    for (int c = 0; c < NCH; ++c) {
       const int chunk = threadIdx.x + c * kLnThreads;
       if (chunk < n_chunks) {
         const uint4 sh = *reinterpret_cast<const uint4*>(shift + b * mod_batch_stride + chunk * 8);
@@ -98,6 +101,92 @@ __global__ void __launch_bounds__(kLnThreads) ln_modulate_kernel(const uint16_t*
         *reinterpret_cast<uint4*>(orow + chunk * 8) = o;
       }
     }
+  }
+}
+
+// Warp-per-row variant for row lengths that are multiples of 256: a lane keeps its CH 16-byte chunks of the
+// row in registers (all loads of a row in flight at once), reductions are warp shuffles only, and a CTA of
+// 8 warps walks 8 rows at a time -- no __syncthreads on the critical path.
+template <bool FP16, int CH>
+__global__ void __launch_bounds__(256) ln_modulate_warp_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ shift,
+                                                             const uint16_t* __restrict__ scale, uint16_t* __restrict__ out,
+                                                             long long rows, int dim, long long rows_per_batch,
+                                                             long long x_row_stride, long long out_row_stride,
+                                                             long long mod_batch_stride, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long warp_global = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const long long n_warps = static_cast<long long>(gridDim.x) * 8;
+  const float inv_dim = 1.0f / dim;
+  for (long long row = warp_global; row < rows; row += n_warps) {
+    const long long b = row / rows_per_batch;
+    const uint16_t* xr = x + row * x_row_stride;
+    uint4 raw[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) raw[c] = *reinterpret_cast<const uint4*>(xr + (c * 32 + lane) * 8);
+    float v[CH][8];
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const uint16_t* e = reinterpret_cast<const uint16_t*>(&raw[c]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[c][i] = ew_to_f<FP16>(e[i]);
+        s += v[c][i];
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float mean = s * inv_dim;
+    float q = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float d = v[c][i] - mean;
+        q = fmaf(d, d, q);
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    const float rstd = rsqrtf(q * inv_dim + eps);
+    uint16_t* orow = out + row * out_row_stride;
+    const uint16_t* shr = shift + b * mod_batch_stride;
+    const uint16_t* scr = scale + b * mod_batch_stride;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int off = (c * 32 + lane) * 8;
+      const uint4 sh = *reinterpret_cast<const uint4*>(shr + off);
+      const uint4 sc = *reinterpret_cast<const uint4*>(scr + off);
+      const uint16_t* she = reinterpret_cast<const uint16_t*>(&sh);
+      const uint16_t* sce = reinterpret_cast<const uint16_t*>(&sc);
+      uint4 o;
+      uint16_t* oe = reinterpret_cast<uint16_t*>(&o);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        oe[i] = ew_from_f<FP16>(fmaf((v[c][i] - mean) * rstd, 1.0f + ew_to_f<FP16>(sce[i]), ew_to_f<FP16>(she[i])));
+      *reinterpret_cast<uint4*>(orow + off) = o;
+    }
+  }
+}
+
+template <bool FP16, int CH>
+void launch_ln_warp(const uint16_t* x, const uint16_t* sh, const uint16_t* sc, uint16_t* out, long long rows, int dim,
+                    long long rpb, long long xs, long long os, long long ms, float eps, cudaStream_t st) {
+  long long blocks = (rows + 7) / 8;
+  if (blocks > 148LL * 8) blocks = 148LL * 8;
+  ln_modulate_warp_kernel<FP16, CH><<<static_cast<unsigned>(blocks), 256, 0, st>>>(x, sh, sc, out, rows, dim, rpb, xs, os,
+                                                                                 ms, eps);
+}
+
+template <bool FP16>
+bool try_ln_warp(const uint16_t* x, const uint16_t* sh, const uint16_t* sc, uint16_t* out, long long rows, int dim,
+                 long long rpb, long long xs, long long os, long long ms, float eps, cudaStream_t st) {
+  if (dim % 256 != 0) return false;
+  switch (dim / 256) {
+    case 1: launch_ln_warp<FP16, 1>(x, sh, sc, out, rows, dim, rpb, xs, os, ms, eps, st); return true;
+    case 2: launch_ln_warp<FP16, 2>(x, sh, sc, out, rows, dim, rpb, xs, os, ms, eps, st); return true;
+    case 4: launch_ln_warp<FP16, 4>(x, sh, sc, out, rows, dim, rpb, xs, os, ms, eps, st); return true;
+    case 6: launch_ln_warp<FP16, 6>(x, sh, sc, out, rows, dim, rpb, xs, os, ms, eps, st); return true;
+    default: return false;
   }
 }
 
@@ -163,12 +252,32 @@ extern "C" int hdit_ln_modulate(int32_t dtype, const void* x, const void* shift,
   auto sh = static_cast<const uint16_t*>(shift);
   auto sc = static_cast<const uint16_t*>(scale);
   auto op = static_cast<uint16_t*>(out);
-  if (dtype == HDIT_FP16)
-    ln_modulate_kernel<true><<<grid, kLnThreads, 0, st>>>(xp, sh, sc, op, rows, static_cast<int>(dim), rows_per_batch,
-                                                          x_row_stride, out_row_stride, mod_batch_stride, eps);
-  else
-    ln_modulate_kernel<false><<<grid, kLnThreads, 0, st>>>(xp, sh, sc, op, rows, static_cast<int>(dim), rows_per_batch,
-                                                           x_row_stride, out_row_stride, mod_batch_stride, eps);
+  const bool fast = (dtype == HDIT_FP16)
+                        ? try_ln_warp<true>(xp, sh, sc, op, rows, static_cast<int>(dim), rows_per_batch, x_row_stride,
+                                            out_row_stride, mod_batch_stride, eps, st)
+                        : try_ln_warp<false>(xp, sh, sc, op, rows, static_cast<int>(dim), rows_per_batch, x_row_stride,
+                                             out_row_stride, mod_batch_stride, eps, st);
+  if (fast) {
+    HDIT_CUDA_OK(cudaGetLastError());
+    return HDIT_OK;
+  }
+  const int nch = static_cast<int>((dim / 8 + kLnThreads - 1) / kLnThreads);
+  const int d = static_cast<int>(dim);
+#define HDIT_LN_CASE(N)                                                                                          \
+  case N:                                                                                                        \
+    if (dtype == HDIT_FP16)                                                                                      \
+      ln_modulate_kernel<true, N><<<grid, kLnThreads, 0, st>>>(xp, sh, sc, op, rows, d, rows_per_batch,          \
+                                                               x_row_stride, out_row_stride, mod_batch_stride, eps); \
+    else                                                                                                         \
+      ln_modulate_kernel<false, N><<<grid, kLnThreads, 0, st>>>(xp, sh, sc, op, rows, d, rows_per_batch,         \
+                                                                x_row_stride, out_row_stride, mod_batch_stride, eps); \
+    break;
+  switch (nch) {
+    HDIT_LN_CASE(1) HDIT_LN_CASE(2) HDIT_LN_CASE(3) HDIT_LN_CASE(4) HDIT_LN_CASE(5) HDIT_LN_CASE(6) HDIT_LN_CASE(7)
+    HDIT_LN_CASE(8)
+    default: return set_error(HDIT_ERR_SHAPE, "row too long");
+  }
+#undef HDIT_LN_CASE
   HDIT_CUDA_OK(cudaGetLastError());
   return HDIT_OK;
 }

@@ -214,7 +214,7 @@ extern "C" int hdit_qk_norm_rope(const hdit_norm_rope_args* a) {
   threads = (threads + 31) / 32 * 32;
   if (threads > 512) threads = 512;
   const long long n_tok = static_cast<long long>(a->batch) * a->seq;
-  const long long cap = 148LL * 8;
+  const long long cap = 148LL * 32;  // short blocks (one 16-byte load per thread per token): many resident CTAs
   dim3 grid(static_cast<unsigned>(n_tok < cap ? n_tok : cap), static_cast<unsigned>(a->n_tensors));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
   const bool fp16 = a->dtype == HDIT_FP16;
