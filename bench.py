@@ -236,6 +236,13 @@ def run_gpu(args):
         for _ in range(max(args.warmup, 3)):
             step(resident)
         barrier()
+        if args.profile_one_step:
+            # profiler aid: exactly one eager step between cudaProfilerStart/Stop, so that
+            # `ncu --profile-from-start off` lists this step's launches and nothing else
+            torch.cuda.cudart().cudaProfilerStart()
+            step(resident)
+            torch.cuda.synchronize()
+            torch.cuda.cudart().cudaProfilerStop()
         # (1) eager pass: per-launch CUDA events around every attention kernel (for the roofline) and the
         #     count of this library's launches per step
         kernels.reset_counters()
@@ -494,6 +501,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a captured CUDA graph")
+    ap.add_argument("--profile-one-step", action="store_true",
+                    help="wrap one extra eager step in cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--kernel-case", default="", help="profiling aid: attn:<batch> or copy:<MiB>")
     args = ap.parse_args()
     if args.kernel_case.startswith("usp:"):

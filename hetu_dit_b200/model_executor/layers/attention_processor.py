@@ -89,9 +89,12 @@ class SingleAttnProcessor:
         self._hybrid_world = 0
 
     def __call__(self, attn, hidden_states, encoder_hidden_states=None, image_rotary_emb=None, text_len=None,
-                 token_offset: int = 0):
+                 token_offset: int = 0, out=None):
+        """out: optional (B, S, H*D)-shaped view (any row stride) the single-GPU path writes into, e.g. the left
+        part of the buffer the block's output projection reads, which saves a concatenation."""
         B, S, _ = hidden_states.shape
         q, k, v = (_heads(p(hidden_states), attn) for p in (attn.to_q, attn.to_k, attn.to_v))
+        out4 = None if out is None else out.view(B, S, attn.heads, attn.head_dim)
         S_txt = int(text_len or 0)
         if token_offset == 0:
             _norm_rope(attn, q, k, attn.norm_q, attn.norm_k, image_rotary_emb, 0)
@@ -110,10 +113,10 @@ class SingleAttnProcessor:
         elif _cached(attn) and S_txt:
             ki, vi = get_cache_manager().update_and_get_kv_cache(new_kv=[k[:, S_txt:], v[:, S_txt:]], layer=attn,
                                                                  slice_dim=1, layer_type="attn")
-            out = kernels.attn_fwd([q], [k[:, :S_txt], ki], [v[:, :S_txt], vi])
+            out = kernels.attn_fwd([q], [k[:, :S_txt], ki], [v[:, :S_txt], vi], out=out4)
         else:
-            out = kernels.attn_fwd([q], [k], [v])
-        return out.reshape(B, out.shape[1], attn.heads * attn.head_dim)
+            out = kernels.attn_fwd([q], [k], [v], out=out4)
+        return out.reshape(B, out.shape[1], attn.heads * attn.head_dim) if out4 is None else None
 
 
 def _cached(attn) -> bool:

@@ -23,6 +23,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ... import kernels
+from ...core.distributed import parallel_state as ps
 from ..layers.attention_processor import JointAttnProcessor, SingleAttnProcessor
 
 
@@ -126,9 +127,9 @@ class Attention(nn.Module):
         self.processor = JointAttnProcessor() if joint else SingleAttnProcessor()
 
     def forward(self, hidden_states, encoder_hidden_states=None, image_rotary_emb=None, text_len=None,
-                token_offset=0):
+                token_offset=0, **kw):
         return self.processor(self, hidden_states, encoder_hidden_states=encoder_hidden_states,
-                              image_rotary_emb=image_rotary_emb, text_len=text_len, token_offset=token_offset)
+                              image_rotary_emb=image_rotary_emb, text_len=text_len, token_offset=token_offset, **kw)
 
 
 def _modulate(x, shift, scale):
@@ -181,6 +182,14 @@ class SingleBlock(nn.Module):
     def forward(self, x, temb, rope, text_len, token_offset=0):
         shift, scale, gate = self.norm.linear(F.silu(temb)).chunk(3, dim=-1)
         h = kernels.ln_modulate(x, shift, scale)
+        if ps.get_sequence_parallel_world_size() == 1:
+            # attention output and GELU(MLP) land side by side in the buffer the output projection reads:
+            # no concatenated copy
+            B, S, d = x.shape
+            buf = torch.empty((B, S, 5 * d), dtype=x.dtype, device=x.device)
+            torch.ops.aten.gelu.out(self.proj_mlp(h), approximate="tanh", out=buf[..., d:])
+            self.attn(h, image_rotary_emb=rope, text_len=text_len, token_offset=token_offset, out=buf[..., :d])
+            return kernels.gate_residual(x, gate, self.proj_out(buf))
         mlp = F.gelu(self.proj_mlp(h), approximate="tanh")
         a = self.attn(h, image_rotary_emb=rope, text_len=text_len, token_offset=token_offset)
         return kernels.gate_residual(x, gate, self.proj_out(torch.cat([a, mlp], dim=-1)))
