@@ -222,6 +222,46 @@ __global__ void __launch_bounds__(256) gate_residual_kernel(const uint16_t* __re
   }
 }
 
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), tanh on the MUFU unit
+  const float u = 0.7978845608028654f * fmaf(0.044715f * x, x * x, x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return 0.5f * x * (1.0f + t);
+}
+
+// out[r, :] = gelu_tanh(x[r, :]); rows may be strided on both sides (e.g. the output is a column block of
+// a wider buffer). Two 16-byte loads in flight per thread.
+template <bool FP16>
+__global__ void __launch_bounds__(256) gelu_tanh_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out,
+                                                       long long rows, int dim, long long x_row_stride,
+                                                       long long out_row_stride) {
+  const unsigned chunks_per_row = static_cast<unsigned>(dim / 8);
+  const long long total = rows * chunks_per_row;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += 2 * stride) {
+    const long long i1 = i + stride;
+    const bool has1 = i1 < total;
+    const long long r0 = i / chunks_per_row, r1 = has1 ? i1 / chunks_per_row : 0;
+    const long long c0 = i - r0 * chunks_per_row, c1 = has1 ? i1 - r1 * chunks_per_row : 0;
+    const uint4 a = *reinterpret_cast<const uint4*>(x + r0 * x_row_stride + c0 * 8);
+    uint4 bq = make_uint4(0, 0, 0, 0);
+    if (has1) bq = *reinterpret_cast<const uint4*>(x + r1 * x_row_stride + c1 * 8);
+    uint4 oa, ob;
+    const uint16_t* ae = reinterpret_cast<const uint16_t*>(&a);
+    const uint16_t* be = reinterpret_cast<const uint16_t*>(&bq);
+    uint16_t* oae = reinterpret_cast<uint16_t*>(&oa);
+    uint16_t* obe = reinterpret_cast<uint16_t*>(&ob);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      oae[k] = ew_from_f<FP16>(gelu_tanh_f(ew_to_f<FP16>(ae[k])));
+      obe[k] = ew_from_f<FP16>(gelu_tanh_f(ew_to_f<FP16>(be[k])));
+    }
+    *reinterpret_cast<uint4*>(out + r0 * out_row_stride + c0 * 8) = oa;
+    if (has1) *reinterpret_cast<uint4*>(out + r1 * out_row_stride + c1 * 8) = ob;
+  }
+}
+
 int check_common(int dtype, int64_t rows, int64_t dim, int64_t rows_per_batch) {
   if (dtype != HDIT_BF16 && dtype != HDIT_FP16) return set_error(HDIT_ERR_BAD_ARG, "dtype must be bf16 or fp16");
   if (rows < 0 || dim <= 0 || rows_per_batch <= 0) return set_error(HDIT_ERR_BAD_ARG, "bad sizes");
@@ -309,6 +349,31 @@ extern "C" int hdit_gate_residual(int32_t dtype, const void* x, const void* gate
     gate_residual_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
         xp, gp, yp, op, rows, static_cast<int>(dim), rows_per_batch, x_row_stride, y_row_stride, out_row_stride,
         gate_batch_stride);
+  HDIT_CUDA_OK(cudaGetLastError());
+  return HDIT_OK;
+}
+
+extern "C" int hdit_gelu_tanh(int32_t dtype, const void* x, void* out, int64_t rows, int64_t dim, int64_t x_row_stride,
+                              int64_t out_row_stride, void* stream) {
+  using namespace hdit;
+  if (dtype != HDIT_BF16 && dtype != HDIT_FP16) return set_error(HDIT_ERR_BAD_ARG, "dtype must be bf16 or fp16");
+  if (rows < 0 || dim <= 0 || dim % 8 != 0) return set_error(HDIT_ERR_SHAPE, "row length must be a positive multiple of 8");
+  if (rows == 0) return HDIT_OK;
+  if (x == nullptr || out == nullptr) return set_error(HDIT_ERR_BAD_ARG, "null pointer");
+  if (misaligned(x, x_row_stride) || misaligned(out, out_row_stride))
+    return set_error(HDIT_ERR_SHAPE, "pointers must be 16-byte aligned and strides multiples of 8 elements");
+  const long long total = rows * (dim / 8);
+  long long blocks = (total + 511) / 512;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == HDIT_FP16)
+    gelu_tanh_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const uint16_t*>(x), static_cast<uint16_t*>(out), rows, static_cast<int>(dim), x_row_stride,
+        out_row_stride);
+  else
+    gelu_tanh_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const uint16_t*>(x), static_cast<uint16_t*>(out), rows, static_cast<int>(dim), x_row_stride,
+        out_row_stride);
   HDIT_CUDA_OK(cudaGetLastError());
   return HDIT_OK;
 }

@@ -270,6 +270,11 @@ def qk_norm_rope(tensors, *, eps=1e-6, cos=None, sin=None, rope_seq_start=0, rop
     _count()
 
 
+def _require_cuda(t):
+    if not t.is_cuda:
+        raise RuntimeError("hetu_dit_b200 kernels need CUDA tensors; there is no CPU path")
+
+
 def _even_rows(x):
     return x.stride(2) == 1 and (x.shape[0] == 1 or x.stride(0) == x.shape[1] * x.stride(1))
 
@@ -284,6 +289,7 @@ def _rows_view(x):
 
 def ln_modulate(x, shift, scale, eps=1e-6, out=None):
     """LayerNorm(x) * (1 + scale[:, None]) + shift[:, None] for x (B, S, Dm), shift / scale (B, Dm) views."""
+    _require_cuda(x)
     if out is None:
         out = torch.empty(tuple(x.shape), dtype=x.dtype, device=x.device)
     if x.shape[0] > 1 and not _even_rows(x):  # e.g. a token slice of a batch: one launch per batch element
@@ -303,6 +309,7 @@ def ln_modulate(x, shift, scale, eps=1e-6, out=None):
 
 def gate_residual(x, gate, y, out=None):
     """x + gate[:, None] * y for x, y (B, S, Dm) and gate a (B, Dm) view."""
+    _require_cuda(x)
     if x.shape != y.shape:
         raise ValueError("x and y differ in shape")
     if out is None:
@@ -317,5 +324,22 @@ def gate_residual(x, gate, y, out=None):
         _C.check(_C.lib().hdit_gate_residual(_DTYPE_CODE[x.dtype], x.data_ptr(), gate.data_ptr(), y.data_ptr(),
                                              out.data_ptr(), rows, dim, rpb, xs, ys, out.stride(1), gate.stride(0),
                                              _stream_ptr(x.device)))
+    _count()
+    return out
+
+
+def gelu_tanh(x, out=None):
+    """tanh-approximated GELU over the last dim of a (B, S, Dm) tensor with evenly strided rows; `out` may be
+    `x` itself or a column block of a wider buffer with the same (B, S)."""
+    _require_cuda(x)
+    rows, dim, _, xs = _rows_view(x)
+    if out is None:
+        out = torch.empty(tuple(x.shape), dtype=x.dtype, device=x.device)
+    rows_o, dim_o, _, os_ = _rows_view(out)
+    if (rows_o, dim_o) != (rows, dim):
+        raise ValueError("out differs from x in shape")
+    with torch.cuda.device(x.device):
+        _C.check(_C.lib().hdit_gelu_tanh(_DTYPE_CODE[x.dtype], x.data_ptr(), out.data_ptr(), rows, dim, xs, os_,
+                                         _stream_ptr(x.device)))
     _count()
     return out

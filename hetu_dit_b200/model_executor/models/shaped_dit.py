@@ -87,7 +87,8 @@ class _GELUProj(nn.Module):
         self.proj = nn.Linear(d_in, d_out)
 
     def forward(self, x):
-        return F.gelu(self.proj(x), approximate="tanh")
+        y = self.proj(x)
+        return kernels.gelu_tanh(y, out=y)
 
 
 class FeedForward(nn.Module):
@@ -187,10 +188,11 @@ class SingleBlock(nn.Module):
             # no concatenated copy
             B, S, d = x.shape
             buf = torch.empty((B, S, 5 * d), dtype=x.dtype, device=x.device)
-            torch.ops.aten.gelu.out(self.proj_mlp(h), approximate="tanh", out=buf[..., d:])
+            kernels.gelu_tanh(self.proj_mlp(h), out=buf[..., d:])
             self.attn(h, image_rotary_emb=rope, text_len=text_len, token_offset=token_offset, out=buf[..., :d])
             return kernels.gate_residual(x, gate, self.proj_out(buf))
-        mlp = F.gelu(self.proj_mlp(h), approximate="tanh")
+        mlp = self.proj_mlp(h)
+        kernels.gelu_tanh(mlp, out=mlp)
         a = self.attn(h, image_rotary_emb=rope, text_len=text_len, token_offset=token_offset)
         return kernels.gate_residual(x, gate, self.proj_out(torch.cat([a, mlp], dim=-1)))
 

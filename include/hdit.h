@@ -311,6 +311,15 @@ HDIT_API int hdit_gate_residual(int32_t dtype, const void* x, const void* gate, 
                                 int64_t rows, int64_t dim, int64_t rows_per_batch, int64_t x_row_stride,
                                 int64_t y_row_stride, int64_t out_row_stride, int64_t gate_batch_stride, void* stream);
 
+/*
+ * out[r, :] = GELU(x[r, :]) with the tanh approximation (fp32 arithmetic, tanh on the special-function
+ * unit), rows strided on both sides so the result can land in a column block of a wider buffer.
+ * Stands in for the activation inside the MLPs the reference takes from diffusers (call sites
+ * hetu_dit/model_executor/diffusion_executor/layers/feedforward.py:73-78).
+ */
+HDIT_API int hdit_gelu_tanh(int32_t dtype, const void* x, void* out, int64_t rows, int64_t dim, int64_t x_row_stride,
+                            int64_t out_row_stride, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -155,3 +155,18 @@ def test_ln_modulate_and_gate_residual(dim):
     # strided rows (a slice of a longer sequence) work too
     got = kernels.gate_residual(xd[:, 5:20], ga, yd[:, 5:20])
     assert torch.equal(got.cpu(), want[:, 5:20].bfloat16())
+
+
+def test_gelu_tanh_matches_torch():
+    from hetu_dit_b200 import kernels
+    gen = torch.Generator().manual_seed(4)
+    x = (3 * torch.randn(2, 33, 512, generator=gen)).bfloat16()
+    want = torch.nn.functional.gelu(x.float(), approximate="tanh")
+    xd = x.to(DEV)
+    got = kernels.gelu_tanh(xd)
+    assert (got.cpu().float() - want).abs().max().item() <= 2 ** -7 * want.abs().max().item()
+    wide = torch.zeros(2, 33, 640, dtype=torch.bfloat16, device=DEV)
+    kernels.gelu_tanh(xd, out=wide[..., 128:])
+    assert torch.equal(wide[..., 128:], got) and wide[..., :128].abs().sum() == 0
+    kernels.gelu_tanh(xd, out=xd)  # in place
+    assert torch.equal(xd, got)
