@@ -131,6 +131,8 @@ def _declare(lib):
     lib.hdit_device_status.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int32), ctypes.c_int]
     lib.hdit_attn_fwd.restype = ctypes.c_int
     lib.hdit_attn_fwd.argtypes = [ctypes.POINTER(AttnArgs)]
+    lib.hdit_attn_fwd_splitkv.restype = ctypes.c_int
+    lib.hdit_attn_fwd_splitkv.argtypes = [ctypes.POINTER(AttnArgs), ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
     lib.hdit_attn_fwd_split_static.restype = ctypes.c_int
     lib.hdit_attn_fwd_split_static.argtypes = [ctypes.POINTER(AttnArgs), ctypes.c_int32]
     lib.hdit_copy_pieces.restype = ctypes.c_int

@@ -83,6 +83,10 @@ struct alignas(64) AttnKernelParams {
   float* acc_lse;
   long long sq_total;
   int32_t* status;
+  // split-KV: blockIdx.y owns KV blocks [y * kv_split_blocks, ...) and writes its partial result to
+  // acc_out + y * split_acc_stride / acc_lse + y * split_lse_stride (0 = no split)
+  int kv_split_blocks;
+  long long split_acc_stride, split_lse_stride;
 };
 
 template <int D>
@@ -182,7 +186,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
   const int b = idx / p.heads;
   const int tile0 = pair * 2;
   const bool tile1_valid = (tile0 + 1) < p.n_tiles;
-  const int nblk = p.n_kv_blocks;
+  int j_begin = 0;
+  int nblk = p.n_kv_blocks;
+  if (p.kv_split_blocks > 0) {
+    j_begin = static_cast<int>(blockIdx.y) * p.kv_split_blocks;
+    nblk = min(p.n_kv_blocks - j_begin, p.kv_split_blocks);
+  }
+  float* const acc_out = p.acc_out + static_cast<long long>(blockIdx.y) * p.split_acc_stride;
+  float* const acc_lse = p.acc_lse + static_cast<long long>(blockIdx.y) * p.split_lse_stride;
 
   // ---- set-up ----------------------------------------------------------
   if (threadIdx.x == 0) {
@@ -232,6 +243,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
           load_tile(&p.q_map[seg], p.q_swap[seg], smem_q + t * C::kTileBytes, &q_full[t], C::kPanels, h, row0, b);
         }
         KvCursor cur{0, 0};
+        for (int i = 0; i < j_begin; ++i) cur.advance(p);
         bool ok = true;
         for (int j = 0; j < nblk && ok; ++j) {
           const int st = j % C::kStages;
@@ -364,6 +376,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       float l_run = 0.f;
       bool ok = true;
       KvCursor cur{0, 0};
+      for (int i = 0; i < j_begin; ++i) cur.advance(p);
 
       for (int j = 0; j < nblk; ++j) {
         // warp-uniform outcome: the tcgen05.ld/st below need the whole warp converged
@@ -468,7 +481,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         const bool merge = (p.mode == HDIT_ATTN_PARTIAL_MERGE || p.mode == HDIT_ATTN_MERGE_FINAL);
         const bool to_acc = (p.mode == HDIT_ATTN_PARTIAL_FIRST || p.mode == HDIT_ATTN_PARTIAL_MERGE);
         if (merge && row_valid) {
-          const float prev = p.acc_lse[lse_idx];
+          const float prev = acc_lse[lse_idx];
           const float blk = blk_lse2 * kLn2;
           const float mx = fmaxf(prev, blk);
           const float merged = mx + logf(expf(prev - mx) + expf(blk - mx));
@@ -478,7 +491,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         }
         if (row_valid) {
           if (to_acc)
-            p.acc_lse[lse_idx] = lse_out;
+            acc_lse[lse_idx] = lse_out;
           else if (p.lse != nullptr)
             p.lse[lse_idx] = lse_out;
         }
@@ -492,7 +505,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
 #pragma unroll
             for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(o[i]) * w_blk;
             if (merge) {
-              const float4* prev = reinterpret_cast<const float4*>(p.acc_out + acc_row + c * 32);
+              const float4* prev = reinterpret_cast<const float4*>(acc_out + acc_row + c * 32);
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const float4 v = prev[i];
@@ -503,7 +516,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
               }
             }
             if (to_acc) {
-              float4* dst = reinterpret_cast<float4*>(p.acc_out + acc_row + c * 32);
+              float4* dst = reinterpret_cast<float4*>(acc_out + acc_row + c * 32);
 #pragma unroll
               for (int i = 0; i < 8; ++i) dst[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
             } else {
@@ -617,7 +630,7 @@ int encode_seg(CUtensorMap* map, unsigned char* swapped, const hdit_seg& seg, in
 }
 
 template <int D, bool FP16>
-int launch(const AttnKernelParams& kp, int grid, cudaStream_t stream) {
+int launch(const AttnKernelParams& kp, int grid, int grid_y, cudaStream_t stream) {
   auto kernel = attn_fwd_kernel<D, FP16>;
   // The attribute is per device: set it whenever this thread meets a new device.
   static thread_local int last_dev = -1;
@@ -627,16 +640,73 @@ int launch(const AttnKernelParams& kp, int grid, cudaStream_t stream) {
     HDIT_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
     last_dev = dev;
   }
-  kernel<<<grid, kNumThreads, Cfg<D>::kSmemBytes, stream>>>(kp);
+  kernel<<<dim3(grid, grid_y), kNumThreads, Cfg<D>::kSmemBytes, stream>>>(kp);
   HDIT_CUDA_OK(cudaGetLastError());
   return HDIT_OK;
 }
 
+// Merges the partial results of a split-KV launch: out = sum_s w_s O_s with w_s = exp(lse_s - lse),
+// lse = log sum_s exp(lse_s). One warp per (batch, query, head) row.
+template <int D, bool FP16>
+__global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restrict__ part_out,
+                                                          const float* __restrict__ part_lse, int n_split,
+                                                          long long acc_stride, long long lse_stride, int batch,
+                                                          long long sq, int heads, void* out, long long out_sb,
+                                                          long long out_ss, long long out_sh, float* lse) {
+  const int lane = threadIdx.x & 31;
+  const long long n_rows = static_cast<long long>(batch) * sq * heads;
+  const long long warps = static_cast<long long>(gridDim.x) * 8;
+  for (long long r = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5); r < n_rows; r += warps) {
+    const int h = static_cast<int>(r % heads);
+    const long long bq = r / heads;
+    const long long q = bq % sq;
+    const int b = static_cast<int>(bq / sq);
+    const long long lse_idx = (static_cast<long long>(b) * heads + h) * sq + q;
+    float mx = -INFINITY;
+    for (int s = 0; s < n_split; ++s) mx = fmaxf(mx, part_lse[s * lse_stride + lse_idx]);
+    float wsum = 0.f;
+    constexpr int E = D / 32;
+    float acc[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) acc[i] = 0.f;
+    for (int s = 0; s < n_split; ++s) {
+      const float w = expf(part_lse[s * lse_stride + lse_idx] - mx);
+      wsum += w;
+      const float* src = part_out + s * acc_stride + r * D + lane * E;
+#pragma unroll
+      for (int i = 0; i < E; ++i) acc[i] = fmaf(w, src[i], acc[i]);
+    }
+    const float inv = 1.0f / wsum;
+    uint16_t* dst = reinterpret_cast<uint16_t*>(out) + b * out_sb + q * out_ss + static_cast<long long>(h) * out_sh +
+                    lane * E;
+#pragma unroll
+    for (int i = 0; i < E; i += 2) *reinterpret_cast<uint32_t*>(dst + i) = pack2<FP16>(acc[i] * inv, acc[i + 1] * inv);
+    if (lse != nullptr && lane == 0) lse[lse_idx] = mx + logf(wsum);
+  }
+}
+
+int attn_fwd_impl(const hdit_attn_args* a, int n_split, float* split_out, float* split_lse);
+
 }  // namespace
 }  // namespace hdit
 
-extern "C" int hdit_attn_fwd(const hdit_attn_args* a) {
+extern "C" int hdit_attn_fwd(const hdit_attn_args* a) { return hdit::attn_fwd_impl(a, 1, nullptr, nullptr); }
+
+extern "C" int hdit_attn_fwd_splitkv(const hdit_attn_args* a, int32_t n_split, float* split_out, float* split_lse) {
   using namespace hdit;
+  if (n_split < 1 || n_split > 16) return set_error(HDIT_ERR_BAD_ARG, "n_split must be 1..16");
+  if (n_split == 1) return attn_fwd_impl(a, 1, nullptr, nullptr);
+  if (a == nullptr) return set_error(HDIT_ERR_BAD_ARG, "args is null");
+  if (a->mode != HDIT_ATTN_FINAL) return set_error(HDIT_ERR_BAD_ARG, "split-KV needs mode HDIT_ATTN_FINAL");
+  if (split_out == nullptr || split_lse == nullptr || (reinterpret_cast<uintptr_t>(split_out) & 15) != 0)
+    return set_error(HDIT_ERR_BAD_ARG, "split scratch missing or misaligned");
+  return attn_fwd_impl(a, n_split, split_out, split_lse);
+}
+
+namespace hdit {
+namespace {
+
+int attn_fwd_impl(const hdit_attn_args* a, int n_split, float* split_out, float* split_lse) {
   if (a == nullptr) return set_error(HDIT_ERR_BAD_ARG, "args is null");
   if (a->dtype != HDIT_BF16 && a->dtype != HDIT_FP16) return set_error(HDIT_ERR_BAD_ARG, "dtype must be bf16 or fp16");
   if (a->head_dim != 64 && a->head_dim != 128) return set_error(HDIT_ERR_SHAPE, "head_dim must be 64 or 128");
@@ -716,12 +786,45 @@ extern "C" int hdit_attn_fwd(const hdit_attn_args* a) {
   if (grid > 0x7fffffffLL) return set_error(HDIT_ERR_TOO_LARGE, "grid too large");
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
   const bool fp16 = a->dtype == HDIT_FP16;
+  int grid_y = 1;
+  if (n_split > 1 && nblk >= 2) {
+    // every split gets the same number of 128-row KV blocks (the last one possibly fewer, never zero)
+    const int bps = (nblk + n_split - 1) / n_split;
+    grid_y = (nblk + bps - 1) / bps;
+    kp.kv_split_blocks = bps;
+    kp.mode = HDIT_ATTN_PARTIAL_FIRST;
+    kp.acc_out = split_out;
+    kp.acc_lse = split_lse;
+    kp.split_acc_stride = static_cast<long long>(a->batch) * sq * a->heads * a->head_dim;
+    kp.split_lse_stride = static_cast<long long>(a->batch) * a->heads * sq;
+  }
+  int rc;
   if (a->head_dim == 128)
-    return fp16 ? launch<128, true>(kp, static_cast<int>(grid), stream)
-                : launch<128, false>(kp, static_cast<int>(grid), stream);
-  return fp16 ? launch<64, true>(kp, static_cast<int>(grid), stream)
-              : launch<64, false>(kp, static_cast<int>(grid), stream);
+    rc = fp16 ? launch<128, true>(kp, static_cast<int>(grid), grid_y, stream)
+              : launch<128, false>(kp, static_cast<int>(grid), grid_y, stream);
+  else
+    rc = fp16 ? launch<64, true>(kp, static_cast<int>(grid), grid_y, stream)
+              : launch<64, false>(kp, static_cast<int>(grid), grid_y, stream);
+  if (rc != HDIT_OK || grid_y == 1) return rc;
+  const long long n_rows = static_cast<long long>(a->batch) * sq * a->heads;
+  long long blocks = (n_rows + 7) / 8;
+  if (blocks > 148LL * 8) blocks = 148LL * 8;
+#define HDIT_COMBINE(DD, FF)                                                                                       \
+  attn_combine_kernel<DD, FF><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                                   \
+      split_out, split_lse, grid_y, kp.split_acc_stride, kp.split_lse_stride, a->batch, sq, a->heads, a->out,      \
+      a->out_stride_b, a->out_stride_s, a->out_stride_h, a->lse)
+  if (a->head_dim == 128) {
+    if (fp16) HDIT_COMBINE(128, true); else HDIT_COMBINE(128, false);
+  } else {
+    if (fp16) HDIT_COMBINE(64, true); else HDIT_COMBINE(64, false);
+  }
+#undef HDIT_COMBINE
+  HDIT_CUDA_OK(cudaGetLastError());
+  return HDIT_OK;
 }
+
+}  // namespace
+}  // namespace hdit
 
 // ---------------------------------------------------------------------------------------------
 // Two-pass attention whose fp32 running result lives in a static device array.

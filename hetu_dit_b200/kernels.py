@@ -68,6 +68,7 @@ def attn_fwd(
     mode=_C.ATTN_FINAL,
     acc_out=None,
     acc_lse=None,
+    kv_split=None,
 ):
     """softmax(Q K^T * scale) V over segment lists, (B, S, H, D) layout.
 
@@ -76,6 +77,10 @@ def attn_fwd(
     dtype (and the (B, H, Sq) fp32 log-sum-exp when return_lse is set). In the
     PARTIAL modes nothing is returned; the fp32 running result lives in acc_out /
     acc_lse, which a later MERGE call combines with its own block by log-sum-exp.
+
+    kv_split (FINAL mode only): number of CTAs that share one query tile pair, each over its own
+    range of KV blocks, merged by a second small kernel. None picks it from the grid size: a head-
+    and sequence-sharded call can have fewer tile pairs than the GPU has SMs.
     """
     q0 = q_segs[0]
     if not q0.is_cuda:
@@ -121,19 +126,58 @@ def attn_fwd(
         a.acc_out = acc_out.data_ptr()
         a.acc_lse = acc_lse.data_ptr()
     a.stream = _stream_ptr(q0.device)
+    n_split = 1
+    if mode == _C.ATTN_FINAL:
+        n_split = _pick_kv_split(q_segs, k_segs, B, H) if kv_split is None else int(kv_split)
     with torch.cuda.device(q0.device):
+        if n_split > 1:
+            part_out = torch.empty((n_split, B, sq, H, D), dtype=torch.float32, device=q0.device)
+            part_lse = torch.empty((n_split, B, H, sq), dtype=torch.float32, device=q0.device)
+            call = lambda: _C.lib().hdit_attn_fwd_splitkv(ctypes.byref(a), n_split, part_out.data_ptr(),
+                                                          part_lse.data_ptr())
+        else:
+            call = lambda: _C.lib().hdit_attn_fwd(ctypes.byref(a))
         if _attn_timing:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            _C.check(_C.lib().hdit_attn_fwd(ctypes.byref(a)))
+            _C.check(call())
             e1.record()
             _attn_events.append((e0, e1))
         else:
-            _C.check(_C.lib().hdit_attn_fwd(ctypes.byref(a)))
-    _count()
+            _C.check(call())
+    _count(2 if n_split > 1 else 1)
     if not writes_out:
         return None
     return (out, lse) if return_lse else out
+
+
+_SM_COUNT = 148
+
+
+def _pick_kv_split(q_segs, k_segs, batch, heads):
+    """How many ways to split the KV range. One CTA per SM runs a pair of 128-row query tiles over all KV
+    blocks, so the launch takes ceil(ctas / SMs) waves; splitting the KV range s ways makes waves of 1/s the
+    length and pays a fixed cost per CTA plus the merge pass. Costs are in units of one KV block of one CTA
+    (about 2 us at head_dim 128), fitted to timings of 3..12 heads at 4.6k and 17.8k tokens; a split must
+    promise 10 % to be taken."""
+    q_tiles = sum((int(t.shape[1]) + 127) // 128 for t in q_segs)
+    ctas = (q_tiles + 1) // 2 * heads * batch
+    kv_blocks = sum((int(t.shape[1]) + 127) // 128 for t in k_segs)
+    if ctas <= 0:
+        return 1
+    sq = sum(int(t.shape[1]) for t in q_segs)
+    part_bytes = batch * sq * heads * int(q_segs[0].shape[3]) * 4
+
+    def cost(s):
+        waves = -(-ctas * s // _SM_COUNT)
+        c = waves * (kv_blocks / s + 6.0)
+        return c if s == 1 else c + 5.0 + part_bytes * s / 1e7
+
+    best, best_cost = 1, cost(1) * 0.9
+    for s in (2, 3, 4):
+        if kv_blocks // s >= 4 and cost(s) < best_cost:
+            best, best_cost = s, cost(s)
+    return best
 
 
 def copy_pieces(pieces, device):

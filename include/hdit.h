@@ -270,6 +270,26 @@ HDIT_API int hdit_peer_signal(int32_t* flag, int32_t value, void* stream);
 HDIT_API int hdit_peer_wait(const int32_t* flag, int32_t value, int64_t max_spins, int32_t tag, void* stream);
 
 /*
+ * hdit_attn_fwd (mode HDIT_ATTN_FINAL) with the KV range split over n_split CTAs per query tile
+ * pair, for calls whose grid would leave SMs idle. Replaces the same call sites as hdit_attn_fwd:
+ * after the Ulysses all-to-all (hetu_dit/core/parallel/hybrid/attn_layer.py:150-166) a rank holds
+ * heads / U heads of the whole sequence, so at U = 8 a 24-head model launches only 3 heads' worth of
+ * query tiles -- fewer CTAs than a B200 has SMs.
+ *
+ * Launch 1 runs the attention kernel on a (tile pairs * heads * batch, splits) grid; split s attends
+ * KV blocks [s * ceil(n_blocks / n_split), ...) of the concatenated segment list (blocks of 128 rows,
+ * never crossing a segment boundary) and writes a normalised fp32 partial result. Launch 2 merges
+ * the partials by log-sum-exp and writes `out` (+ `lse`). The result equals hdit_attn_fwd's up to fp32
+ * summation order.
+ *
+ * split_out: n_split * batch * Sq * heads * head_dim floats, 16-byte aligned; split_lse: n_split *
+ * batch * heads * Sq floats. Both are scratch: contents before and after the call mean nothing.
+ * n_split in [1, 16]; 1 (or fewer than 2 KV blocks) is hdit_attn_fwd itself.
+ */
+HDIT_API int hdit_attn_fwd_splitkv(const hdit_attn_args* args, int32_t n_split, float* split_out,
+                                   float* split_lse);
+
+/*
  * hdit_attn_fwd in two launches without any caller-provided or freshly allocated scratch.
  * (No counterpart in the reference: it exists for hosts that cannot allocate device memory
  * around the call -- e.g. a serving process whose HBM is entirely owned by its own pool, or a

@@ -166,6 +166,48 @@ def test_video_shapes_properties(name, H, D, s_vid, s_txt):
     assert (lse2 - lse).abs().max().item() <= LSE_ATOL
 
 
+@pytest.mark.parametrize("D,dtype", [(64, torch.bfloat16), (128, torch.bfloat16), (128, torch.float16)])
+@pytest.mark.parametrize("n_split", [2, 3, 16])
+def test_split_kv_matches_single_launch(D, dtype, n_split):
+    """KV range split over several CTAs per query tile pair + log-sum-exp combine == one launch == oracle.
+    Ragged joint segments put a block boundary inside every split; n_split 16 exceeds what 11 KV blocks
+    allow, so the library uses fewer."""
+    gen = torch.Generator().manual_seed(40 + D + n_split)
+    qs = [_mk((2, 300, 3, D), dtype, gen), _mk((2, 77, 3, D), dtype, gen)]
+    lens = [77, 640, 333, 129]
+    ks = [_mk((2, n, 3, D), dtype, gen) for n in lens]
+    vs = [_mk((2, n, 3, D), dtype, gen) for n in lens]
+    out, lse = _run(qs, ks, vs, kv_split=n_split)
+    _check(out, lse, qs, ks, vs)
+    ref, ref_lse = _run(qs, ks, vs, kv_split=1)
+    cos, rel = oa.cosine_and_max_rel(out.float().cpu(), ref.float().cpu())
+    # both round to 16 bits independently: an element may differ by one unit in the last place
+    assert cos >= COS_MIN and rel <= MAX_REL, (cos, rel)
+    assert (lse - ref_lse).abs().max().item() <= 1e-4
+
+
+def test_split_kv_auto_small_grid():
+    """The shape one rank sees after the Ulysses exchange at degree 8 of a 24-head model: 3 heads of the whole
+    sequence. The wrapper picks a split by itself; strided output (heads of a wider buffer) is honoured."""
+    from hetu_dit_b200 import kernels
+    gen = torch.Generator().manual_seed(77)
+    q, k, v = (_mk((1, 2400, 3, 128), torch.bfloat16, gen) for _ in range(3))
+    assert kernels._pick_kv_split([q], [k], 1, 3) > 1
+    wide = torch.zeros(1, 2400, 6, 128, dtype=torch.bfloat16, device="cuda:0")
+    out, lse = _run([q], [k], [v], out=wide[:, :, 3:])
+    _check(out, lse, [q], [k], [v])
+    assert wide[:, :, :3].abs().max().item() == 0
+
+
+def test_split_kv_argument_errors():
+    from hetu_dit_b200 import _C, kernels
+    dev = torch.device("cuda:0")
+    q = torch.zeros(1, 256, 2, 64, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(_C.HditError) as e:
+        kernels.attn_fwd([q], [q], [q], kv_split=17)
+    assert e.value.code == _C.HDIT_ERR_BAD_ARG
+
+
 def test_argument_errors():
     from hetu_dit_b200 import _C, kernels
     dev = torch.device("cuda:0")
