@@ -198,6 +198,7 @@ def run_gpu(args):
     torch.set_default_dtype(torch.float32)
     model.init_weights(seed=0, std=0.02)
     model.register_cache()
+    model.shard_text = not args.replicated_text
     host = {k: v.pin_memory() for k, v in _inputs(shape).items()}
     s_loc = S_IMG // world
     rows_loc = GRID[0] // world
@@ -325,6 +326,8 @@ def run_gpu(args):
         "config": {"workload": "flux.1-dev-shaped denoise step, 4096 image + 512 text tokens, batch 1, "
                                "19 double + 38 single blocks, hidden 3072, 24x128 heads",
                    "parallelism": f"ulysses{world}" if world > 1 else "single",
+                   "text_stream": "n/a" if world == 1 else ("replicated on every rank (reference layout)"
+                                                            if args.replicated_text else "sharded over the ranks"),
                    "l2": "weights (23.8 GB) and activations exceed the 126 MB L2; no explicit flush",
                    "cuda_graph": graph is not None, "ms_per_step_eager_launches": ms_eager,
                    "step_flops": model.flops_per_step(S_IMG, S_TXT),
@@ -501,6 +504,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a captured CUDA graph")
+    ap.add_argument("--replicated-text", action="store_true",
+                    help="N > 1: keep the whole text stream on every rank (the reference's layout) instead of "
+                         "sharding it with the image tokens")
     ap.add_argument("--profile-one-step", action="store_true",
                     help="wrap one extra eager step in cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--kernel-case", default="", help="profiling aid: attn:<batch> or copy:<MiB>")

@@ -152,14 +152,17 @@ class JointBlock(nn.Module):
         self.ff_context = _Wrapped(FeedForward(d))
         self.d = d
 
-    def forward(self, hidden, context, temb, rope, token_offset=0):
+    def forward(self, hidden, context, temb, rope, token_offset=0, text_offset=None, text_total=None):
+        """text_offset / text_total: `context` holds rows [text_offset, ...) of a text stream of text_total
+        tokens sharded over the sequence-parallel ranks; None = the whole text stream (reference layout)."""
         d = self.d
         mod = self.norm1.linear(F.silu(temb)).chunk(6, dim=-1)
         cmod = self.norm1_context.linear(F.silu(temb)).chunk(6, dim=-1)
         # LayerNorm + modulation and gate + residual are one fused pass each (csrc/elementwise.cu)
         h = kernels.ln_modulate(hidden, mod[0], mod[1])
         c = kernels.ln_modulate(context, cmod[0], cmod[1])
-        a_img, a_txt = self.attn(h, encoder_hidden_states=c, image_rotary_emb=rope, token_offset=token_offset)
+        a_img, a_txt = self.attn(h, encoder_hidden_states=c, image_rotary_emb=rope, token_offset=token_offset,
+                                 text_len=text_total, text_offset=text_offset)
         hidden = kernels.gate_residual(hidden, mod[2], a_img)
         hidden = kernels.gate_residual(hidden, mod[5], self.ff(kernels.ln_modulate(hidden, mod[3], mod[4])))
         context = kernels.gate_residual(context, cmod[2], a_txt)
@@ -180,7 +183,7 @@ class SingleBlock(nn.Module):
         self.proj_out = nn.Linear(5 * d, d)
         self.d = d
 
-    def forward(self, x, temb, rope, text_len, token_offset=0):
+    def forward(self, x, temb, rope, text_len, token_offset=0, text_offset=None, text_total=None):
         shift, scale, gate = self.norm.linear(F.silu(temb)).chunk(3, dim=-1)
         h = kernels.ln_modulate(x, shift, scale)
         if ps.get_sequence_parallel_world_size() == 1:
@@ -193,7 +196,8 @@ class SingleBlock(nn.Module):
             return kernels.gate_residual(x, gate, self.proj_out(buf))
         mlp = self.proj_mlp(h)
         kernels.gelu_tanh(mlp, out=mlp)
-        a = self.attn(h, image_rotary_emb=rope, text_len=text_len, token_offset=token_offset)
+        a = self.attn(h, image_rotary_emb=rope, text_len=text_len, token_offset=token_offset, text_offset=text_offset,
+                      text_total=text_total)
         return kernels.gate_residual(x, gate, self.proj_out(torch.cat([a, mlp], dim=-1)))
 
 
@@ -226,6 +230,8 @@ class ShapedDiT(nn.Module):
         if shape.rope_axes is None:
             self.pos_embed_max = 192  # learned-position stand-in: sin-cos table cropped to the latent grid
         self._rope_cache = {}
+        # shard the text stream over the sequence-parallel ranks when it divides evenly (see forward)
+        self.shard_text = True
 
     @torch.no_grad()
     def init_weights(self, seed: int = 0, std: float = 0.02):
@@ -296,20 +302,30 @@ class ShapedDiT(nn.Module):
             g = guidance if guidance is not None else torch.ones_like(timestep)
             temb = temb + self.guidance_embed(timestep_embedding(g * 1000.0).to(dtype))
         hidden = self.x_embedder(latent_tokens)
+        # Text stream: the reference keeps all of it on every sequence-parallel rank. When it divides evenly
+        # each rank takes a contiguous shard instead (the result is the same, the text-stream work is not
+        # repeated on every rank); PipeFusion stages keep the reference layout.
+        text_offset = text_total = None
+        sp = ps.get_sequence_parallel_world_size()
+        if self.shard_text and sp > 1 and S_txt % sp == 0 and ps.get_pipeline_parallel_world_size() == 1:
+            text_total = S_txt
+            S_txt = S_txt // sp
+            text_offset = ps.get_sequence_parallel_rank() * S_txt
+            text_embeds = text_embeds[:, text_offset:text_offset + S_txt]
         context = self.context_embedder(text_embeds)
         fg = full_grid or grid
         rope = None
         if shp.rope_axes is not None:
-            rope = self._rope(S_txt, fg[0], fg[1], latent_tokens.device)
+            rope = self._rope(text_total or S_txt, fg[0], fg[1], latent_tokens.device)
         else:
             pos = self._sincos_pos(fg[0], fg[1], latent_tokens.device, dtype)
             hidden = hidden + pos[:, token_offset:token_offset + S_img]
         for blk in self.transformer_blocks:
-            hidden, context = blk(hidden, context, temb, rope, token_offset)
+            hidden, context = blk(hidden, context, temb, rope, token_offset, text_offset, text_total)
         if len(self.single_transformer_blocks):
             x = torch.cat([context, hidden], dim=1)
             for blk in self.single_transformer_blocks:
-                x = blk(x, temb, rope, S_txt, token_offset)
+                x = blk(x, temb, rope, S_txt, token_offset, text_offset, text_total)
             hidden = x[:, S_txt:]
         shift, scale = self.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
         return self.proj_out(kernels.ln_modulate(hidden.contiguous(), shift, scale))

@@ -99,6 +99,53 @@ def usp_case(rank, world, port, fixture, errq):
         raise
 
 
+def model_sp_case(rank, world, port, kind, ulysses, errq):
+    """One denoise step of a tiny Flux- / SD3-shaped model under sequence parallelism: every rank's band of the
+    output against the CPU oracle of the whole model, with the text stream sharded and with the reference's
+    replicated text layout."""
+    try:
+        dist, ps, heap, dev = _setup(rank, world, port)
+        from hetu_dit_b200 import _C
+        from hetu_dit_b200.model_executor.models.shaped_dit import DiTShape, ShapedDiT
+        from oracle import attention as oa
+        from oracle import shaped_dit as osd
+        ps.initialize_model_parallel(sequence_parallel_degree=world, ulysses_degree=ulysses, ring_degree=world // ulysses)
+        if kind == "flux":
+            shape = DiTShape("flux-tiny", 2, 3, 512, 4, 128, 64, 256, 96, True, (16, 56, 56), True)
+        else:
+            shape = DiTShape("sd3-tiny", 3, 0, 256, 4, 64, 64, 256, 128, False, None, False)
+        model = ShapedDiT(shape).init_weights(seed=3, std=0.05).bfloat16()
+        gh, gw, s_txt = 24, 12, 32
+        gen = torch.Generator().manual_seed(21)
+        lat = torch.randn(1, gh * gw, shape.token_in, generator=gen).bfloat16()
+        txt = torch.randn(1, s_txt, shape.text_dim, generator=gen).bfloat16()
+        pooled = torch.randn(1, shape.pooled_dim, generator=gen).bfloat16()
+        t, g = torch.tensor([0.7]), torch.tensor([3.5])
+        sd = {k: v.float() for k, v in model.state_dict().items()}
+        want = osd.denoise_step(sd, shape, lat, txt, pooled, t, g, grid=(gh, gw))
+        model = model.to(dev)
+        model.register_cache()
+        rows = gh // world
+        s_loc = rows * gw
+        tok0 = rank * s_loc
+        for shard_text in (True, False):
+            model.shard_text = shard_text
+            with torch.no_grad():
+                got = model(lat[:, tok0:tok0 + s_loc].to(dev), txt.to(dev), pooled.to(dev), t.to(dev), g.to(dev),
+                            grid=(rows, gw), token_offset=tok0, full_grid=(gh, gw))
+            torch.cuda.synchronize()
+            heap.check()
+            assert _C.device_status(rank, clear=True)[0] == 0
+            cos, rel = oa.cosine_and_max_rel(got.float().cpu(), want[:, tok0:tok0 + s_loc])
+            assert cos >= 0.999 and rel <= 5e-2, f"rank {rank} shard_text={shard_text}: cosine {cos} max_rel {rel}"
+            ps.get_world_group().barrier()
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errq.put(f"rank {rank}:\n{traceback.format_exc()}")
+        raise
+
+
 def pipefusion_case(rank, world, port, errq):
     """Ring of stages passes patches around twice; payloads must arrive bit-exact and in FIFO order."""
     try:

@@ -41,6 +41,13 @@ def test_usp_operator_matches_reference_fixture(path):
     _spawn(usp_case, _world_of(path), path)
 
 
+@pytest.mark.parametrize("kind,world,ulysses", [("flux", 2, 2), ("sd3", 2, 2), ("flux", 2, 1), ("flux", 4, 2)])
+def test_model_step_under_sequence_parallelism(kind, world, ulysses):
+    """Whole tiny model, text stream sharded over the SP ranks and replicated, against the CPU oracle."""
+    from tests.multi_gpu_worker import model_sp_case
+    _spawn(model_sp_case, world, kind, ulysses)
+
+
 @pytest.mark.parametrize("world", [2, 4])
 def test_pipefusion_patch_ring(world):
     from tests.multi_gpu_worker import pipefusion_case
