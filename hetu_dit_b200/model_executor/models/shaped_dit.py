@@ -152,12 +152,16 @@ class JointBlock(nn.Module):
         self.ff_context = _Wrapped(FeedForward(d))
         self.d = d
 
-    def forward(self, hidden, context, temb, rope, token_offset=0, text_offset=None, text_total=None):
+    def modulation(self, silu_temb):
+        """The block's adaLN vectors; they depend on the timestep embedding only."""
+        return (self.norm1.linear(silu_temb).chunk(6, dim=-1), self.norm1_context.linear(silu_temb).chunk(6, dim=-1))
+
+    def forward(self, hidden, context, temb, rope, token_offset=0, text_offset=None, text_total=None, mods=None):
         """text_offset / text_total: `context` holds rows [text_offset, ...) of a text stream of text_total
-        tokens sharded over the sequence-parallel ranks; None = the whole text stream (reference layout)."""
+        tokens sharded over the sequence-parallel ranks; None = the whole text stream (reference layout).
+        mods: the result of modulation() when the caller has computed it ahead of time."""
         d = self.d
-        mod = self.norm1.linear(F.silu(temb)).chunk(6, dim=-1)
-        cmod = self.norm1_context.linear(F.silu(temb)).chunk(6, dim=-1)
+        mod, cmod = mods if mods is not None else self.modulation(F.silu(temb))
         # LayerNorm + modulation and gate + residual are one fused pass each (csrc/elementwise.cu)
         h = kernels.ln_modulate(hidden, mod[0], mod[1])
         c = kernels.ln_modulate(context, cmod[0], cmod[1])
@@ -183,8 +187,11 @@ class SingleBlock(nn.Module):
         self.proj_out = nn.Linear(5 * d, d)
         self.d = d
 
-    def forward(self, x, temb, rope, text_len, token_offset=0, text_offset=None, text_total=None):
-        shift, scale, gate = self.norm.linear(F.silu(temb)).chunk(3, dim=-1)
+    def modulation(self, silu_temb):
+        return self.norm.linear(silu_temb).chunk(3, dim=-1)
+
+    def forward(self, x, temb, rope, text_len, token_offset=0, text_offset=None, text_total=None, mods=None):
+        shift, scale, gate = mods if mods is not None else self.modulation(F.silu(temb))
         h = kernels.ln_modulate(x, shift, scale)
         if ps.get_sequence_parallel_world_size() == 1:
             # attention output and GELU(MLP) land side by side in the buffer the output projection reads:
@@ -232,6 +239,9 @@ class ShapedDiT(nn.Module):
         self._rope_cache = {}
         # shard the text stream over the sequence-parallel ranks when it divides evenly (see forward)
         self.shard_text = True
+        # compute every block's adaLN vectors on a second stream, ahead of the blocks (see _modulations_ahead)
+        self.modulation_ahead = True
+        self._mod_stream = {}
 
     @torch.no_grad()
     def init_weights(self, seed: int = 0, std: float = 0.02):
@@ -320,15 +330,58 @@ class ShapedDiT(nn.Module):
         else:
             pos = self._sincos_pos(fg[0], fg[1], latent_tokens.device, dtype)
             hidden = hidden + pos[:, token_offset:token_offset + S_img]
-        for blk in self.transformer_blocks:
-            hidden, context = blk(hidden, context, temb, rope, token_offset, text_offset, text_total)
+        ahead = self._modulations_ahead(temb) if self.modulation_ahead and temb.is_cuda else None
+        main = torch.cuda.current_stream(temb.device) if ahead is not None else None
+
+        def mods_of(i):
+            if ahead is None:
+                return None
+            ev, m = ahead[i]
+            main.wait_event(ev)
+            return m
+
+        n_double = len(self.transformer_blocks)
+        for i, blk in enumerate(self.transformer_blocks):
+            hidden, context = blk(hidden, context, temb, rope, token_offset, text_offset, text_total, mods_of(i))
         if len(self.single_transformer_blocks):
             x = torch.cat([context, hidden], dim=1)
-            for blk in self.single_transformer_blocks:
-                x = blk(x, temb, rope, S_txt, token_offset, text_offset, text_total)
+            for i, blk in enumerate(self.single_transformer_blocks):
+                x = blk(x, temb, rope, S_txt, token_offset, text_offset, text_total, mods_of(n_double + i))
             hidden = x[:, S_txt:]
-        shift, scale = self.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
+        if ahead is not None:
+            shift, scale = mods_of(len(ahead) - 1)
+            main.wait_stream(self._mod_stream[temb.device])
+        else:
+            shift, scale = self.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
         return self.proj_out(kernels.ln_modulate(hidden.contiguous(), shift, scale))
+
+    def _modulations_ahead(self, temb):
+        """Every block's adaLN vectors depend only on the timestep embedding, and each is a matrix-vector
+        product that streams its weight once from HBM (6.4 GB per step at the Flux shape) while the blocks'
+        GEMMs are tensor-bound. They are therefore enqueued on a second stream right after the
+        embedding, one event per block, and fill the gaps between the blocks' kernels. Returns
+        [(event, vectors)] for the double blocks, the single blocks and the output norm, in that order. The
+        caller waits on each event before use and joins the stream at the end, which also keeps the vectors'
+        memory from being handed out again while the main stream still reads it."""
+        dev = temb.device
+        side = self._mod_stream.get(dev)
+        if side is None:
+            side = self._mod_stream[dev] = torch.cuda.Stream(device=dev)
+        main = torch.cuda.current_stream(dev)
+        side.wait_stream(main)
+        out = []
+        with torch.cuda.stream(side):
+            silu = F.silu(temb)
+            for blk in list(self.transformer_blocks) + list(self.single_transformer_blocks):
+                m = blk.modulation(silu)
+                ev = torch.cuda.Event()
+                ev.record(side)
+                out.append((ev, m))
+            m = self.norm_out.linear(silu).chunk(2, dim=-1)
+            ev = torch.cuda.Event()
+            ev.record(side)
+            out.append((ev, m))
+        return out
 
     def flops_per_step(self, s_img: int, s_txt: int, batch: int = 1) -> float:
         """Algorithmic FLOPs of one step: 4*S^2*Dm attention + 2*12*Dm^2*S linear per block."""
