@@ -133,6 +133,34 @@ class Attention(nn.Module):
                               image_rotary_emb=image_rotary_emb, text_len=text_len, token_offset=token_offset, **kw)
 
 
+_BRANCH_STREAMS = {}
+
+
+class _Branch:
+    """`with _Branch(device) as br:` runs the body on a second stream that starts after everything already
+    enqueued on the current stream; br.join() makes the current stream wait for it. Used under sequence
+    parallelism to run independent work of a block next to its attention, whose peer exchanges leave the
+    GPU idle while flags cross NVLink. Tensors made inside the body must stay referenced until join()."""
+
+    def __init__(self, device):
+        self.side = _BRANCH_STREAMS.get(device)
+        if self.side is None:
+            self.side = _BRANCH_STREAMS[device] = torch.cuda.Stream(device=device)
+        self.main = torch.cuda.current_stream(device)
+        self._ctx = torch.cuda.stream(self.side)
+
+    def __enter__(self):
+        self.side.wait_stream(self.main)
+        self._ctx.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        return self._ctx.__exit__(*exc)
+
+    def join(self):
+        self.main.wait_stream(self.side)
+
+
 def _modulate(x, shift, scale):
     return x * (1 + scale[:, None]) + shift[:, None]
 
@@ -167,6 +195,18 @@ class JointBlock(nn.Module):
         c = kernels.ln_modulate(context, cmod[0], cmod[1])
         a_img, a_txt = self.attn(h, encoder_hidden_states=c, image_rotary_emb=rope, token_offset=token_offset,
                                  text_len=text_total, text_offset=text_offset)
+        if ps.get_sequence_parallel_world_size() > 1 and hidden.is_cuda:
+            # the text stream's tail is independent of the image stream's: under sequence parallelism its
+            # GEMMs have few rows and stream their weights, so they run beside the image stream's
+            with _Branch(hidden.device) as br:
+                ctx_in = context
+                context = kernels.gate_residual(ctx_in, cmod[2], a_txt)
+                context = kernels.gate_residual(context, cmod[5],
+                                                self.ff_context(kernels.ln_modulate(context, cmod[3], cmod[4])))
+            hidden = kernels.gate_residual(hidden, mod[2], a_img)
+            hidden = kernels.gate_residual(hidden, mod[5], self.ff(kernels.ln_modulate(hidden, mod[3], mod[4])))
+            br.join()
+            return hidden, context
         hidden = kernels.gate_residual(hidden, mod[2], a_img)
         hidden = kernels.gate_residual(hidden, mod[5], self.ff(kernels.ln_modulate(hidden, mod[3], mod[4])))
         context = kernels.gate_residual(context, cmod[2], a_txt)
@@ -201,11 +241,18 @@ class SingleBlock(nn.Module):
             kernels.gelu_tanh(self.proj_mlp(h), out=buf[..., d:])
             self.attn(h, image_rotary_emb=rope, text_len=text_len, token_offset=token_offset, out=buf[..., :d])
             return kernels.gate_residual(x, gate, self.proj_out(buf))
-        mlp = self.proj_mlp(h)
-        kernels.gelu_tanh(mlp, out=mlp)
+        # MLP branch beside the attention: its GEMM fills the SMs that the head-sharded attention grid leaves
+        # free and the time the two peer exchanges spend waiting on flags
+        B, S, d = x.shape
+        buf = torch.empty((B, S, 5 * d), dtype=x.dtype, device=x.device)
+        with _Branch(x.device) as br:
+            mlp = self.proj_mlp(h)
+            kernels.gelu_tanh(mlp, out=buf[..., d:])
         a = self.attn(h, image_rotary_emb=rope, text_len=text_len, token_offset=token_offset, text_offset=text_offset,
                       text_total=text_total)
-        return kernels.gate_residual(x, gate, self.proj_out(torch.cat([a, mlp], dim=-1)))
+        buf[..., :d].copy_(a)
+        br.join()
+        return kernels.gate_residual(x, gate, self.proj_out(buf))
 
 
 def rope_tables(ids: torch.Tensor, axes, theta: float = 10000.0):
