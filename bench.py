@@ -359,11 +359,22 @@ def run_kernel_case(args):
     dev = torch.device("cuda:0")
     torch.manual_seed(0)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    extra = {}
     if kind == "attn":
         B = int(arg or 1)
         q, k, v = (torch.randn(B, S_IMG + S_TXT, 24, 128, device=dev, dtype=torch.bfloat16) for _ in range(3))
         fn = lambda: kernels.attn_fwd([q], [k], [v])
         work = 4.0 * B * (S_IMG + S_TXT) ** 2 * 24 * 128
+        unit = "TFLOP/s"
+    elif kind in ("attnheads", "attnheads1"):
+        # the shape one rank attends after the Ulysses exchange: `arg` of the 24 heads, all 4608 tokens.
+        # "attnheads" lets the wrapper split the KV range (and reports its choice), "attnheads1" forbids it.
+        Hl = int(arg or 3)
+        q, k, v = (torch.randn(1, S_IMG + S_TXT, Hl, 128, device=dev, dtype=torch.bfloat16) for _ in range(3))
+        split = 1 if kind == "attnheads1" else None
+        fn = lambda: kernels.attn_fwd([q], [k], [v], kv_split=split)
+        extra["kv_split"] = 1 if split == 1 else kernels._pick_kv_split([q], [k], 1, Hl)
+        work = 4.0 * (S_IMG + S_TXT) ** 2 * Hl * 128
         unit = "TFLOP/s"
     elif kind == "copy":
         n = int(arg or 512) << 20
@@ -413,7 +424,8 @@ def run_kernel_case(args):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
     rate = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
-    print(json.dumps({"kernel_case": args.kernel_case, "ms_per_launch": ms, "rate": rate, "unit": unit}), flush=True)
+    print(json.dumps({"kernel_case": args.kernel_case, "ms_per_launch": ms, "rate": rate, "unit": unit, **extra}),
+          flush=True)
 
 
 USP_CASES = {
@@ -509,7 +521,9 @@ def main():
                          "sharding it with the image tokens")
     ap.add_argument("--profile-one-step", action="store_true",
                     help="wrap one extra eager step in cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--kernel-case", default="", help="profiling aid: attn:<batch> or copy:<MiB>")
+    ap.add_argument("--kernel-case", default="",
+                    help="one kernel instead of the step: attn:<batch>, attnheads:<heads> (attnheads1: no KV split), "
+                         "copy:<MiB>, normrope:<batch>, lnmod:<batch>, gate:<batch>, usp:<flux|cogvideox|hunyuan>")
     args = ap.parse_args()
     if args.kernel_case.startswith("usp:"):
         run_usp_case(args)

@@ -175,6 +175,7 @@ class PeerGroup:
         self.rank_in_group = self.ranks.index(my_global_rank) if my_global_rank in self.ranks else -1
         self.global_rank = my_global_rank
         self.heap = heap
+        self._gather_parity = {}
 
     @property
     def rank(self):
@@ -185,6 +186,46 @@ class PeerGroup:
             if self.heap is None:
                 raise RuntimeError("a multi-rank group needs the peer heap")
             self.heap.barrier(self.ranks, max_spins)
+
+    def all_gather(self, input_: torch.Tensor, dim: int = 0, separate_tensors: bool = False):
+        """GroupCoordinator.all_gather of the reference (core/distributed/group_coordinator.py:225-264): the
+        group's tensors concatenated along `dim` in group-rank order, or as a list when separate_tensors is
+        set. Used once per request for the sequence-parallel latents
+        (pipeline_stable_diffusion_3.py:1449,1660) and for the CFG halves (:1708).
+
+        Every rank stores its tensor into its slot of a gathered buffer in each peer's heap (one copy
+        launch), then a flag barrier. The result is copied out of the heap; two gathered buffers per shape
+        are used alternately, because a fast peer may start the next gather of the same shape before this
+        rank has copied the current one out (it cannot get two ahead: the barrier in between needs this
+        rank)."""
+        world = self.world_size
+        if world == 1:
+            return input_
+        if not -input_.dim() <= dim < input_.dim():
+            raise ValueError(f"Invalid dim ({dim}) for input tensor with shape {tuple(input_.size())}")
+        if self.heap is None:
+            raise RuntimeError("a multi-rank group needs the peer heap")
+        from ... import kernels
+        if dim < 0:
+            dim += input_.dim()
+        x = input_.contiguous()
+        key = (tuple(x.shape), x.dtype)
+        parity = self._gather_parity[key] = 1 - self._gather_parity.get(key, 0)
+        buf, off = self.heap.alloc((world,) + tuple(x.shape), x.dtype, name=f"all_gather{parity}_{key}_{self.ranks}")
+        nbytes = x.numel() * x.element_size()
+        if nbytes:
+            me = self.rank_in_group
+            kernels.copy_pieces([(x.data_ptr(), self.heap.peer_ptr(r, off) + me * nbytes, 1, 0, 0, 1, 0, 0, nbytes)
+                                 for r in self.ranks], x.device)
+        self.barrier()
+        out = buf.clone()
+        if separate_tensors:
+            return [out[i] for i in range(world)]
+        if dim != 0:
+            out = out.movedim(0, dim)
+        size = list(x.shape)
+        size[dim] *= world
+        return out.reshape(size)
 
     def next_rank(self):
         return self.ranks[(self.rank_in_group + 1) % self.world_size]

@@ -325,6 +325,7 @@ class BaseBlockCache:
         target_tp = tuple(new_tp_range) if new_tp_range is not None else tuple(old_tp_range)
         if set(self.active_block_indices) == set(required) and tuple(old_tp_range) == target_tp and all(
                 i in self.cache and self.cache[i][1] == target_tp for i in required):
+            self._last_p2p_preplans, self._last_p2p_all_pieces = {}, []   # nothing was needed
             return transformer
         plans, pieces = self.plan_needed_pieces(required, cpu_full_transformer, target_tp, slice_bias, component_name)
         if peer_directories:

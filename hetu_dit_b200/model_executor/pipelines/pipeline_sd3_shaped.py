@@ -72,10 +72,8 @@ class SD3ShapedPipeline:
         dtype = hidden_states.dtype
         temb = m.time_embed(timestep_embedding(timestep * 1000.0).to(dtype)) + m.pooled_embed(pooled)
         if ps.is_pipeline_first_stage():
-            n = hidden_states.shape[1]
-            tok0 = rt.pp_patches_token_start_idx_local[rt.pipeline_patch_idx] if rt.patch_mode else 0
-            pos = m._sincos_pos(self.grid[0], self.grid[1], hidden_states.device, dtype)
-            hidden_states = m.x_embedder(hidden_states) + pos[:, tok0:tok0 + n]
+            hidden_states = m.x_embedder(hidden_states) + self._positions(hidden_states.shape[1],
+                                                                          hidden_states.device, dtype)
             encoder_hidden_states = m.context_embedder(encoder_hidden_states)
         for i, block in self._stage_blocks():
             if rt.patch_mode and rt.pipeline_patch_idx == 0:
@@ -89,6 +87,39 @@ class SD3ShapedPipeline:
             shift, scale = m.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
             hidden_states = m.proj_out(_modulate(F.layer_norm(hidden_states, (d,), eps=1e-6), shift, scale))
         return hidden_states, encoder_hidden_states
+
+    def _positions(self, n, device, dtype):
+        """Position embeddings of the tokens this rank holds: the rows of the current patch (patch mode) or
+        of all its patches, by their global token index (under sequence parallelism a rank holds one slice of
+        every patch, so its tokens are not one contiguous range)."""
+        rt = get_runtime_state()
+        pos = self.model._sincos_pos(self.grid[0], self.grid[1], device, dtype)
+        bounds = rt.pp_patches_token_start_end_idx_global
+        if rt.patch_mode:
+            s, e = bounds[rt.pipeline_patch_idx]
+            out = pos[:, s:e]
+        elif ps.get_sequence_parallel_world_size() == 1:
+            out = pos[:, :n]
+        else:
+            out = torch.cat([pos[:, s:e] for s, e in bounds], dim=1)
+        if out.shape[1] != n:
+            raise ValueError(f"{n} tokens passed, the patch layout of this rank holds {out.shape[1]}")
+        return out
+
+    def _sp_local(self, latents):
+        """This sequence-parallel rank's tokens: its slice of every pipeline patch, patches in order (the
+        reference's _init_sync_pipeline, base_pipeline.py:327-335, on latent rows)."""
+        bounds = get_runtime_state().pp_patches_token_start_end_idx_global
+        return torch.cat([latents[:, s:e] for s, e in bounds], dim=1)
+
+    def _sp_gather(self, latents):
+        """Whole latents from every rank's local ones: gather, then patch by patch the ranks' slices in rank
+        order (pipeline_stable_diffusion_3.py:1449-1465, 1660-1677)."""
+        rt = get_runtime_state()
+        parts = ps.get_sp_group().all_gather(latents, separate_tensors=True)
+        starts = rt.pp_patches_token_start_idx_local
+        return torch.cat([part[:, starts[p]:starts[p + 1]] for p in range(rt.num_pipeline_patch) for part in parts],
+                         dim=1)
 
     def _backbone_forward(self, latents, encoder_hidden_states, pooled, t):
         if ps.is_pipeline_first_stage():
@@ -228,6 +259,9 @@ class SD3ShapedPipeline:
         self.encoder_hidden_states_cache = {}
         warmup = min(rt.runtime_config.warmup_steps, num_inference_steps)
         steps = list(range(num_inference_steps))
+        sp = ps.get_sequence_parallel_world_size()
+        if sp > 1:
+            latents = self._sp_local(latents)
         patched = rt.num_pipeline_patch > 1 and num_inference_steps > warmup
         if patched:
             latents = self._sync_pipeline(latents, prompt_embeds, pooled, steps[:warmup])
@@ -237,4 +271,6 @@ class SD3ShapedPipeline:
             if not ps.is_pipeline_last_stage():
                 latents = None
         rt.set_patched_mode(False)
+        if sp > 1 and latents is not None:
+            latents = self._sp_gather(latents)
         return latents

@@ -25,9 +25,33 @@ def flow_match_sigmas(num_steps, shift=3.0):
     return torch.cat([s, torch.zeros(1, dtype=torch.float64)]).float()
 
 
-def denoise(sd, shape, latents, prompt_embeds, pooled, num_steps, guidance_scale, num_patch_tokens, warmup_steps, grid):
+def warmup_cache_order(num_patch_tokens, ulysses):
+    """Token order of the stale-KV buffer a warm-up step leaves behind under Ulysses sequence parallelism.
+
+    Rank r holds slice r of every patch. After the head exchange of a whole-image step the gathered K/V is
+    ordered rank-major, patch-minor, and the reference stores it in that order
+    (core/resource_manager/cache_manager.py:170-184). Patch-mode updates then write the gathered patch p --
+    its slices in rank order, i.e. the patch in image order -- at [U * local_start[p], U * local_start[p+1])
+    (:186-205), which is the patch's place in *image* order. Until every patch has been refreshed once the
+    buffer therefore mixes the two orders: some stale rows are attended twice and some not at all. Returns
+    the image-order index of every buffer row after warm-up."""
+    starts = [0]
+    for n in num_patch_tokens:
+        starts.append(starts[-1] + n)
+    order = []
+    for r in range(ulysses):
+        for p, n in enumerate(num_patch_tokens):
+            share = n // ulysses
+            order.extend(range(starts[p] + r * share, starts[p] + (r + 1) * share))
+    return torch.tensor(order, dtype=torch.long)
+
+
+def denoise(sd, shape, latents, prompt_embeds, pooled, num_steps, guidance_scale, num_patch_tokens, warmup_steps, grid,
+            ulysses=1):
     """latents (1, S, token_in); prompt_embeds (2, S_txt, text_dim) = [uncond, cond]; pooled (2, pooled_dim).
-    num_patch_tokens: tokens per pipeline patch (pp_patches_token_num). Returns the final latents, fp32."""
+    num_patch_tokens: tokens per pipeline patch over all sequence-parallel ranks. ulysses: Ulysses degree of the
+    plan being modelled (it changes which stale rows the first patched step sees, see warmup_cache_order).
+    Returns the final latents, fp32."""
     sd = {k: v.float() for k, v in sd.items()}
     H, D, d = shape.heads, shape.head_dim, shape.hidden
     sig = flow_match_sigmas(num_steps)
@@ -40,6 +64,7 @@ def denoise(sd, shape, latents, prompt_embeds, pooled, num_steps, guidance_scale
     starts = [0]
     for n in num_patch_tokens:
         starts.append(starts[-1] + n)
+    order = warmup_cache_order(num_patch_tokens, ulysses) if ulysses > 1 and len(num_patch_tokens) > 1 else None
 
     def temb_of(i):
         t = sig[i].expand(2)
@@ -56,7 +81,8 @@ def denoise(sd, shape, latents, prompt_embeds, pooled, num_steps, guidance_scale
         for l in range(n_layers):
             def hook(k, v, l=l):
                 if patch is None:
-                    kv[l] = (k.clone(), v.clone())
+                    kv[l] = (k.clone(), v.clone()) if order is None else (k[:, order].clone(), v[:, order].clone())
+                    return k, v
                 else:
                     kv[l][0][:, lo:lo + n] = k
                     kv[l][1][:, lo:lo + n] = v

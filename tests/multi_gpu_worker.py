@@ -146,6 +146,36 @@ def model_sp_case(rank, world, port, kind, ulysses, errq):
         raise
 
 
+def all_gather_case(rank, world, port, errq):
+    """Group all_gather over peer stores: concatenation along a dim and separate tensors, bit-exact, repeated
+    with fresh data so that the alternating gathered buffers are exercised."""
+    try:
+        dist, ps, heap, dev = _setup(rank, world, port)
+        ps.initialize_model_parallel(sequence_parallel_degree=world, ulysses_degree=world)
+        g = ps.get_sp_group()
+        for rnd in range(4):
+            gen = torch.Generator().manual_seed(100 + rnd)
+            parts = [torch.randn(2, 16, 24, 32, generator=gen).bfloat16() for _ in range(world)]
+            mine = parts[rank].to(dev)
+            got = g.all_gather(mine, dim=0)
+            assert torch.equal(got.cpu(), torch.cat(parts, 0)), f"dim 0 round {rnd}"
+            got = g.all_gather(mine, dim=-2)
+            assert torch.equal(got.cpu(), torch.cat(parts, 2)), f"dim -2 round {rnd}"
+            lst = g.all_gather(mine.transpose(1, 2), separate_tensors=True)
+            assert len(lst) == world and all(torch.equal(a.cpu(), b.transpose(1, 2)) for a, b in zip(lst, parts))
+            ints = g.all_gather(torch.full((3,), rank * 10 + rnd, dtype=torch.int64, device=dev))
+            assert ints.cpu().tolist() == [r * 10 + rnd for r in range(world) for _ in range(3)]
+        heap.check()
+        solo = ps.get_tp_group()
+        x = torch.ones(3, device=dev)
+        assert solo.all_gather(x) is x          # single-rank group: the input itself, as in the reference
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errq.put(f"rank {rank}:\n{traceback.format_exc()}")
+        raise
+
+
 def pipefusion_case(rank, world, port, errq):
     """Ring of stages passes patches around twice; payloads must arrive bit-exact and in FIFO order."""
     try:

@@ -54,6 +54,12 @@ def test_pipefusion_patch_ring(world):
     _spawn(pipefusion_case, world)
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_group_all_gather(world):
+    from tests.multi_gpu_worker import all_gather_case
+    _spawn(all_gather_case, world)
+
+
 def test_barrier_timeout_is_reported_not_hung():
     from tests.multi_gpu_worker import barrier_timeout_case
     _spawn(barrier_timeout_case, 2)

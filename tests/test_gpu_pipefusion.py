@@ -112,6 +112,32 @@ def _worker_case(rank, world, port, errq):
         cos, rel = oa.cosine_and_max_rel(out.cpu(), want)
         assert cos >= 0.999 and rel <= 5e-2, ("solo", cos, rel)
         assert w.get_worker_state()["stage"] == "idle"
+
+        # plan C: Ulysses degree 2 over both GPUs, 4 patches of which every rank holds one half; nothing to
+        # migrate (both ranks hold all blocks). The whole latents come back on both ranks (end-of-denoise
+        # gather). The oracle models the order in which the reference keeps the stale K/V under Ulysses.
+        cfg2 = EngineConfig()
+        cfg2.parallel_config.sp_config.ulysses_degree = 2
+        cfg2.parallel_config.pp_config.num_pipeline_patch = 4
+        cfg2.runtime_config.warmup_steps = 1
+        w.switch_parallel_env(cfg2, [0, 1])
+        stats = w.hotspa_model()
+        assert stats["from_peers"] == 0 and stats["from_cpu"] == 0, stats
+        from hetu_dit_b200.core.distributed.runtime_state import get_runtime_state
+        out = w.execute_diffusion_stage(lat.to(dev), prompt.to(dev), pooled.to(dev), 4, height=512, width=256)
+        assert get_runtime_state().pp_patches_token_num == [64] * 4
+        want_sp = opf.denoise(sd, shape, lat, prompt, pooled, 4, 4.0, [128] * 4, 1, (32, 16), ulysses=2)
+        cos, rel = oa.cosine_and_max_rel(out.cpu(), want_sp)
+        assert cos >= 0.999 and rel <= 5e-2, ("ulysses2", cos, rel)
+        # and without patches the sequence-parallel result is the plain one
+        cfg3 = EngineConfig()
+        cfg3.parallel_config.sp_config.ulysses_degree = 2
+        w.switch_parallel_env(cfg3, [0, 1])
+        w.hotspa_model()
+        out = w.execute_diffusion_stage(lat.to(dev), prompt.to(dev), pooled.to(dev), 2, height=512, width=256)
+        want_full = opf.denoise(sd, shape, lat, prompt, pooled, 2, 4.0, [512], 0, (32, 16))
+        cos, rel = oa.cosine_and_max_rel(out.cpu(), want_full)
+        assert cos >= 0.999 and rel <= 5e-2, ("ulysses2 unpatched", cos, rel)
         dist.barrier()
         dist.destroy_process_group()
     except Exception:

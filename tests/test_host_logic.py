@@ -237,3 +237,12 @@ def test_two_rank_host_protocol_on_gloo():
         while not errq.empty():
             msgs.append(errq.get())
         pytest.fail("\n".join(msgs) or "gloo worker failed")
+
+
+def test_oracle_warmup_cache_order_under_ulysses():
+    """Rank-major, patch-minor order of the stale K/V a warm-up step leaves under Ulysses (the oracle's model of
+    cache_manager.py:170-184 of the reference); degree 1 is the identity."""
+    from oracle.pipefusion import warmup_cache_order
+    assert warmup_cache_order([4, 4], 1).tolist() == list(range(8))
+    assert warmup_cache_order([4, 4], 2).tolist() == [0, 1, 4, 5, 2, 3, 6, 7]
+    assert warmup_cache_order([4, 4, 2], 2).tolist() == [0, 1, 4, 5, 8, 2, 3, 6, 7, 9]
