@@ -113,3 +113,78 @@ def denoise(sd, shape, latents, prompt_embeds, pooled, num_steps, guidance_scale
                 new.append(xp + dt * backbone(xp, i, p))
             x = torch.cat(new, dim=1)
     return x
+
+
+def denoise_flux(sd, shape, latents, prompt_embeds, pooled, num_steps, guidance, num_patch_tokens, warmup_steps, grid,
+                 stage_starts=(0,)):
+    """PipeFusion denoising of the Flux-shaped model (double + single blocks, rotary positions, embedded
+    guidance, no classifier-free batch). latents (1, S, token_in); prompt_embeds (1, S_txt, text_dim); pooled
+    (1, pooled_dim); guidance: float. stage_starts: global index (double blocks first, then single blocks) of
+    the first block of every pipeline stage.
+
+    Follows the reference's Flux pipeline (hetu_dit/model_executor/pipelines/pipeline_flux.py: _sync_pipeline
+    :447-555, _async_pipeline :557-723) and transformer wrapper
+    (diffusion_executor/models/transformers/transformer_flux.py:101-206): every patch carries the text stream
+    through all blocks of the first stage again; a later stage receives the text stream only with patch 0 of a
+    step and re-uses it for the step's other patches (:598-603, :659-663). Stale K/V holds image tokens only."""
+    sd = {k: v.float() for k, v in sd.items()}
+    H, D, d = shape.heads, shape.head_dim, shape.hidden
+    sig = flow_match_sigmas(num_steps)
+    x = latents.float()
+    S, S_txt = x.shape[1], prompt_embeds.shape[1]
+    ids = torch.zeros(S_txt + S, 3)
+    yy, xx = torch.meshgrid(torch.arange(grid[0]), torch.arange(grid[1]), indexing="ij")
+    ids[S_txt:, 1], ids[S_txt:, 2] = yy.flatten(), xx.flatten()
+    rope = osd.rope_tables(ids, shape.rope_axes)
+    n_double, n_total = shape.n_double, shape.n_double + shape.n_single
+    kv = [None] * n_total
+    boundary_text = {}
+    starts = [0]
+    for n in num_patch_tokens:
+        starts.append(starts[-1] + n)
+    g_vec = torch.full((1,), float(guidance))
+
+    def backbone(tokens, i, patch):
+        t = sig[i].expand(1)
+        temb = (osd._mlp_embed(sd, "time_embed", osd._timestep_embedding(t * 1000.0))
+                + osd._mlp_embed(sd, "pooled_embed", pooled.float())
+                + osd._mlp_embed(sd, "guidance_embed", osd._timestep_embedding(g_vec * 1000.0)))
+        lo = 0 if patch is None else starts[patch]
+        n = tokens.shape[1]
+        hidden = osd._lin(sd, "x_embedder", tokens)
+        context = osd._lin(sd, "context_embedder", prompt_embeds.float())
+        for g in range(n_total):
+            if g > 0 and g in stage_starts and patch is not None:
+                if patch == 0:
+                    boundary_text[g] = context
+                else:
+                    context = boundary_text[g]
+
+            def hook(k, v, g=g):
+                if patch is None:
+                    kv[g] = (k.clone(), v.clone())
+                    return k, v
+                kv[g][0][:, lo:lo + n] = k
+                kv[g][1][:, lo:lo + n] = v
+                return kv[g]
+            if g < n_double:
+                hidden, context = osd.joint_block(sd, f"transformer_blocks.{g}", hidden, context, temb, rope, H, D,
+                                                  "front", kv_hook=hook, row0=S_txt + lo)
+            else:
+                xs = osd.single_block(sd, f"single_transformer_blocks.{g - n_double}", torch.cat([context, hidden], 1),
+                                      temb, rope, H, D, text_len=S_txt, row0=S_txt + lo, kv_hook=hook)
+                context, hidden = xs[:, :S_txt], xs[:, S_txt:]
+        shift, scale = osd._lin(sd, "norm_out.linear", F.silu(temb)).chunk(2, dim=-1)
+        return osd._lin(sd, "proj_out", osd._mod(F.layer_norm(hidden, (d,), eps=1e-6), shift, scale))
+
+    for i in range(num_steps):
+        dt = sig[i + 1] - sig[i]
+        if i < warmup_steps or len(num_patch_tokens) == 1:
+            x = x + dt * backbone(x, i, None)
+        else:
+            new = []
+            for p in range(len(num_patch_tokens)):
+                xp = x[:, starts[p]:starts[p + 1]]
+                new.append(xp + dt * backbone(xp, i, p))
+            x = torch.cat(new, dim=1)
+    return x

@@ -95,15 +95,29 @@ def joint_block(sd, p, hidden, context, temb, rope, H, D, order, kv_hook=None, r
     return hidden, context
 
 
-def single_block(sd, p, x, temb, rope, H, D):
+def single_block(sd, p, x, temb, rope, H, D, text_len=None, row0=None, kv_hook=None):
+    """x = [text; image] rows. text_len / row0: the first text_len rows take rotary rows [0, text_len), the
+    rest rows [row0, ...) (a patch of the image); kv_hook(k_img, v_img) -> (k_all, v_all) is PipeFusion's
+    stale-KV cache of the image tokens (attention_processor.py:898-917 of the reference)."""
     d = x.shape[-1]
     shift, scale, gate = _lin(sd, p + ".norm.linear", F.silu(temb)).chunk(3, dim=-1)
     h = _mod(F.layer_norm(x, (d,), eps=1e-6), shift, scale)
     mlp = F.gelu(_lin(sd, p + ".proj_mlp", h), approximate="tanh")
     a = p + ".attn.module"
-    q = _qk(sd, a, _lin(sd, a + ".to_q", h), H, D, "norm_q", rope, 0)
-    k = _qk(sd, a, _lin(sd, a + ".to_k", h), H, D, "norm_k", rope, 0)
+    if text_len is None:
+        q = _qk(sd, a, _lin(sd, a + ".to_q", h), H, D, "norm_q", rope, 0)
+        k = _qk(sd, a, _lin(sd, a + ".to_k", h), H, D, "norm_k", rope, 0)
+    else:
+        r0 = text_len if row0 is None else row0
+        ql, kl = _lin(sd, a + ".to_q", h), _lin(sd, a + ".to_k", h)
+        q = torch.cat([_qk(sd, a, ql[:, :text_len], H, D, "norm_q", rope, 0),
+                       _qk(sd, a, ql[:, text_len:], H, D, "norm_q", rope, r0)], dim=1)
+        k = torch.cat([_qk(sd, a, kl[:, :text_len], H, D, "norm_k", rope, 0),
+                       _qk(sd, a, kl[:, text_len:], H, D, "norm_k", rope, r0)], dim=1)
     v = _heads(_lin(sd, a + ".to_v", h), H, D)
+    if kv_hook is not None:
+        ki, vi = kv_hook(k[:, text_len:], v[:, text_len:])
+        k, v = torch.cat([k[:, :text_len], ki], dim=1), torch.cat([v[:, :text_len], vi], dim=1)
     o = oa.sdpa(q, k, v).reshape(x.shape[0], x.shape[1], d)
     return x + gate[:, None] * _lin(sd, p + ".proj_out", torch.cat([o, mlp], dim=-1))
 

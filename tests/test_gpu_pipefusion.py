@@ -54,6 +54,117 @@ def test_single_stage_patches_with_stale_kv():
     reset_cache_manager()
 
 
+def _tiny_flux():
+    from hetu_dit_b200.model_executor.models.shaped_dit import DiTShape, ShapedDiT
+    shape = DiTShape("flux-tiny", 2, 3, 256, 4, 64, 64, 128, 96, True, (16, 24, 24), True)
+    model = ShapedDiT(shape).init_weights(seed=21, std=0.05).bfloat16()
+    gen = torch.Generator().manual_seed(22)
+    lat = torch.randn(1, 32 * 16, 64, generator=gen).bfloat16()
+    prompt = torch.randn(1, 24, 128, generator=gen).bfloat16()
+    pooled = torch.randn(1, 96, generator=gen).bfloat16()
+    return shape, model, lat, prompt, pooled
+
+
+def test_flux_single_stage_patches_with_stale_kv():
+    """Flux-shaped PipeFusion on one stage: rotary rows per patch, stale K/V in double and single blocks."""
+    from hetu_dit_b200 import _C
+    from hetu_dit_b200.config import EngineConfig
+    from hetu_dit_b200.core.distributed import parallel_state as ps
+    from hetu_dit_b200.core.distributed.runtime_state import ModelGeometry, initialize_runtime_state, reset_runtime_state
+    from hetu_dit_b200.core.resource_manager.cache_manager import reset_cache_manager
+    from hetu_dit_b200.model_executor.pipelines.pipeline_flux_shaped import FluxShapedPipeline
+    from oracle import attention as oa
+    from oracle import pipefusion as opf
+    shape, model, lat, prompt, pooled = _tiny_flux()
+    dev = torch.device("cuda:0")
+    ps.destroy_model_parallel()
+    reset_cache_manager()
+    cfg = EngineConfig()
+    cfg.parallel_config.pp_config.num_pipeline_patch = 4
+    cfg.runtime_config.warmup_steps = 1
+    rt = initialize_runtime_state(ModelGeometry(4, 64), cfg)
+    rt.set_input_parameters(height=512, width=256, batch_size=1, num_inference_steps=4)
+    assert rt.pp_patches_token_num == [128] * 4
+    gpu_model = model.to(dev)
+    gpu_model.register_cache()
+    pipe = FluxShapedPipeline(gpu_model, guidance_scale=3.5, grid=(32, 16))
+    got = pipe.diffusion_stage(lat.to(dev), prompt.to(dev), pooled.to(dev), 4)
+    torch.cuda.synchronize()
+    assert _C.device_status(0, clear=True)[0] == 0
+    sd = {k: v.float().cpu() for k, v in gpu_model.state_dict().items()}
+    want = opf.denoise_flux(sd, shape, lat, prompt, pooled, 4, 3.5, [128] * 4, 1, (32, 16))
+    cos, rel = oa.cosine_and_max_rel(got.cpu(), want)
+    assert cos >= 0.999 and rel <= 5e-2, (cos, rel)
+    full = opf.denoise_flux(sd, shape, lat, prompt, pooled, 4, 3.5, [512], 1, (32, 16))
+    g = got.cpu().float()
+    assert (g - want).abs().mean() < (g - full).abs().mean()
+    reset_runtime_state()
+    reset_cache_manager()
+
+
+def _flux_worker_case(rank, world, port, errq):
+    """Two PipeFusion stages of the Flux-shaped model through the worker plan API: stage 0 holds the double
+    blocks, stage 1 the single blocks, which re-use the text stream that arrives with patch 0."""
+    import traceback
+    try:
+        import os
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from hetu_dit_b200.config import EngineConfig
+        from hetu_dit_b200.core.distributed.runtime_state import ModelGeometry
+        from hetu_dit_b200.model_executor.pipelines.pipeline_flux_shaped import FluxShapedPipeline
+        from hetu_dit_b200.worker.worker import Worker
+        from oracle import attention as oa
+        from oracle import pipefusion as opf
+
+        def exchange(obj):
+            out = [None] * world
+            dist.all_gather_object(out, obj)
+            return out
+
+        shape, model, lat, prompt, pooled = _tiny_flux()
+        sd = {k: v.float() for k, v in model.state_dict().items()}
+        w = Worker(rank, world, exchange=exchange, heap_bytes=128 << 20, arena_bytes=64 << 20)
+        w.init_static_env()
+        w.init_instance_model(model, ModelGeometry(4, 64), lambda t: FluxShapedPipeline(t, guidance_scale=3.5, grid=(32, 16)))
+        dev = w.device
+        cfg = EngineConfig()
+        cfg.parallel_config.pp_config.pp_degree = 2
+        cfg.parallel_config.pp_config.num_pipeline_patch = 4
+        cfg.runtime_config.warmup_steps = 1
+        w.switch_parallel_env(cfg, [0, 1])
+        w.hotspa_model()
+        assert sorted(w.cache.cache) == ([0, 1] if rank == 0 else [2, 3, 4])
+        out = w.execute_diffusion_stage(lat.to(dev), prompt.to(dev), pooled.to(dev), 4, height=512, width=256)
+        if rank == 1:
+            want = opf.denoise_flux(sd, shape, lat, prompt, pooled, 4, 3.5, [128] * 4, 1, (32, 16), stage_starts=(0, 2))
+            cos, rel = oa.cosine_and_max_rel(out.cpu(), want)
+            assert cos >= 0.999 and rel <= 5e-2, ("flux pp2", cos, rel)
+        else:
+            assert out is None
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errq.put(f"rank {rank}:\n{traceback.format_exc()}")
+        raise
+
+
+def test_flux_two_stage_pipeline_two_gpus():
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    try:
+        mp.spawn(_flux_worker_case, args=(2, 29813, errq), nprocs=2, join=True)
+    except Exception:
+        msgs = []
+        while not errq.empty():
+            msgs.append(errq.get())
+        pytest.fail("\n".join(msgs) or "worker failed")
+
+
 def _worker_case(rank, world, port, errq):
     import traceback
     try:

@@ -246,3 +246,30 @@ def test_oracle_warmup_cache_order_under_ulysses():
     assert warmup_cache_order([4, 4], 1).tolist() == list(range(8))
     assert warmup_cache_order([4, 4], 2).tolist() == [0, 1, 4, 5, 2, 3, 6, 7]
     assert warmup_cache_order([4, 4, 2], 2).tolist() == [0, 1, 4, 5, 8, 2, 3, 6, 7, 9]
+
+
+def test_oracle_flux_pipefusion_is_consistent_with_the_plain_step():
+    """The Flux-shaped PipeFusion oracle: one un-patched step is the plain model step + one Euler update; with as
+    many warm-up steps as steps the patches never matter; stale K/V makes the patched result differ, a little."""
+    import torch
+    from hetu_dit_b200.model_executor.models.shaped_dit import DiTShape, ShapedDiT
+    from oracle import pipefusion as opf
+    from oracle import shaped_dit as osd
+    shape = DiTShape("flux-tiny", 1, 2, 128, 2, 64, 64, 64, 32, True, (16, 24, 24), True)
+    sd = {k: v.float() for k, v in ShapedDiT(shape).init_weights(seed=5, std=0.05).state_dict().items()}
+    gen = torch.Generator().manual_seed(9)
+    lat = torch.randn(1, 8 * 4, 64, generator=gen)
+    txt = torch.randn(1, 6, 64, generator=gen)
+    pooled = torch.randn(1, 32, generator=gen)
+    sig = opf.flow_match_sigmas(1)
+    one = opf.denoise_flux(sd, shape, lat, txt, pooled, 1, 3.5, [32], 0, (8, 4))
+    step = osd.denoise_step(sd, shape, lat, txt, pooled, sig[:1], torch.tensor([3.5]), grid=(8, 4))
+    assert torch.allclose(one, lat + (sig[1] - sig[0]) * step, atol=1e-5)
+    full = opf.denoise_flux(sd, shape, lat, txt, pooled, 3, 3.5, [32], 0, (8, 4))
+    warm = opf.denoise_flux(sd, shape, lat, txt, pooled, 3, 3.5, [16, 16], 3, (8, 4))
+    assert torch.equal(full, warm)
+    patched = opf.denoise_flux(sd, shape, lat, txt, pooled, 3, 3.5, [16, 16], 1, (8, 4))
+    staged = opf.denoise_flux(sd, shape, lat, txt, pooled, 3, 3.5, [16, 16], 1, (8, 4), stage_starts=(0, 2))
+    diff = (patched - full).abs().max().item()
+    assert 0 < diff < 0.5 * full.abs().max().item()
+    assert 0 < (staged - patched).abs().max().item() < diff * 10
