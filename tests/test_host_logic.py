@@ -273,3 +273,25 @@ def test_oracle_flux_pipefusion_is_consistent_with_the_plain_step():
     diff = (patched - full).abs().max().item()
     assert 0 < diff < 0.5 * full.abs().max().item()
     assert 0 < (staged - patched).abs().max().item() < diff * 10
+
+
+def test_kv_split_choice_follows_the_wave_model():
+    """The wrapper's split-KV choice is pure host arithmetic: split when the grid leaves most SMs idle or
+    spills a little over a wave, never for grids that fill the GPU or for short KV ranges."""
+    from hetu_dit_b200.kernels import _pick_kv_split
+
+    class T:
+        def __init__(self, s, d):
+            self.shape = (1, s, 1, d)
+
+    def pick(batch, heads, d, s):
+        return _pick_kv_split([T(s, d)], [T(s, d)], batch, heads)
+
+    assert pick(1, 3, 128, 4608) == 2       # Ulysses 8 of 24 heads: 54 CTAs on 148 SMs
+    assert pick(1, 6, 128, 4608) == 1       # 108 CTAs: two half-length waves cost what one wave costs
+    assert pick(1, 24, 128, 4608) == 1      # the single-GPU grid
+    assert pick(1, 3, 128, 17776) == 2      # 210 CTAs = 1.4 waves -> 3 half-length waves
+    assert pick(1, 6, 128, 17776) == 1
+    assert pick(2, 3, 128, 377) == 1        # 3 KV blocks: nothing to split
+    # two query segments count their tiles separately, like the kernel's grid does
+    assert _pick_kv_split([T(512, 128), T(4096, 128)], [T(4608, 128)], 1, 3) == 2
