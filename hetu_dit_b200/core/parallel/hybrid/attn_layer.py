@@ -58,6 +58,40 @@ class _UlyssesExchange:
         g.barrier()
         return outs
 
+    def gather_heads_fused(self, query, key, value, prologue):
+        """gather_heads for Q, K and V with the per-head RMSNorm and the rotary embedding of Q and K applied on
+        the way: the kernel that normalises and rotates a row stores each head slice straight into the peer
+        that attends it, so the projections' output is read once and nothing is written locally.
+
+        prologue: [(row_lo, row_hi, q_norm_weight, k_norm_weight, eps, (cos, sin) or None, rope_row0)], row
+        ranges that tile [0, S_loc) -- one launch per range (ranges differ in norm weights or rotary rows)."""
+        g, U, me = self.group, self.group.world_size, self.group.rank_in_group
+        B, S, H, D = query.shape
+        if H % U != 0:
+            raise RuntimeError(f"{H} heads are not divisible by the Ulysses degree {U}")
+        if sorted((lo, hi) for lo, hi, *_ in prologue) != [(lo, hi) for lo, hi, *_ in prologue] or \
+                prologue[0][0] != 0 or prologue[-1][1] != S or \
+                any(a[1] != b[0] for a, b in zip(prologue, prologue[1:])):
+            raise ValueError("prologue row ranges must tile [0, S_loc) in order")
+        outs, dsts = [], []
+        for t, tag in zip((query, key, value), ("q", "k", "v")):
+            if tuple(t.shape) != (B, S, H, D):
+                raise ValueError("query, key and value must share one (B, S, H, D) shape")
+            buf, off = self.heap.alloc((B, U * S, H // U, D), t.dtype, name=f"usp_{tag}_{(B, S, H, D)}_{t.dtype}")
+            outs.append(buf)
+            dsts.append(kernels.RawDst([self.heap.peer_ptr(r, off) for r in g.ranks], buf.stride()[:3]))
+        for lo, hi, wq, wk, eps, rope, row0 in prologue:
+            if hi <= lo:
+                continue
+            cos, sin = rope if rope is not None else (None, None)
+            kernels.qk_norm_rope([(query[:, lo:hi], wq, wq is not None, rope is not None),
+                                  (key[:, lo:hi], wk, wk is not None, rope is not None),
+                                  (value[:, lo:hi], None, False, False)],
+                                 eps=eps, cos=cos, sin=sin, rope_seq_start=0, rope_row0=row0, dsts=dsts,
+                                 dst_seq_offset=me * S + lo)
+        g.barrier()
+        return outs
+
     def scatter_sequence(self, ctx: Tensor, tag: str, joint_len: int = 0, joint_front: bool = True) -> Tensor:
         """SeqAllToAll4D(scatter_idx=1, gather_idx=2): (B, U*S_loc, H/U, D) -> (B, S_loc, H, D).
 
@@ -125,7 +159,7 @@ class hetuDiTLongContextAttention(torch.nn.Module):
         self.ulysses_pg = ps.PROCESS_GROUP.ULYSSES_PG
 
     def _run(self, attn, query, key, value, joint_k, joint_v, joint_strategy, dropout_p, softmax_scale, causal,
-             window_size, alibi_slopes, deterministic, return_attn_probs, joint_q=None):
+             window_size, alibi_slopes, deterministic, return_attn_probs, joint_q=None, qk_prologue=None):
         """joint_q stays its own query segment. The reference concatenates it into every rank's query before
         the all-to-all, so each Ulysses rank attends U identical copies of the text queries; here the
         replicated rows are attended once per head slice and their context rows are sent to all peers."""
@@ -139,7 +173,17 @@ class hetuDiTLongContextAttention(torch.nn.Module):
                 if joint_q is not None:
                     joint_q = joint_q[..., hpr * r:hpr * (r + 1), :]
             xchg = _UlyssesExchange(self.ulysses_pg)
-            query, key, value = xchg.gather_heads([query, key, value], ["q", "k", "v"])
+            if qk_prologue is not None:
+                query, key, value = xchg.gather_heads_fused(query, key, value, qk_prologue)
+            else:
+                query, key, value = xchg.gather_heads([query, key, value], ["q", "k", "v"])
+        elif qk_prologue is not None:
+            for lo, hi, wq, wk, eps, rope, row0 in qk_prologue:
+                cos, sin = rope if rope is not None else (None, None)
+                if hi > lo and (wq is not None or rope is not None):
+                    kernels.qk_norm_rope([(query[:, lo:hi], wq, wq is not None, rope is not None),
+                                          (key[:, lo:hi], wk, wk is not None, rope is not None)],
+                                         eps=eps, cos=cos, sin=sin, rope_seq_start=0, rope_row0=row0)
         out = self.ring_attn_fn(query, key, value, dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal,
                                 window_size=window_size, alibi_slopes=alibi_slopes, deterministic=deterministic,
                                 return_attn_probs=return_attn_probs, group=self.ring_pg,
@@ -155,11 +199,17 @@ class hetuDiTLongContextAttention(torch.nn.Module):
     def forward(self, attn, query: Tensor, key: Tensor, value: Tensor, *, joint_tensor_query=None,
                 joint_tensor_key=None, joint_tensor_value=None, dropout_p=0.0, softmax_scale=None, causal=False,
                 window_size=(-1, -1), alibi_slopes=None, deterministic=False, return_attn_probs=False,
-                joint_strategy="none") -> Tensor:
-        """3 x (B, S/P, H, D) -> (B, S/P, H, D)."""
+                joint_strategy="none", qk_prologue=None) -> Tensor:
+        """3 x (B, S/P, H, D) -> (B, S/P, H, D).
+
+        qk_prologue (not in the reference's signature): per-head RMSNorm and rotary embedding of query and key
+        that the caller has *not* applied yet, as row ranges [(row_lo, row_hi, q_norm_weight, k_norm_weight,
+        eps, (cos, sin) or None, rope_row0)] tiling the local rows. Under Ulysses they are applied by the kernel
+        that performs the head exchange (one pass over the projections' output instead of two); without
+        Ulysses they are applied in place before the ring."""
         self._bind_groups()
         return self._run(attn, query, key, value, None, None, "none", dropout_p, softmax_scale, causal, window_size,
-                         alibi_slopes, deterministic, return_attn_probs)
+                         alibi_slopes, deterministic, return_attn_probs, qk_prologue=qk_prologue)
 
 
 class hetuDiTJointLongContextAttention(hetuDiTLongContextAttention):

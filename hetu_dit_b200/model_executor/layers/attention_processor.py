@@ -37,6 +37,13 @@ def _norm_rope(attn, q, k, wq, wk, rope, row0):
                          eps=wq.eps if do_norm else 1e-6, cos=cos, sin=sin, rope_seq_start=0, rope_row0=row0)
 
 
+def _prologue_range(lo, hi, wq, wk, rope, row0):
+    """One row range of the operator's qk_prologue: norm weights (or None), eps, rotary tables, first table row."""
+    do_norm = wq is not None
+    return (lo, hi, wq.weight if do_norm else None, wk.weight if do_norm else None, wq.eps if do_norm else 1e-6,
+            rope, row0)
+
+
 def _project_into(buf, row0, x, linear):
     """buf[:, row0:row0 + S] = linear(x) without a temporary when the rows are one contiguous block."""
     B, S, _ = x.shape
@@ -89,11 +96,10 @@ class JointAttnProcessor:
             _project_into(buf, t0, encoder_hidden_states, txt_p)
             bufs.append(_heads(buf, attn))
         q, k, v = bufs
-        _norm_rope(attn, q[:, i0:i0 + S_img], k[:, i0:i0 + S_img], attn.norm_q, attn.norm_k, rope,
-                   text_total + token_offset)
-        _norm_rope(attn, q[:, t0:t0 + S_txt], k[:, t0:t0 + S_txt], attn.norm_added_q, attn.norm_added_k, rope,
-                   text_offset)
-        out = self._plain.get()(attn, q, k, v, dropout_p=0.0, causal=False)
+        # QK-norm and RoPE ride on the head exchange (or run in place when the plan has no Ulysses exchange)
+        ranges = [_prologue_range(i0, i0 + S_img, attn.norm_q, attn.norm_k, rope, text_total + token_offset),
+                  _prologue_range(t0, t0 + S_txt, attn.norm_added_q, attn.norm_added_k, rope, text_offset)]
+        out = self._plain.get()(attn, q, k, v, dropout_p=0.0, causal=False, qk_prologue=sorted(ranges))
         out = out.reshape(B, S_txt + S_img, attn.heads * attn.head_dim)
         return attn.to_out[0](out[:, i0:i0 + S_img]), attn.to_add_out(out[:, t0:t0 + S_txt])
 
@@ -158,10 +164,10 @@ class SingleAttnProcessor:
         out4 = None if out is None else out.view(B, S, attn.heads, attn.head_dim)
         S_txt = int(text_len or 0)
         if text_offset is not None and ps.get_sequence_parallel_world_size() > 1:
-            _norm_rope(attn, q[:, :S_txt], k[:, :S_txt], attn.norm_q, attn.norm_k, image_rotary_emb, text_offset)
-            _norm_rope(attn, q[:, S_txt:], k[:, S_txt:], attn.norm_q, attn.norm_k, image_rotary_emb,
-                       int(text_total) + token_offset)
-            ctx = self._plain.get()(attn, q, k, v, dropout_p=0.0, causal=False)
+            ranges = [_prologue_range(0, S_txt, attn.norm_q, attn.norm_k, image_rotary_emb, text_offset),
+                      _prologue_range(S_txt, S, attn.norm_q, attn.norm_k, image_rotary_emb,
+                                      int(text_total) + token_offset)]
+            ctx = self._plain.get()(attn, q, k, v, dropout_p=0.0, causal=False, qk_prologue=ranges)
             return ctx.reshape(B, S, attn.heads * attn.head_dim)
         if token_offset == 0:
             _norm_rope(attn, q, k, attn.norm_q, attn.norm_k, image_rotary_emb, 0)
