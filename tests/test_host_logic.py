@@ -295,3 +295,39 @@ def test_kv_split_choice_follows_the_wave_model():
     assert pick(2, 3, 128, 377) == 1        # 3 KV blocks: nothing to split
     # two query segments count their tiles separately, like the kernel's grid does
     assert _pick_kv_split([T(512, 128), T(4096, 128)], [T(4608, 128)], 1, 3) == 2
+
+
+@pytest.mark.parametrize("sp,n_patch,height", [(2, 4, 64), (4, 2, 64), (2, 3, 48), (1, 4, 64)])
+def test_pipeline_sp_split_and_gather_round_trip(monkeypatch, sp, n_patch, height):
+    """Every SP rank takes its slice of every pipeline patch; the end-of-denoise gather re-interleaves them patch
+    by patch (pipeline_stable_diffusion_3.py:1449-1465 of the reference). Together they are the identity whenever
+    all patches have the same height. (With a shorter last patch the reference's own index lists pair the ranks'
+    slices inconsistently -- the golden bookkeeping fixtures pin that -- and its gather, like this one, is then
+    not the inverse of the split; the slices still cover every row once, which the last assertion of the split
+    loop checks for all cases.)"""
+    import types
+    import torch
+    from hetu_dit_b200.core.distributed.runtime_state import split_patches
+    from hetu_dit_b200.model_executor.pipelines import pipeline_sd3_shaped as mod
+    width = 32
+    tokens = (height // 2) * (width // 2)
+    latents = torch.arange(tokens * 3, dtype=torch.float32).view(1, tokens, 3)
+    metas = [split_patches(height, width, 2, n_patch, sp, r) for r in range(sp)]
+    pipe = mod.SD3ShapedPipeline.__new__(mod.SD3ShapedPipeline)
+    locals_ = []
+    for r in range(sp):
+        n, _, _, _, tok_local, tok_bounds, tok_num = metas[r]
+        rt = types.SimpleNamespace(num_pipeline_patch=n, pp_patches_token_start_idx_local=tok_local,
+                                   pp_patches_token_start_end_idx_global=tok_bounds, pp_patches_token_num=tok_num)
+        monkeypatch.setattr(mod, "get_runtime_state", lambda rt=rt: rt)
+        locals_.append(pipe._sp_local(latents))
+        assert locals_[-1].shape[1] == sum(tok_num)
+    assert sum(x.shape[1] for x in locals_) == tokens
+    group = types.SimpleNamespace(all_gather=lambda x, separate_tensors=False: list(locals_))
+    monkeypatch.setattr(mod.ps, "get_sp_group", lambda: group)
+    for r in range(sp):
+        n, _, _, _, tok_local, tok_bounds, tok_num = metas[r]
+        rt = types.SimpleNamespace(num_pipeline_patch=n, pp_patches_token_start_idx_local=tok_local,
+                                   pp_patches_token_start_end_idx_global=tok_bounds, pp_patches_token_num=tok_num)
+        monkeypatch.setattr(mod, "get_runtime_state", lambda rt=rt: rt)
+        assert torch.equal(pipe._sp_gather(locals_[r]), latents)

@@ -152,3 +152,29 @@ def test_usp_attention(path):
                 torch.testing.assert_close(ctx[:, dst * rows:(dst + 1) * rows], d[f"out_patch1_rank{dst}"][:, :, hs],
                                            rtol=2e-5, atol=2e-5)
             assert q_loc.shape[1] == rows
+
+
+def test_pipefusion_oracle_stale_kv_order_matches_the_reference_run():
+    """oracle/pipefusion.py models the stale K/V of a plan with Ulysses by a row order (warmup_cache_order) and
+    patch writes at image-order positions. The kv-cache fixture was recorded from the reference's own
+    CacheManager and operator on two ranks: the model must reproduce its patch-step outputs."""
+    from oracle import pipefusion as opf
+    path = os.path.join(os.path.dirname(__file__), "golden", "usp_kvcache_rear_u2.npz")
+    spec, d = _load_usp(path)
+    U, S_loc = spec["ulysses"], spec["s_loc"]
+    n_patch, tok = 2, S_loc // 2
+    B, S, H, D = d["k"].shape
+
+    def image_order(x):
+        # fixture rows are (rank, patch, i); the pipeline's image order is (patch, rank, i)
+        return x.view(B, U, n_patch, tok, H, D).transpose(1, 2).reshape(B, S, H, D)
+
+    order = opf.warmup_cache_order([U * tok] * n_patch, U)
+    buf_k, buf_v = image_order(d["k"])[:, order].clone(), image_order(d["v"])[:, order].clone()
+    assert torch.equal(buf_k, d["k"])               # after warm-up the buffer holds the gathered (rank-major) rows
+    lo = U * tok                                    # image-order start of patch 1 = where the reference writes it
+    buf_k[:, lo:lo + U * tok], buf_v[:, lo:lo + U * tok] = d["fresh_k"], d["fresh_v"]
+    keys, vals = torch.cat([buf_k, d["jk"]], 1), torch.cat([buf_v, d["jv"]], 1)
+    for r in range(U):
+        q = torch.cat([d["fresh_q"][:, r * tok:(r + 1) * tok], d["jq"]], 1)      # "rear": [local; joint]
+        torch.testing.assert_close(oa.sdpa(q, keys, vals), d[f"out_patch1_rank{r}"], rtol=2e-5, atol=2e-5)
