@@ -646,13 +646,17 @@ int launch(const AttnKernelParams& kp, int grid, int grid_y, cudaStream_t stream
 }
 
 // Merges the partial results of a split-KV launch: out = sum_s w_s O_s with w_s = exp(lse_s - lse),
-// lse = log sum_s exp(lse_s). One warp per (batch, query, head) row.
-template <int D, bool FP16>
+// lse = log sum_s exp(lse_s). One warp per (batch, query, head) row, one vector load per lane and split.
+// NS > 0 fixes the split count at compile time: all partial rows and LSEs of a row are then requested
+// before any of them is used (the kernel is latency-bound: 17 MB per call at the Flux shape).
+template <int D, bool FP16, int NS>
 __global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restrict__ part_out,
                                                           const float* __restrict__ part_lse, int n_split,
                                                           long long acc_stride, long long lse_stride, int batch,
                                                           long long sq, int heads, void* out, long long out_sb,
                                                           long long out_ss, long long out_sh, float* lse) {
+  constexpr int E = D / 32;  // floats per lane: 4 (D = 128) or 2 (D = 64)
+  constexpr int kMaxNs = NS > 0 ? NS : 1;
   const int lane = threadIdx.x & 31;
   const long long n_rows = static_cast<long long>(batch) * sq * heads;
   const long long warps = static_cast<long long>(gridDim.x) * 8;
@@ -662,25 +666,57 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restri
     const long long q = bq % sq;
     const int b = static_cast<int>(bq / sq);
     const long long lse_idx = (static_cast<long long>(b) * heads + h) * sq + q;
-    float mx = -INFINITY;
-    for (int s = 0; s < n_split; ++s) mx = fmaxf(mx, part_lse[s * lse_stride + lse_idx]);
-    float wsum = 0.f;
-    constexpr int E = D / 32;
+    const float* src0 = part_out + r * D + lane * E;
     float acc[E];
+    float mx = -INFINITY, wsum = 0.f;
+    if constexpr (NS > 0) {
+      float l[kMaxNs];
+      float o[kMaxNs][E];
 #pragma unroll
-    for (int i = 0; i < E; ++i) acc[i] = 0.f;
-    for (int s = 0; s < n_split; ++s) {
-      const float w = expf(part_lse[s * lse_stride + lse_idx] - mx);
-      wsum += w;
-      const float* src = part_out + s * acc_stride + r * D + lane * E;
+      for (int s = 0; s < NS; ++s) {
+        l[s] = part_lse[s * lse_stride + lse_idx];
+        if constexpr (E == 4) {
+          const float4 v = *reinterpret_cast<const float4*>(src0 + s * acc_stride);
+          o[s][0] = v.x, o[s][1] = v.y, o[s][2] = v.z, o[s][3] = v.w;
+        } else {
+          const float2 v = *reinterpret_cast<const float2*>(src0 + s * acc_stride);
+          o[s][0] = v.x, o[s][1] = v.y;
+        }
+      }
 #pragma unroll
-      for (int i = 0; i < E; ++i) acc[i] = fmaf(w, src[i], acc[i]);
+      for (int s = 0; s < NS; ++s) mx = fmaxf(mx, l[s]);
+#pragma unroll
+      for (int i = 0; i < E; ++i) acc[i] = 0.f;
+#pragma unroll
+      for (int s = 0; s < NS; ++s) {
+        const float w = expf(l[s] - mx);
+        wsum += w;
+#pragma unroll
+        for (int i = 0; i < E; ++i) acc[i] = fmaf(w, o[s][i], acc[i]);
+      }
+    } else {
+      for (int s = 0; s < n_split; ++s) mx = fmaxf(mx, part_lse[s * lse_stride + lse_idx]);
+#pragma unroll
+      for (int i = 0; i < E; ++i) acc[i] = 0.f;
+      for (int s = 0; s < n_split; ++s) {
+        const float w = expf(part_lse[s * lse_stride + lse_idx] - mx);
+        wsum += w;
+        const float* src = src0 + s * acc_stride;
+#pragma unroll
+        for (int i = 0; i < E; ++i) acc[i] = fmaf(w, src[i], acc[i]);
+      }
     }
     const float inv = 1.0f / wsum;
     uint16_t* dst = reinterpret_cast<uint16_t*>(out) + b * out_sb + q * out_ss + static_cast<long long>(h) * out_sh +
                     lane * E;
-#pragma unroll
-    for (int i = 0; i < E; i += 2) *reinterpret_cast<uint32_t*>(dst + i) = pack2<FP16>(acc[i] * inv, acc[i + 1] * inv);
+    if constexpr (E == 4) {
+      uint2 v;
+      v.x = pack2<FP16>(acc[0] * inv, acc[1] * inv);
+      v.y = pack2<FP16>(acc[2] * inv, acc[3] * inv);
+      *reinterpret_cast<uint2*>(dst) = v;
+    } else {
+      *reinterpret_cast<uint32_t*>(dst) = pack2<FP16>(acc[0] * inv, acc[1] * inv);
+    }
     if (lse != nullptr && lane == 0) lse[lse_idx] = mx + logf(wsum);
   }
 }
@@ -809,15 +845,23 @@ int attn_fwd_impl(const hdit_attn_args* a, int n_split, float* split_out, float*
   const long long n_rows = static_cast<long long>(a->batch) * sq * a->heads;
   long long blocks = (n_rows + 7) / 8;
   if (blocks > 148LL * 8) blocks = 148LL * 8;
-#define HDIT_COMBINE(DD, FF)                                                                                       \
-  attn_combine_kernel<DD, FF><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                                   \
+#define HDIT_COMBINE_NS(DD, FF, NN)                                                                                \
+  attn_combine_kernel<DD, FF, NN><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                               \
       split_out, split_lse, grid_y, kp.split_acc_stride, kp.split_lse_stride, a->batch, sq, a->heads, a->out,      \
       a->out_stride_b, a->out_stride_s, a->out_stride_h, a->lse)
+#define HDIT_COMBINE(DD, FF)                                                                                       \
+  do {                                                                                                             \
+    if (grid_y == 2) HDIT_COMBINE_NS(DD, FF, 2);                                                                   \
+    else if (grid_y == 3) HDIT_COMBINE_NS(DD, FF, 3);                                                              \
+    else if (grid_y == 4) HDIT_COMBINE_NS(DD, FF, 4);                                                              \
+    else HDIT_COMBINE_NS(DD, FF, 0);                                                                               \
+  } while (0)
   if (a->head_dim == 128) {
     if (fp16) HDIT_COMBINE(128, true); else HDIT_COMBINE(128, false);
   } else {
     if (fp16) HDIT_COMBINE(64, true); else HDIT_COMBINE(64, false);
   }
+#undef HDIT_COMBINE_NS
 #undef HDIT_COMBINE
   HDIT_CUDA_OK(cudaGetLastError());
   return HDIT_OK;
