@@ -3,6 +3,11 @@ with stale K/V), fp32, one process.
 
 TEST INFRASTRUCTURE ONLY. Nothing under hetu_dit_b200/ may import this module.
 
+Parity unpinned for the step and patch loops: the reference's pipelines subclass diffusers classes and
+diffusers is not installed, so they cannot be run to record fixtures. Pinned underneath: the patch index
+lists and the stale-KV update order (fixtures recorded from the reference's own runtime_state and
+CacheManager), attention and the rotary embedding.
+
 Restates the schedule of the reference's SD3 pipeline
 (hetu_dit/model_executor/pipelines/pipeline_stable_diffusion_3.py: _sync_pipeline :1352-1467,
 _async_pipeline :1515-1678, _backbone_forward with classifier-free guidance :1680-1717) and of its

@@ -11,6 +11,10 @@ reference's processors take without flash-attn or a GPU
 hetu_dit/envs.py:81-104). Token order follows the reference: [image; text] for
 the SD3 shape (:742-744), [text; image] for the Flux shape (:895-897).
 Also the timed CPU baseline of bench.py.
+
+Parity unpinned for the block wiring (adaLN order, residuals, MLP): it restates diffusers' MMDiT / Flux
+blocks from the architecture description, and diffusers is not installed to record fixtures from. Pinned
+underneath: attention, RMSNorm + rotary embedding (fixtures recorded from the reference's own code).
 """
 import math
 
