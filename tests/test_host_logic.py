@@ -331,3 +331,47 @@ def test_pipeline_sp_split_and_gather_round_trip(monkeypatch, sp, n_patch, heigh
                                    pp_patches_token_start_end_idx_global=tok_bounds, pp_patches_token_num=tok_num)
         monkeypatch.setattr(mod, "get_runtime_state", lambda rt=rt: rt)
         assert torch.equal(pipe._sp_gather(locals_[r]), latents)
+
+
+def test_flux_pipeline_stage_split_and_first_token(monkeypatch):
+    """Blocks are numbered double first, then single; a stage takes a contiguous range of that numbering. The
+    first token of a call selects its rotary rows: the patch's global start in patch mode."""
+    import types
+    from hetu_dit_b200.model_executor.pipelines import pipeline_flux_shaped as mod
+    pipe = mod.FluxShapedPipeline.__new__(mod.FluxShapedPipeline)
+    pipe.stage_sliced = False
+    pipe.model = types.SimpleNamespace(transformer_blocks=[f"d{i}" for i in range(3)],
+                                       single_transformer_blocks=[f"s{i}" for i in range(5)])
+    rt = types.SimpleNamespace(parallel_config=types.SimpleNamespace(pp_config=types.SimpleNamespace(
+        attn_layer_num_for_pp=None)), patch_mode=False, pipeline_patch_idx=0,
+        pp_patches_token_start_end_idx_global=[[0, 64], [128, 192]])
+    monkeypatch.setattr(mod, "get_runtime_state", lambda: rt)
+    got = []
+    for world in (1, 2, 4):
+        monkeypatch.setattr(mod.ps, "get_pipeline_parallel_world_size", lambda world=world: world)
+        stages = []
+        for r in range(world):
+            monkeypatch.setattr(mod.ps, "get_pipeline_parallel_rank", lambda r=r: r)
+            stages.append(pipe._stage_blocks())
+        got.append(stages)
+        assert sum((d for d, _ in stages), []) == pipe.model.transformer_blocks
+        assert sum((s for _, s in stages), []) == pipe.model.single_transformer_blocks
+    assert got[1] == [(["d0", "d1", "d2"], ["s0"]), ([], ["s1", "s2", "s3", "s4"])]
+    assert got[2] == [(["d0", "d1"], []), (["d2"], ["s0"]), ([], ["s1", "s2"]), ([], ["s3", "s4"])]
+    rt.parallel_config.pp_config.attn_layer_num_for_pp = [2, 6]
+    monkeypatch.setattr(mod.ps, "get_pipeline_parallel_world_size", lambda: 2)
+    monkeypatch.setattr(mod.ps, "get_pipeline_parallel_rank", lambda: 0)
+    assert pipe._stage_blocks() == (["d0", "d1"], [])
+    pipe.stage_sliced = True                      # the worker's block cache already placed this stage's blocks
+    assert pipe._stage_blocks() == (pipe.model.transformer_blocks, pipe.model.single_transformer_blocks)
+
+    monkeypatch.setattr(mod.ps, "get_sequence_parallel_world_size", lambda: 1)
+    assert pipe._first_token() == 0
+    rt.patch_mode, rt.pipeline_patch_idx = True, 1
+    assert pipe._first_token() == 128
+    rt.patch_mode = False
+    monkeypatch.setattr(mod.ps, "get_sequence_parallel_world_size", lambda: 2)
+    with pytest.raises(NotImplementedError):
+        pipe._first_token()
+    rt.pp_patches_token_start_end_idx_global = [[256, 512]]
+    assert pipe._first_token() == 256
