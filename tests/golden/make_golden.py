@@ -565,7 +565,7 @@ def gen_usp(ref):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of a Hetu-DiT checkout")
     ap.add_argument("--only", default="")
     a = ap.parse_args()
     logging.basicConfig(level=logging.ERROR)
