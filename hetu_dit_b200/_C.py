@@ -88,6 +88,7 @@ class NormRopeTensor(ctypes.Structure):
         ("x_stride_s", ctypes.c_int64),
         ("x_stride_h", ctypes.c_int64),
         ("norm_weight", ctypes.c_void_p),
+        ("norm_bias", ctypes.c_void_p),
         ("do_norm", ctypes.c_int32),
         ("do_rope", ctypes.c_int32),
         ("dst", ctypes.c_void_p * 8),

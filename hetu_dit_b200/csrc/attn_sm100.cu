@@ -49,6 +49,24 @@ constexpr uint32_t kSpinLimit = 8u * 1000u * 1000u;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 constexpr float kLn2 = 0.69314718055994531f;
 
+// Development aid (off in the shipped library): -DHDIT_ATTN_TRACE records SM cycle stamps of one CTA's
+// softmax and MMA phases for the first 64 KV blocks; hdit_attn_trace_read() copies them out.
+#ifdef HDIT_ATTN_TRACE
+__device__ long long g_attn_trace[2][64][8];      // [tile][block][event]
+__device__ long long g_attn_trace_mma[2][64][4];  // [tile][block][event]
+#define HDIT_TRACE_SM(ev)                                                                  \
+  do {                                                                                     \
+    if (trace_on && row == 0 && j < 64) g_attn_trace[t][j][ev] = clock64();                \
+  } while (0)
+#define HDIT_TRACE_MMA(tt, jj, ev)                                                         \
+  do {                                                                                     \
+    if (trace_on && (jj) < 64) g_attn_trace_mma[tt][jj][ev] = clock64();                   \
+  } while (0)
+#else
+#define HDIT_TRACE_SM(ev) do {} while (0)
+#define HDIT_TRACE_MMA(tt, jj, ev) do {} while (0)
+#endif
+
 enum Where : int {
   W_PROD_KEMPTY = 1,
   W_PROD_VEMPTY = 2,
@@ -89,16 +107,35 @@ struct alignas(64) AttnKernelParams {
   long long split_acc_stride, split_lse_stride;
 };
 
+// Tuning switches (compile-time so that variants can be measured against each other).
+//   HDIT_ATTN_STALE_MAX  1: from the second KV block on, exponentiate against the running maximum known
+//                           *before* the block (its own maximum is computed alongside and takes effect one
+//                           block later), which takes the row-maximum pass off the S -> P critical path.
+//   HDIT_ATTN_POLY8      of every 8 scores, how many (0, 2, 4) take a degree-3 polynomial exp2 on the FMA
+//                           pipe instead of ex2 on the special-function unit.
+//   HDIT_ATTN_VSTAGES128 V ring depth at head_dim 128 (K stays at 2: 227 KB of shared memory).
+#ifndef HDIT_ATTN_STALE_MAX
+#define HDIT_ATTN_STALE_MAX 1
+#endif
+#ifndef HDIT_ATTN_POLY8
+#define HDIT_ATTN_POLY8 0
+#endif
+#ifndef HDIT_ATTN_VSTAGES128
+#define HDIT_ATTN_VSTAGES128 3
+#endif
+constexpr float kOverflowGuard = 64.0f;  // log2 units a block may exceed the stale maximum before it is redone
+
 template <int D>
 struct Cfg {
   static constexpr int kPanels = D / 64;
   static constexpr int kTileBytes = kPanels * kPanelBytes;
-  static constexpr int kStages = (D == 128) ? 2 : 4;
+  static constexpr int kStagesK = (D == 128) ? 2 : 4;
+  static constexpr int kStagesV = (D == 128) ? HDIT_ATTN_VSTAGES128 : 4;
   static constexpr int kSmemQ = 2 * kTileBytes;
-  static constexpr int kSmemK = kStages * kTileBytes;
-  static constexpr int kSmemV = kStages * kTileBytes;
-  static constexpr int kNumBars = 2 + 4 * kStages + 6;
+  static constexpr int kSmemK = kStagesK * kTileBytes;
+  static constexpr int kSmemV = kStagesV * kTileBytes;
   static constexpr int kSmemBytes = kSmemQ + kSmemK + kSmemV + 1024 /*align*/ + 512 /*barriers etc.*/;
+  static_assert(kSmemBytes <= 232448, "exceeds the 227 KB a CTA may use");
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kColS = 0;      // + t * 128
   static constexpr uint32_t kColO = 256;    // + t * D
@@ -165,11 +202,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
   char* smem_v = smem_k + C::kSmemK;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_v + C::kSmemV);
   uint64_t* q_full = bars;                       // [2]
-  uint64_t* k_full = q_full + 2;                 // [stages]
-  uint64_t* k_empty = k_full + C::kStages;       // [stages]
-  uint64_t* v_full = k_empty + C::kStages;       // [stages]
-  uint64_t* v_empty = v_full + C::kStages;       // [stages]
-  uint64_t* s_full = v_empty + C::kStages;       // [2]
+  uint64_t* k_full = q_full + 2;                 // [K stages]
+  uint64_t* k_empty = k_full + C::kStagesK;      // [K stages]
+  uint64_t* v_full = k_empty + C::kStagesK;      // [V stages]
+  uint64_t* v_empty = v_full + C::kStagesV;      // [V stages]
+  uint64_t* s_full = v_empty + C::kStagesV;      // [2]
   uint64_t* p_ready = s_full + 2;                // [2]
   uint64_t* o_done = p_ready + 2;                // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
@@ -194,6 +231,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
   }
   float* const acc_out = p.acc_out + static_cast<long long>(blockIdx.y) * p.split_acc_stride;
   float* const acc_lse = p.acc_lse + static_cast<long long>(blockIdx.y) * p.split_lse_stride;
+#ifdef HDIT_ATTN_TRACE
+  const bool trace_on = blockIdx.x == gridDim.x / 2 && blockIdx.y == 0;
+#endif
 
   // ---- set-up ----------------------------------------------------------
   if (threadIdx.x == 0) {
@@ -204,9 +244,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       mbar_init(&p_ready[i], 128);
       mbar_init(&o_done[i], 1);
     }
-    for (int i = 0; i < C::kStages; ++i) {
+    for (int i = 0; i < C::kStagesK; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
+    }
+    for (int i = 0; i < C::kStagesV; ++i) {
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
     }
@@ -246,27 +288,27 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         for (int i = 0; i < j_begin; ++i) cur.advance(p);
         bool ok = true;
         for (int j = 0; j < nblk && ok; ++j) {
-          const int st = j % C::kStages;
-          const uint32_t n = static_cast<uint32_t>(j / C::kStages);
-          if (j >= C::kStages) {
-            if (!mbar_wait_bounded(&k_empty[st], (n - 1) & 1, abort_flag, kSpinLimit)) {
+          const int sk = j % C::kStagesK, sv = j % C::kStagesV;
+          const uint32_t nk = static_cast<uint32_t>(j / C::kStagesK), nv = static_cast<uint32_t>(j / C::kStagesV);
+          if (j >= C::kStagesK) {
+            if (!mbar_wait_bounded(&k_empty[sk], (nk - 1) & 1, abort_flag, kSpinLimit)) {
               report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_PROD_KEMPTY, j);
               ok = false;
               break;
             }
           }
-          mbar_expect_tx(&k_full[st], C::kTileBytes);
-          load_tile(&p.k_map[cur.seg], p.k_swap[cur.seg], smem_k + st * C::kTileBytes, &k_full[st], C::kPanels, h,
+          mbar_expect_tx(&k_full[sk], C::kTileBytes);
+          load_tile(&p.k_map[cur.seg], p.k_swap[cur.seg], smem_k + sk * C::kTileBytes, &k_full[sk], C::kPanels, h,
                     cur.row0, b);
-          if (j >= C::kStages) {
-            if (!mbar_wait_bounded(&v_empty[st], (n - 1) & 1, abort_flag, kSpinLimit)) {
+          if (j >= C::kStagesV) {
+            if (!mbar_wait_bounded(&v_empty[sv], (nv - 1) & 1, abort_flag, kSpinLimit)) {
               report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_PROD_VEMPTY, j);
               ok = false;
               break;
             }
           }
-          mbar_expect_tx(&v_full[st], C::kTileBytes);
-          load_tile(&p.v_map[cur.seg], p.v_swap[cur.seg], smem_v + st * C::kTileBytes, &v_full[st], C::kPanels, h,
+          mbar_expect_tx(&v_full[sv], C::kTileBytes);
+          load_tile(&p.v_map[cur.seg], p.v_swap[cur.seg], smem_v + sv * C::kTileBytes, &v_full[sv], C::kPanels, h,
                     cur.row0, b);
           cur.advance(p);
         }
@@ -335,13 +377,15 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
 
         const int last_t = tile1_valid ? 1 : 0;
         for (int j = 0; j < nblk && ok; ++j) {
-          const int st = j % C::kStages;
-          const uint32_t ph = static_cast<uint32_t>(j / C::kStages) & 1;
-          const int stn = (j + 1) % C::kStages;
-          const uint32_t phn = static_cast<uint32_t>((j + 1) / C::kStages) & 1;
+          const int st = j % C::kStagesV;                                       // V stage of block j
+          const uint32_t ph = static_cast<uint32_t>(j / C::kStagesV) & 1;
+          const int stn = (j + 1) % C::kStagesK;                                // K stage of block j + 1
+          const uint32_t phn = static_cast<uint32_t>((j + 1) / C::kStagesK) & 1;
           for (int t = 0; t <= last_t && ok; ++t) {
             if (t == 0) wait(&v_full[st], ph, W_MMA_VFULL, j);
+            HDIT_TRACE_MMA(t, j, 0);
             wait(&p_ready[t], j & 1, W_MMA_PREADY, j * 2 + t);
+            HDIT_TRACE_MMA(t, j, 1);
             if (!ok) break;
             tc_fence_after();
             issue_pv(t, st, j > 0);
@@ -356,6 +400,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
             } else {
               tc_commit(&o_done[t]);
             }
+            HDIT_TRACE_MMA(t, j, 2);
           }
         }
       }
@@ -379,6 +424,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       for (int i = 0; i < j_begin; ++i) cur.advance(p);
 
       for (int j = 0; j < nblk; ++j) {
+        HDIT_TRACE_SM(0);
         // warp-uniform outcome: the tcgen05.ld/st below need the whole warp converged
         if (!__all_sync(0xffffffffu, mbar_wait_bounded(&s_full[t], j & 1, abort_flag, kSpinLimit))) {
           report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_SM_SFULL, j * 2 + t);
@@ -386,10 +432,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
           break;
         }
         tc_fence_after();
+        HDIT_TRACE_SM(1);
         uint32_t s[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(tm_s + c * 32, s[c]);
         tc_wait_ld();
+        HDIT_TRACE_SM(2);
 
         const int valid = min(kBlockN, p.kv_len[cur.seg] - cur.row0);
         cur.advance(p);
@@ -432,6 +480,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
           }
         }
 
+        HDIT_TRACE_SM(3);
         // p = 2^(s * scale - m): packed fp32x2 FMA and add halve the issue slots of the row loop
         const float2 scale2 = make_float2(scale_log2, scale_log2);
         const float2 neg_m2 = make_float2(-m_run, -m_run);
@@ -456,9 +505,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         }
         const float sum0 = acc0.x + acc0.y, sum1 = acc1.x + acc1.y;
         l_run += sum0 + sum1;
+        HDIT_TRACE_SM(4);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(&p_ready[t]);
+        HDIT_TRACE_SM(5);
       }
 
       // ------------------------------ epilogue ------------------------------
@@ -725,6 +776,15 @@ int attn_fwd_impl(const hdit_attn_args* a, int n_split, float* split_out, float*
 
 }  // namespace
 }  // namespace hdit
+
+#ifdef HDIT_ATTN_TRACE
+extern "C" __attribute__((visibility("default"))) int hdit_attn_trace_read(long long* softmax_out, long long* mma_out) {
+  using namespace hdit;
+  HDIT_CUDA_OK(cudaMemcpyFromSymbol(softmax_out, g_attn_trace, sizeof(long long) * 2 * 64 * 8));
+  HDIT_CUDA_OK(cudaMemcpyFromSymbol(mma_out, g_attn_trace_mma, sizeof(long long) * 2 * 64 * 4));
+  return HDIT_OK;
+}
+#endif
 
 extern "C" int hdit_attn_fwd(const hdit_attn_args* a) { return hdit::attn_fwd_impl(a, 1, nullptr, nullptr); }
 

@@ -29,7 +29,8 @@ struct NormRopeTensor {
   const void* x;
   long long xs_b, xs_s, xs_h;
   const void* weight;  // 16-bit (D) or null
-  int do_norm;
+  const void* bias;    // 16-bit (D) or null (LayerNorm mode only)
+  int do_norm;         // 0 none, 1 RMSNorm, 2 LayerNorm
   int do_rope;
   void* dst[kMaxDst];
   long long ds_b, ds_s, ds_h;
@@ -102,7 +103,42 @@ __global__ void __launch_bounds__(512) norm_rope_kernel(const __grid_constant__ 
 #pragma unroll
       for (int i = 0; i < 8; ++i) f[i] = to_f<FP16>(e[i]);
 
-      if (t.do_norm) {
+      if (t.do_norm == 2) {
+        // LayerNorm over the head dimension (CogVideoX-style QK norm): fp32 throughout, one rounding,
+        // as torch's layer_norm does for 16-bit inputs
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum += f[i];
+#pragma unroll
+        for (int off = TPR / 2; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        const float mean = sum * (1.0f / D);
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          f[i] -= mean;
+          ss = fmaf(f[i], f[i], ss);
+        }
+#pragma unroll
+        for (int off = TPR / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        const float rstd = rsqrtf(ss * (1.0f / D) + p.eps);
+        float w[8], bb[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = 1.f, bb[i] = 0.f;
+        if (t.weight != nullptr) {
+          const uint4 wraw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(t.weight) + part * 8);
+          const uint16_t* wp = reinterpret_cast<const uint16_t*>(&wraw);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w[i] = to_f<FP16>(wp[i]);
+        }
+        if (t.bias != nullptr) {
+          const uint4 braw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(t.bias) + part * 8);
+          const uint16_t* bp = reinterpret_cast<const uint16_t*>(&braw);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) bb[i] = to_f<FP16>(bp[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = to_f<FP16>(from_f<FP16>(fmaf(f[i] * rstd, w[i], bb[i])));
+      } else if (t.do_norm) {
         float ss = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
@@ -176,6 +212,10 @@ extern "C" int hdit_qk_norm_rope(const hdit_norm_rope_args* a) {
     d.xs_s = s.x_stride_s;
     d.xs_h = s.x_stride_h;
     d.weight = s.norm_weight;
+    d.bias = s.norm_bias;
+    if (s.do_norm < 0 || s.do_norm > 2) return set_error(HDIT_ERR_BAD_ARG, "tensor %d: do_norm must be 0, 1 or 2", i);
+    if (s.norm_bias != nullptr && (reinterpret_cast<uintptr_t>(s.norm_bias) & 15))
+      return set_error(HDIT_ERR_SHAPE, "tensor %d: norm bias must be 16-byte aligned", i);
     d.do_norm = s.do_norm;
     d.do_rope = s.do_rope;
     any_rope |= s.do_rope != 0;

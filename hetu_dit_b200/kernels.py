@@ -272,8 +272,10 @@ def qk_norm_rope(tensors, *, eps=1e-6, cos=None, sin=None, rope_seq_start=0, rop
                  dst_seq_offset=0):
     """Fused RMSNorm + RoPE (+ head scatter) over up to three (B, S, H, D) tensors.
 
-    tensors: list of (x, norm_weight or None, do_norm, do_rope). dsts: None for in-place, or a list (one
-    entry per tensor) of lists of destination tensors (B, S_dst, H/n_dst, D); all tensors share n_dst.
+    tensors: list of (x, norm_weight or None, do_norm, do_rope[, norm_bias]). do_norm: False / 0 = none,
+    True / 1 = RMSNorm, 2 = LayerNorm over the head dimension (weight and bias optional). dsts: None for
+    in-place, or a list (one entry per tensor) of lists of destination tensors (B, S_dst, H/n_dst, D); all
+    tensors share n_dst.
     """
     x0 = tensors[0][0]
     B, S, H, D = x0.shape
@@ -289,14 +291,16 @@ def qk_norm_rope(tensors, *, eps=1e-6, cos=None, sin=None, rope_seq_start=0, rop
     a.rope_seq_start, a.rope_row0 = int(rope_seq_start), int(rope_row0)
     n_dst = 1 if dsts is None else len(dsts[0])
     a.n_dst = n_dst
-    for i, (x, w, do_norm, do_rope) in enumerate(tensors):
+    for i, (x, w, do_norm, do_rope, *rest) in enumerate(tensors):
+        bias = rest[0] if rest else None
         if tuple(x.shape) != (B, S, H, D) or x.stride(3) != 1:
             raise ValueError("all tensors must be (B, S, H, D) with contiguous D")
         t = a.t[i]
         t.x = x.data_ptr()
         t.x_stride_b, t.x_stride_s, t.x_stride_h = x.stride(0), x.stride(1), x.stride(2)
         t.norm_weight = w.data_ptr() if w is not None else None
-        t.do_norm, t.do_rope = int(bool(do_norm)), int(bool(do_rope))
+        t.norm_bias = bias.data_ptr() if bias is not None else None
+        t.do_norm, t.do_rope = int(do_norm), int(bool(do_rope))
         outs = [x] if dsts is None else dsts[i]
         if isinstance(outs, RawDst):
             for j, ptr in enumerate(outs.ptrs):
@@ -336,7 +340,7 @@ def ln_modulate(x, shift, scale, eps=1e-6, out=None):
     _require_cuda(x)
     if out is None:
         out = torch.empty(tuple(x.shape), dtype=x.dtype, device=x.device)
-    if x.shape[0] > 1 and not _even_rows(x):  # e.g. a token slice of a batch: one launch per batch element
+    if x.shape[0] > 1 and not (_even_rows(x) and _even_rows(out)):  # e.g. a token slice of a batch: one launch per batch element
         for b in range(x.shape[0]):
             ln_modulate(x[b:b + 1], shift[b:b + 1], scale[b:b + 1], eps, out[b:b + 1])
         return out
@@ -358,7 +362,7 @@ def gate_residual(x, gate, y, out=None):
         raise ValueError("x and y differ in shape")
     if out is None:
         out = torch.empty(tuple(x.shape), dtype=x.dtype, device=x.device)
-    if x.shape[0] > 1 and not (_even_rows(x) and _even_rows(y)):
+    if x.shape[0] > 1 and not (_even_rows(x) and _even_rows(y) and _even_rows(out)):
         for b in range(x.shape[0]):
             gate_residual(x[b:b + 1], gate[b:b + 1], y[b:b + 1], out[b:b + 1])
         return out

@@ -1,11 +1,14 @@
 """Attention processors of the -shaped DiT blocks.
 
 They play the role of the reference's hetuDiTJointAttnProcessor2_0 (SD3,
-hetu_dit/model_executor/diffusion_executor/layers/attention_processor.py:632-793)
-and hetuDiTFluxAttnProcessor2_0 (:797-987): QKV (+ added QKV) projections,
-per-head QK-RMSNorm, rotary embedding, PipeFusion stale-KV update, then either
-the single-GPU attention kernel or the USP operator, and the split back into
-image and text streams.
+hetu_dit/model_executor/diffusion_executor/layers/attention_processor.py:632-793),
+hetuDiTFluxAttnProcessor2_0 (:797-987), hetuDiTCogVideoXAttnProcessor2_0 (:991-1158) and
+hetuDiTHunyuanVideoAttnProcessor2_0 (:1346-1531): QKV (+ added QKV) projections,
+per-head QK norm, rotary embedding (on every row for Flux, on the video rows only
+for CogVideoX and HunyuanVideo), PipeFusion stale-KV update, then either the
+single-GPU attention kernel or the USP operator, and the split back into image
+and text streams. Token order: [image; text] ("rear") for SD3 and HunyuanVideo,
+[text; image] ("front") for Flux and CogVideoX.
 
 What is fused here and eager in the reference: norm + RoPE run as one in-place
 kernel over Q and K (the reference round-trips fp32 copies, :68-120); text and
@@ -26,20 +29,30 @@ def _heads(x, attn):
     return x.view(B, S, attn.heads, attn.head_dim)
 
 
-def _norm_rope(attn, q, k, wq, wk, rope, row0):
-    """In-place QK-RMSNorm and RoPE over (B, S, H, D) views; `row0` is the table row of token 0."""
-    do_norm = wq is not None
-    if not do_norm and rope is None:
+def _norm_entry(x, w, rope):
+    """One tensor of a qk_norm_rope call: (x, weight, norm code, rotate?, bias)."""
+    if w is None:
+        return (x, None, 0, rope is not None, None)
+    return (x, w.weight, w.kind, rope is not None, getattr(w, "bias", None))
+
+
+def _norm_rope(attn, q, k, wq, wk, rope, row0, rope_seq_start=0):
+    """In-place QK norm and RoPE over (B, S, H, D) views; rows below `rope_seq_start` are normalised but not
+    rotated, row `rope_seq_start` takes table row `row0`."""
+    if wq is None and rope is None:
+        return
+    if q.shape[1] == 0:
         return
     cos, sin = rope if rope is not None else (None, None)
-    kernels.qk_norm_rope([(q, wq.weight if do_norm else None, do_norm, rope is not None),
-                          (k, wk.weight if do_norm else None, do_norm, rope is not None)],
-                         eps=wq.eps if do_norm else 1e-6, cos=cos, sin=sin, rope_seq_start=0, rope_row0=row0)
+    kernels.qk_norm_rope([_norm_entry(q, wq, rope), _norm_entry(k, wk, rope)], eps=wq.eps if wq is not None else 1e-6,
+                         cos=cos, sin=sin, rope_seq_start=rope_seq_start, rope_row0=row0)
 
 
 def _prologue_range(lo, hi, wq, wk, rope, row0):
     """One row range of the operator's qk_prologue: norm weights (or None), eps, rotary tables, first table row."""
     do_norm = wq is not None
+    if do_norm and wq.kind != 1:
+        raise NotImplementedError("the fused head-exchange prologue applies RMSNorm only")
     return (lo, hi, wq.weight if do_norm else None, wk.weight if do_norm else None, wq.eps if do_norm else 1e-6,
             rope, row0)
 
@@ -53,22 +66,27 @@ def _project_into(buf, row0, x, linear):
         buf[:, row0:row0 + S] = linear(x)
 
 
-class _PlainOperator:
-    """Lazily built hetuDiTLongContextAttention (no joint tensors), rebuilt when the SP degree changes."""
+class _Operators:
+    """Lazily built USP operators of one attention layer, rebuilt when the SP degree changes (the reference
+    re-creates them in worker.py:1848-1983 on a plan switch)."""
 
     def __init__(self):
-        self.op, self.world = None, 0
+        self._ops, self._world = {}, 0
 
-    def get(self):
+    def get(self, cls):
         world = ps.get_sequence_parallel_world_size()
-        if self.op is None or self.world != world:
-            self.op, self.world = hetuDiTLongContextAttention(use_kv_cache=True), world
-        return self.op
+        if self._world != world:
+            self._ops, self._world = {}, world
+        if cls not in self._ops:
+            self._ops[cls] = cls(use_kv_cache=True)
+        return self._ops[cls]
 
 
 class JointAttnProcessor:
     """Double-stream (text + image) attention. joint_strategy "rear" = [image; text] (SD3 order,
-    attention_processor.py:742-744), "front" = [text; image] (Flux order, :895-897).
+    attention_processor.py:742-744; HunyuanVideo :1441-1443), "front" = [text; image] (Flux order, :895-897);
+    the owning Attention module's `text_first` selects it, its `rope_on_text` says whether the rotary table
+    has rows for the text tokens (Flux) or covers the image / video tokens only (HunyuanVideo :1410-1434).
 
     The reference keeps the whole text stream on every sequence-parallel rank and hands it to the USP
     operator as joint tensors. When the caller passes `text_offset` the text stream is sharded like the
@@ -79,15 +97,17 @@ class JointAttnProcessor:
     once instead of once per rank."""
 
     def __init__(self):
-        self.hybrid_seq_parallel_attn = None
-        self._hybrid_world = 0
-        self._plain = _PlainOperator()
+        self._ops = _Operators()
+
+    @property
+    def hybrid_seq_parallel_attn(self):
+        ops = list(self._ops._ops.values())
+        return ops[0] if ops else None
 
     def _sharded_text(self, attn, hidden_states, encoder_hidden_states, rope, text_total, token_offset, text_offset):
         B, S_img, _ = hidden_states.shape
         S_txt = encoder_hidden_states.shape[1]
-        front = rope is not None
-        t0, i0 = (0, S_txt) if front else (S_img, 0)
+        t0, i0 = (0, S_txt) if attn.text_first else (S_img, 0)
         bufs = []
         for img_p, txt_p in ((attn.to_q, attn.add_q_proj), (attn.to_k, attn.add_k_proj), (attn.to_v, attn.add_v_proj)):
             buf = torch.empty((B, S_txt + S_img, attn.heads * attn.head_dim), dtype=hidden_states.dtype,
@@ -97,23 +117,18 @@ class JointAttnProcessor:
             bufs.append(_heads(buf, attn))
         q, k, v = bufs
         # QK-norm and RoPE ride on the head exchange (or run in place when the plan has no Ulysses exchange)
-        ranges = [_prologue_range(i0, i0 + S_img, attn.norm_q, attn.norm_k, rope, text_total + token_offset),
-                  _prologue_range(t0, t0 + S_txt, attn.norm_added_q, attn.norm_added_k, rope, text_offset)]
-        out = self._plain.get()(attn, q, k, v, dropout_p=0.0, causal=False, qk_prologue=sorted(ranges))
+        text_rows = text_total if attn.rope_on_text else 0
+        ranges = [_prologue_range(i0, i0 + S_img, attn.norm_q, attn.norm_k, rope, text_rows + token_offset),
+                  _prologue_range(t0, t0 + S_txt, attn.norm_added_q, attn.norm_added_k,
+                                  rope if attn.rope_on_text else None, text_offset)]
+        out = self._ops.get(hetuDiTLongContextAttention)(attn, q, k, v, dropout_p=0.0, causal=False,
+                                                         qk_prologue=sorted(ranges, key=lambda r: r[0]))
         out = out.reshape(B, S_txt + S_img, attn.heads * attn.head_dim)
         return attn.to_out[0](out[:, i0:i0 + S_img]), attn.to_add_out(out[:, t0:t0 + S_txt])
 
-    def _operator(self, strategy):
-        world = ps.get_sequence_parallel_world_size()
-        if self.hybrid_seq_parallel_attn is None or self._hybrid_world != world:
-            cls = hetuDiTFluxLongContextAttention if strategy == "front" else hetuDiTJointLongContextAttention
-            self.hybrid_seq_parallel_attn = cls(use_kv_cache=True)
-            self._hybrid_world = world
-        return self.hybrid_seq_parallel_attn
-
     def __call__(self, attn, hidden_states, encoder_hidden_states=None, image_rotary_emb=None, text_len=None,
                  token_offset: int = 0, text_offset=None):
-        strategy = "front" if image_rotary_emb is not None else "rear"
+        strategy = "front" if attn.text_first else "rear"
         B, S_img, _ = hidden_states.shape
         S_txt = encoder_hidden_states.shape[1]
         if text_offset is not None and ps.get_sequence_parallel_world_size() > 1:
@@ -121,12 +136,15 @@ class JointAttnProcessor:
                                       int(text_len or S_txt), token_offset, text_offset)
         q, k, v = (_heads(p(hidden_states), attn) for p in (attn.to_q, attn.to_k, attn.to_v))
         tq, tk, tv = (_heads(p(encoder_hidden_states), attn) for p in (attn.add_q_proj, attn.add_k_proj, attn.add_v_proj))
-        _norm_rope(attn, q, k, attn.norm_q, attn.norm_k, image_rotary_emb, S_txt + token_offset)
-        _norm_rope(attn, tq, tk, attn.norm_added_q, attn.norm_added_k, image_rotary_emb, 0)
+        text_rows = S_txt if attn.rope_on_text else 0
+        _norm_rope(attn, q, k, attn.norm_q, attn.norm_k, image_rotary_emb, text_rows + token_offset)
+        _norm_rope(attn, tq, tk, attn.norm_added_q, attn.norm_added_k,
+                   image_rotary_emb if attn.rope_on_text else None, 0)
 
         if ps.get_sequence_parallel_world_size() > 1:
-            out = self._operator(strategy)(attn, q, k, v, dropout_p=0.0, causal=False, joint_tensor_query=tq,
-                                           joint_tensor_key=tk, joint_tensor_value=tv, joint_strategy=strategy)
+            cls = hetuDiTFluxLongContextAttention if strategy == "front" else hetuDiTJointLongContextAttention
+            out = self._ops.get(cls)(attn, q, k, v, dropout_p=0.0, causal=False, joint_tensor_query=tq,
+                                     joint_tensor_key=tk, joint_tensor_value=tv, joint_strategy=strategy)
         else:
             k, v = get_cache_manager().update_and_get_kv_cache(new_kv=[k, v], layer=attn, slice_dim=1,
                                                                layer_type="attn") if _cached(attn) else (k, v)
@@ -143,53 +161,94 @@ class JointAttnProcessor:
 
 
 class SingleAttnProcessor:
-    """Single-stream attention over the [text; image] sequence (Flux single blocks,
-    attention_processor.py:898-901 for the text/image split under SP)."""
+    """Single-stream attention over the [text; image] (Flux) or [image; text] (HunyuanVideo) sequence; the
+    text / image split under SP follows attention_processor.py:898-901 and :1464-1468."""
 
     def __init__(self):
-        self.hybrid_seq_parallel_attn = None
-        self._hybrid_world = 0
-        self._plain = _PlainOperator()
+        self._ops = _Operators()
+
+    @property
+    def hybrid_seq_parallel_attn(self):
+        ops = list(self._ops._ops.values())
+        return ops[0] if ops else None
 
     def __call__(self, attn, hidden_states, encoder_hidden_states=None, image_rotary_emb=None, text_len=None,
                  token_offset: int = 0, out=None, text_offset=None, text_total=None):
         """out: optional (B, S, H*D)-shaped view (any row stride) the single-GPU path writes into, e.g. the left
         part of the buffer the block's output projection reads, which saves a concatenation.
 
-        text_offset / text_total: the first `text_len` rows are rows [text_offset, text_offset + text_len) of
-        a text stream of text_total tokens that is sharded over the sequence-parallel ranks (see
+        text_len: how many of the rows are text rows (the first ones when the layer's `text_first` is set, the
+        last ones otherwise). text_offset / text_total: those rows are rows [text_offset, text_offset + text_len)
+        of a text stream of text_total tokens that is sharded over the sequence-parallel ranks (see
         JointAttnProcessor); None = the whole text stream is present on every rank, as in the reference."""
         B, S, _ = hidden_states.shape
         q, k, v = (_heads(p(hidden_states), attn) for p in (attn.to_q, attn.to_k, attn.to_v))
         out4 = None if out is None else out.view(B, S, attn.heads, attn.head_dim)
         S_txt = int(text_len or 0)
-        if text_offset is not None and ps.get_sequence_parallel_world_size() > 1:
-            ranges = [_prologue_range(0, S_txt, attn.norm_q, attn.norm_k, image_rotary_emb, text_offset),
-                      _prologue_range(S_txt, S, attn.norm_q, attn.norm_k, image_rotary_emb,
-                                      int(text_total) + token_offset)]
-            ctx = self._plain.get()(attn, q, k, v, dropout_p=0.0, causal=False, qk_prologue=ranges)
+        front = attn.text_first
+        t_lo, t_hi = (0, S_txt) if front else (S - S_txt, S)
+        i_lo, i_hi = (S_txt, S) if front else (0, S - S_txt)
+        rope = image_rotary_emb
+        rope_txt = rope if attn.rope_on_text else None
+        sp = ps.get_sequence_parallel_world_size()
+        if text_offset is not None and sp > 1:
+            text_rows = int(text_total) if attn.rope_on_text else 0
+            ranges = [_prologue_range(t_lo, t_hi, attn.norm_q, attn.norm_k, rope_txt, text_offset),
+                      _prologue_range(i_lo, i_hi, attn.norm_q, attn.norm_k, rope, text_rows + token_offset)]
+            ctx = self._ops.get(hetuDiTLongContextAttention)(attn, q, k, v, dropout_p=0.0, causal=False,
+                                                             qk_prologue=sorted(ranges, key=lambda r: r[0]))
             return ctx.reshape(B, S, attn.heads * attn.head_dim)
-        if token_offset == 0:
-            _norm_rope(attn, q, k, attn.norm_q, attn.norm_k, image_rotary_emb, 0)
+        text_rows = S_txt if attn.rope_on_text else 0
+        if front and attn.rope_on_text and token_offset == 0:
+            _norm_rope(attn, q, k, attn.norm_q, attn.norm_k, rope, 0)
+        elif front and not attn.rope_on_text:
+            _norm_rope(attn, q, k, attn.norm_q, attn.norm_k, rope, token_offset, rope_seq_start=S_txt)
         else:
-            _norm_rope(attn, q[:, :S_txt], k[:, :S_txt], attn.norm_q, attn.norm_k, image_rotary_emb, 0)
-            _norm_rope(attn, q[:, S_txt:], k[:, S_txt:], attn.norm_q, attn.norm_k, image_rotary_emb, S_txt + token_offset)
-        if ps.get_sequence_parallel_world_size() > 1:
-            world = ps.get_sequence_parallel_world_size()
-            if self.hybrid_seq_parallel_attn is None or self._hybrid_world != world:
-                self.hybrid_seq_parallel_attn = hetuDiTFluxLongContextAttention(use_kv_cache=True)
-                self._hybrid_world = world
-            out = self.hybrid_seq_parallel_attn(attn, q[:, S_txt:], k[:, S_txt:], v[:, S_txt:], dropout_p=0.0,
-                                                causal=False, joint_tensor_query=q[:, :S_txt],
-                                                joint_tensor_key=k[:, :S_txt], joint_tensor_value=v[:, :S_txt],
-                                                joint_strategy="front")
+            _norm_rope(attn, q[:, t_lo:t_hi], k[:, t_lo:t_hi], attn.norm_q, attn.norm_k, rope_txt, 0)
+            _norm_rope(attn, q[:, i_lo:i_hi], k[:, i_lo:i_hi], attn.norm_q, attn.norm_k, rope, text_rows + token_offset)
+        if sp > 1:
+            strategy = "front" if front else "rear"
+            cls = hetuDiTFluxLongContextAttention if front else hetuDiTJointLongContextAttention
+            out = self._ops.get(cls)(attn, q[:, i_lo:i_hi], k[:, i_lo:i_hi], v[:, i_lo:i_hi], dropout_p=0.0,
+                                     causal=False, joint_tensor_query=q[:, t_lo:t_hi], joint_tensor_key=k[:, t_lo:t_hi],
+                                     joint_tensor_value=v[:, t_lo:t_hi], joint_strategy=strategy)
         elif _cached(attn) and S_txt:
-            ki, vi = get_cache_manager().update_and_get_kv_cache(new_kv=[k[:, S_txt:], v[:, S_txt:]], layer=attn,
+            ki, vi = get_cache_manager().update_and_get_kv_cache(new_kv=[k[:, i_lo:i_hi], v[:, i_lo:i_hi]], layer=attn,
                                                                  slice_dim=1, layer_type="attn")
-            out = kernels.attn_fwd([q], [k[:, :S_txt], ki], [v[:, :S_txt], vi], out=out4)
+            out = kernels.attn_fwd([q], [k[:, t_lo:t_hi], ki], [v[:, t_lo:t_hi], vi], out=out4)
         else:
             out = kernels.attn_fwd([q], [k], [v], out=out4)
         return out.reshape(B, out.shape[1], attn.heads * attn.head_dim) if out4 is None else None
+
+
+class CogVideoXAttnProcessor:
+    """Attention of the CogVideoX block (attention_processor.py:991-1158): one set of Q/K/V projections over the
+    [text; video] rows, QK norm on every row, rotary embedding on the video rows only (:1075-1082). Under
+    sequence parallelism the text rows are replicated on every rank and travel as joint tensors with the
+    "front" strategy (:1117-1133); the reference passes attn=None there, so this model never uses the stale-KV
+    cache."""
+
+    def __init__(self):
+        self._ops = _Operators()
+
+    @property
+    def hybrid_seq_parallel_attn(self):
+        ops = list(self._ops._ops.values())
+        return ops[0] if ops else None
+
+    def __call__(self, attn, hidden_states, encoder_hidden_states=None, image_rotary_emb=None, text_len=None,
+                 token_offset: int = 0, **_):
+        B, S, _ = hidden_states.shape
+        T = int(text_len or 0)
+        q, k, v = (_heads(p(hidden_states), attn) for p in (attn.to_q, attn.to_k, attn.to_v))
+        _norm_rope(attn, q, k, attn.norm_q, attn.norm_k, image_rotary_emb, token_offset, rope_seq_start=T)
+        if ps.get_sequence_parallel_world_size() > 1:
+            out = self._ops.get(hetuDiTJointLongContextAttention)(
+                None, q[:, T:], k[:, T:], v[:, T:], dropout_p=0.0, causal=False, joint_tensor_query=q[:, :T],
+                joint_tensor_key=k[:, :T], joint_tensor_value=v[:, :T], joint_strategy="front")
+        else:
+            out = kernels.attn_fwd([q], [k], [v])
+        return out.reshape(B, S, attn.heads * attn.head_dim)
 
 
 def _cached(attn) -> bool:
@@ -200,3 +259,5 @@ def _cached(attn) -> bool:
 hetuDiTJointAttnProcessor2_0 = JointAttnProcessor
 hetuDiTFluxAttnProcessor2_0 = JointAttnProcessor
 hetuDiTFluxSingleAttnProcessor2_0 = SingleAttnProcessor
+hetuDiTCogVideoXAttnProcessor2_0 = CogVideoXAttnProcessor
+hetuDiTHunyuanVideoAttnProcessor2_0 = JointAttnProcessor

@@ -1,12 +1,17 @@
-"""SD3-medium-shaped and Flux.1-dev-shaped MMDiT denoisers with seeded random weights.
+"""SD3-medium-, Flux.1-dev-, CogVideoX-1.5-5B- and HunyuanVideo-shaped DiT denoisers with seeded random weights.
 
 The reference takes its block definitions from diffusers (absent here) and wraps
 them (hetu_dit/model_executor/diffusion_executor/models/transformers/
-transformer_sd3.py:29-198, transformer_flux.py:30-221). These classes restate
-the architecture from its published shape -- joint (double-stream) blocks with
-adaLN-Zero modulation, optional single-stream blocks, per-head QK RMSNorm,
-3-axis rotary embedding for the Flux shape -- so that one denoising step has the
-reference model's tensor shapes, FLOPs and memory traffic. Module names follow
+transformer_sd3.py:29-198, transformer_flux.py:30-221,
+cogvideox_transformer_3d.py:30-175, transformer_hunyuan_video.py:56-345). These
+classes restate the architectures from their published shapes -- joint
+(double-stream) blocks with adaLN-Zero modulation, optional single-stream blocks,
+per-head QK RMSNorm, 3-axis rotary embedding (Flux: over text and image rows;
+HunyuanVideo: video rows only, text rows last), and the CogVideoX block (one set
+of attention / MLP weights over [text; video] rows, separate adaLN vectors per
+stream, LayerNorm over the head dimension of Q and K, rotary embedding on the
+video rows only) -- so that one denoising step has the reference model's tensor
+shapes, token order, FLOPs and memory traffic. Module names follow
 the reference's wrapped layout (`attn.module.to_q`, `ff.module.net.0.proj`,
 ...) because parameter-slice migration addresses Linear layers by those names
 (hetu_dit/model_executor/cache/transformer_cache.py:113-154).
@@ -24,7 +29,7 @@ import torch.nn.functional as F
 
 from ... import kernels
 from ...core.distributed import parallel_state as ps
-from ..layers.attention_processor import JointAttnProcessor, SingleAttnProcessor
+from ..layers.attention_processor import CogVideoXAttnProcessor, JointAttnProcessor, SingleAttnProcessor
 
 
 @dataclass
@@ -43,14 +48,36 @@ class DiTShape:
     guidance_embed: bool
     latent_channels: int = 16
     patch: int = 2
+    text_first: Optional[bool] = None    # token order [text; image] ("front"); None: True when there is a rotary table
+    rope_on_text: bool = True            # the rotary table has (zero-angle) rows for the text tokens (Flux)
+    qk_norm_kind: str = "rms"            # "rms" or "layer" (LayerNorm with weight and bias over head_dim)
+    block_kind: str = "mmdit"            # "mmdit": double (+ single) stream blocks; "cogvideox": n_double CogVideoX blocks
+    temb_dim: Optional[int] = None       # width of the timestep embedding; None = hidden
+
+    def __post_init__(self):
+        if self.text_first is None:
+            self.text_first = self.rope_axes is not None
+        if self.temb_dim is None:
+            self.temb_dim = self.hidden
 
     @property
     def n_blocks(self):
         return self.n_double + self.n_single
 
+    @property
+    def joint_strategy(self):
+        return "front" if self.text_first else "rear"
+
 
 SD3_MEDIUM = DiTShape("sd3-medium", 24, 0, 1536, 24, 64, 64, 4096, 2048, False, None, False)
 FLUX_DEV = DiTShape("flux.1-dev", 19, 38, 3072, 24, 128, 64, 4096, 768, True, (16, 56, 56), True)
+# 42 blocks, 48 x 64 heads, patch 2x2x2 over a 16-channel latent (128 features per token), text front, rotary
+# embedding on the video rows only, no pooled text vector, 512-wide timestep embedding
+COGVIDEOX_5B = DiTShape("cogvideox-1.5-5b", 42, 0, 3072, 48, 64, 128, 4096, 0, True, (16, 24, 24), False,
+                        text_first=True, rope_on_text=False, qk_norm_kind="layer", block_kind="cogvideox", temb_dim=512)
+# 20 double + 40 single blocks, 24 x 128 heads, patch 1x2x2 (64 features per token), text rear
+HUNYUAN_VIDEO = DiTShape("hunyuanvideo", 20, 40, 3072, 24, 128, 64, 4096, 768, True, (16, 56, 56), True,
+                         text_first=False, rope_on_text=False)
 
 
 def timestep_embedding(t: torch.Tensor, dim: int = 256, max_period: float = 10000.0) -> torch.Tensor:
@@ -104,10 +131,22 @@ class FeedForward(nn.Module):
 
 class RMSNormWeight(nn.Module):
     """Holds the per-head RMSNorm weight; the normalisation itself is fused into the QK kernel."""
+    kind = 1  # do_norm code of the kernel
 
     def __init__(self, dim, eps=1e-6):
         super().__init__()
         self.weight = nn.Parameter(torch.ones(dim))
+        self.eps = eps
+
+
+class LayerNormWeight(nn.Module):
+    """Weight and bias of a LayerNorm over the head dimension (the QK norm of the CogVideoX shape)."""
+    kind = 2
+
+    def __init__(self, dim, eps=1e-6):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.bias = nn.Parameter(torch.zeros(dim))
         self.eps = eps
 
 
@@ -116,16 +155,21 @@ class Attention(nn.Module):
         super().__init__()
         d = shape.hidden
         self.heads, self.head_dim = shape.heads, shape.head_dim
+        self.text_first, self.rope_on_text = bool(shape.text_first), bool(shape.rope_on_text)
+        norm_cls = LayerNormWeight if shape.qk_norm_kind == "layer" else RMSNormWeight
         self.to_q, self.to_k, self.to_v = nn.Linear(d, d), nn.Linear(d, d), nn.Linear(d, d)
-        self.norm_q = RMSNormWeight(shape.head_dim) if shape.qk_norm else None
-        self.norm_k = RMSNormWeight(shape.head_dim) if shape.qk_norm else None
+        self.norm_q = norm_cls(shape.head_dim) if shape.qk_norm else None
+        self.norm_k = norm_cls(shape.head_dim) if shape.qk_norm else None
         self.to_out = nn.ModuleList([nn.Linear(d, d), nn.Identity()]) if out_proj else None
         if joint:
             self.add_q_proj, self.add_k_proj, self.add_v_proj = nn.Linear(d, d), nn.Linear(d, d), nn.Linear(d, d)
-            self.norm_added_q = RMSNormWeight(shape.head_dim) if shape.qk_norm else None
-            self.norm_added_k = RMSNormWeight(shape.head_dim) if shape.qk_norm else None
+            self.norm_added_q = norm_cls(shape.head_dim) if shape.qk_norm else None
+            self.norm_added_k = norm_cls(shape.head_dim) if shape.qk_norm else None
             self.to_add_out = nn.Linear(d, d)
-        self.processor = JointAttnProcessor() if joint else SingleAttnProcessor()
+        if shape.block_kind == "cogvideox":
+            self.processor = CogVideoXAttnProcessor()
+        else:
+            self.processor = JointAttnProcessor() if joint else SingleAttnProcessor()
 
     def forward(self, hidden_states, encoder_hidden_states=None, image_rotary_emb=None, text_len=None,
                 token_offset=0, **kw):
@@ -255,6 +299,46 @@ class SingleBlock(nn.Module):
         return kernels.gate_residual(x, gate, self.proj_out(buf))
 
 
+class CogVideoXBlock(nn.Module):
+    """CogVideoX-shaped block: text and video rows share the attention and MLP weights but take their own
+    adaLN-Zero vectors (two sets of six: around the attention and around the MLP); attention runs over
+    [text; video]."""
+
+    def __init__(self, shape: DiTShape):
+        super().__init__()
+        d = shape.hidden
+        self.norm1 = nn.Module()
+        self.norm1.linear = nn.Linear(shape.temb_dim, 6 * d)
+        self.attn1 = _Wrapped(Attention(shape, joint=False, out_proj=True))
+        self.norm2 = nn.Module()
+        self.norm2.linear = nn.Linear(shape.temb_dim, 6 * d)
+        self.ff = _Wrapped(FeedForward(d))
+        self.d = d
+
+    def modulation(self, silu_temb):
+        return self.norm1.linear(silu_temb).chunk(6, dim=-1), self.norm2.linear(silu_temb).chunk(6, dim=-1)
+
+    def forward(self, hidden, context, temb, rope, token_offset=0, mods=None):
+        """hidden (B, S_vid, d) video rows of this rank, context (B, S_txt, d) all text rows. Each vector set is
+        (shift, scale, gate) for the video rows followed by (shift, scale, gate) for the text rows."""
+        m1, m2 = mods if mods is not None else self.modulation(F.silu(temb))
+        B, S_vid, d = hidden.shape
+        S_txt = context.shape[1]
+        x = torch.empty((B, S_txt + S_vid, d), dtype=hidden.dtype, device=hidden.device)
+        kernels.ln_modulate(context, m1[3], m1[4], out=x[:, :S_txt])
+        kernels.ln_modulate(hidden, m1[0], m1[1], out=x[:, S_txt:])
+        attn = self.attn1.module
+        a = attn.to_out[0](self.attn1(x, image_rotary_emb=rope, text_len=S_txt, token_offset=token_offset))
+        hidden = kernels.gate_residual(hidden, m1[2], a[:, S_txt:])
+        context = kernels.gate_residual(context, m1[5], a[:, :S_txt])
+        kernels.ln_modulate(context, m2[3], m2[4], out=x[:, :S_txt])
+        kernels.ln_modulate(hidden, m2[0], m2[1], out=x[:, S_txt:])
+        f = self.ff(x)
+        hidden = kernels.gate_residual(hidden, m2[2], f[:, S_txt:])
+        context = kernels.gate_residual(context, m2[5], f[:, :S_txt])
+        return hidden, context
+
+
 def rope_tables(ids: torch.Tensor, axes, theta: float = 10000.0):
     """cos / sin tables (S, D) for integer position ids (S, 3); each axis owns axes[i] dims, pairs share a frequency."""
     cos, sin = [], []
@@ -273,13 +357,16 @@ class ShapedDiT(nn.Module):
         d = shape.hidden
         self.x_embedder = nn.Linear(shape.token_in, d)
         self.context_embedder = nn.Linear(shape.text_dim, d)
-        self.time_embed = _MLPEmbed(256, d)
-        self.pooled_embed = _MLPEmbed(shape.pooled_dim, d)
-        self.guidance_embed = _MLPEmbed(256, d) if shape.guidance_embed else None
-        self.transformer_blocks = nn.ModuleList([JointBlock(shape) for _ in range(shape.n_double)])
+        self.time_embed = _MLPEmbed(256, shape.temb_dim)
+        self.pooled_embed = _MLPEmbed(shape.pooled_dim, shape.temb_dim) if shape.pooled_dim else None
+        self.guidance_embed = _MLPEmbed(256, shape.temb_dim) if shape.guidance_embed else None
+        block_cls = CogVideoXBlock if shape.block_kind == "cogvideox" else JointBlock
+        self.transformer_blocks = nn.ModuleList([block_cls(shape) for _ in range(shape.n_double)])
         self.single_transformer_blocks = nn.ModuleList([SingleBlock(shape) for _ in range(shape.n_single)])
+        # the CogVideoX shape normalises [text; video] once more (with weight and bias) before the output adaLN
+        self.norm_final = nn.LayerNorm(d, eps=1e-5) if shape.block_kind == "cogvideox" else None
         self.norm_out = nn.Module()
-        self.norm_out.linear = nn.Linear(d, 2 * d)
+        self.norm_out.linear = nn.Linear(shape.temb_dim, 2 * d)
         self.proj_out = nn.Linear(d, shape.token_in)
         if shape.rope_axes is None:
             self.pos_embed_max = 192  # learned-position stand-in: sin-cos table cropped to the latent grid
@@ -314,14 +401,19 @@ class ShapedDiT(nn.Module):
             if isinstance(m, Attention):
                 get_cache_manager().register_cache_entry(m, "attn", kind)
 
-    def _rope(self, text_len, grid_h, grid_w, device):
-        key = (text_len, grid_h, grid_w, str(device))
+    def _rope(self, text_rows, grid, device):
+        """cos / sin tables with `text_rows` zero-angle rows followed by one row per latent token of `grid`
+        ((rows, cols) for images, (frames, rows, cols) for video; axis 0 of the ids is the frame index)."""
+        grid = tuple(int(g) for g in grid)
+        key = (text_rows, grid, str(device))
         if key not in self._rope_cache:
-            ids = torch.zeros(text_len + grid_h * grid_w, 3, device=device)
-            yy, xx = torch.meshgrid(torch.arange(grid_h, device=device), torch.arange(grid_w, device=device),
-                                    indexing="ij")
-            ids[text_len:, 1] = yy.flatten()
-            ids[text_len:, 2] = xx.flatten()
+            g3 = grid if len(grid) == 3 else (1,) + grid
+            n = g3[0] * g3[1] * g3[2]
+            ids = torch.zeros(text_rows + n, 3, device=device)
+            tt, yy, xx = torch.meshgrid(*(torch.arange(g, device=device) for g in g3), indexing="ij")
+            ids[text_rows:, 0] = tt.flatten()
+            ids[text_rows:, 1] = yy.flatten()
+            ids[text_rows:, 2] = xx.flatten()
             self._rope_cache[key] = rope_tables(ids, self.shape.rope_axes)
         return self._rope_cache[key]
 
@@ -340,13 +432,16 @@ class ShapedDiT(nn.Module):
         return self._rope_cache[key]
 
     def forward(self, latent_tokens, text_embeds, pooled, timestep, guidance=None, grid=None, token_offset: int = 0,
-                full_grid: Optional[Tuple[int, int]] = None):
-        """latent_tokens (B, S_img, token_in); text_embeds (B, S_txt, text_dim); pooled (B, pooled_dim);
+                full_grid: Optional[Tuple[int, ...]] = None, token_index: Optional[torch.Tensor] = None):
+        """latent_tokens (B, S_img, token_in); text_embeds (B, S_txt, text_dim); pooled (B, pooled_dim) or None;
         timestep, guidance (B,). Returns the predicted noise (B, S_img, token_in).
 
-        Under sequence parallelism a rank passes its contiguous band of latent rows: `grid` is the
-        band's (rows, cols), `full_grid` the whole latent grid and `token_offset` the index of the
-        band's first token, which selects the band's rows of the rotary / position tables."""
+        Under sequence parallelism a rank passes its share of the latent tokens. `full_grid` is the whole
+        latent grid ((rows, cols), or (frames, rows, cols) for video) and selects the rotary / position
+        tables; the rank's tokens are either one contiguous range starting at `token_offset` (a band of rows of
+        an image, or HunyuanVideo's chunk of the flattened token axis, transformer_hunyuan_video.py:226-231),
+        or any subset given by `token_index` (global token ids, e.g. a band of rows of every frame, as the
+        reference shards video latents, base_pipeline.py:337-344)."""
         shp = self.shape
         B, S_img, _ = latent_tokens.shape
         S_txt = text_embeds.shape[1]
@@ -354,17 +449,20 @@ class ShapedDiT(nn.Module):
             side = int(math.isqrt(S_img))
             grid = (side, S_img // side)
         dtype = latent_tokens.dtype
-        temb = self.time_embed(timestep_embedding(timestep * 1000.0).to(dtype)) + self.pooled_embed(pooled)
+        temb = self.time_embed(timestep_embedding(timestep * 1000.0).to(dtype))
+        if self.pooled_embed is not None:
+            temb = temb + self.pooled_embed(pooled)
         if self.guidance_embed is not None:
             g = guidance if guidance is not None else torch.ones_like(timestep)
             temb = temb + self.guidance_embed(timestep_embedding(g * 1000.0).to(dtype))
         hidden = self.x_embedder(latent_tokens)
         # Text stream: the reference keeps all of it on every sequence-parallel rank. When it divides evenly
         # each rank takes a contiguous shard instead (the result is the same, the text-stream work is not
-        # repeated on every rank); PipeFusion stages keep the reference layout.
+        # repeated on every rank); PipeFusion stages and the CogVideoX shape keep the reference layout.
         text_offset = text_total = None
         sp = ps.get_sequence_parallel_world_size()
-        if self.shard_text and sp > 1 and S_txt % sp == 0 and ps.get_pipeline_parallel_world_size() == 1:
+        if self.shard_text and sp > 1 and S_txt % sp == 0 and ps.get_pipeline_parallel_world_size() == 1 and \
+                shp.block_kind == "mmdit":
             text_total = S_txt
             S_txt = S_txt // sp
             text_offset = ps.get_sequence_parallel_rank() * S_txt
@@ -373,10 +471,19 @@ class ShapedDiT(nn.Module):
         fg = full_grid or grid
         rope = None
         if shp.rope_axes is not None:
-            rope = self._rope(text_total or S_txt, fg[0], fg[1], latent_tokens.device)
+            text_rows = (text_total or S_txt) if shp.rope_on_text else 0
+            rope = self._rope(text_rows, fg, latent_tokens.device)
+            if token_index is not None:
+                # the rank's rows of the table, text rows first: a local table addressed from token 0
+                rows = token_index + text_rows
+                if text_rows:
+                    rows = torch.cat([torch.arange(text_rows, device=rows.device), rows])
+                rope = (rope[0].index_select(0, rows), rope[1].index_select(0, rows))
+                token_offset = 0
         else:
             pos = self._sincos_pos(fg[0], fg[1], latent_tokens.device, dtype)
-            hidden = hidden + pos[:, token_offset:token_offset + S_img]
+            hidden = hidden + (pos[:, token_offset:token_offset + S_img] if token_index is None
+                               else pos.index_select(1, token_index))
         ahead = self._modulations_ahead(temb) if self.modulation_ahead and temb.is_cuda else None
         main = torch.cuda.current_stream(temb.device) if ahead is not None else None
 
@@ -388,13 +495,18 @@ class ShapedDiT(nn.Module):
             return m
 
         n_double = len(self.transformer_blocks)
-        for i, blk in enumerate(self.transformer_blocks):
-            hidden, context = blk(hidden, context, temb, rope, token_offset, text_offset, text_total, mods_of(i))
+        if shp.block_kind == "cogvideox":
+            for i, blk in enumerate(self.transformer_blocks):
+                hidden, context = blk(hidden, context, temb, rope, token_offset, mods_of(i))
+            hidden = self.norm_final(hidden)
+        else:
+            for i, blk in enumerate(self.transformer_blocks):
+                hidden, context = blk(hidden, context, temb, rope, token_offset, text_offset, text_total, mods_of(i))
         if len(self.single_transformer_blocks):
-            x = torch.cat([context, hidden], dim=1)
+            x = torch.cat([context, hidden] if shp.text_first else [hidden, context], dim=1)
             for i, blk in enumerate(self.single_transformer_blocks):
                 x = blk(x, temb, rope, S_txt, token_offset, text_offset, text_total, mods_of(n_double + i))
-            hidden = x[:, S_txt:]
+            hidden = x[:, S_txt:] if shp.text_first else x[:, :S_img]
         if ahead is not None:
             shift, scale = mods_of(len(ahead) - 1)
             main.wait_stream(self._mod_stream[temb.device])

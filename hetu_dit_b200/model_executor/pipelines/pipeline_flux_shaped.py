@@ -66,7 +66,7 @@ class FluxShapedPipeline(SD3ShapedPipeline):
             encoder_hidden_states = m.context_embedder(encoder_hidden_states)
         s_txt = encoder_hidden_states.shape[1]
         tok0 = self._first_token()
-        rope = m._rope(s_txt, self.grid[0], self.grid[1], hidden_states.device)
+        rope = m._rope(s_txt, self.grid, hidden_states.device)
         doubles, singles = self._stage_blocks()
         for block in doubles:
             hidden_states, encoder_hidden_states = block(hidden_states, encoder_hidden_states, temb, rope, tok0)

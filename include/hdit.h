@@ -176,7 +176,8 @@ typedef struct hdit_norm_rope_tensor {
   const void* x;
   int64_t x_stride_b, x_stride_s, x_stride_h;   /* elements; D contiguous */
   const void* norm_weight;                      /* (D) in `dtype`, or NULL for a weightless norm */
-  int32_t do_norm;                              /* 0 = skip RMSNorm */
+  const void* norm_bias;                        /* (D) in `dtype` or NULL; used by the LayerNorm mode only */
+  int32_t do_norm;                              /* 0 = no norm, 1 = RMSNorm, 2 = LayerNorm over head_dim */
   int32_t do_rope;                              /* 0 = skip rotary embedding */
   void* dst[8];                                 /* n_dst destinations; dst[j] receives heads [j*H/n_dst, (j+1)*H/n_dst) */
   int64_t dst_stride_b, dst_stride_s, dst_stride_h;
@@ -184,7 +185,8 @@ typedef struct hdit_norm_rope_tensor {
 } hdit_norm_rope_tensor;
 
 /*
- * Fused per-head RMSNorm + rotary embedding for up to three tensors of one layer (Q, K
+ * Fused per-head RMSNorm (or, for the CogVideoX-style QK norm, LayerNorm over head_dim: fp32 arithmetic, one
+ * rounding) + rotary embedding for up to three tensors of one layer (Q, K
  * and, copy only, V), written in place, to a plain destination, or head-sliced into
  * n_dst buffers at a sequence offset. With the buffers of the Ulysses peers as
  * destinations this is the head->sequence all-to-all done as peer stores from the

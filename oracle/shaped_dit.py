@@ -1,4 +1,4 @@
-"""CPU oracle: one denoising step of the SD3-/Flux-shaped MMDiT in plain fp32 torch.
+"""CPU oracle: one denoising step of the SD3- / Flux- / CogVideoX- / HunyuanVideo-shaped DiT in plain fp32 torch.
 
 TEST INFRASTRUCTURE ONLY. Nothing under hetu_dit_b200/ may import this module.
 
@@ -9,7 +9,9 @@ reference's processors take without flash-attn or a GPU
 (hetu_dit/model_executor/diffusion_executor/layers/attention_processor.py:
 759-783 for the joint blocks, :969-979 for the Flux blocks; selection in
 hetu_dit/envs.py:81-104). Token order follows the reference: [image; text] for
-the SD3 shape (:742-744), [text; image] for the Flux shape (:895-897).
+the SD3 shape (:742-744) and the HunyuanVideo shape (:1441-1443), [text; image]
+for the Flux shape (:895-897) and the CogVideoX shape (:1042); the video shapes
+rotate the video rows only (:1075-1082, :1410-1434).
 Also the timed CPU baseline of bench.py.
 
 Parity unpinned for the block wiring (adaLN order, residuals, MLP): it restates diffusers' MMDiT / Flux
@@ -52,21 +54,26 @@ def _heads(x, H, D):
 
 
 def _qk(sd, prefix, x, H, D, norm_name, rope, row0, eps=1e-6):
-    """projection -> heads -> RMSNorm -> RoPE; x (B, S, H*D) -> (B, S, H, D)."""
+    """projection -> heads -> QK norm -> RoPE; x (B, S, H*D) -> (B, S, H, D). The norm is an RMSNorm, or a
+    LayerNorm over the head dimension when the layer has a norm bias (the CogVideoX shape)."""
     y = _heads(x, H, D)
     w = sd.get(prefix + "." + norm_name + ".weight")
-    if w is not None:
+    b = sd.get(prefix + "." + norm_name + ".bias")
+    if w is not None and b is not None:
+        y = F.layer_norm(y, (D,), w.float(), b.float(), eps)
+    elif w is not None:
         y = oa.rms_norm(y, w.float(), eps)
-    if rope is not None:
+    if rope is not None and y.shape[1] > 0:
         cos, sin = rope
         S = y.shape[1]
         y = oa.apply_rotary_emb(y.transpose(1, 2), cos[row0:row0 + S], sin[row0:row0 + S]).transpose(1, 2)
     return y
 
 
-def joint_block(sd, p, hidden, context, temb, rope, H, D, order, kv_hook=None, row0=None):
+def joint_block(sd, p, hidden, context, temb, rope, H, D, order, kv_hook=None, row0=None, rope_on_text=True):
     """kv_hook(k_img, v_img) -> (k_all, v_all): PipeFusion's stale-KV cache for the image tokens
-    (attention_processor.py:702-707); row0: rotary table row of the first image token."""
+    (attention_processor.py:702-707); row0: rotary table row of the first image token; rope_on_text: the
+    table has rows for the text tokens (Flux) -- otherwise only the image / video rows are rotated."""
     d = hidden.shape[-1]
     mod = _lin(sd, p + ".norm1.linear", F.silu(temb)).chunk(6, dim=-1)
     cmod = _lin(sd, p + ".norm1_context.linear", F.silu(temb)).chunk(6, dim=-1)
@@ -74,14 +81,15 @@ def joint_block(sd, p, hidden, context, temb, rope, H, D, order, kv_hook=None, r
     c = _mod(F.layer_norm(context, (d,), eps=1e-6), cmod[0], cmod[1])
     a = p + ".attn.module"
     S_txt, S_img = c.shape[1], h.shape[1]
-    r0 = S_txt if row0 is None else row0
+    r0 = (S_txt if rope_on_text else 0) if row0 is None else row0
     q = _qk(sd, a, _lin(sd, a + ".to_q", h), H, D, "norm_q", rope, r0)
     k = _qk(sd, a, _lin(sd, a + ".to_k", h), H, D, "norm_k", rope, r0)
     v = _heads(_lin(sd, a + ".to_v", h), H, D)
     if kv_hook is not None:
         k, v = kv_hook(k, v)
-    tq = _qk(sd, a, _lin(sd, a + ".add_q_proj", c), H, D, "norm_added_q", rope, 0)
-    tk = _qk(sd, a, _lin(sd, a + ".add_k_proj", c), H, D, "norm_added_k", rope, 0)
+    rope_txt = rope if rope_on_text else None
+    tq = _qk(sd, a, _lin(sd, a + ".add_q_proj", c), H, D, "norm_added_q", rope_txt, 0)
+    tk = _qk(sd, a, _lin(sd, a + ".add_k_proj", c), H, D, "norm_added_k", rope_txt, 0)
     tv = _heads(_lin(sd, a + ".add_v_proj", c), H, D)
     if order == "rear":
         o = oa.sdpa(torch.cat([q, tq], 1), torch.cat([k, tk], 1), torch.cat([v, tv], 1))
@@ -99,15 +107,35 @@ def joint_block(sd, p, hidden, context, temb, rope, H, D, order, kv_hook=None, r
     return hidden, context
 
 
-def single_block(sd, p, x, temb, rope, H, D, text_len=None, row0=None, kv_hook=None):
+def single_block(sd, p, x, temb, rope, H, D, text_len=None, row0=None, kv_hook=None, text_first=True,
+                 rope_on_text=True):
     """x = [text; image] rows. text_len / row0: the first text_len rows take rotary rows [0, text_len), the
     rest rows [row0, ...) (a patch of the image); kv_hook(k_img, v_img) -> (k_all, v_all) is PipeFusion's
-    stale-KV cache of the image tokens (attention_processor.py:898-917 of the reference)."""
+    stale-KV cache of the image tokens (attention_processor.py:898-917 of the reference).
+    text_first=False: x = [image; text] (HunyuanVideo single blocks, :1464-1468); rope_on_text=False: only the
+    image / video rows are rotated, from table row `row0` (default 0)."""
     d = x.shape[-1]
     shift, scale, gate = _lin(sd, p + ".norm.linear", F.silu(temb)).chunk(3, dim=-1)
     h = _mod(F.layer_norm(x, (d,), eps=1e-6), shift, scale)
     mlp = F.gelu(_lin(sd, p + ".proj_mlp", h), approximate="tanh")
     a = p + ".attn.module"
+    if not (text_first and rope_on_text):
+        assert kv_hook is None and text_len is not None
+        S = x.shape[1]
+        t_lo, t_hi = (0, text_len) if text_first else (S - text_len, S)
+        i_lo, i_hi = (text_len, S) if text_first else (0, S - text_len)
+        ql, kl = _lin(sd, a + ".to_q", h), _lin(sd, a + ".to_k", h)
+        rope_txt = rope if rope_on_text else None
+        r0 = (text_len if rope_on_text else 0) if row0 is None else row0
+        parts_q = {t_lo: _qk(sd, a, ql[:, t_lo:t_hi], H, D, "norm_q", rope_txt, 0),
+                   i_lo: _qk(sd, a, ql[:, i_lo:i_hi], H, D, "norm_q", rope, r0)}
+        parts_k = {t_lo: _qk(sd, a, kl[:, t_lo:t_hi], H, D, "norm_k", rope_txt, 0),
+                   i_lo: _qk(sd, a, kl[:, i_lo:i_hi], H, D, "norm_k", rope, r0)}
+        q = torch.cat([parts_q[i] for i in sorted(parts_q)], dim=1)
+        k = torch.cat([parts_k[i] for i in sorted(parts_k)], dim=1)
+        v = _heads(_lin(sd, a + ".to_v", h), H, D)
+        o = oa.sdpa(q, k, v).reshape(x.shape[0], x.shape[1], d)
+        return x + gate[:, None] * _lin(sd, p + ".proj_out", torch.cat([o, mlp], dim=-1))
     if text_len is None:
         q = _qk(sd, a, _lin(sd, a + ".to_q", h), H, D, "norm_q", rope, 0)
         k = _qk(sd, a, _lin(sd, a + ".to_k", h), H, D, "norm_k", rope, 0)
@@ -124,6 +152,33 @@ def single_block(sd, p, x, temb, rope, H, D, text_len=None, row0=None, kv_hook=N
         k, v = torch.cat([k[:, :text_len], ki], dim=1), torch.cat([v[:, :text_len], vi], dim=1)
     o = oa.sdpa(q, k, v).reshape(x.shape[0], x.shape[1], d)
     return x + gate[:, None] * _lin(sd, p + ".proj_out", torch.cat([o, mlp], dim=-1))
+
+
+def cogvideox_block(sd, p, hidden, context, temb, rope, H, D, row0=0):
+    """CogVideoX-shaped block: shared attention / MLP weights over [text; video], own adaLN vectors per stream,
+    rotary embedding on the video rows only (attention_processor.py:1042-1082 of the reference)."""
+    d = hidden.shape[-1]
+    S_txt = context.shape[1]
+    m1 = _lin(sd, p + ".norm1.linear", F.silu(temb)).chunk(6, dim=-1)
+    m2 = _lin(sd, p + ".norm2.linear", F.silu(temb)).chunk(6, dim=-1)
+    x = torch.cat([_mod(F.layer_norm(context, (d,), eps=1e-6), m1[3], m1[4]),
+                   _mod(F.layer_norm(hidden, (d,), eps=1e-6), m1[0], m1[1])], dim=1)
+    a = p + ".attn1.module"
+    ql, kl = _lin(sd, a + ".to_q", x), _lin(sd, a + ".to_k", x)
+    q = torch.cat([_qk(sd, a, ql[:, :S_txt], H, D, "norm_q", None, 0),
+                   _qk(sd, a, ql[:, S_txt:], H, D, "norm_q", rope, row0)], dim=1)
+    k = torch.cat([_qk(sd, a, kl[:, :S_txt], H, D, "norm_k", None, 0),
+                   _qk(sd, a, kl[:, S_txt:], H, D, "norm_k", rope, row0)], dim=1)
+    v = _heads(_lin(sd, a + ".to_v", x), H, D)
+    o = _lin(sd, a + ".to_out.0", oa.sdpa(q, k, v).reshape(x.shape[0], x.shape[1], d))
+    hidden = hidden + m1[2][:, None] * o[:, S_txt:]
+    context = context + m1[5][:, None] * o[:, :S_txt]
+    x = torch.cat([_mod(F.layer_norm(context, (d,), eps=1e-6), m2[3], m2[4]),
+                   _mod(F.layer_norm(hidden, (d,), eps=1e-6), m2[0], m2[1])], dim=1)
+    f = _ff(sd, p + ".ff", x)
+    hidden = hidden + m2[2][:, None] * f[:, S_txt:]
+    context = context + m2[5][:, None] * f[:, :S_txt]
+    return hidden, context
 
 
 def rope_tables(ids, axes, theta=10000.0):
@@ -147,47 +202,73 @@ def sincos_pos(grid_h, grid_w, d):
     return torch.cat(parts, dim=-1)[None]
 
 
-def denoise_step(sd, shape, latent_tokens, text_embeds, pooled, timestep, guidance=None, grid=None, max_blocks=None):
-    """One full step in fp32. `shape` is the DiTShape record; `sd` maps parameter names to tensors."""
+def grid_ids(text_rows, grid):
+    """Position ids (text_rows + tokens, 3): zero rows for the text, then (frame, row, col) per latent token."""
+    g3 = tuple(grid) if len(grid) == 3 else (1,) + tuple(grid)
+    n = g3[0] * g3[1] * g3[2]
+    ids = torch.zeros(text_rows + n, 3)
+    tt, yy, xx = torch.meshgrid(*(torch.arange(g) for g in g3), indexing="ij")
+    ids[text_rows:, 0] = tt.flatten()
+    ids[text_rows:, 1] = yy.flatten()
+    ids[text_rows:, 2] = xx.flatten()
+    return ids
+
+
+def denoise_step(sd, shape, latent_tokens, text_embeds, pooled, timestep, guidance=None, grid=None, max_blocks=None,
+                 block_outputs=None):
+    """One full step in fp32. `shape` is the DiTShape record; `sd` maps parameter names to tensors; `grid` is
+    (rows, cols) or (frames, rows, cols). block_outputs: optional list that receives every block's image /
+    video stream output (B, S_img, hidden), in order."""
     sd = {k: v.float() for k, v in sd.items()}
-    x, txt, pooled = latent_tokens.float(), text_embeds.float(), pooled.float()
+    x, txt = latent_tokens.float(), text_embeds.float()
     B, S_img, _ = x.shape
     S_txt = txt.shape[1]
     if grid is None:
         side = int(math.isqrt(S_img))
         grid = (side, S_img // side)
     H, D, d = shape.heads, shape.head_dim, shape.hidden
-    temb = _mlp_embed(sd, "time_embed", _timestep_embedding(timestep * 1000.0)) + _mlp_embed(sd, "pooled_embed", pooled)
+    temb = _mlp_embed(sd, "time_embed", _timestep_embedding(timestep * 1000.0))
+    if shape.pooled_dim:
+        temb = temb + _mlp_embed(sd, "pooled_embed", pooled.float())
     if shape.guidance_embed:
         g = guidance if guidance is not None else torch.ones_like(timestep)
         temb = temb + _mlp_embed(sd, "guidance_embed", _timestep_embedding(g * 1000.0))
     hidden = _lin(sd, "x_embedder", x)
     context = _lin(sd, "context_embedder", txt)
     rope = None
+    order = "front" if shape.text_first else "rear"
     if shape.rope_axes is not None:
-        ids = torch.zeros(S_txt + S_img, 3)
-        yy, xx = torch.meshgrid(torch.arange(grid[0]), torch.arange(grid[1]), indexing="ij")
-        ids[S_txt:, 1] = yy.flatten()
-        ids[S_txt:, 2] = xx.flatten()
-        rope = rope_tables(ids, shape.rope_axes)
-        order = "front"
+        rope = rope_tables(grid_ids(S_txt if shape.rope_on_text else 0, grid), shape.rope_axes)
     else:
         hidden = hidden + sincos_pos(grid[0], grid[1], d)
-        order = "rear"
     n = 0
     for i in range(shape.n_double):
         if max_blocks is not None and n >= max_blocks:
             break
-        hidden, context = joint_block(sd, f"transformer_blocks.{i}", hidden, context, temb, rope, H, D, order)
+        if shape.block_kind == "cogvideox":
+            hidden, context = cogvideox_block(sd, f"transformer_blocks.{i}", hidden, context, temb, rope, H, D)
+        else:
+            hidden, context = joint_block(sd, f"transformer_blocks.{i}", hidden, context, temb, rope, H, D, order,
+                                          rope_on_text=shape.rope_on_text)
+        if block_outputs is not None:
+            block_outputs.append(hidden)
         n += 1
+    if shape.block_kind == "cogvideox":
+        hidden = F.layer_norm(hidden, (d,), sd["norm_final.weight"], sd["norm_final.bias"], 1e-5)
     if shape.n_single:
-        xs = torch.cat([context, hidden], dim=1)
+        xs = torch.cat([context, hidden] if shape.text_first else [hidden, context], dim=1)
         for i in range(shape.n_single):
             if max_blocks is not None and n >= max_blocks:
                 break
-            xs = single_block(sd, f"single_transformer_blocks.{i}", xs, temb, rope, H, D)
+            if shape.text_first and shape.rope_on_text:
+                xs = single_block(sd, f"single_transformer_blocks.{i}", xs, temb, rope, H, D)
+            else:
+                xs = single_block(sd, f"single_transformer_blocks.{i}", xs, temb, rope, H, D, text_len=S_txt,
+                                  text_first=shape.text_first, rope_on_text=shape.rope_on_text)
+            if block_outputs is not None:
+                block_outputs.append(xs[:, S_txt:] if shape.text_first else xs[:, :S_img])
             n += 1
-        hidden = xs[:, S_txt:]
+        hidden = xs[:, S_txt:] if shape.text_first else xs[:, :S_img]
     shift, scale = _lin(sd, "norm_out.linear", F.silu(temb)).chunk(2, dim=-1)
     hidden = _mod(F.layer_norm(hidden, (d,), eps=1e-6), shift, scale)
     return _lin(sd, "proj_out", hidden)
