@@ -22,8 +22,43 @@ if ROOT not in sys.path:
 
 import torch  # noqa: E402
 
-S_IMG, S_TXT, GRID = 4096, 512, (64, 64)
 METRIC, UNIT = "denoise_step_tokens_per_s", "tokens/s"
+
+# The BASELINE configurations: shape, latent token grid, text tokens, and the sequence-parallel plan per GPU
+# count as (ulysses, ring). "flux" is the default (the configuration the headline metric is quoted on).
+CONFIGS = {
+    "flux": dict(shape="FLUX_DEV", grid=(64, 64), s_txt=512, plans={1: (1, 1), 2: (2, 1), 4: (4, 1), 8: (8, 1)},
+                 shard="rows", workload="flux.1-dev-shaped denoise step, 4096 image + 512 text tokens, batch 1, "
+                                         "19 double + 38 single blocks, hidden 3072, 24x128 heads"),
+    "sd3": dict(shape="SD3_MEDIUM", grid=(64, 64), s_txt=333, plans={1: (1, 1), 2: (2, 1), 4: (4, 1), 8: (8, 1)},
+                shard="rows", workload="sd3-medium-shaped denoise step, 4096 image + 333 text tokens, batch 1, "
+                                       "24 joint blocks, hidden 1536, 24x64 heads"),
+    "cogvideox": dict(shape="COGVIDEOX_5B", grid=(11, 48, 85), s_txt=224,
+                      plans={1: (1, 1), 2: (1, 2), 4: (1, 4), 8: (1, 8)}, shard="frame_rows",
+                      workload="cogvideox-1.5-5b-shaped denoise step, 44880 video + 224 text tokens, batch 1, "
+                               "42 blocks, hidden 3072, 48x64 heads"),
+    "hunyuan": dict(shape="HUNYUAN_VIDEO", grid=(33, 45, 80), s_txt=256,
+                    plans={1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (4, 2)}, shard="chunk",
+                    workload="hunyuanvideo-shaped denoise step, 118800 video + 256 text tokens, batch 1, "
+                             "20 double + 40 single blocks, hidden 3072, 24x128 heads"),
+}
+# Tiny twins (8 heads so that every plan up to 8 ranks divides them) for the parity check that precedes the timing.
+TINY = {
+    "flux": (("flux-tiny", 2, 2, 1024, 8, 128, 64, 128, 96, True, (16, 56, 56), True), {}, (32, 16), 64),
+    "sd3": (("sd3-tiny", 3, 0, 512, 8, 64, 64, 128, 96, False, None, False), {}, (32, 16), 40),
+    "cogvideox": (("cogvideox-tiny", 3, 0, 512, 8, 64, 128, 128, 0, True, (16, 24, 24), False),
+                  dict(text_first=True, rope_on_text=False, qk_norm_kind="layer", block_kind="cogvideox", temb_dim=128),
+                  (3, 16, 8), 40),
+    "hunyuan": (("hunyuan-tiny", 2, 2, 1024, 8, 128, 64, 128, 96, True, (16, 56, 56), True),
+                dict(text_first=False, rope_on_text=False), (3, 16, 8), 32),
+}
+
+
+def _n_tokens(grid):
+    n = 1
+    for g in grid:
+        n *= g
+    return n
 
 
 def _peaks():
@@ -80,56 +115,105 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
-def _inputs(shape, seed=0):
+def _inputs(shape, n_img, s_txt, seed=0):
     gen = torch.Generator().manual_seed(seed)
-    return dict(latent=torch.randn(1, S_IMG, shape.token_in, generator=gen).bfloat16(),
-                text=torch.randn(1, S_TXT, shape.text_dim, generator=gen).bfloat16(),
-                pooled=torch.randn(1, shape.pooled_dim, generator=gen).bfloat16(),
+    return dict(latent=torch.randn(1, n_img, shape.token_in, generator=gen).bfloat16(),
+                text=torch.randn(1, s_txt, shape.text_dim, generator=gen).bfloat16(),
+                pooled=torch.randn(1, max(shape.pooled_dim, 1), generator=gen).bfloat16(),
                 t=torch.tensor([1.0]), g=torch.tensor([3.5]))
 
 
+def _shard_tokens(kind, grid, rank, world):
+    """Which latent tokens a sequence-parallel rank holds: (token_offset, count, token_index or None, band grid).
+    "rows": a band of rows of the image; "chunk": a contiguous chunk of the flattened token axis (HunyuanVideo,
+    transformer_hunyuan_video.py:226-231 of the reference); "frame_rows": a band of rows of every frame (how the
+    reference shards video latents, base_pipeline.py:337-344)."""
+    n = _n_tokens(grid)
+    if world == 1:
+        return 0, n, None, grid
+    if kind == "rows":
+        rows = grid[0] // world
+        return rank * rows * grid[1], rows * grid[1], None, (rows, grid[1])
+    if kind == "chunk":
+        return rank * (n // world), n // world, None, grid
+    T, Hh, W = grid
+    rows = Hh // world
+    idx = (torch.arange(T)[:, None, None] * Hh * W + (rank * rows + torch.arange(rows))[None, :, None] * W
+           + torch.arange(W)[None, None, :]).reshape(-1)
+    return 0, idx.numel(), idx, grid
+
+
 # ------------------------------------------------------------------------------------- CPU arm
-def cpu_step_sample(threads, blocks=(1, 1)):
-    """Times the reference's CPU path on a bounded sample of the workload: `blocks` = (double, single)
-    blocks of the Flux-shaped model at full sequence length, fp32, F.scaled_dot_product_attention.
-    Returns (seconds for a whole 19+38-block step, extrapolated; description)."""
-    from hetu_dit_b200.model_executor.models.shaped_dit import FLUX_DEV, JointBlock, SingleBlock, rope_tables
+def cpu_step_sample(threads, cfg_name="flux", blocks=(1, 1)):
+    """Times the reference's CPU path (fp32, F.scaled_dot_product_attention) on a bounded sample of the workload and
+    extrapolates to the whole step. Flux / SD3: `blocks` = (double, single) whole blocks at full sequence length.
+    Video configurations: the linear layers of one block on 4096 token rows and the attention of 2 heads for 2048
+    query rows against the full key/value length, scaled to all rows, heads and blocks.
+    Returns (seconds per step, description, number of timed samples)."""
+    import hetu_dit_b200.model_executor.models.shaped_dit as M
+    from oracle import attention as oa
     from oracle import shaped_dit as osd
     torch.set_num_threads(threads)
-    shape = FLUX_DEV
+    cfg = CONFIGS[cfg_name]
+    shape = getattr(M, cfg["shape"])
+    s_img, s_txt = _n_tokens(cfg["grid"]), cfg["s_txt"]
     gen = torch.Generator().manual_seed(0)
     d = shape.hidden
+    if cfg_name in ("cogvideox", "hunyuan"):
+        S = s_img + s_txt
+        rows, heads, q_rows = 4096, 2, 2048
+        x = torch.randn(1, rows, d, generator=gen)
+        w1, w2 = torch.randn(4 * d, d, generator=gen) * 0.02, torch.randn(d, 4 * d, generator=gen) * 0.02
+        wq = torch.randn(4 * d, d, generator=gen) * 0.02  # q, k, v and output projections together
+        q = torch.randn(1, q_rows, heads, shape.head_dim, generator=gen)
+        k = torch.randn(1, S, heads, shape.head_dim, generator=gen)
+        v = torch.randn(1, S, heads, shape.head_dim, generator=gen)
+        with torch.no_grad():
+            t0 = time.perf_counter()
+            torch.nn.functional.linear(torch.nn.functional.gelu(torch.nn.functional.linear(x, w1), approximate="tanh"), w2)
+            torch.nn.functional.linear(x, wq)
+            t1 = time.perf_counter()
+            oa.sdpa(q, k, v)
+            t2 = time.perf_counter()
+        per_block = (t1 - t0) * (S / rows) + (t2 - t1) * (S / q_rows) * (shape.heads / heads)
+        return per_block * shape.n_blocks, (
+            f"{cfg_name}: linear layers of one block on {rows} of {S} rows + attention of {heads} of {shape.heads} heads "
+            f"for {q_rows} query rows against all {S} keys (fp32 SDPA path), extrapolated to {shape.n_blocks} blocks"), 1
 
     def weights(mod, prefix):
         return {prefix + "." + k: torch.randn(v.shape, generator=gen) * (0.02 if v.dim() > 1 else 0.0) + (
             1.0 if (v.dim() == 1 and not k.endswith("bias")) else 0.0) for k, v in mod.state_dict().items()}
 
     with torch.device("meta"):
-        jb, sb = JointBlock(shape), SingleBlock(shape)
+        jb = M.JointBlock(shape)
+        sb = M.SingleBlock(shape) if shape.n_single else None
     sd = {}
     sd.update(weights(jb, "j"))
-    sd.update(weights(sb, "s"))
-    hidden = torch.randn(1, S_IMG, d, generator=gen)
-    context = torch.randn(1, S_TXT, d, generator=gen)
+    if sb is not None:
+        sd.update(weights(sb, "s"))
+    hidden = torch.randn(1, s_img, d, generator=gen)
+    context = torch.randn(1, s_txt, d, generator=gen)
     temb = torch.randn(1, d, generator=gen)
-    ids = torch.zeros(S_TXT + S_IMG, 3)
-    yy, xx = torch.meshgrid(torch.arange(GRID[0]), torch.arange(GRID[1]), indexing="ij")
-    ids[S_TXT:, 1], ids[S_TXT:, 2] = yy.flatten(), xx.flatten()
-    rope = rope_tables(ids, shape.rope_axes)
+    rope = None
+    if shape.rope_axes is not None:
+        rope = osd.rope_tables(osd.grid_ids(s_txt, cfg["grid"]), shape.rope_axes)
+    order = "front" if shape.text_first else "rear"
     with torch.no_grad():
         t0 = time.perf_counter()
         for _ in range(blocks[0]):
-            osd.joint_block(sd, "j", hidden, context, temb, rope, shape.heads, shape.head_dim, "front")
+            osd.joint_block(sd, "j", hidden, context, temb, rope, shape.heads, shape.head_dim, order)
         t1 = time.perf_counter()
         x = torch.cat([context, hidden], 1)
-        for _ in range(blocks[1]):
+        n_single = blocks[1] if sb is not None else 0
+        for _ in range(n_single):
             osd.single_block(sd, "s", x, temb, rope, shape.heads, shape.head_dim)
         t2 = time.perf_counter()
     per_double = (t1 - t0) / max(blocks[0], 1)
-    per_single = (t2 - t1) / max(blocks[1], 1)
+    per_single = (t2 - t1) / max(n_single, 1)
     total = per_double * shape.n_double + per_single * shape.n_single
-    return total, (f"{blocks[0]} double + {blocks[1]} single block(s) of the Flux-shaped step at full length "
-                   f"({S_IMG}+{S_TXT} tokens, fp32 SDPA path), extrapolated to 19+38 blocks")
+    return total, (f"{blocks[0]} double + {n_single} single block(s) of the {cfg_name}-shaped step at full length "
+                   f"({s_img}+{s_txt} tokens, fp32 SDPA path), extrapolated to {shape.n_double}+{shape.n_single} blocks"), \
+        blocks[0] + n_single
 
 
 def run_reference(args):
@@ -137,22 +221,25 @@ def run_reference(args):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
+    cfg = CONFIGS[args.config]
     for _ in range(max(args.warmup, 0) and 1):
-        cpu_step_sample(threads, (1, 0))
+        cpu_step_sample(threads, args.config, (1, 0))
     times = []
-    desc = ""
+    desc, n_samples = "", 0
     for _ in range(max(1, min(args.steps, 3))):
-        t, desc = cpu_step_sample(threads, (1, 1))
+        t, desc, n_samples = cpu_step_sample(threads, args.config, (1, 1))
         times.append(t)
     times.sort()
     step_s = times[len(times) // 2]
-    value = (S_IMG + S_TXT) / step_s
+    tokens = _n_tokens(cfg["grid"]) + cfg["s_txt"]
+    value = tokens / step_s
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "flux.1-dev-shaped denoise step, 4096 image + 512 text tokens, batch 1",
-                   "parallelism": "cpu"},
+        "config": {"workload": cfg["workload"], "parallelism": "cpu"},
+        "extrapolated": True, "blocks_timed_per_sample": n_samples, "samples": len(times),
+        "sample_spread_ms": [t * 1e3 for t in times],
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -161,12 +248,86 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------------- GPU arm
+def _block_hooks(model, s_loc):
+    """Forward hooks collecting every block's image / video rows of this rank (B, s_loc, hidden)."""
+    outs, handles = [], []
+    first = model.shape.text_first
+
+    def double(_m, _i, out):
+        outs.append(out[0].detach().float())
+
+    def single(_m, _i, out):
+        outs.append((out[:, -s_loc:] if first else out[:, :s_loc]).detach().float())
+
+    for b in model.transformer_blocks:
+        handles.append(b.register_forward_hook(double))
+    for b in model.single_transformer_blocks:
+        handles.append(b.register_forward_hook(single))
+    return outs, handles
+
+
+def parity_check(cfg_name, rank, world, plan, dev, ps, dist):
+    """Outside the timed region: one step of a tiny seeded model of the benchmarked family under the benchmarked
+    plan, every block's output and the final output of this rank's tokens against the same model run by this rank
+    alone on all tokens (solo plan, same kernels). Returns the worst cosine / max |a-b| / max |b| over blocks,
+    layouts and ranks; raises when a block misses cosine >= 0.9999 or 2e-2."""
+    from hetu_dit_b200.model_executor.models.shaped_dit import DiTShape, ShapedDiT
+    targs, tkw, grid, s_txt = TINY[cfg_name]
+    shape = DiTShape(*targs, **tkw)
+    model = ShapedDiT(shape).to(dev).init_weights(seed=11, std=0.05).bfloat16()
+    inp = {k: v.to(dev) for k, v in _inputs(shape, _n_tokens(grid), s_txt, seed=12).items()}
+    inp["t"] = torch.tensor([0.7], device=dev)
+    pg = ps.get_parallel_groups()
+
+    def run(tok0, n, index, band, hook_rows):
+        outs, handles = _block_hooks(model, hook_rows)
+        lat = inp["latent"][:, tok0:tok0 + n] if index is None else inp["latent"].index_select(1, index.to(dev))
+        with torch.no_grad():
+            y = model(lat, inp["text"], inp["pooled"], inp["t"], inp["g"], grid=band, token_offset=tok0,
+                      full_grid=grid, token_index=None if index is None else index.to(dev))
+        for h in handles:
+            h.remove()
+        torch.cuda.synchronize()
+        return outs + [y.float()]
+
+    pg.activate_plan([rank])
+    solo = run(0, _n_tokens(grid), None, grid, _n_tokens(grid))
+    worst_cos, worst_rel = 1.0, 0.0
+    layouts = []
+    if world > 1:
+        U, R = plan
+        pg.activate_plan(list(range(world)), ulysses=U, ring=R)
+        tok0, n, index, band = _shard_tokens(CONFIGS[cfg_name]["shard"], grid, rank, world)
+        rows = torch.arange(tok0, tok0 + n, device=dev) if index is None else index.to(dev)
+        for shard_text in ((True, False) if shape.block_kind == "mmdit" and s_txt % world == 0 else (False,)):
+            model.shard_text = shard_text
+            layouts.append("sharded" if shard_text else "replicated")
+            got = run(tok0, n, index, band, n)
+            for a, b in zip(got, solo):
+                b = b.index_select(1, rows)
+                cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
+                rel = ((a - b).abs().max() / b.abs().max()).item()
+                worst_cos, worst_rel = min(worst_cos, cos), max(worst_rel, rel)
+            ps.get_world_group().barrier()
+        t = torch.tensor([-worst_cos, worst_rel], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        worst_cos, worst_rel = -t[0].item(), t[1].item()
+    else:
+        # one GPU: the kernel path against itself has nothing to compare; check the solo run is finite
+        assert all(torch.isfinite(x).all().item() for x in solo)
+    res = {"cos": worst_cos, "max_rel": worst_rel, "vs": "n1", "model": shape.name, "blocks": shape.n_blocks,
+           "text_layouts": layouts, "plan": f"ulysses{plan[0]}xring{plan[1]}"}
+    if worst_cos < 0.9999 or worst_rel > 2e-2:
+        raise SystemExit(f"parity check failed: {res}")
+    return res
+
+
 def run_gpu(args):
     import torch.distributed as dist
+    import hetu_dit_b200.model_executor.models.shaped_dit as M
     from hetu_dit_b200 import _C, kernels
     from hetu_dit_b200.core.distributed import parallel_state as ps
     from hetu_dit_b200.core.distributed.peer import PeerHeap
-    from hetu_dit_b200.model_executor.models.shaped_dit import FLUX_DEV, ShapedDiT
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -174,6 +335,10 @@ def run_gpu(args):
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    cfg = CONFIGS[args.config]
+    if world not in cfg["plans"]:
+        raise SystemExit(f"config {args.config} has no plan for {world} GPUs")
+    U, R = cfg["plans"][world]
     dev = torch.device(f"cuda:{local_rank}")
     torch.cuda.set_device(dev)
     _C.lib()  # fail loudly if the extension is missing
@@ -186,32 +351,38 @@ def run_gpu(args):
             dist.all_gather_object(out, b)
             return out
 
-        heap = PeerHeap(1 << 30, rank, world, dev, gather)
+        heap = PeerHeap((1 << 30) if args.config in ("flux", "sd3") else (3 << 30), rank, world, dev, gather)
     ps.init_distributed_environment(rank, world, heap)
-    ps.initialize_model_parallel(sequence_parallel_degree=world, ulysses_degree=world, ring_degree=1)
 
-    shape = FLUX_DEV
-    # build the 11.9 B-parameter model directly on the device in bf16 (no 48 GB fp32 host copy per rank)
+    parity = None
+    if not args.no_parity_check:
+        parity = parity_check(args.config, rank, world, (U, R), dev, ps, dist)
+        if heap is not None:
+            heap.check()
+            heap.reset()
+    ps.get_parallel_groups().activate_plan(list(range(world)), ulysses=U, ring=R)
+
+    shape = getattr(M, cfg["shape"])
+    grid, S_TXT = cfg["grid"], cfg["s_txt"]
+    S_IMG = _n_tokens(grid)
+    # build the model directly on the device in bf16 (no fp32 host copy per rank)
     torch.set_default_dtype(torch.bfloat16)
     with torch.device(dev):
-        model = ShapedDiT(shape)
+        model = M.ShapedDiT(shape)
     torch.set_default_dtype(torch.float32)
     model.init_weights(seed=0, std=0.02)
-    model.register_cache()
+    if shape.block_kind == "mmdit" and shape.n_single and shape.text_first:
+        model.register_cache()
     model.shard_text = not args.replicated_text
-    host = {k: v.pin_memory() for k, v in _inputs(shape).items()}
-    s_loc = S_IMG // world
-    rows_loc = GRID[0] // world
-    tok0 = rank * s_loc
-
-    def shard(latent):
-        return latent[:, tok0:tok0 + s_loc]
-
+    host = {k: v.pin_memory() for k, v in _inputs(shape, S_IMG, S_TXT).items()}
+    tok0, s_loc, index, band = _shard_tokens(cfg["shard"], grid, rank, world)
+    index_dev = None if index is None else index.to(dev)
     resident = {k: v.to(dev) for k, v in host.items()}
 
     def step(inp):
-        return model(shard(inp["latent"]), inp["text"], inp["pooled"], inp["t"], inp["g"], grid=(rows_loc, GRID[1]),
-                     token_offset=tok0, full_grid=GRID)
+        lat = inp["latent"][:, tok0:tok0 + s_loc] if index_dev is None else inp["latent"].index_select(1, index_dev)
+        return model(lat, inp["text"], inp["pooled"], inp["t"], inp["g"], grid=band, token_offset=tok0,
+                     full_grid=grid, token_index=index_dev)
 
     def barrier():
         if world > 1:
@@ -232,6 +403,27 @@ def run_gpu(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = t.item()
         return ms / n
+
+    def capture():
+        """The step as one CUDA graph (None when capture fails: the eager path stays valid)."""
+        if args.no_graph:
+            return None, None
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                step(resident)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                out = step(resident)
+            barrier()
+            return g, out
+        except Exception as e:
+            print(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); timing eager launches",
+                  file=sys.stderr)
+            return None, None
 
     with torch.no_grad():
         for _ in range(max(args.warmup, 3)):
@@ -255,23 +447,7 @@ def run_gpu(args):
 
         # (2) the timed region proper: the same step captured once in a CUDA graph and replayed, which
         #     takes the Python / launch overhead of ~1.5 k kernels per step off the critical path
-        graph, out_static = None, None
-        if not args.no_graph:
-            try:
-                side = torch.cuda.Stream(device=dev)
-                side.wait_stream(torch.cuda.current_stream(dev))
-                with torch.cuda.stream(side):
-                    step(resident)
-                torch.cuda.current_stream(dev).wait_stream(side)
-                barrier()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    out_static = step(resident)
-                barrier()
-            except Exception as e:  # capture is an optimisation; the eager path stays valid
-                print(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); timing eager launches",
-                      file=sys.stderr)
-                graph = None
+        graph, out_static = capture()
         run_step = graph.replay if graph is not None else (lambda: step(resident))
         for _ in range(2):
             run_step()
@@ -294,6 +470,21 @@ def run_gpu(args):
         for _ in range(2):
             e2e_step()
         ms_e2e = timed(e2e_step, args.steps)
+
+        # (4) N > 1, double/single-stream shapes: the same step with the text stream replicated on every rank and
+        #     handed to the USP operators as joint tensors (the reference's layout), timed the same way
+        ms_replicated = None
+        if world > 1 and shape.block_kind == "mmdit" and model.shard_text and S_TXT % world == 0:
+            del graph
+            model.shard_text = False
+            for _ in range(2):
+                step(resident)
+            graph2, _ = capture()
+            run2 = graph2.replay if graph2 is not None else (lambda: step(resident))
+            for _ in range(2):
+                run2()
+            ms_replicated = timed(run2, args.steps)
+            model.shard_text = True
     status = _C.device_status(local_rank, clear=True)
     if status[0] != 0:
         raise SystemExit(f"device-side wait timed out during the bench: {status}")
@@ -306,49 +497,56 @@ def run_gpu(args):
     peak_tf, peak_hbm, peak_kind = _peaks()
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = out_host.numel() * out_host.element_size()
-    # dominant kernel of this repo: the attention kernel (one launch per block, 57 per step)
-    heads_loc = shape.heads // world
-    s_q_gathered = tokens  # replicated text queries are attended once per head slice, not once per rank
-    attn_flops = 4.0 * s_q_gathered * tokens * heads_loc * shape.head_dim
-    achieved = attn_flops / (attn_ms["mean_ms"] * 1e-3) / 1e12 if attn_ms["mean_ms"] else None
-    # DRAM bytes of one launch at this shape, from the committed ncu summary (single-GPU shape only)
+    # dominant kernel of this repo: the attention kernel; achieved = algorithmic FLOPs of the timed launches
+    # (4 * Sq * Skv * heads * head_dim each) over their summed CUDA-event time
+    achieved = attn_ms["flops"] / (attn_ms["total_ms"] * 1e-3) / 1e12 if attn_ms["total_ms"] else None
+    # DRAM bytes of one launch at this shape, from the committed ncu summary (single-GPU Flux shape only)
     traffic = None
     prof = os.path.join(ROOT, "profiles", "attn_fwd_kernel_flux_shape.txt")
-    if os.path.exists(prof) and world == 1:
+    if os.path.exists(prof) and world == 1 and args.config == "flux":
         with open(prof) as f:
             for ln in f:
                 if ln.startswith("dram_bytes_per_launch:"):
                     traffic = int(ln.split(":")[1])
+    step_flops = model.flops_per_step(S_IMG, S_TXT)
+    text_layout = "n/a" if world == 1 else (
+        "replicated on every rank (reference layout)" if (args.replicated_text or shape.block_kind != "mmdit"
+                                                         or S_TXT % world != 0) else "sharded over the ranks")
     line = {
         "metric": METRIC, "value": tokens / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "flux.1-dev-shaped denoise step, 4096 image + 512 text tokens, batch 1, "
-                               "19 double + 38 single blocks, hidden 3072, 24x128 heads",
-                   "parallelism": f"ulysses{world}" if world > 1 else "single",
-                   "text_stream": "n/a" if world == 1 else ("replicated on every rank (reference layout)"
-                                                            if args.replicated_text else "sharded over the ranks"),
-                   "l2": "weights (23.8 GB) and activations exceed the 126 MB L2; no explicit flush",
-                   "cuda_graph": graph is not None, "ms_per_step_eager_launches": ms_eager,
-                   "step_flops": model.flops_per_step(S_IMG, S_TXT),
-                   "step_tflops_achieved": model.flops_per_step(S_IMG, S_TXT) / (ms_step * 1e-3) / 1e12 / world},
+        "config": {"workload": cfg["workload"],
+                   "parallelism": f"ulysses{U}xring{R}" if world > 1 else "single",
+                   "text_stream": text_layout,
+                   "l2": "weights and activations exceed the 126 MB L2; no explicit flush",
+                   "cuda_graph": graph is not None if world == 1 or ms_replicated is None else True,
+                   "ms_per_step_eager_launches": ms_eager,
+                   "ms_per_step_replicated_text": ms_replicated,
+                   "step_flops": step_flops,
+                   "step_tflops_achieved": step_flops / (ms_step * 1e-3) / 1e12 / world},
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "clocks": clk.summary(),
-        "roofline": {"kernel": "attn_fwd_kernel<128,bf16>", "bound": "tensor", "achieved": achieved, "peak": peak_tf,
-                     "unit": "TFLOP/s", "frac": (achieved / peak_tf) if achieved else None, "traffic": traffic,
-                     "peak_source": f"bf16_tflops_sustained, {peak_kind}", "launches_timed": attn_ms["count"],
-                     "flops_per_launch": attn_flops},
+        "roofline": {"kernel": f"attn_fwd_kernel<{shape.head_dim},bf16>", "bound": "tensor", "achieved": achieved,
+                     "peak": peak_tf, "unit": "TFLOP/s", "frac": (achieved / peak_tf) if achieved else None,
+                     "traffic": traffic, "peak_source": f"bf16_tflops_sustained, {peak_kind}",
+                     "launches_timed": attn_ms["count"],
+                     "flops_per_launch": attn_ms["flops"] / max(attn_ms["count"], 1)},
+        "parity_check": parity,
     }
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        total_s, desc = cpu_step_sample(threads, (1, 1))
+        total_s, desc, _ = cpu_step_sample(threads, args.config, (1, 1))
         line["cpu_baseline"] = {"value": tokens / total_s, "unit": UNIT, "cores": threads, "kind": "port",
-                                "sample": desc}
+                                "sample": desc, "extrapolated": True}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+S_IMG, S_TXT = 4096, 512  # the Flux shape, used by the single-kernel cases below
 
 
 def run_kernel_case(args):
@@ -508,12 +706,99 @@ def run_usp_case(args):
     dist.destroy_process_group()
 
 
+def run_trace(args):
+    """BASELINE's serving-trace configuration on N GPUs: SD3-medium-shaped model, seeded Poisson arrivals at 2
+    requests/s, four resolutions, text length 77..333, 20 steps per request, PipeFusion with 4 patches and one
+    warm-up step, the plan (PipeFusion degree x Ulysses degree) taken from a fixed table per resolution and every
+    change of plan made through the worker plan API with parameter-slice migration. Prints mean / p95 request
+    latency and the share of requests within 5x their single-GPU latency. `--trace-requests` shortens the
+    2000-request trace (the line says so)."""
+    import torch.distributed as dist
+    import hetu_dit_b200.model_executor.models.shaped_dit as M
+    from hetu_dit_b200 import _C, kernels
+    from hetu_dit_b200.core.distributed.runtime_state import ModelGeometry
+    from hetu_dit_b200.model_executor.pipelines.pipeline_sd3_shaped import SD3ShapedPipeline
+    from hetu_dit_b200.serving.trace_driver import TraceDriver, make_trace
+    from hetu_dit_b200.worker.worker import Worker
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    _C.lib()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def exchange(obj):
+        if world == 1:
+            return [obj]
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
+
+    def reduce_max(x):
+        if world == 1:
+            return float(x)
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    shape = M.SD3_MEDIUM
+    # the CPU master copy every slice is cut from: built on the GPU (seeded), then moved to host memory
+    torch.set_default_dtype(torch.bfloat16)
+    with torch.device(dev):
+        model = M.ShapedDiT(shape)
+    torch.set_default_dtype(torch.float32)
+    model.init_weights(seed=0, std=0.02)
+    cpu_master = model.cpu()
+    del model
+    torch.cuda.empty_cache()
+    worker = Worker(rank, world, local_rank=local_rank, exchange=exchange, heap_bytes=1 << 30, arena_bytes=6 << 30)
+    worker.init_static_env()
+    worker.init_instance_model(cpu_master, ModelGeometry(shape.heads, shape.head_dim),
+                               lambda t: SD3ShapedPipeline(t, guidance_scale=5.0))
+    driver = TraceDriver(worker, reduce_max, shape.text_dim, shape.pooled_dim)
+    n_req = args.trace_requests
+    trace = make_trace(2000, rate_per_s=2.0, seed=0, steps=20)[:n_req]
+    kernels.reset_counters()
+    t0 = time.perf_counter()
+    with ClockSampler(local_rank) as clk:
+        res = driver.run(trace)
+    wall = time.perf_counter() - t0
+    status = _C.device_status(local_rank, clear=True)
+    if status[0] != 0:
+        raise SystemExit(f"device-side wait timed out during the trace: {status}")
+    if rank == 0:
+        line = {"metric": "trace_request_latency_p95", "value": res["p95_s"], "unit": "s", "n_gpus": world,
+                "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic",
+                "config": {"workload": "SD3-medium-shaped serving trace: Poisson arrivals 2 req/s (seed 0), 20 steps, "
+                                       "resolutions 512/768/1024/1536 squared, text 77..333 tokens, CFG batch 2, "
+                                       "PipeFusion 4 patches, 1 warm-up step, FIFO admission, plan per resolution "
+                                       "from a fixed table, plan switches through the worker API",
+                           "requests": n_req, "requests_in_full_trace": 2000,
+                           "arrivals": "virtual clock; service times measured on the GPUs (max over ranks)",
+                           "slo": "latency <= 5 x single-GPU latency of the same resolution"},
+                "trace": res, "wall_s": wall, "gpu_launches": kernels.launch_count(), "clocks": clk.summary()}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="flux", choices=sorted(CONFIGS) + ["trace"],
+                    help="which BASELINE configuration to run (default: the Flux.1-dev-shaped step); `trace` is "
+                         "the serving trace of the SD3-medium-shaped model")
+    ap.add_argument("--trace-requests", type=int, default=200,
+                    help="--config trace: how many of the 2000 requests of the trace to run")
+    ap.add_argument("--no-parity-check", action="store_true",
+                    help="skip the tiny-model parity check that precedes the timed region")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a captured CUDA graph")
     ap.add_argument("--replicated-text", action="store_true",
@@ -529,6 +814,12 @@ def main():
         run_usp_case(args)
     elif args.kernel_case:
         run_kernel_case(args)
+    elif args.config == "trace":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the serving trace has no CPU arm: the reference's "
+                              "scheduler and HTTP engine are outside the denoising hot path"}), flush=True)
+        else:
+            run_trace(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -64,6 +64,11 @@ class AttnArgs(ctypes.Structure):
         ("acc_out", ctypes.c_void_p),
         ("acc_lse", ctypes.c_void_p),
         ("stream", ctypes.c_void_p),
+        ("n_out_dst", ctypes.c_int32),
+        ("kv_interleave", ctypes.c_int32),
+        ("out_dst", ctypes.c_void_p * 8),
+        ("q_rows_per_dst", ctypes.c_int64 * HDIT_MAX_Q_SEG),
+        ("q_dst_row0", ctypes.c_int64 * HDIT_MAX_Q_SEG),
     ]
 
 
@@ -164,9 +169,10 @@ def _declare(lib):
     lib.hdit_peer_barrier.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
                                       ctypes.c_int, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
     lib.hdit_peer_signal.restype = ctypes.c_int
-    lib.hdit_peer_signal.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
+    lib.hdit_peer_signal.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
     lib.hdit_peer_wait.restype = ctypes.c_int
-    lib.hdit_peer_wait.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p]
+    lib.hdit_peer_wait.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
+                                   ctypes.c_void_p]
 
 
 def lib():

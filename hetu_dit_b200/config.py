@@ -64,6 +64,35 @@ class ParallelConfig:
         return (self.sp_config.sp_degree * self.pp_config.pp_degree * self.tp_config.tp_degree *
                 self.dp_config.dp_degree * self.dp_config.cfg_degree)
 
+    # flat views, as the reference's ParallelConfig exposes them (config.py:204-244)
+    @property
+    def tp_degree(self) -> int:
+        return self.tp_config.tp_degree
+
+    @property
+    def sp_degree(self) -> int:
+        return self.sp_config.sp_degree
+
+    @property
+    def ulysses_degree(self) -> int:
+        return self.sp_config.ulysses_degree
+
+    @property
+    def ring_degree(self) -> int:
+        return self.sp_config.ring_degree
+
+    @property
+    def pp_degree(self) -> int:
+        return self.pp_config.pp_degree
+
+    @property
+    def cfg_degree(self) -> int:
+        return self.dp_config.cfg_degree
+
+    @property
+    def dp_degree(self) -> int:
+        return self.dp_config.dp_degree
+
 
 @dataclass
 class InputConfig:
@@ -71,8 +100,13 @@ class InputConfig:
     width: int = 1024
     num_frames: int = 1
     batch_size: int = 1
+    prompt: str = ""
+    negative_prompt: str = ""
     num_inference_steps: int = 20
+    max_sequence_length: int = 256
     seed: int = 42
+    output_type: str = "latent"
+    task_id: str = ""
 
 
 @dataclass
@@ -80,3 +114,6 @@ class EngineConfig:
     runtime_config: RuntimeConfig = field(default_factory=RuntimeConfig)
     parallel_config: ParallelConfig = field(default_factory=ParallelConfig)
     input_config: InputConfig = field(default_factory=InputConfig)
+    # which global ranks run the stages of the current request (set by the scheduler; config.py:253-258)
+    encode_stage_rank: Optional[int] = None
+    diffusion_stage_ranks: Optional[List[int]] = None

@@ -52,7 +52,7 @@ class PipelineGroupCoordinator:
         self.inbox = None
         self.inbox_offset = 0
         self.inbox_bytes = inbox_bytes
-        self.max_spins = DEFAULT_MAX_SPINS
+        self.max_spins = None  # None: the heap's bound (PeerHeap.max_spins)
         if self.world_size > 1:
             if self.heap is None:
                 raise RuntimeError("PipeFusion across ranks needs the peer heap")

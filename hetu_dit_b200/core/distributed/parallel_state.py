@@ -137,34 +137,58 @@ class ParallelGroups:
         PROCESS_GROUP.ULYSSES_PG, PROCESS_GROUP.RING_PG = upg, rpg
         self._pp_coordinator = None
 
-    # reference-named switches: each re-activates the plan with one axis given explicitly
-    def set_activate_world_group(self, ranks: Sequence[int]):
+    # reference-named switches (parallel_state.py:977-1124), called by Worker.switch_parallel_env the way the
+    # reference calls them: set_activate_<axis>_group(degree, ranks, group_ranks[, ...]) where `ranks` are the
+    # plan's global ranks and `group_ranks` the partition of them along that axis; this rank's group is the
+    # member list that contains it. The old one-argument forms (just this rank's member list) still work.
+    def _mine(self, ranks, group_ranks):
+        if group_ranks is None:
+            return list(ranks)
+        for g in group_ranks:
+            if self.rank in g:
+                return list(g)
+        raise ValueError(f"rank {self.rank} is in none of the groups {group_ranks}")
+
+    def set_activate_world_group(self, degree=None, ranks=None, group_ranks=None):
+        if ranks is None:            # one-argument form: set_activate_world_group(ranks)
+            degree, ranks = None, degree
         self.rank_map = sorted(ranks)
         self._groups["world"] = PeerGroup(self.rank_map, self.rank, self.heap)
+        self.activate_world_groups = [list(g) for g in (group_ranks or [self.rank_map])]
 
-    def set_activate_sp_group(self, ranks: Sequence[int], ulysses_degree: int, ring_degree: int):
-        upg, rpg = set_seq_parallel_pg(ulysses_degree, ring_degree, self.rank, len(ranks), list(ranks), heap=self.heap)
-        self._groups["sp"] = SequenceParallelGroup(sorted(ranks), self.rank, self.heap, upg, rpg)
+    def set_activate_sp_group(self, degree=None, ranks=None, group_ranks=None, ulysses_degree=1, ring_degree=1):
+        if not isinstance(degree, int) or ranks is None or isinstance(ranks, int):
+            # old form: set_activate_sp_group(member_ranks, ulysses_degree, ring_degree)
+            members, ulysses_degree, ring_degree = list(degree), ranks, group_ranks
+        else:
+            members = self._mine(ranks, group_ranks)
+        upg, rpg = set_seq_parallel_pg(ulysses_degree, ring_degree, self.rank, len(members), list(members),
+                                       heap=self.heap)
+        self._groups["sp"] = SequenceParallelGroup(sorted(members), self.rank, self.heap, upg, rpg)
         self.degrees["ulysses"], self.degrees["ring"] = ulysses_degree, ring_degree
         PROCESS_GROUP.ULYSSES_PG, PROCESS_GROUP.RING_PG = upg, rpg
 
-    def _set_axis(self, axis: str, ranks: Sequence[int]):
-        self._groups[axis] = PeerGroup(list(ranks), self.rank, self.heap)
-        self.degrees[axis] = len(ranks)
+    def _set_axis(self, axis: str, degree, ranks, group_ranks):
+        if ranks is None:            # one-argument form: the member list itself
+            members = list(degree)
+        else:
+            members = self._mine(ranks, group_ranks)
+        self._groups[axis] = PeerGroup(members, self.rank, self.heap)
+        self.degrees[axis] = len(members)
         if axis == "pp":
             self._pp_coordinator = None
 
-    def set_activate_tp_group(self, ranks):
-        self._set_axis("tp", ranks)
+    def set_activate_tp_group(self, degree=None, ranks=None, group_ranks=None):
+        self._set_axis("tp", degree, ranks, group_ranks)
 
-    def set_activate_pp_group(self, ranks):
-        self._set_axis("pp", ranks)
+    def set_activate_pp_group(self, degree=None, ranks=None, group_ranks=None):
+        self._set_axis("pp", degree, ranks, group_ranks)
 
-    def set_activate_cfg_group(self, ranks):
-        self._set_axis("cfg", ranks)
+    def set_activate_cfg_group(self, degree=None, ranks=None, group_ranks=None):
+        self._set_axis("cfg", degree, ranks, group_ranks)
 
-    def set_activate_dp_group(self, ranks):
-        self._set_axis("dp", ranks)
+    def set_activate_dp_group(self, degree=None, ranks=None, group_ranks=None):
+        self._set_axis("dp", degree, ranks, group_ranks)
 
     def group(self, axis: str) -> PeerGroup:
         return self._groups[axis]

@@ -20,6 +20,8 @@ MAX_RANKS_PER_NODE = 8
 _BARRIER_SLOTS = 256 * MAX_RANKS_PER_NODE  # one row of 8 counters per rank subset (bit mask of members)
 _P2P_BASE = _BARRIER_SLOTS      # then 8 x 8 x 16 point-to-point sequence counters
 _EPOCH_BASE = _P2P_BASE + 8 * 8 * 16  # then one barrier epoch counter per rank subset (device-side)
+_P2P_SENT_BASE = _EPOCH_BASE + 256    # then, per link and channel, how many messages this rank has signalled ...
+_P2P_EXPECT_BASE = _P2P_SENT_BASE + 8 * 8 * 16  # ... and how many it has waited for (device-side, graph-replayable)
 DEFAULT_MAX_SPINS = 20_000_000  # about two seconds of polling
 
 
@@ -40,9 +42,10 @@ class PeerHeap:
         self.nbytes = int(nbytes)
         self.rank, self.world_size, self.device = rank, world_size, torch.device(device)
         self._cursor = FLAG_BYTES
+        self.max_spins = DEFAULT_MAX_SPINS  # default bound of every device-side wait; a plan may raise it
         self._named: Dict[str, tuple] = {}
         self._epochs: Dict[int, int] = {}
-        self._p2p_seq: Dict[tuple, int] = {}
+        self._flip: Dict[str, int] = {}
         lib = _C.lib()
         with torch.cuda.device(self.device):
             base = ctypes.c_void_p()
@@ -69,6 +72,7 @@ class PeerHeap:
         """Forget every buffer (plan switch). Ranks of a new group then allocate from the same offset."""
         self._cursor = FLAG_BYTES
         self._named.clear()
+        self._flip.clear()
 
     def alloc(self, shape: Sequence[int], dtype: torch.dtype, name: Optional[str] = None):
         """(tensor, offset): a zero-copy view of `shape` at a 256-byte aligned heap offset. A `name`
@@ -92,6 +96,12 @@ class PeerHeap:
             self._named[name] = (t, off)
         return t, off
 
+    def flip(self, name: str) -> int:
+        """0, 1, 0, ... per name: which of two alternately used buffers the next exchange of that name takes.
+        Every rank of a group calls it once per exchange, so the ranks agree."""
+        v = self._flip[name] = 1 - self._flip.get(name, 1)
+        return v
+
     def offset_of(self, t: torch.Tensor) -> int:
         off = t.data_ptr() - self.base
         if off < 0 or off >= self.nbytes:
@@ -108,8 +118,9 @@ class PeerHeap:
     def _flag_ptr(self, rank: int, index: int) -> int:
         return self.peer_ptr(rank, index * 4)
 
-    def barrier(self, ranks: Sequence[int], max_spins: int = DEFAULT_MAX_SPINS):
+    def barrier(self, ranks: Sequence[int], max_spins: Optional[int] = None):
         """Stream-ordered barrier among `ranks` (global ranks of this node, this rank included)."""
+        max_spins = self.max_spins if max_spins is None else max_spins
         ranks = list(ranks)
         n = len(ranks)
         if n == 1:
@@ -136,26 +147,35 @@ class PeerHeap:
         return _P2P_BASE + ((src % 8) * 8 + (dst % 8)) * 16 + channel
 
     def signal(self, dst: int, channel: int):
-        """Bump the (me -> dst, channel) sequence counter in dst's heap after all earlier stream work."""
-        key = (self.rank, dst, channel)
-        seq = self._p2p_seq.get(key, 0) + 1
-        self._p2p_seq[key] = seq
+        """Bump the (me -> dst, channel) sequence counter in dst's heap after all earlier stream work. The
+        sequence number lives in this rank's heap and is advanced by the kernel, so the call can be captured
+        in a CUDA graph and replayed."""
+        idx = self.p2p_flag_index(self.rank, dst, channel)
+        counter = self._flag_ptr(self.rank, _P2P_SENT_BASE + idx - _P2P_BASE)
         with torch.cuda.device(self.device):
             stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-            _C.check(_C.lib().hdit_peer_signal(self._flag_ptr(dst, self.p2p_flag_index(self.rank, dst, channel)), seq,
-                                               stream))
-        return seq
+            _C.check(_C.lib().hdit_peer_signal(self._flag_ptr(dst, idx), 0, counter, stream))
 
-    def wait(self, src: int, channel: int, max_spins: int = DEFAULT_MAX_SPINS):
-        """Hold the stream until the next (src -> me, channel) message has been signalled."""
-        key = (src, self.rank, channel)
-        seq = self._p2p_seq.get(key, 0) + 1
-        self._p2p_seq[key] = seq
+    def wait(self, src: int, channel: int, max_spins: Optional[int] = None):
+        """Hold the stream until the next (src -> me, channel) message has been signalled (bounded: on expiry
+        the kernel records HDIT_ERR_PEER_TIMEOUT and the stream moves on; check() raises it)."""
+        max_spins = self.max_spins if max_spins is None else max_spins
+        idx = self.p2p_flag_index(src, self.rank, channel)
+        counter = self._flag_ptr(self.rank, _P2P_EXPECT_BASE + idx - _P2P_BASE)
         with torch.cuda.device(self.device):
             stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-            _C.check(_C.lib().hdit_peer_wait(self._flag_ptr(self.rank, self.p2p_flag_index(src, self.rank, channel)),
-                                             seq, max_spins, src * 16 + channel, stream))
-        return seq
+            _C.check(_C.lib().hdit_peer_wait(self._flag_ptr(self.rank, idx), 0, counter, max_spins, src * 16 + channel,
+                                             stream))
+
+    def resync_flags(self, host_barrier: Callable[[], None]):
+        """After a reported timeout the counters of the ranks no longer agree. Collective over all ranks of the
+        node: every rank drains its GPU, all meet on the host, every rank zeroes its own flag block (barrier
+        rows, point-to-point flags and every device-side counter), all meet again."""
+        torch.cuda.synchronize(self.device)
+        host_barrier()
+        self._bytes[:FLAG_BYTES].zero_()
+        torch.cuda.synchronize(self.device)
+        host_barrier()
 
     def check(self):
         """Synchronise and raise if a bounded device-side wait ran out since the last check."""
@@ -181,7 +201,7 @@ class PeerGroup:
     def rank(self):
         return self.rank_in_group
 
-    def barrier(self, max_spins: int = DEFAULT_MAX_SPINS):
+    def barrier(self, max_spins: Optional[int] = None):
         if self.world_size > 1:
             if self.heap is None:
                 raise RuntimeError("a multi-rank group needs the peer heap")
@@ -281,6 +301,12 @@ class ParamArena:
             else:
                 merged.append((o, s))
         self._free = merged
+
+    def flip(self, name: str) -> int:
+        """0, 1, 0, ... per name: which of two alternately used buffers the next exchange of that name takes.
+        Every rank of a group calls it once per exchange, so the ranks agree."""
+        v = self._flip[name] = 1 - self._flip.get(name, 1)
+        return v
 
     def offset_of(self, t: torch.Tensor) -> int:
         return t.data_ptr() - self.heap.base

@@ -92,32 +92,53 @@ class _UlyssesExchange:
         g.barrier()
         return outs
 
-    def scatter_sequence(self, ctx: Tensor, tag: str, joint_len: int = 0, joint_front: bool = True) -> Tensor:
-        """SeqAllToAll4D(scatter_idx=1, gather_idx=2): (B, U*S_loc, H/U, D) -> (B, S_loc, H, D).
+    def scatter_plan(self, B: int, S_tot: int, Hl: int, D: int, dtype, tag: str, joint_len: int = 0,
+                     joint_front: bool = True):
+        """SeqAllToAll4D(scatter_idx=1, gather_idx=2), (B, U*S_loc, H/U, D) -> (B, S_loc, H, D), as a store plan
+        for the attention epilogue instead of a pass of its own: returns (out, scatter) where `out` is this
+        rank's (B, joint_len + S_loc, H, D) result buffer in the peer heap and `scatter` tells the attention
+        kernel where each of its result rows goes -- the image rows of source rank p into p's buffer, the rows
+        of the replicated joint (text) queries, computed once per head slice, into every peer's buffer; both at
+        this rank's head slice. The caller runs attention with it and then calls finish().
 
-        With joint_len > 0 the context also carries `joint_len` rows of the replicated joint (text)
-        queries, computed once per head slice: those rows go to *every* peer, the image rows of source
-        rank p go to p. The result is (B, joint_len + S_loc, H, D) in [joint; local] ("front") or
-        [local; joint] order."""
+        Two buffers are used alternately: a peer writes this rank's buffer for layer L+1 only after the barrier
+        that follows layer L+1's head exchange, which this rank enters after it has enqueued (on the same stream)
+        everything that reads layer L's result; alternating adds one more layer of slack for a caller that keeps
+        the returned view a little longer."""
         g, U, me = self.group, self.group.world_size, self.group.rank_in_group
-        B, S_tot, Hl, D = ctx.shape
         S = (S_tot - joint_len) // U
         rows = S + joint_len
-        # Two buffers used alternately: a peer writes this rank's buffer for layer L+1 only after the
-        # barrier that follows layer L+1's head exchange, which this rank enters after it has enqueued
-        # (on the same stream) everything that reads layer L's result; alternating adds one more layer
-        # of slack for a caller that keeps the returned view a little longer.
-        parity = _UlyssesExchange._parity = 1 - getattr(_UlyssesExchange, "_parity", 0)
-        out, off = self.heap.alloc((B, rows, Hl * U, D), ctx.dtype,
-                                   name=f"usp_{tag}{parity}_{(B, rows, Hl * U, D)}_{ctx.dtype}")
+        # sized for the joint length rounded up to 512 rows, so that requests whose text lengths differ share
+        # the buffer instead of growing the heap by one per length
+        cap = S + -(-joint_len // 512) * 512
+        name = f"usp_{tag}_{(B, cap, Hl * U, D)}_{dtype}_{g.ranks}"
+        buf, off = self.heap.alloc((B, cap, Hl * U, D), dtype, name=f"{name}_{self.heap.flip(name)}")
+        out = buf[:, :rows]
+        es = out.element_size()
+        ptrs = [self.heap.peer_ptr(r, off) + me * Hl * D * es for r in g.ranks]
+        scatter = dict(dsts=kernels.RawDst(ptrs, out.stride()[:3]),
+                       q=(S, joint_len if joint_front else 0),       # (rows per destination, first destination row)
+                       joint=(0, 0 if joint_front else S))           # 0 rows per destination = to every destination
+        return out, scatter
+
+    def finish(self):
+        """Orders the peers' result stores against this rank's readers (and this rank's stores against theirs)."""
+        self.group.barrier()
+
+    def scatter_sequence(self, ctx: Tensor, tag: str, joint_len: int = 0, joint_front: bool = True) -> Tensor:
+        """The same exchange for a context tensor that already exists (one copy launch): used when the
+        attention call cannot scatter by itself."""
+        g, U = self.group, self.group.world_size
+        B, S_tot, Hl, D = ctx.shape
+        S = (S_tot - joint_len) // U
+        out, plan = self.scatter_plan(B, S_tot, Hl, D, ctx.dtype, tag, joint_len, joint_front)
         es = ctx.element_size()
         img0_src = joint_len if joint_front else 0      # first image row in ctx
-        img0_dst = joint_len if joint_front else 0      # first image row in out
+        img0_dst = plan["q"][1]
         jnt_src = 0 if joint_front else U * S
-        jnt_dst = 0 if joint_front else S
+        jnt_dst = plan["joint"][1]
         pieces = []
-        for p, r in enumerate(g.ranks):
-            base = self.heap.peer_ptr(r, off) + me * Hl * D * es
+        for p, base in enumerate(plan["dsts"].ptrs):
             src = ctx[:, img0_src + p * S:img0_src + (p + 1) * S]
             pieces.append((src.data_ptr(), base + img0_dst * out.stride(1) * es, B, ctx.stride(0) * es,
                            out.stride(0) * es, S, ctx.stride(1) * es, out.stride(1) * es, Hl * D * es))
@@ -184,16 +205,24 @@ class hetuDiTLongContextAttention(torch.nn.Module):
                     kernels.qk_norm_rope([(query[:, lo:hi], wq, wq is not None, rope is not None),
                                           (key[:, lo:hi], wk, wk is not None, rope is not None)],
                                          eps=eps, cos=cos, sin=sin, rope_seq_start=0, rope_row0=row0)
+        scatter = out_buf = None
+        if U > 1:
+            # the reverse all-to-all is done by the attention epilogue: every result row is stored straight into
+            # the buffer of the rank that owns it
+            B, S_g, Hl, D = query.shape
+            joint_len = 0 if joint_q is None else joint_q.shape[1]
+            out_buf, scatter = xchg.scatter_plan(B, S_g + joint_len, Hl, D, query.dtype, "o", joint_len,
+                                                 joint_strategy == "front")
         out = self.ring_attn_fn(query, key, value, dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal,
                                 window_size=window_size, alibi_slopes=alibi_slopes, deterministic=deterministic,
                                 return_attn_probs=return_attn_probs, group=self.ring_pg,
                                 attn_layer=attn if self.use_kv_cache else None, joint_tensor_key=joint_k,
-                                joint_tensor_value=joint_v, joint_strategy=joint_strategy, joint_tensor_query=joint_q)
-        context = out[0] if isinstance(out, tuple) else out
+                                joint_tensor_value=joint_v, joint_strategy=joint_strategy, joint_tensor_query=joint_q,
+                                out_scatter=scatter)
         if U > 1:
-            context = xchg.scatter_sequence(context, "o", joint_len=0 if joint_q is None else joint_q.shape[1],
-                                            joint_front=joint_strategy == "front")
-        return context
+            xchg.finish()
+            return out_buf
+        return out[0] if isinstance(out, tuple) else out
 
     @torch.compiler.disable
     def forward(self, attn, query: Tensor, key: Tensor, value: Tensor, *, joint_tensor_query=None,

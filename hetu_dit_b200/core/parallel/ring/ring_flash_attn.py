@@ -23,15 +23,16 @@ from ...distributed.peer import PeerGroup
 from ...resource_manager.cache_manager import get_cache_manager
 
 _SUPPORTED_JOINT = ["none", "front", "rear"]
-_side_streams = {}
-_staging = {}
 
 
-def _side_stream(device):
-    key = (device.type, device.index)
-    if key not in _side_streams:
-        _side_streams[key] = torch.cuda.Stream(device=device)
-    return _side_streams[key]
+def _ring_state(heap, device):
+    """Side stream and staging buffers of the ring pulls, owned by the heap (one per plan group) and keyed by
+    the stream the caller runs on: two models, or two streams, in one process do not share them."""
+    state = heap.__dict__.setdefault("_ring_state", {})
+    key = torch.cuda.current_stream(device).cuda_stream
+    if key not in state:
+        state[key] = {"side": torch.cuda.Stream(device=device), "staging": {}}
+    return state[key]
 
 
 def _in_heap(heap, t: torch.Tensor) -> bool:
@@ -51,12 +52,16 @@ def _publish(heap, t: torch.Tensor, tag: str) -> torch.Tensor:
 def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                             softmax_scale, dropout_p=0, causal=True, window_size=(-1, -1), alibi_slopes=None,
                             deterministic=False, attn_layer=None, joint_tensor_key=None, joint_tensor_value=None,
-                            joint_strategy="none", joint_tensor_query=None):
+                            joint_strategy="none", joint_tensor_query=None, out_scatter=None):
     """(out in q.dtype, lse (B, H, Sq) fp32) for this rank's queries against the whole ring's K/V.
 
     joint_tensor_query (not in the reference's signature): joint queries kept as their own segment
     instead of being concatenated into `q` by the caller; output rows are [joint; q] for "front" and
-    [q; joint] for "rear", exactly as if they had been concatenated."""
+    [q; joint] for "rear", exactly as if they had been concatenated.
+
+    out_scatter (not in the reference's signature): dict(dsts=RawDst, q=(rows per destination, first row),
+    joint=(...)) -- the launch that produces the final result stores its rows into these destination buffers
+    (the Ulysses reverse all-to-all from the attention epilogue) and `out` is returned as None."""
     if joint_strategy not in _SUPPORTED_JOINT:
         raise ValueError(
             f"joint_strategy: {joint_strategy} not supprted. supported joint strategy: {_SUPPORTED_JOINT}")
@@ -72,15 +77,23 @@ def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor,
     world = 1 if process_group is None else process_group.world_size
     front = [joint_tensor_key], [joint_tensor_value]
     q_segs = [q]
+    roles = ["q"]
     if joint_tensor_query is not None:
-        q_segs = [joint_tensor_query, q] if joint_strategy == "front" else [q, joint_tensor_query]
+        front_q = joint_strategy == "front"
+        q_segs = [joint_tensor_query, q] if front_q else [q, joint_tensor_query]
+        roles = ["joint", "q"] if front_q else ["q", "joint"]
+    scatter_kw = {}
+    if out_scatter is not None:
+        scatter_kw = dict(out_dsts=out_scatter["dsts"], q_rows_per_dst=[out_scatter[r][0] for r in roles],
+                          q_dst_row0=[out_scatter[r][1] for r in roles])
     if world == 1:
         ks, vs = [k], [v]
         if joint_strategy == "rear":
             ks, vs = [k, joint_tensor_key], [v, joint_tensor_value]
         elif joint_strategy == "front":
             ks, vs = [joint_tensor_key, k], [joint_tensor_value, v]
-        return kernels.attn_fwd(q_segs, ks, vs, softmax_scale=softmax_scale, return_lse=True)
+        res = kernels.attn_fwd(q_segs, ks, vs, softmax_scale=softmax_scale, return_lse=True, **scatter_kw)
+        return (None, res) if out_scatter is not None else res
 
     heap = process_group.heap
     if heap is None:
@@ -92,14 +105,15 @@ def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor,
 
     me = process_group.rank_in_group
     B, S_blk, H, D = k_pub.shape
-    key = (dev.index, world, tuple(k_pub.shape), k_pub.dtype)
-    if key not in _staging:
-        _staging[key] = torch.empty((2, world - 1) + tuple(k_pub.shape), dtype=k_pub.dtype, device=dev)
-    stage = _staging[key]
+    state = _ring_state(heap, dev)
+    key = (world, tuple(k_pub.shape), k_pub.dtype)
+    if key not in state["staging"]:
+        state["staging"][key] = torch.empty((2, world - 1) + tuple(k_pub.shape), dtype=k_pub.dtype, device=dev)
+    stage = state["staging"][key]
     nbytes = k_pub.numel() * k_pub.element_size()
 
     # pull the R-1 remote blocks on the side stream, in the order the ring would deliver them
-    side = _side_stream(dev)
+    side = state["side"]
     side.wait_stream(torch.cuda.current_stream(dev))
     with torch.cuda.stream(side):
         pieces = []
@@ -125,15 +139,17 @@ def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor,
     vs = [stage[1, i] for i in range(world - 1)]
     if joint_strategy == "rear":
         ks, vs = ks + [joint_tensor_key], vs + [joint_tensor_value]
-    out, lse = kernels.attn_fwd(q_segs, ks, vs, softmax_scale=softmax_scale, mode=_C.ATTN_MERGE_FINAL, acc_out=acc,
-                                acc_lse=acc_lse, return_lse=True)
+    res = kernels.attn_fwd(q_segs, ks, vs, softmax_scale=softmax_scale, mode=_C.ATTN_MERGE_FINAL, acc_out=acc,
+                           acc_lse=acc_lse, return_lse=True, **scatter_kw)
+    out, lse = (None, res) if out_scatter is not None else res
     process_group.barrier()  # peers have finished pulling this rank's block
     return out, lse
 
 
 def ring_flash_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
                          alibi_slopes=None, deterministic=False, return_attn_probs=False, group=None, attn_layer=None,
-                         joint_tensor_key=None, joint_tensor_value=None, joint_strategy="none", joint_tensor_query=None):
+                         joint_tensor_key=None, joint_tensor_value=None, joint_strategy="none", joint_tensor_query=None,
+                         out_scatter=None):
     """Forward only (inference): returns out, or (out, lse, None) when return_attn_probs is set."""
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** (-0.5)
@@ -142,5 +158,5 @@ def ring_flash_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=Fals
                                        window_size=window_size, alibi_slopes=alibi_slopes, deterministic=False,
                                        attn_layer=attn_layer, joint_tensor_key=joint_tensor_key,
                                        joint_tensor_value=joint_tensor_value, joint_strategy=joint_strategy,
-                                       joint_tensor_query=joint_tensor_query)
+                                       joint_tensor_query=joint_tensor_query, out_scatter=out_scatter)
     return out if not return_attn_probs else (out, lse, None)

@@ -56,7 +56,12 @@ class hetuDiTUlyssesAttention(torch.nn.Module):
             ks, vs = [key, joint_tensor_key], [value, joint_tensor_value]
         elif has_joint and joint_strategy == "front":
             ks, vs = [joint_tensor_key, key], [joint_tensor_value, value]
-        context = kernels.attn_fwd([query], ks, vs, softmax_scale=softmax_scale)
-        if U > 1:
-            context = xchg.scatter_sequence(context, "o")
-        return context
+        if U == 1:
+            return kernels.attn_fwd([query], ks, vs, softmax_scale=softmax_scale)
+        # the reverse exchange rides on the attention epilogue: rows go straight into their owners' buffers
+        B, S_g, Hl, D = query.shape
+        out, plan = xchg.scatter_plan(B, S_g, Hl, D, query.dtype, "o")
+        kernels.attn_fwd([query], ks, vs, softmax_scale=softmax_scale, out_dsts=plan["dsts"],
+                         q_rows_per_dst=[plan["q"][0]], q_dst_row0=[plan["q"][1]])
+        xchg.finish()
+        return out

@@ -6,6 +6,10 @@
 //   warp 8      TMA producer   : Q tiles once, then K/V blocks through two rings
 //   warp 9      MMA issuer     : S = Q K^T (tcgen05.mma, smem x smem -> TMEM)
 //                                O += P V  (tcgen05.mma, TMEM x smem -> TMEM)
+//                                (issuing a tcgen05.mma holds the issuing thread for about as long as the
+//                                MMA runs -- 64 cycles at 128x128x16 -- so whatever else this thread does
+//                                between two MMAs idles the tensor pipe: operand barriers are polled before
+//                                the softmax hand-over, never after it)
 //   warps 10-11 idle           : complete the third warpgroup so registers can be handed over
 //                                (setmaxnreg: 72 per thread there, 216 for the softmax threads;
 //                                72 + 2 * 216 = 3 * 168, the pool the CTA was launched with --
@@ -14,7 +18,12 @@
 //   warps 4-7   softmax group 1: owns Q tile 1
 //
 // The two softmax groups ping-pong against the tensor pipe: while group 0
-// exponentiates S0 the MMA warp runs P1 V and the next Q1 K^T, and vice versa.
+// exponentiates S0 the tensor pipe runs P1 V and the next Q1 K^T, and vice versa.
+//
+// Small grids (fewer tile pairs than SMs, e.g. the head-sharded calls after a Ulysses exchange) run in
+// "interleaved" mode instead: a CTA owns ONE Q tile, its two halves (softmax group + MMA issuer each)
+// take the even and the odd KV blocks, and the two partial results are merged through shared memory in
+// the epilogue -- twice as many CTAs, each half as long, no round trip through HBM.
 // P overwrites S in TMEM as packed 16-bit pairs and is consumed from there.
 // The running maximum is updated lazily (only when it grows by more than 2^8),
 // so O is rescaled in TMEM rarely.
@@ -34,6 +43,7 @@
 #include <math.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "host_common.h"
 #include "ptx_sm100.cuh"
@@ -48,20 +58,26 @@ constexpr int kPanelBytes = 128 * 128;  // 128 rows x 64 16-bit elements, 128B-s
 constexpr uint32_t kSpinLimit = 8u * 1000u * 1000u;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 constexpr float kLn2 = 0.69314718055994531f;
+constexpr int kSmCount = 148;
 
 // Development aid (off in the shipped library): -DHDIT_ATTN_TRACE records SM cycle stamps of one CTA's
 // softmax and MMA phases for the first 64 KV blocks; hdit_attn_trace_read() copies them out.
 #ifdef HDIT_ATTN_TRACE
 __device__ long long g_attn_trace[2][64][8];      // [tile][block][event]
 __device__ long long g_attn_trace_mma[2][64][4];  // [tile][block][event]
+#if HDIT_ATTN_TRACE == 2  // only the loop-start / loop-end stamps of the MMA warp
+#define HDIT_TRACE_SM(ev) do {} while (0)
+#define HDIT_TRACE_MMA(tt, jj, ev) do {} while (0)
+#else
 #define HDIT_TRACE_SM(ev)                                                                  \
   do {                                                                                     \
     if (trace_on && row == 0 && j < 64) g_attn_trace[t][j][ev] = clock64();                \
   } while (0)
 #define HDIT_TRACE_MMA(tt, jj, ev)                                                         \
   do {                                                                                     \
-    if (trace_on && (jj) < 64) g_attn_trace_mma[tt][jj][ev] = clock64();                   \
+    if (trace_on && (jj) < 63) g_attn_trace_mma[tt][jj][ev] = clock64();                   \
   } while (0)
+#endif
 #else
 #define HDIT_TRACE_SM(ev) do {} while (0)
 #define HDIT_TRACE_MMA(tt, jj, ev) do {} while (0)
@@ -105,9 +121,18 @@ struct alignas(64) AttnKernelParams {
   // acc_out + y * split_acc_stride / acc_lse + y * split_lse_stride (0 = no split)
   int kv_split_blocks;
   long long split_acc_stride, split_lse_stride;
+  // interleaved mode: one Q tile per CTA, even KV blocks on half 0, odd ones on half 1
+  int interleave;
+  // result scatter (reverse all-to-all from the epilogue): n_dst == 0 writes `out` only
+  int n_dst;
+  void* dst[8];
+  long long seg_rows_per_dst[HDIT_MAX_Q_SEG];  // 0 = rows of the segment go to every destination
+  long long seg_dst_row0[HDIT_MAX_Q_SEG];
 };
 
-// Tuning switches (compile-time so that variants can be measured against each other).
+// Tuning switches (compile-time so that variants can be measured against each other). The defaults are what
+// measured fastest on B200: the stale maximum, the polynomial exp2 and a third V stage each measured neutral or
+// slower (the S -> P -> MMA chain, not the special-function unit or the loads, bounds a KV block).
 //   HDIT_ATTN_STALE_MAX  1: from the second KV block on, exponentiate against the running maximum known
 //                           *before* the block (its own maximum is computed alongside and takes effect one
 //                           block later), which takes the row-maximum pass off the S -> P critical path.
@@ -115,13 +140,16 @@ struct alignas(64) AttnKernelParams {
 //                           pipe instead of ex2 on the special-function unit.
 //   HDIT_ATTN_VSTAGES128 V ring depth at head_dim 128 (K stays at 2: 227 KB of shared memory).
 #ifndef HDIT_ATTN_STALE_MAX
-#define HDIT_ATTN_STALE_MAX 1
+#define HDIT_ATTN_STALE_MAX 0
 #endif
 #ifndef HDIT_ATTN_POLY8
 #define HDIT_ATTN_POLY8 0
 #endif
+#ifndef HDIT_ATTN_LATE_KWAIT
+#define HDIT_ATTN_LATE_KWAIT 1  // 1: poll the next K block between P V and Q K^T instead of before the hand-over
+#endif
 #ifndef HDIT_ATTN_VSTAGES128
-#define HDIT_ATTN_VSTAGES128 3
+#define HDIT_ATTN_VSTAGES128 2
 #endif
 constexpr float kOverflowGuard = 64.0f;  // log2 units a block may exceed the stale maximum before it is redone
 
@@ -192,7 +220,26 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
-template <int D, bool FP16>
+// 2^x for a pair of scores on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-3
+// polynomial (relative error 7.5e-5, well below the 16-bit rounding of P), 2^n by adding n to the exponent
+// field. Inputs below -126 (masked scores are -inf) clamp to 2^-126.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -126.0f);
+  x.y = fmaxf(x.y, -126.0f);
+  const float2 magic = make_float2(12582912.0f, 12582912.0f);  // 1.5 * 2^23: the sum's low mantissa bits hold n
+  const float2 t = __fadd2_rn(x, magic);
+  const float2 r = __fadd2_rn(t, make_float2(-12582912.0f, -12582912.0f));
+  const float2 f = __ffma2_rn(r, make_float2(-1.0f, -1.0f), x);
+  float2 q = __ffma2_rn(f, make_float2(0.05517167f, 0.05517167f), make_float2(0.24261113f, 0.24261113f));
+  q = __ffma2_rn(q, f, make_float2(0.69326097f, 0.69326097f));
+  q = __ffma2_rn(q, f, make_float2(0.99992806f, 0.99992806f));
+  float2 out;
+  out.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23));
+  out.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23));
+  return out;
+}
+
+template <int D, bool FP16, bool IL>
 __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_constant__ AttnKernelParams p) {
   using C = Cfg<D>;
   extern __shared__ char smem_raw[];
@@ -209,7 +256,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
   uint64_t* s_full = v_empty + C::kStagesV;      // [2]
   uint64_t* p_ready = s_full + 2;                // [2]
   uint64_t* o_done = p_ready + 2;                // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+  uint64_t* merge_bar = o_done + 2;              // [1] interleaved mode: half 1's partial result is in smem
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(merge_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -221,14 +269,17 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
   idx /= p.n_pairs;
   const int h = idx % p.heads;
   const int b = idx / p.heads;
-  const int tile0 = pair * 2;
-  const bool tile1_valid = (tile0 + 1) < p.n_tiles;
+  constexpr bool il = IL;  // interleaved mode is its own instantiation: the paired loop carries none of its branches
+  const int tile0 = il ? pair : pair * 2;
   int j_begin = 0;
   int nblk = p.n_kv_blocks;
   if (p.kv_split_blocks > 0) {
     j_begin = static_cast<int>(blockIdx.y) * p.kv_split_blocks;
     nblk = min(p.n_kv_blocks - j_begin, p.kv_split_blocks);
   }
+  // half t (softmax group t + MMA issuer t): its Q tile, and which KV blocks it walks
+  const bool half1_active = il ? (nblk >= 2) : ((tile0 + 1) < p.n_tiles);
+  const int blk_step = il ? 2 : 1;
   float* const acc_out = p.acc_out + static_cast<long long>(blockIdx.y) * p.split_acc_stride;
   float* const acc_lse = p.acc_lse + static_cast<long long>(blockIdx.y) * p.split_lse_stride;
 #ifdef HDIT_ATTN_TRACE
@@ -241,9 +292,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_ready[i], 128);
+      mbar_init(&p_ready[i], 4);  // one arrival per softmax warp
       mbar_init(&o_done[i], 1);
     }
+    mbar_init(merge_bar, 4);
     for (int i = 0; i < C::kStagesK; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
@@ -278,7 +330,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
           tma_prefetch_desc(&p.v_map[s]);
         }
         for (int t = 0; t < 2; ++t) {
-          if (t == 1 && !tile1_valid) break;
+          if (t == 1 && (il || !half1_active)) break;  // interleaved: both halves share the tile in slot 0
           int seg, row0, orow;
           tile_coords(p, tile0 + t, seg, row0, orow);
           mbar_expect_tx(&q_full[t], C::kTileBytes);
@@ -297,9 +349,17 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
               break;
             }
           }
-          mbar_expect_tx(&k_full[sk], C::kTileBytes);
-          load_tile(&p.k_map[cur.seg], p.k_swap[cur.seg], smem_k + sk * C::kTileBytes, &k_full[sk], C::kPanels, h,
-                    cur.row0, b);
+#if defined(HDIT_ATTN_PROBE) && HDIT_ATTN_PROBE == 3
+          // timing probe (wrong results): after the first ring fill nothing is loaded any more
+          if (j >= C::kStagesK) {
+            mbar_arrive(&k_full[sk]);
+          } else
+#endif
+          {
+            mbar_expect_tx(&k_full[sk], C::kTileBytes);
+            load_tile(&p.k_map[cur.seg], p.k_swap[cur.seg], smem_k + sk * C::kTileBytes, &k_full[sk], C::kPanels, h,
+                      cur.row0, b);
+          }
           if (j >= C::kStagesV) {
             if (!mbar_wait_bounded(&v_empty[sv], (nv - 1) & 1, abort_flag, kSpinLimit)) {
               report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_PROD_VEMPTY, j);
@@ -307,33 +367,42 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
               break;
             }
           }
-          mbar_expect_tx(&v_full[sv], C::kTileBytes);
-          load_tile(&p.v_map[cur.seg], p.v_swap[cur.seg], smem_v + sv * C::kTileBytes, &v_full[sv], C::kPanels, h,
-                    cur.row0, b);
+#if defined(HDIT_ATTN_PROBE) && HDIT_ATTN_PROBE == 3
+          if (j >= C::kStagesV) {
+            mbar_arrive(&v_full[sv]);
+          } else
+#endif
+          {
+            mbar_expect_tx(&v_full[sv], C::kTileBytes);
+            load_tile(&p.v_map[cur.seg], p.v_swap[cur.seg], smem_v + sv * C::kTileBytes, &v_full[sv], C::kPanels, h,
+                      cur.row0, b);
+          }
           cur.advance(p);
         }
       }
     } else if (warp == 9) {
       // ============================ MMA issuer ============================
+      // One thread issues for both halves. (A second issuing thread, one per half, measured slower: 852 vs
+      // 1023 TFLOP/s at the Flux shape -- concurrent issuers slow each other down more than the barrier polls
+      // of a single one idle the pipe.)
       if (lane == 0) {
         constexpr uint32_t kFmt = FP16 ? 0u : 1u;
         constexpr uint32_t idesc_qk = make_idesc_f16(kBlockM, kBlockN, kFmt, 0);
         constexpr uint32_t idesc_pv = make_idesc_f16(kBlockM, D, kFmt, 1);
-        const uint32_t q_addr = smem_u32(smem_q);
-        const uint32_t k_addr = smem_u32(smem_k);
-        const uint32_t v_addr = smem_u32(smem_v);
         bool ok = true;
+        const int last_t = half1_active ? 1 : 0;
+        const int n_iter = il ? (nblk + 1) / 2 : nblk;
 
         // Descriptors differ from a per-tile base only in the start-address field (low word, units of
         // 16 bytes), so a k-step costs one 32-bit add instead of a rebuilt 64-bit descriptor.
-        const uint64_t q_desc0 = make_smem_desc_sw128(q_addr, 16, 1024);
-        const uint64_t k_desc0 = make_smem_desc_sw128(k_addr, 16, 1024);
-        const uint64_t v_desc0 = make_smem_desc_sw128(v_addr, kPanelBytes, 1024);
+        const uint64_t q_desc0 = make_smem_desc_sw128(smem_u32(smem_q), 16, 1024);
+        const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(smem_k), 16, 1024);
+        const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(smem_v), kPanelBytes, 1024);
         auto issue_qk = [&](int t, int stage) {
           const uint32_t d_tmem = tmem_base + C::kColS + t * 128;
-          const uint64_t a0 = q_desc0 + static_cast<uint32_t>((t * C::kTileBytes) >> 4);
+          const uint64_t a0 = q_desc0 + static_cast<uint32_t>(((il ? 0 : t) * C::kTileBytes) >> 4);
           const uint64_t b0 = k_desc0 + static_cast<uint32_t>((stage * C::kTileBytes) >> 4);
-  #pragma unroll
+#pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint32_t off = ((kk >> 2) * kPanelBytes + (kk & 3) * 32) >> 4;
             umma_ss(d_tmem, a0 + off, b0 + off, idesc_qk, kk > 0 ? 1u : 0u);
@@ -343,7 +412,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
           const uint32_t d_tmem = tmem_base + C::kColO + t * D;
           const uint32_t a_tmem = tmem_base + C::kColS + t * 128;
           const uint64_t b0 = v_desc0 + static_cast<uint32_t>((stage * C::kTileBytes) >> 4);
-  #pragma unroll
+#pragma unroll
           for (int kk = 0; kk < kBlockN / 16; ++kk) {
             umma_ts(d_tmem, a_tmem + kk * 8, b0 + static_cast<uint32_t>((kk * 2048) >> 4), idesc_pv,
                     (accumulate || kk > 0) ? 1u : 0u);
@@ -356,74 +425,108 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
             ok = false;
           }
         };
+        auto k_stage = [](int j) { return j % C::kStagesK; };
+        auto k_phase = [](int j) { return static_cast<uint32_t>(j / C::kStagesK) & 1; };
+        auto v_stage = [](int j) { return j % C::kStagesV; };
+        auto v_phase = [](int j) { return static_cast<uint32_t>(j / C::kStagesV) & 1; };
 
-        // prologue: S(t,0) for both tiles
+        // prologue: S of each half's first block (block 0 for both when paired; blocks 0 and 1 when interleaved)
         wait(&q_full[0], 0, W_MMA_QFULL, 0);
         wait(&k_full[0], 0, W_MMA_KFULL, 0);
         if (ok) {
           tc_fence_after();
           issue_qk(0, 0);
           tc_commit(&s_full[0]);
+          if (il) tc_commit(&k_empty[0]);
         }
-        if (tile1_valid) {
-          wait(&q_full[1], 0, W_MMA_QFULL, 1);
+        if (half1_active) {
+          const int j1 = il ? 1 : 0;
+          if (!il) wait(&q_full[1], 0, W_MMA_QFULL, 1);
+          if (il) wait(&k_full[k_stage(1)], k_phase(1), W_MMA_KFULL, 1);
           if (ok) {
             tc_fence_after();
-            issue_qk(1, 0);
+            issue_qk(1, k_stage(j1));
             tc_commit(&s_full[1]);
+            if (il) tc_commit(&k_empty[k_stage(1)]);
           }
         }
-        if (ok) tc_commit(&k_empty[0]);
+        if (ok && !il) tc_commit(&k_empty[0]);
 
-        const int last_t = tile1_valid ? 1 : 0;
-        for (int j = 0; j < nblk && ok; ++j) {
-          const int st = j % C::kStagesV;                                       // V stage of block j
-          const uint32_t ph = static_cast<uint32_t>(j / C::kStagesV) & 1;
-          const int stn = (j + 1) % C::kStagesK;                                // K stage of block j + 1
-          const uint32_t phn = static_cast<uint32_t>((j + 1) / C::kStagesK) & 1;
+#ifdef HDIT_ATTN_TRACE
+        if (trace_on) {
+          unsigned long long ns;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+          g_attn_trace_mma[0][63][0] = clock64();
+          g_attn_trace_mma[0][63][1] = static_cast<long long>(ns);
+        }
+#endif
+        for (int i = 0; i < n_iter && ok; ++i) {
           for (int t = 0; t <= last_t && ok; ++t) {
-            if (t == 0) wait(&v_full[st], ph, W_MMA_VFULL, j);
-            HDIT_TRACE_MMA(t, j, 0);
-            wait(&p_ready[t], j & 1, W_MMA_PREADY, j * 2 + t);
-            HDIT_TRACE_MMA(t, j, 1);
+            // half t's i-th KV block and the one after it
+            const int j = il ? 2 * i + t : i;
+            if (j >= nblk) break;  // interleaved, odd block count: half 1 has one block fewer
+            const int jn = j + blk_step;
+            const bool has_next = jn < nblk;
+            const bool releases = il || t == last_t;  // the last reader of a stage hands it back
+            if (il || t == 0) {
+              wait(&v_full[v_stage(j)], v_phase(j), W_MMA_VFULL, j);
+#if !HDIT_ATTN_LATE_KWAIT
+              if (has_next) wait(&k_full[k_stage(jn)], k_phase(jn), W_MMA_KFULL, jn);
+#endif
+            }
+            HDIT_TRACE_MMA(t, i, 0);
+            wait(&p_ready[t], i & 1, W_MMA_PREADY, i * 2 + t);
+            HDIT_TRACE_MMA(t, i, 1);
             if (!ok) break;
             tc_fence_after();
-            issue_pv(t, st, j > 0);
-            if (t == last_t) tc_commit(&v_empty[st]);
-            if (j + 1 < nblk) {
-              if (t == 0) wait(&k_full[stn], phn, W_MMA_KFULL, j + 1);
+            issue_pv(t, v_stage(j), i > 0);
+            if (releases) tc_commit(&v_empty[v_stage(j)]);  // at once: the V ring is only two deep at head_dim 128
+            if (has_next) {
+#if HDIT_ATTN_LATE_KWAIT
+              if (il || t == 0) wait(&k_full[k_stage(jn)], k_phase(jn), W_MMA_KFULL, jn);
               if (!ok) break;
-              tc_fence_after();
-              issue_qk(t, stn);
+#endif
+              issue_qk(t, k_stage(jn));
               tc_commit(&s_full[t]);
-              if (t == last_t) tc_commit(&k_empty[stn]);
+              if (releases) tc_commit(&k_empty[k_stage(jn)]);
             } else {
               tc_commit(&o_done[t]);
             }
-            HDIT_TRACE_MMA(t, j, 2);
+            HDIT_TRACE_MMA(t, i, 2);
           }
         }
+#ifdef HDIT_ATTN_TRACE
+        if (trace_on) {
+          unsigned long long ns;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+          g_attn_trace_mma[0][63][2] = clock64();
+          g_attn_trace_mma[0][63][3] = static_cast<long long>(ns);
+        }
+#endif
       }
     }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ========================= softmax / epilogue =========================
-    const int t = warp >> 2;           // which Q tile this warpgroup owns
+    const int t = warp >> 2;           // which half (Q tile, or KV parity when interleaved) this warpgroup owns
     const int quarter = warp & 3;      // TMEM lane quarter this warp may touch
     const int row = quarter * 32 + lane;
-    const bool active = (t == 0) || tile1_valid;
+    const bool active = (t == 0) || half1_active;
     if (active) {
       const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
       const uint32_t tm_s = tmem_base + lane_base + C::kColS + t * 128;
       const uint32_t tm_o = tmem_base + lane_base + C::kColO + t * D;
       const float scale_log2 = p.scale_log2;
-      float m_run = -INFINITY;
+      float m_run = -INFINITY;   // maximum the stored P and O are scaled against (log2 units)
+      float m_pend = -INFINITY;  // largest score seen so far; m_run catches up with it lazily
       float l_run = 0.f;
       bool ok = true;
+      const int first = il ? t : 0;
+      const int n_mine = il ? (nblk - t + 1) / 2 : nblk;
       KvCursor cur{0, 0};
-      for (int i = 0; i < j_begin; ++i) cur.advance(p);
+      for (int i = 0; i < j_begin + first; ++i) cur.advance(p);
 
-      for (int j = 0; j < nblk; ++j) {
+      for (int j = 0; j < n_mine; ++j) {  // j counts this half's blocks
         HDIT_TRACE_SM(0);
         // warp-uniform outcome: the tcgen05.ld/st below need the whole warp converged
         if (!__all_sync(0xffffffffu, mbar_wait_bounded(&s_full[t], j & 1, abort_flag, kSpinLimit))) {
@@ -433,14 +536,35 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         }
         tc_fence_after();
         HDIT_TRACE_SM(1);
+        const int valid = min(kBlockN, p.kv_len[cur.seg] - cur.row0);
+        for (int i = 0; i < blk_step; ++i) cur.advance(p);
+#if defined(HDIT_ATTN_PROBE) && (HDIT_ATTN_PROBE == 1 || HDIT_ATTN_PROBE == 3)
+        // timing probe (wrong results): no softmax work at all, only the barrier hand-shake
+        m_run = 0.f;
+        l_run = 1.f;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[t]);
+        continue;
+#endif
         uint32_t s[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(tm_s + c * 32, s[c]);
         tc_wait_ld();
         HDIT_TRACE_SM(2);
 
-        const int valid = min(kBlockN, p.kv_len[cur.seg] - cur.row0);
-        cur.advance(p);
+#if defined(HDIT_ATTN_PROBE) && HDIT_ATTN_PROBE == 2
+        // timing probe (wrong results): S is read and P written, but nothing is computed
+        m_run = 0.f;
+        l_run = 1.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_st16(tm_s + c * 16, s[c]);
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[t]);
+        continue;
+#endif
         if (valid < kBlockN) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
@@ -449,20 +573,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
               if (c * 32 + i >= valid) s[c][i] = 0xff800000u;  // -inf
         }
 
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            mx0 = max3(mx0, __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
-            mx1 = max3(mx1, __uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3]));
-            mx2 = max3(mx2, __uint_as_float(s[c][i + 4]), __uint_as_float(s[c][i + 5]));
-            mx3 = max3(mx3, __uint_as_float(s[c][i + 6]), __uint_as_float(s[c][i + 7]));
-          }
-        const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
-        const float m_new = fmaxf(m_run, m_blk);
-        const bool grow = (m_new - m_run) > kRescaleThreshold;  // true on the first block (m_run = -inf)
-        if (__any_sync(0xffffffffu, grow)) {
+        // Rescale the running state to a larger maximum (rare: only when it grows by more than 2^8).
+        auto rescale_to = [&](bool grow, float m_new) {
           const float alpha = grow ? ex2_approx(m_run - m_new) : 1.0f;
           if (grow) m_run = m_new;
           l_run *= alpha;
@@ -478,37 +590,89 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
               tmem_st32(tm_o + c * 32, o);
             }
           }
-        }
-
-        HDIT_TRACE_SM(3);
-        // p = 2^(s * scale - m): packed fp32x2 FMA and add halve the issue slots of the row loop
-        const float2 scale2 = make_float2(scale_log2, scale_log2);
-        const float2 neg_m2 = make_float2(-m_run, -m_run);
-        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+        };
+        // P = 2^(s * scale - m_run) for the whole row, stored over S as packed 16-bit pairs; returns the row sum.
+        // With track_max the row maximum of the raw scores is computed in the same pass. Packed fp32x2 FMA and
+        // add halve the issue slots; of every 8 scores the last HDIT_ATTN_POLY8 take the polynomial exp2.
+        auto exp_pass = [&](auto track_max, float& raw_max) -> float {
+          const float2 scale2 = make_float2(scale_log2, scale_log2);
+          const float2 neg_m2 = make_float2(-m_run, -m_run);
+          float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+          float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
+          for (int c = 0; c < 4; ++c) {
+            uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), scale2,
-                                         neg_m2);
-            const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3])),
-                                         scale2, neg_m2);
-            const float2 p0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
-            const float2 p1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
-            acc0 = __fadd2_rn(acc0, p0);
-            acc1 = __fadd2_rn(acc1, p1);
-            pk[i >> 1] = pack2<FP16>(p0.x, p0.y);
-            pk[(i >> 1) + 1] = pack2<FP16>(p1.x, p1.y);
+            for (int i = 0; i < 32; i += 4) {
+              const float2 r0 = make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+              const float2 r1 = make_float2(__uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3]));
+              if constexpr (decltype(track_max)::value) {
+                mx0 = max3(mx0, r0.x, r0.y);
+                mx1 = max3(mx1, r1.x, r1.y);
+              }
+              const float2 x0 = __ffma2_rn(r0, scale2, neg_m2);
+              const float2 x1 = __ffma2_rn(r1, scale2, neg_m2);
+              // position of this group of four within its group of eight decides the pipe
+              constexpr int kPolyPairs = HDIT_ATTN_POLY8 / 2;
+              const bool second_half = (i & 4) != 0;
+              const bool poly0 = second_half ? (kPolyPairs >= 2) : (kPolyPairs >= 4);
+              const bool poly1 = second_half ? (kPolyPairs >= 1) : (kPolyPairs >= 3);
+              const float2 p0 = poly0 ? ex2_poly2(x0) : make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
+              const float2 p1 = poly1 ? ex2_poly2(x1) : make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
+              acc0 = __fadd2_rn(acc0, p0);
+              acc1 = __fadd2_rn(acc1, p1);
+              pk[i >> 1] = pack2<FP16>(p0.x, p0.y);
+              pk[(i >> 1) + 1] = pack2<FP16>(p1.x, p1.y);
+            }
+            tmem_st16(tm_s + c * 16, pk);
           }
-          tmem_st16(tm_s + c * 16, pk);
+          raw_max = fmaxf(mx0, mx1);
+          return (acc0.x + acc0.y) + (acc1.x + acc1.y);
+        };
+
+        bool classic = (j == 0) || (HDIT_ATTN_STALE_MAX == 0);
+        if (!classic) {
+          // The maximum used for this block is the one known before it; what the previous block added to it
+          // takes effect now.
+          const bool grow = (m_pend - m_run) > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, grow)) rescale_to(grow, m_pend);
+          HDIT_TRACE_SM(3);
+          float raw_max;
+          const float sum = exp_pass(std::true_type{}, raw_max);
+          const float m_blk = raw_max * scale_log2;
+          if (__any_sync(0xffffffffu, (m_blk - m_run) > kOverflowGuard)) {
+            classic = true;  // a score far above everything seen so far: redo the block against its own maximum
+          } else {
+            l_run += sum;
+            m_pend = fmaxf(m_run, m_blk);
+          }
         }
-        const float sum0 = acc0.x + acc0.y, sum1 = acc1.x + acc1.y;
-        l_run += sum0 + sum1;
+        if (classic) {
+          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              mx0 = max3(mx0, __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+              mx1 = max3(mx1, __uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3]));
+              mx2 = max3(mx2, __uint_as_float(s[c][i + 4]), __uint_as_float(s[c][i + 5]));
+              mx3 = max3(mx3, __uint_as_float(s[c][i + 6]), __uint_as_float(s[c][i + 7]));
+            }
+          const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+          const float m_new = fmaxf(m_run, m_blk);
+          const bool grow = (m_new - m_run) > kRescaleThreshold;  // true on the first block (m_run = -inf)
+          if (__any_sync(0xffffffffu, grow)) rescale_to(grow, m_new);
+          if (j == 0) HDIT_TRACE_SM(3);
+          float unused;
+          l_run += exp_pass(std::false_type{}, unused);
+          m_pend = fmaxf(m_run, m_blk);
+        }
         HDIT_TRACE_SM(4);
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(&p_ready[t]);
+        // one arrival per warp: 128 arrivals on one barrier word would serialise on the S -> P -> MMA path
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[t]);
         HDIT_TRACE_SM(5);
       }
 
@@ -517,10 +681,51 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_SM_ODONE, t);
         ok = false;
       }
-      if (ok) {
+      // Interleaved mode: half 1 hands its unnormalised partial result (O1, m1, l1) to half 0 through the
+      // K / V rings, which no MMA reads any more once both halves are done.
+      float* const xo = reinterpret_cast<float*>(smem_k);   // [D][128] fp32, column-major: conflict-free
+      float* const xml = reinterpret_cast<float*>(smem_v);  // [2][128]: m, l
+      float scale0 = 1.0f, scale1 = 0.0f;
+      bool writes_result = true;
+      if (il && t == 1) {
+        writes_result = false;
+        if (ok && !__all_sync(0xffffffffu, mbar_wait_bounded(&o_done[0], 0, abort_flag, kSpinLimit))) {
+          report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_SM_ODONE, 2);
+          ok = false;
+        }
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tm_o + c * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) xo[(c * 32 + i) * 128 + row] = __uint_as_float(o[i]);
+          }
+          xml[row] = m_run;
+          xml[128 + row] = l_run;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(merge_bar);
+        }
+      } else if (il && half1_active) {
+        if (ok && !__all_sync(0xffffffffu, mbar_wait_bounded(merge_bar, 0, abort_flag, kSpinLimit))) {
+          report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_SM_ODONE, 3);
+          ok = false;
+        }
+        if (ok) {
+          const float m1 = xml[row], l1 = xml[128 + row];
+          const float m = fmaxf(m_run, m1);
+          scale0 = ex2_approx(m_run - m);
+          scale1 = ex2_approx(m1 - m);
+          l_run = scale0 * l_run + scale1 * l1;
+          m_run = m;
+        }
+      }
+      if (ok && writes_result) {
         tc_fence_after();
         int seg, row0, orow0;
-        tile_coords(p, tile0 + t, seg, row0, orow0);
+        tile_coords(p, tile0 + (il ? 0 : t), seg, row0, orow0);
         const bool row_valid = (row0 + row) < p.q_len[seg];
         const long long qpos = orow0 + row;
         const float blk_lse2 = m_run + log2f(l_run);  // log2 domain
@@ -546,6 +751,23 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
           else if (p.lse != nullptr)
             p.lse[lse_idx] = lse_out;
         }
+        // where the 16-bit result row goes: `out`, or (reverse all-to-all) the buffer of the rank that owns the row
+        int d_lo = 0, d_hi = 1;
+        long long drow = qpos;
+        if (p.n_dst > 0) {
+          const long long r = row0 + row;  // row within its Q segment
+          const long long rpd = p.seg_rows_per_dst[seg];
+          if (rpd > 0) {
+            d_lo = static_cast<int>(r / rpd);
+            d_hi = d_lo + 1;
+            drow = p.seg_dst_row0[seg] + (r - d_lo * rpd);
+          } else {
+            d_lo = 0;
+            d_hi = p.n_dst;
+            drow = p.seg_dst_row0[seg] + r;
+          }
+        }
+        const float w0 = w_blk * scale0, w1 = w_blk * scale1;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
@@ -554,7 +776,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
           if (row_valid) {
             float f[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(o[i]) * w_blk;
+            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(o[i]) * w0;
+            if (il && half1_active) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) f[i] = fmaf(xo[(c * 32 + i) * 128 + row], w1, f[i]);
+            }
             if (merge) {
               const float4* prev = reinterpret_cast<const float4*>(acc_out + acc_row + c * 32);
 #pragma unroll
@@ -571,17 +797,21 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
 #pragma unroll
               for (int i = 0; i < 8; ++i) dst[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
             } else {
-              uint16_t* base = reinterpret_cast<uint16_t*>(p.out) + static_cast<long long>(b) * p.out_sb +
-                               qpos * p.out_ss + static_cast<long long>(h) * p.out_sh + c * 32;
-              uint4* dst = reinterpret_cast<uint4*>(base);
+              uint4 v[4];
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
-                uint4 v;
-                v.x = pack2<FP16>(f[8 * i + 0], f[8 * i + 1]);
-                v.y = pack2<FP16>(f[8 * i + 2], f[8 * i + 3]);
-                v.z = pack2<FP16>(f[8 * i + 4], f[8 * i + 5]);
-                v.w = pack2<FP16>(f[8 * i + 6], f[8 * i + 7]);
-                dst[i] = v;
+                v[i].x = pack2<FP16>(f[8 * i + 0], f[8 * i + 1]);
+                v[i].y = pack2<FP16>(f[8 * i + 2], f[8 * i + 3]);
+                v[i].z = pack2<FP16>(f[8 * i + 4], f[8 * i + 5]);
+                v[i].w = pack2<FP16>(f[8 * i + 6], f[8 * i + 7]);
+              }
+              const long long off = static_cast<long long>(b) * p.out_sb + drow * p.out_ss +
+                                    static_cast<long long>(h) * p.out_sh + c * 32;
+              for (int d = d_lo; d < d_hi; ++d) {
+                uint16_t* base = reinterpret_cast<uint16_t*>(p.n_dst > 0 ? p.dst[d] : p.out) + off;
+                uint4* dst = reinterpret_cast<uint4*>(base);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dst[i] = v[i];
               }
             }
           }
@@ -680,9 +910,9 @@ int encode_seg(CUtensorMap* map, unsigned char* swapped, const hdit_seg& seg, in
   return HDIT_OK;
 }
 
-template <int D, bool FP16>
+template <int D, bool FP16, bool IL>
 int launch(const AttnKernelParams& kp, int grid, int grid_y, cudaStream_t stream) {
-  auto kernel = attn_fwd_kernel<D, FP16>;
+  auto kernel = attn_fwd_kernel<D, FP16, IL>;
   // The attribute is per device: set it whenever this thread meets a new device.
   static thread_local int last_dev = -1;
   int dev = 0;
@@ -696,6 +926,15 @@ int launch(const AttnKernelParams& kp, int grid, int grid_y, cudaStream_t stream
   return HDIT_OK;
 }
 
+// Result scatter of the split-KV merge pass (same meaning as in AttnKernelParams).
+struct ScatterParams {
+  int n_dst;
+  long long q_len0;  // length of Q segment 0 (rows below it belong to segment 0)
+  void* dst[8];
+  long long seg_rows_per_dst[HDIT_MAX_Q_SEG];
+  long long seg_dst_row0[HDIT_MAX_Q_SEG];
+};
+
 // Merges the partial results of a split-KV launch: out = sum_s w_s O_s with w_s = exp(lse_s - lse),
 // lse = log sum_s exp(lse_s). One warp per (batch, query, head) row, one vector load per lane and split.
 // NS > 0 fixes the split count at compile time: all partial rows and LSEs of a row are then requested
@@ -705,7 +944,8 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restri
                                                           const float* __restrict__ part_lse, int n_split,
                                                           long long acc_stride, long long lse_stride, int batch,
                                                           long long sq, int heads, void* out, long long out_sb,
-                                                          long long out_ss, long long out_sh, float* lse) {
+                                                          long long out_ss, long long out_sh, float* lse,
+                                                          const __grid_constant__ ScatterParams sc) {
   constexpr int E = D / 32;  // floats per lane: 4 (D = 128) or 2 (D = 64)
   constexpr int kMaxNs = NS > 0 ? NS : 1;
   const int lane = threadIdx.x & 31;
@@ -758,15 +998,32 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restri
       }
     }
     const float inv = 1.0f / wsum;
-    uint16_t* dst = reinterpret_cast<uint16_t*>(out) + b * out_sb + q * out_ss + static_cast<long long>(h) * out_sh +
-                    lane * E;
-    if constexpr (E == 4) {
-      uint2 v;
-      v.x = pack2<FP16>(acc[0] * inv, acc[1] * inv);
-      v.y = pack2<FP16>(acc[2] * inv, acc[3] * inv);
-      *reinterpret_cast<uint2*>(dst) = v;
-    } else {
-      *reinterpret_cast<uint32_t*>(dst) = pack2<FP16>(acc[0] * inv, acc[1] * inv);
+    int d_lo = 0, d_hi = 1;
+    long long drow = q;
+    if (sc.n_dst > 0) {
+      const int seg = (q >= sc.q_len0) ? 1 : 0;
+      const long long r = seg ? q - sc.q_len0 : q;
+      const long long rpd = sc.seg_rows_per_dst[seg];
+      if (rpd > 0) {
+        d_lo = static_cast<int>(r / rpd);
+        d_hi = d_lo + 1;
+        drow = sc.seg_dst_row0[seg] + (r - d_lo * rpd);
+      } else {
+        d_hi = sc.n_dst;
+        drow = sc.seg_dst_row0[seg] + r;
+      }
+    }
+    for (int d = d_lo; d < d_hi; ++d) {
+      uint16_t* dst = reinterpret_cast<uint16_t*>(sc.n_dst > 0 ? sc.dst[d] : out) + b * out_sb + drow * out_ss +
+                      static_cast<long long>(h) * out_sh + lane * E;
+      if constexpr (E == 4) {
+        uint2 v;
+        v.x = pack2<FP16>(acc[0] * inv, acc[1] * inv);
+        v.y = pack2<FP16>(acc[2] * inv, acc[3] * inv);
+        *reinterpret_cast<uint2*>(dst) = v;
+      } else {
+        *reinterpret_cast<uint32_t*>(dst) = pack2<FP16>(acc[0] * inv, acc[1] * inv);
+      }
     }
     if (lse != nullptr && lane == 0) lse[lse_idx] = mx + logf(wsum);
   }
@@ -814,10 +1071,18 @@ int attn_fwd_impl(const hdit_attn_args* a, int n_split, float* split_out, float*
   const bool needs_out = a->mode == HDIT_ATTN_FINAL || a->mode == HDIT_ATTN_MERGE_FINAL;
   if (needs_acc && (a->acc_out == nullptr || a->acc_lse == nullptr))
     return set_error(HDIT_ERR_BAD_ARG, "acc_out / acc_lse required for partial and merge modes");
+  if (a->n_out_dst < 0 || a->n_out_dst > 8) return set_error(HDIT_ERR_BAD_ARG, "n_out_dst must be 0..8");
+  if (a->kv_interleave < 0 || a->kv_interleave > 2) return set_error(HDIT_ERR_BAD_ARG, "kv_interleave must be 0, 1 or 2");
   if (needs_out) {
-    if (a->out == nullptr) return set_error(HDIT_ERR_BAD_ARG, "out is null");
-    if ((reinterpret_cast<uintptr_t>(a->out) & 15) != 0 || a->out_stride_s % 8 != 0 || a->out_stride_h % 8 != 0 ||
-        a->out_stride_b % 8 != 0)
+    if (a->n_out_dst == 0) {
+      if (a->out == nullptr) return set_error(HDIT_ERR_BAD_ARG, "out is null");
+      if ((reinterpret_cast<uintptr_t>(a->out) & 15) != 0)
+        return set_error(HDIT_ERR_SHAPE, "out must be 16-byte aligned with strides multiple of 8 elements");
+    }
+    for (int i = 0; i < a->n_out_dst; ++i)
+      if (a->out_dst[i] == nullptr || (reinterpret_cast<uintptr_t>(a->out_dst[i]) & 15) != 0)
+        return set_error(HDIT_ERR_BAD_ARG, "out_dst[%d] is null or not 16-byte aligned", i);
+    if (a->out_stride_s % 8 != 0 || a->out_stride_h % 8 != 0 || a->out_stride_b % 8 != 0)
       return set_error(HDIT_ERR_SHAPE, "out must be 16-byte aligned with strides multiple of 8 elements");
   }
   if (needs_acc && (reinterpret_cast<uintptr_t>(a->acc_out) & 15) != 0)
@@ -877,6 +1142,43 @@ int attn_fwd_impl(const hdit_attn_args* a, int n_split, float* split_out, float*
   kp.acc_lse = a->acc_lse;
   kp.status = device_status_ptr();
   if (kp.status == nullptr) return HDIT_ERR_CUDA;
+  ScatterParams sc;
+  memset(&sc, 0, sizeof(sc));
+  if (needs_out && a->n_out_dst > 0) {
+    // the segment index of a row is its position in the caller's list; empty segments were dropped above, so
+    // map the caller's per-segment values onto the kernel's compacted list
+    int kq = 0;
+    for (int i = 0; i < a->n_q_seg; ++i) {
+      if (a->q[i].len == 0) continue;
+      if (a->q_rows_per_dst[i] < 0 || a->q_dst_row0[i] < 0)
+        return set_error(HDIT_ERR_BAD_ARG, "negative q_rows_per_dst / q_dst_row0");
+      if (a->q_rows_per_dst[i] > 0 && (a->q[i].len + a->q_rows_per_dst[i] - 1) / a->q_rows_per_dst[i] > a->n_out_dst)
+        return set_error(HDIT_ERR_SHAPE, "q segment %d: %lld rows at %lld per destination exceed %d destinations", i,
+                         static_cast<long long>(a->q[i].len), static_cast<long long>(a->q_rows_per_dst[i]),
+                         a->n_out_dst);
+      kp.seg_rows_per_dst[kq] = sc.seg_rows_per_dst[kq] = a->q_rows_per_dst[i];
+      kp.seg_dst_row0[kq] = sc.seg_dst_row0[kq] = a->q_dst_row0[i];
+      ++kq;
+    }
+    kp.n_dst = sc.n_dst = a->n_out_dst;
+    sc.q_len0 = kp.q_len[0];
+    for (int i = 0; i < a->n_out_dst; ++i) kp.dst[i] = sc.dst[i] = a->out_dst[i];
+  }
+
+  // Interleaved mode (one Q tile per CTA, its two halves on the even and odd KV blocks): taken when it cuts
+  // the number of CTA waves, i.e. for grids smaller than the GPU. Costs are in KV blocks of one CTA.
+  if (n_split <= 1 && a->kv_interleave != 1 && nblk >= 2) {
+    const long long ctas_pair = static_cast<long long>(kp.n_pairs) * a->heads * a->batch;
+    const long long ctas_il = static_cast<long long>(kp.n_tiles) * a->heads * a->batch;
+    // measured at 3 heads x 4608 tokens, head_dim 128: an interleaved iteration (two KV blocks, each ring
+    // effectively half as deep) costs 1.56 paired blocks; about 6 blocks' worth of fixed cost per CTA
+    const double t_pair = static_cast<double>((ctas_pair + kSmCount - 1) / kSmCount) * (nblk + 6.0);
+    const double t_il = static_cast<double>((ctas_il + kSmCount - 1) / kSmCount) * ((nblk + 1) / 2 * 1.56 + 6.0);
+    if (a->kv_interleave == 2 || t_il * 1.05 < t_pair) {
+      kp.interleave = 1;
+      kp.n_pairs = kp.n_tiles;
+    }
+  }
 
   const long long grid = static_cast<long long>(kp.n_pairs) * a->heads * a->batch;
   if (grid > 0x7fffffffLL) return set_error(HDIT_ERR_TOO_LARGE, "grid too large");
@@ -895,12 +1197,18 @@ int attn_fwd_impl(const hdit_attn_args* a, int n_split, float* split_out, float*
     kp.split_lse_stride = static_cast<long long>(a->batch) * a->heads * sq;
   }
   int rc;
-  if (a->head_dim == 128)
-    rc = fp16 ? launch<128, true>(kp, static_cast<int>(grid), grid_y, stream)
-              : launch<128, false>(kp, static_cast<int>(grid), grid_y, stream);
-  else
-    rc = fp16 ? launch<64, true>(kp, static_cast<int>(grid), grid_y, stream)
-              : launch<64, false>(kp, static_cast<int>(grid), grid_y, stream);
+  const int g = static_cast<int>(grid);
+  if (kp.interleave) {
+    if (a->head_dim == 128)
+      rc = fp16 ? launch<128, true, true>(kp, g, grid_y, stream) : launch<128, false, true>(kp, g, grid_y, stream);
+    else
+      rc = fp16 ? launch<64, true, true>(kp, g, grid_y, stream) : launch<64, false, true>(kp, g, grid_y, stream);
+  } else {
+    if (a->head_dim == 128)
+      rc = fp16 ? launch<128, true, false>(kp, g, grid_y, stream) : launch<128, false, false>(kp, g, grid_y, stream);
+    else
+      rc = fp16 ? launch<64, true, false>(kp, g, grid_y, stream) : launch<64, false, false>(kp, g, grid_y, stream);
+  }
   if (rc != HDIT_OK || grid_y == 1) return rc;
   const long long n_rows = static_cast<long long>(a->batch) * sq * a->heads;
   long long blocks = (n_rows + 7) / 8;
@@ -908,7 +1216,7 @@ int attn_fwd_impl(const hdit_attn_args* a, int n_split, float* split_out, float*
 #define HDIT_COMBINE_NS(DD, FF, NN)                                                                                \
   attn_combine_kernel<DD, FF, NN><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                               \
       split_out, split_lse, grid_y, kp.split_acc_stride, kp.split_lse_stride, a->batch, sq, a->heads, a->out,      \
-      a->out_stride_b, a->out_stride_s, a->out_stride_h, a->lse)
+      a->out_stride_b, a->out_stride_s, a->out_stride_h, a->lse, sc)
 #define HDIT_COMBINE(DD, FF)                                                                                       \
   do {                                                                                                             \
     if (grid_y == 2) HDIT_COMBINE_NS(DD, FF, 2);                                                                   \

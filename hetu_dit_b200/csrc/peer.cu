@@ -73,17 +73,28 @@ __global__ void peer_barrier_kernel(const __grid_constant__ BarrierParams p) {
   }
 }
 
-__global__ void peer_signal_kernel(int32_t* flag, int32_t value) {
+// With `counter` (a device int32 of the calling rank) the sequence number is taken from it and advanced by the
+// kernel itself, so a captured CUDA graph containing the call stays replayable; `value` is then ignored.
+__global__ void peer_signal_kernel(int32_t* flag, int32_t value, int32_t* counter) {
   if (threadIdx.x == 0) {
+    if (counter != nullptr) {
+      value = *counter + 1;
+      *counter = value;
+    }
     __threadfence_system();
     st_release_sys(flag, value);
   }
 }
 
-__global__ void peer_wait_kernel(const int32_t* flag, int32_t value, unsigned max_spins, int32_t* status, int tag) {
+__global__ void peer_wait_kernel(const int32_t* flag, int32_t value, unsigned max_spins, int32_t* status, int tag,
+                                 int32_t* counter) {
   __shared__ int abort_flag;
   if (threadIdx.x == 0) {
     abort_flag = 0;
+    if (counter != nullptr) {
+      value = *counter + 1;
+      *counter = value;
+    }
     bool seen = false;
     for (unsigned i = 0; i < max_spins; ++i) {
       if (ld_acquire_sys(flag) - value >= 0) {
@@ -175,21 +186,22 @@ extern "C" int hdit_peer_barrier(int32_t* const* peer_slots, const int32_t* cons
   return HDIT_OK;
 }
 
-extern "C" int hdit_peer_signal(int32_t* flag, int32_t value, void* stream) {
+extern "C" int hdit_peer_signal(int32_t* flag, int32_t value, int32_t* seq_counter, void* stream) {
   using namespace hdit;
   if (flag == nullptr) return set_error(HDIT_ERR_BAD_ARG, "null flag");
-  peer_signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flag, value);
+  peer_signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flag, value, seq_counter);
   HDIT_CUDA_OK(cudaGetLastError());
   return HDIT_OK;
 }
 
-extern "C" int hdit_peer_wait(const int32_t* flag, int32_t value, int64_t max_spins, int32_t tag, void* stream) {
+extern "C" int hdit_peer_wait(const int32_t* flag, int32_t value, int32_t* seq_counter, int64_t max_spins, int32_t tag,
+                              void* stream) {
   using namespace hdit;
   if (flag == nullptr) return set_error(HDIT_ERR_BAD_ARG, "null flag");
   int32_t* status = device_status_ptr();
   if (status == nullptr) return HDIT_ERR_CUDA;
   const unsigned spins = static_cast<unsigned>(max_spins > 0 ? (max_spins > 0xffffffffLL ? 0xffffffffLL : max_spins) : 1);
-  peer_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flag, value, spins, status, tag);
+  peer_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flag, value, spins, status, tag, seq_counter);
   HDIT_CUDA_OK(cudaGetLastError());
   return HDIT_OK;
 }

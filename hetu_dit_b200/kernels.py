@@ -32,8 +32,9 @@ def enable_attn_timing(on: bool):
 def attn_timing_summary():
     """Mean device time of the attention launches recorded since reset_counters() (synchronises)."""
     torch.cuda.synchronize()
-    ms = [a.elapsed_time(b) for a, b in _attn_events]
-    return {"count": len(ms), "mean_ms": (sum(ms) / len(ms)) if ms else None, "min_ms": min(ms) if ms else None}
+    ms = [a.elapsed_time(b) for a, b, _ in _attn_events]
+    return {"count": len(ms), "mean_ms": (sum(ms) / len(ms)) if ms else None, "min_ms": min(ms) if ms else None,
+            "total_ms": sum(ms), "flops": float(sum(f for _, _, f in _attn_events))}
 
 
 def _count(n=1):
@@ -69,6 +70,10 @@ def attn_fwd(
     acc_out=None,
     acc_lse=None,
     kv_split=None,
+    kv_interleave=0,
+    out_dsts=None,
+    q_rows_per_dst=None,
+    q_dst_row0=None,
 ):
     """softmax(Q K^T * scale) V over segment lists, (B, S, H, D) layout.
 
@@ -81,6 +86,14 @@ def attn_fwd(
     kv_split (FINAL mode only): number of CTAs that share one query tile pair, each over its own
     range of KV blocks, merged by a second small kernel. None picks it from the grid size: a head-
     and sequence-sharded call can have fewer tile pairs than the GPU has SMs.
+    kv_interleave: 0 lets the library decide, 1 forbids, 2 forces the mode in which a CTA owns one query tile
+    and its two halves take the even and odd KV blocks (merged in shared memory; for small grids).
+
+    out_dsts (a RawDst: device addresses + (b, s, h) element strides): scatter the result rows over these
+    buffers instead of returning one tensor -- row r of query segment s goes to destination
+    r // q_rows_per_dst[s] at row q_dst_row0[s] + r % q_rows_per_dst[s], or to every destination at row
+    q_dst_row0[s] + r when q_rows_per_dst[s] is 0. With the Ulysses peers' output buffers as destinations this
+    is the reverse all-to-all done by the attention epilogue. Returns None (or the lse) in that case.
     """
     q0 = q_segs[0]
     if not q0.is_cuda:
@@ -106,7 +119,19 @@ def attn_fwd(
         _fill_seg(a.v[i], v)
     writes_out = mode in (_C.ATTN_FINAL, _C.ATTN_MERGE_FINAL)
     lse = None
-    if writes_out:
+    a.kv_interleave = int(kv_interleave)
+    if writes_out and out_dsts is not None:
+        a.n_out_dst = len(out_dsts)
+        for i, ptr in enumerate(out_dsts.ptrs):
+            a.out_dst[i] = ptr
+        a.out_stride_b, a.out_stride_s, a.out_stride_h = out_dsts.strides
+        for i in range(len(q_segs)):
+            a.q_rows_per_dst[i] = int(q_rows_per_dst[i])
+            a.q_dst_row0[i] = int(q_dst_row0[i])
+        if return_lse:
+            lse = torch.empty((B, H, sq), dtype=torch.float32, device=q0.device)
+            a.lse = lse.data_ptr()
+    elif writes_out:
         if out is None:
             out = torch.empty((B, sq, H, D), dtype=q0.dtype, device=q0.device)
         a.out = out.data_ptr()
@@ -128,7 +153,7 @@ def attn_fwd(
     a.stream = _stream_ptr(q0.device)
     n_split = 1
     if mode == _C.ATTN_FINAL:
-        n_split = _pick_kv_split(q_segs, k_segs, B, H) if kv_split is None else int(kv_split)
+        n_split = _pick_kv_split(q_segs, k_segs, B, H, kv_interleave) if kv_split is None else int(kv_split)
     with torch.cuda.device(q0.device):
         if n_split > 1:
             part_out = torch.empty((n_split, B, sq, H, D), dtype=torch.float32, device=q0.device)
@@ -142,19 +167,29 @@ def attn_fwd(
             e0.record()
             _C.check(call())
             e1.record()
-            _attn_events.append((e0, e1))
+            skv = sum(int(t.shape[1]) for t in k_segs)
+            _attn_events.append((e0, e1, 4.0 * B * sq * skv * H * D))
         else:
             _C.check(call())
     _count(2 if n_split > 1 else 1)
     if not writes_out:
         return None
+    if out_dsts is not None:
+        return lse
     return (out, lse) if return_lse else out
 
 
 _SM_COUNT = 148
 
 
-def _pick_kv_split(q_segs, k_segs, batch, heads):
+def _interleave_cost(q_tiles, kv_blocks, batch, heads):
+    """Cost (in KV blocks of one paired CTA) of running one query tile per CTA with the KV blocks interleaved
+    over its two halves; the constants are the library's own (csrc/attn_sm100.cu)."""
+    ctas_il = q_tiles * heads * batch
+    return -(-ctas_il // _SM_COUNT) * ((kv_blocks + 1) // 2 * 1.56 + 6.0)
+
+
+def _pick_kv_split(q_segs, k_segs, batch, heads, kv_interleave=0):
     """How many ways to split the KV range. One CTA per SM runs a pair of 128-row query tiles over all KV
     blocks, so the launch takes ceil(ctas / SMs) waves; splitting the KV range s ways makes waves of 1/s the
     length and pays a fixed cost per CTA plus the merge pass. Costs are in units of one KV block of one CTA
@@ -165,6 +200,8 @@ def _pick_kv_split(q_segs, k_segs, batch, heads):
     kv_blocks = sum((int(t.shape[1]) + 127) // 128 for t in k_segs)
     if ctas <= 0:
         return 1
+    if kv_interleave == 2:
+        return 1
     sq = sum(int(t.shape[1]) for t in q_segs)
     part_bytes = batch * sq * heads * int(q_segs[0].shape[3]) * 4
 
@@ -174,6 +211,9 @@ def _pick_kv_split(q_segs, k_segs, batch, heads):
         return c if s == 1 else c + 5.0 + part_bytes * s / 1e7
 
     best, best_cost = 1, cost(1) * 0.9
+    if kv_interleave == 0 and kv_blocks >= 2:
+        # without a split the library itself may interleave; a split has to beat that too
+        best_cost = min(best_cost, _interleave_cost(q_tiles, kv_blocks, batch, heads) * 0.95)
     for s in (2, 3, 4):
         if kv_blocks // s >= 4 and cost(s) < best_cost:
             best, best_cost = s, cost(s)

@@ -66,6 +66,8 @@ class BaseBlockCache:
         # be able to pull them); default: ordinary device memory.
         self.allocator = allocator or (lambda shape, dtype: torch.empty(shape, dtype=dtype, device=self.device))
         self.deallocator = deallocator  # deallocator(tensor): gives evicted parameters back to the arena
+        self.defer_release = False      # see _release()
+        self._pending_release: List[torch.Tensor] = []
         self.cache: "OrderedDict[int, Tuple[nn.Module, Tuple[float, float]]]" = OrderedDict()
         self.active_block_indices: List[int] = []
         self._last_p2p_preplans: Dict[int, DataReconstructionPlan] = {}
@@ -294,9 +296,24 @@ class BaseBlockCache:
 
     # ---- LRU ---------------------------------------------------------------------------------------------
     def _release(self, block: Optional[nn.Module]):
+        """Hands a block's parameter memory back. While `defer_release` is set the memory only goes on a list:
+        during a plan switch peers may still pull from a block this rank has already replaced or evicted (they
+        read the directory exchanged before the switch), so the region must not be handed out again until
+        every rank's pulls have completed -- the worker calls flush_released() after that point."""
         if block is not None and self.deallocator is not None:
             for prm in block.parameters():
-                self.deallocator(prm.data)
+                if self.defer_release:
+                    self._pending_release.append(prm.data)
+                else:
+                    self.deallocator(prm.data)
+
+    def flush_released(self) -> int:
+        """Deallocates everything released while `defer_release` was set; returns how many tensors."""
+        n = len(self._pending_release)
+        for t in self._pending_release:
+            self.deallocator(t)
+        self._pending_release = []
+        return n
 
     def _add_or_update(self, idx: int, block: nn.Module, tp_range: Tuple[float, float]):
         old = self.cache.get(idx)

@@ -41,19 +41,27 @@ class FluxShapedPipeline(SD3ShapedPipeline):
         nd = len(doubles)
         return doubles[min(lo, nd):min(hi, nd)], singles[max(lo - nd, 0):max(hi - nd, 0)]
 
-    def _first_token(self):
-        """Global index of the first image token this call holds (selects its rotary rows)."""
+    def _rope_and_first_token(self, s_txt, device):
+        """Rotary tables and the table row (past the text rows) of the first image token this call holds. A
+        patch, or a whole image on one sequence-parallel rank without patches, is one range of rows of the full
+        table. A whole-image step under sequence parallelism with several pipeline patches holds one slice of
+        every patch: its rows are gathered into a local table (text rows first), addressed from row 0."""
         rt = get_runtime_state()
+        rope = self.model._rope(s_txt, self.grid, device)
         bounds = rt.pp_patches_token_start_end_idx_global
         if rt.patch_mode:
-            return bounds[rt.pipeline_patch_idx][0]
+            return rope, bounds[rt.pipeline_patch_idx][0]
         if ps.get_sequence_parallel_world_size() == 1:
-            return 0
-        if len(bounds) != 1:
-            raise NotImplementedError(
-                "a whole-image step under sequence parallelism with several pipeline patches holds one slice of "
-                "every patch: its tokens are not one range of rotary rows")
-        return bounds[0][0]
+            return rope, 0
+        if len(bounds) == 1:
+            return rope, bounds[0][0]
+        key = (s_txt, tuple(tuple(b) for b in bounds), tuple(self.grid), str(device))
+        cache = self.__dict__.setdefault("_rope_local", {})
+        if key not in cache:
+            rows = torch.cat([torch.arange(s_txt, device=device)] +
+                             [torch.arange(s, e, device=device) + s_txt for s, e in bounds])
+            cache[key] = (rope[0].index_select(0, rows), rope[1].index_select(0, rows))
+        return cache[key], 0
 
     def _transformer(self, hidden_states, encoder_hidden_states, pooled, timestep):
         m = self.model
@@ -65,8 +73,7 @@ class FluxShapedPipeline(SD3ShapedPipeline):
             hidden_states = m.x_embedder(hidden_states)
             encoder_hidden_states = m.context_embedder(encoder_hidden_states)
         s_txt = encoder_hidden_states.shape[1]
-        tok0 = self._first_token()
-        rope = m._rope(s_txt, self.grid, hidden_states.device)
+        rope, tok0 = self._rope_and_first_token(s_txt, hidden_states.device)
         doubles, singles = self._stage_blocks()
         for block in doubles:
             hidden_states, encoder_hidden_states = block(hidden_states, encoder_hidden_states, temb, rope, tok0)

@@ -255,6 +255,10 @@ class SD3ShapedPipeline:
         """latents (1, S, 64); prompt_embeds (2, S_txt, text_dim) = [negative, positive]; pooled (2, pooled_dim).
         Returns the denoised latents on the last pipeline stage (None elsewhere)."""
         rt = get_runtime_state()
+        if rt.ready:
+            # the token grid follows the request's resolution (latent pixels / patch size)
+            cell = rt.vae_scale_factor * rt.backbone_patch_size
+            self.grid = (rt.input_config.height // cell, rt.input_config.width // cell)
         self.sigmas = flow_match_sigmas(num_inference_steps, device=latents.device)
         self.encoder_hidden_states_cache = {}
         warmup = min(rt.runtime_config.warmup_steps, num_inference_steps)

@@ -1,8 +1,11 @@
 """Per-GPU worker: the plan API the executor drives by method name.
 
-Mirrors the reference's hetu_dit/worker/worker.py: init_static_env (:183-332),
-init_instance_model (:415), switch_parallel_env (:480-598), hotspa_model (:1571-1993),
-execute_diffusion_stage (:1009-1183), get_worker_state (:1527-1563), rpc_find_sources (:2079).
+Mirrors the reference's hetu_dit/worker/worker.py with its method names and signatures, because the executor
+calls them by name with positional / keyword arguments (executor/gpu_executor.py:176-220):
+init_static_env (:183-332), init_instance_model (:415), switch_parallel_env(world_size, ranks, engine_config)
+(:480-598), async hotspa_model(engine_config) (:1571-1993), execute_diffusion_stage(encode_stage_results,
+engine_config, input_config, model_class, task_id) (:1009-1183), execute_encode_diffusion_stage (:1185-1394),
+get_worker_state (:1527-1563), rpc_find_sources (:2079). run_worker_method() is the by-name call.
 
 A plan names the global ranks it runs on and its degrees. Switching plans re-binds the groups
 (arithmetic only -- there is no communicator pool to look up), drops the stale-KV buffers and the
@@ -20,8 +23,9 @@ from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
 
-from ..config import EngineConfig
+from ..config import EngineConfig, InputConfig
 from ..core.distributed import parallel_state as ps
+from ..core.distributed.utils import RankGenerator
 from ..core.distributed.peer import ParamArena, PeerHeap
 from ..core.distributed.runtime_state import (ModelGeometry, get_runtime_state, initialize_runtime_state,
                                               reset_runtime_state, runtime_state_is_initialized)
@@ -49,7 +53,8 @@ class Worker:
         self.cache: Optional[TransformerBlockCache] = None
         self.cur_metadata = None
         self.plan_ranks: List[int] = [rank]
-        self.worker_state: Dict[str, object] = {"task": None, "stage": "idle"}
+        self.states: Dict[str, object] = {}       # per-request timing / status record (worker.py `self.states`)
+        self.encode = self._synthetic_encode      # stand-in for the text encoders, see execute_encode_diffusion_stage
 
     # ------------------------------------------------------------------ start-up
     def init_static_env(self):
@@ -80,24 +85,40 @@ class Worker:
         self.pipeline.stage_sliced = True
 
     # ------------------------------------------------------------------ plan switch
-    def switch_parallel_env(self, engine_config: EngineConfig, ranks: Sequence[int]):
-        """Bind the groups of the new plan and drop everything sized for the old one."""
+    def switch_parallel_env(self, world_size: int, ranks: Sequence[int] = (), engine_config: EngineConfig = None) -> None:
+        """Bind the groups of the new plan and drop everything sized for the old one. Same signature and the
+        same sequence of set_activate_* calls as the reference (worker/worker.py:480-598); `world_size` is
+        the number of ranks of the plan, as the executor passes it."""
+        ranks = list(ranks)
         pc = engine_config.parallel_config
-        sp = pc.sp_config
-        degrees = dict(tp=pc.tp_config.tp_degree, ulysses=sp.ulysses_degree, ring=sp.ring_degree,
-                       pp=pc.pp_config.pp_degree, cfg=pc.dp_config.cfg_degree, dp=pc.dp_config.dp_degree)
-        prod = 1
-        for v in degrees.values():
-            prod *= v
-        if prod != len(ranks):
-            raise ValueError(f"plan degrees {degrees} need {prod} ranks, got {len(ranks)}")
+        if len(ranks) != pc.tp_degree * pc.sp_degree * pc.pp_degree * pc.cfg_degree * pc.dp_degree:
+            raise AssertionError("Product of parallel degrees must equal length of ranks")
+        groups = ps.get_parallel_groups()
+        groups.set_activate_world_group(len(ranks), ranks, [ranks])
+        rank_map = {i: r for i, r in enumerate(sorted(ranks))}
+        gen = RankGenerator(tp=pc.tp_degree, sp=pc.sp_degree, pp=pc.pp_degree, cfg=pc.cfg_degree, dp=pc.dp_degree,
+                            order="tp-sp-pp-cfg-dp")
+
+        def mapped(axis):
+            return [[rank_map[r] for r in g] for g in gen.get_ranks(axis)]
+
+        groups.set_activate_tp_group(degree=len(ranks), ranks=ranks, group_ranks=mapped("tp"))
+        groups.set_activate_sp_group(degree=len(ranks), ranks=ranks, group_ranks=mapped("sp"),
+                                     ulysses_degree=pc.ulysses_degree, ring_degree=pc.ring_degree)
+        groups.set_activate_pp_group(degree=len(ranks), ranks=ranks, group_ranks=mapped("pp"))
+        groups.set_activate_cfg_group(degree=len(ranks), ranks=ranks, group_ranks=mapped("cfg"))
+        groups.set_activate_dp_group(degree=len(ranks), ranks=ranks, group_ranks=mapped("dp"))
         self.engine_config = engine_config
         self.plan_ranks = sorted(ranks)
-        ps.get_parallel_groups().activate_plan(self.plan_ranks, **degrees)
+        # activation buffers of the old plan: the heap is re-used from its start by the new group
         self.heap.reset()
         reset_runtime_state()
         reset_cache_manager()
         initialize_runtime_state(self.geometry, engine_config, is_serving=True, cur_metadata=self.cur_metadata)
+        # Built right away, as the first heap allocation after the reset: a sender addresses the receiver's
+        # inbox by its own inbox offset, so every stage must carve it from the same place.
+        if pc.pp_degree > 1:
+            ps.get_pp_group()
 
     def rpc_find_sources(self, pieces) -> List[int]:
         """uids of the pieces this worker's cache can serve; none while it is re-slicing itself."""
@@ -105,15 +126,20 @@ class Worker:
             return []
         return self.cache.find_sources(pieces)
 
-    def hotspa_model(self):
-        """Migrate parameters to the ranges of the active plan (collective over ALL workers, because any of
-        them may be asked to serve pieces). Returns the byte counts by source for the caller's log."""
+    async def hotspa_model(self, engine_config: EngineConfig = None):
+        """Migrate parameters to the ranges of the active plan (worker/worker.py:1571; collective over ALL
+        workers, because any of them may be asked to serve pieces). A coroutine, as in the reference, where the
+        executor awaits it on every worker; the work itself is synchronous GPU / host work. Returns the byte
+        counts by source for the caller's log."""
+        return self._migrate(engine_config or self.engine_config)
+
+    def _migrate(self, engine_config: EngineConfig):
         rt = get_runtime_state()
         rt.set_p2p_state("adjusting")
         old = self.cur_metadata or {"tensor_parallel": (0.0, 1.0), "pipeline_parallel": (0.0, 0.0)}
         new = get_gpu_metadata(ps.get_pipeline_parallel_rank(), ps.get_pipeline_parallel_world_size(),
                                ps.get_tensor_model_parallel_rank(), ps.get_tensor_model_parallel_world_size())
-        strategy = self.engine_config.runtime_config.adjust_strategy
+        strategy = engine_config.runtime_config.adjust_strategy
         peer_dirs = None
         if strategy == "p2p" and self.world_size > 1:
             mine = self.cache.directory(ptr_of=self.arena.offset_of)
@@ -132,13 +158,19 @@ class Worker:
             # full reload from the CPU master copy: forget what is cached first
             for idx in list(self.cache.cache):
                 self.cache._release(self.cache.cache.pop(idx)[0])
-        self.cache.adjust_pipeline(self.transformer, self.cpu_full_transformer, old["pipeline_parallel"],
-                                   new["pipeline_parallel"], old["tensor_parallel"], new["tensor_parallel"],
-                                   slice_bias=True, peer_directories=peer_dirs)
-        if self.world_size > 1:
-            # nobody may evict or overwrite a block a peer is still pulling from
-            torch.cuda.synchronize(self.device)
-            self.exchange(None)
+        # Peers pull from the addresses in the directories exchanged above while this rank re-slices and evicts:
+        # memory released during the switch is parked and only handed back once every rank's pulls are done.
+        self.cache.defer_release = self.world_size > 1
+        try:
+            self.cache.adjust_pipeline(self.transformer, self.cpu_full_transformer, old["pipeline_parallel"],
+                                       new["pipeline_parallel"], old["tensor_parallel"], new["tensor_parallel"],
+                                       slice_bias=True, peer_directories=peer_dirs)
+            if self.world_size > 1:
+                torch.cuda.synchronize(self.device)
+                self.exchange(None)
+        finally:
+            self.cache.defer_release = False
+            self.cache.flush_released()
         self.cur_metadata = new
         rt.cur_metadata = new
         if hasattr(self.transformer, "register_cache"):
@@ -149,20 +181,112 @@ class Worker:
                 "from_cpu": sum(1 for p in pieces if p.source_rank < 0)}
 
     # ------------------------------------------------------------------ execution
-    def execute_diffusion_stage(self, latents, prompt_embeds, pooled, num_inference_steps: int, height: int = 1024,
-                                width: int = 1024):
+    def _returns_latents(self, engine_config: EngineConfig) -> bool:
+        """Which worker hands the latents back (worker.py:1053-1066): the last pipeline stage under PipeFusion,
+        else the first of the request's diffusion ranks."""
+        if engine_config.parallel_config.pp_degree > 1:
+            return ps.is_pipeline_last_stage()
+        first = (engine_config.diffusion_stage_ranks or self.plan_ranks)[0]
+        return self.rank == first
+
+    def _run_diffusion(self, latents, prompt_embeds, pooled, engine_config, input_config, task_id):
         rt = get_runtime_state()
         rt.set_p2p_state("computing")
-        self.worker_state.update(task="diffusion", stage="diffusion", diffusion_start_time=time.time())
-        rt.set_input_parameters(height=height, width=width, batch_size=1, num_inference_steps=num_inference_steps)
-        out = self.pipeline.diffusion_stage(latents, prompt_embeds, pooled, num_inference_steps)
+        t1 = time.perf_counter()
+        self.states.update(running_task=task_id, task_start_time=t1, stage_name="diffusion", diffusion_start_time=t1)
+        rt.worker_state = self.states
+        rt.set_input_parameters(height=input_config.height, width=input_config.width,
+                                batch_size=input_config.batch_size or 1,
+                                num_inference_steps=input_config.num_inference_steps)
+        out = self.pipeline.diffusion_stage(latents, prompt_embeds, pooled, input_config.num_inference_steps)
         torch.cuda.synchronize(self.device)
         self.heap.check()
-        self.worker_state.update(task=None, stage="idle", diffusion=time.time() - self.worker_state["diffusion_start_time"],
-                                 diffusion_mem=torch.cuda.max_memory_allocated(self.device))
+        t2 = time.perf_counter()
+        self.states["diffusion"] = t2 - t1
+        self.states["diffusion_mem"] = torch.cuda.max_memory_allocated(self.device)
+        results = {"before": t1, "after": t2, "inner_results": self.states.copy()}
+        self.states = {}
         rt.set_p2p_state("free")
-        return out
+        return results, (out if self._returns_latents(engine_config) else None)
+
+    def _latents_for(self, input_config: InputConfig) -> torch.Tensor:
+        """Initial noise of a request: seeded, in the packed-token layout the -shaped pipelines take."""
+        g = self.geometry
+        h, w = input_config.height // g.vae_scale_factor // g.patch_size, input_config.width // g.vae_scale_factor // g.patch_size
+        gen = torch.Generator().manual_seed(int(input_config.seed))
+        lat = torch.randn(input_config.batch_size or 1, h * w, g.in_channels * g.patch_size ** 2, generator=gen)
+        return lat.to(self.device, self.engine_config.runtime_config.dtype)
+
+    def execute_diffusion_stage(self, encode_stage_results, engine_config: EngineConfig = None,
+                                input_config: InputConfig = None, model_class=None, task_id: str = None):
+        """The denoising loop of one request on this worker (worker/worker.py:1009-1183): embeddings come from the
+        encode stage as {"prompt_embeds", "pooled_prompt_embeds"[, "latents"]}. Returns (timing record, latents
+        or None) -- the latents only on the worker that owns the result, as in the reference."""
+        engine_config = engine_config or self.engine_config
+        input_config = input_config or engine_config.input_config
+        latents = encode_stage_results.get("latents")
+        if latents is None:
+            latents = self._latents_for(input_config)
+        dev = self.device
+        return self._run_diffusion(latents.to(dev), encode_stage_results["prompt_embeds"].to(dev),
+                                   encode_stage_results["pooled_prompt_embeds"].to(dev), engine_config, input_config,
+                                   task_id)
+
+    def execute_encode_diffusion_stage(self, engine_config: EngineConfig = None, input_config: InputConfig = None,
+                                       model_class=None, task_id: str = None):
+        """Encode + denoise on the same worker (worker/worker.py:1185-1394). Text encoders are outside this
+        package: `self.encode(input_config)` supplies the embeddings (by default seeded synthetic ones of the
+        model's text width, a pure function of the prompt and the requested length)."""
+        engine_config = engine_config or self.engine_config
+        input_config = input_config or engine_config.input_config
+        enc = self.encode(input_config)
+        results, latents = self.execute_diffusion_stage(enc, engine_config, input_config, model_class, task_id)
+        results["store"] = time.perf_counter()
+        return results, latents
+
+    def _synthetic_encode(self, input_config: InputConfig):
+        import zlib
+        shape = getattr(self.cpu_full_transformer, "shape", None)
+        text_dim = shape.text_dim if shape is not None else 4096
+        pooled_dim = max(shape.pooled_dim, 1) if shape is not None else 2048
+        gen = torch.Generator().manual_seed(zlib.crc32(str(input_config.prompt).encode()) & 0x7fffffff)
+        dtype = self.engine_config.runtime_config.dtype
+        B = input_config.batch_size or 1
+        return {"prompt_embeds": torch.randn(B, input_config.max_sequence_length, text_dim, generator=gen).to(dtype),
+                "pooled_prompt_embeds": torch.randn(B, pooled_dim, generator=gen).to(dtype)}
 
     def get_worker_state(self):
-        return dict(self.worker_state, rank=self.rank, plan=list(self.plan_ranks), cached_blocks=sorted(self.cache.cache),
-                    arena_bytes=self.arena.bytes_in_use() if self.arena else 0)
+        """The status record the engine polls (worker/worker.py:1527-1563), plus what this implementation knows
+        about its plan and its parameter cache."""
+        now = time.perf_counter()
+        st = self.states
+        result = {"rank": self.rank, "running_task": st.get("running_task"), "last_detected_time": now,
+                  "task_start_time": st.get("task_start_time"),
+                  "memory": torch.cuda.memory_allocated(self.device) if torch.cuda.is_available() else 0,
+                  "running_stage": st.get("stage_name"), "estimated_running_time": st.get("estimated_running_time")}
+        if result["running_stage"] is not None:
+            run = now - st.get(f"{result['running_stage']}_start_time", 0)
+            result["stage_running_time"] = run if run else None
+        else:
+            result["stage_running_time"] = None
+        result["task_running_time"] = (now - result["task_start_time"]) if result["task_start_time"] else None
+        if result["estimated_running_time"] is not None and result["task_running_time"] is not None:
+            left = result["estimated_running_time"] - result["task_running_time"]
+            result["estimated_idle_time"] = left if left > 0 else 2
+        else:
+            result["estimated_idle_time"] = 0
+        result.update(plan=list(self.plan_ranks), cached_blocks=sorted(self.cache.cache) if self.cache else [],
+                      arena_bytes=self.arena.bytes_in_use() if self.arena else 0)
+        return result
+
+
+def run_worker_method(worker: Worker, method: str, *args, **kwargs):
+    """Calls a worker method by name the way the reference's executor does
+    (RayGPUExecutorAsync._run_workers_async, executor/gpu_executor.py:176-220): positional and keyword
+    arguments are passed through unchanged, coroutine methods are awaited."""
+    import asyncio
+    import inspect
+    out = getattr(worker, method)(*args, **kwargs)
+    if inspect.iscoroutine(out):
+        out = asyncio.run(out)
+    return out

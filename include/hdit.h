@@ -124,6 +124,20 @@ typedef struct hdit_attn_args {
   float* acc_out;
   float* acc_lse;
   void* stream;
+  /* Optional scatter of the 16-bit result rows over n_out_dst buffers that share out_stride_* (`out` is then
+   * unused): row r of Q segment s goes to destination r / q_rows_per_dst[s], at row q_dst_row0[s] +
+   * r % q_rows_per_dst[s]; q_rows_per_dst[s] == 0 sends the segment's rows to every destination, at row
+   * q_dst_row0[s] + r. With the Ulysses peers' output buffers as destinations (mapped peer memory, plain
+   * stores) this is the sequence<-head all-to-all that follows attention, SeqAllToAll4D.apply(ulysses_pg,
+   * context, scatter_idx=1, gather_idx=2) at hetu_dit/core/parallel/hybrid/attn_layer.py:134-136, 269-271,
+   * 390-392, done by the attention epilogue instead of a separate pass over the context. n_out_dst = 0: off. */
+  int32_t n_out_dst;
+  /* 0: the library decides, 1: never, 2: always -- run one Q tile per CTA with its two halves on the even and
+   * odd KV blocks, merged in shared memory (for grids with fewer Q tile pairs than SMs). */
+  int32_t kv_interleave;
+  void* out_dst[8];
+  int64_t q_rows_per_dst[HDIT_MAX_Q_SEG];
+  int64_t q_dst_row0[HDIT_MAX_Q_SEG];
 } hdit_attn_args;
 
 HDIT_API int hdit_attn_fwd(const hdit_attn_args* args);
@@ -266,10 +280,13 @@ HDIT_API int hdit_peer_barrier(int32_t* const* peer_slots, const int32_t* const*
  * (bounded as above; where = 101, iteration = tag). Together with hdit_copy_pieces into the
  * peer's receive slot they replace PipelineGroupCoordinator.pipeline_isend / pipeline_recv /
  * get_pipeline_recv_data (hetu_dit/core/distributed/group_coordinator.py:931-1002) without the
- * shape handshake of :848-929 (shapes follow from the patch bookkeeping).
+ * shape handshake of :848-929 (shapes follow from the patch bookkeeping). With `seq_counter` (a device int32 of
+ * the calling rank: one per link and direction) the kernel takes the sequence number from that counter and
+ * advances it itself, which keeps a captured CUDA graph containing the call replayable; `value` is then ignored.
  */
-HDIT_API int hdit_peer_signal(int32_t* flag, int32_t value, void* stream);
-HDIT_API int hdit_peer_wait(const int32_t* flag, int32_t value, int64_t max_spins, int32_t tag, void* stream);
+HDIT_API int hdit_peer_signal(int32_t* flag, int32_t value, int32_t* seq_counter, void* stream);
+HDIT_API int hdit_peer_wait(const int32_t* flag, int32_t value, int32_t* seq_counter, int64_t max_spins, int32_t tag,
+                            void* stream);
 
 /*
  * hdit_attn_fwd (mode HDIT_ATTN_FINAL) with the KV range split over n_split CTAs per query tile

@@ -221,3 +221,60 @@ def test_argument_errors():
         kernels.attn_fwd([q], [empty], [empty])
     with pytest.raises(TypeError):
         kernels.attn_fwd([q.float()], [q.float()], [q.float()])
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("sq,lens", [(1, (1,)), (128, (128, 128)), (129, (643,)), (300, (1500, 20)), (77, (200,)),
+                                     (260, (5, 128, 129, 1, 64))])
+def test_interleaved_kv_mode_matches_oracle(D, sq, lens):
+    """One query tile per CTA, even / odd KV blocks on its two halves, merged in shared memory: odd and even
+    block counts, a single block (half 1 idle), ragged tails, several segments."""
+    gen = torch.Generator().manual_seed(sq + sum(lens) + D)
+    q = _mk((2, sq, 3, D), torch.bfloat16, gen)
+    ks = [_mk((2, n, 3, D), torch.bfloat16, gen) for n in lens]
+    vs = [_mk((2, n, 3, D), torch.bfloat16, gen) for n in lens]
+    out, lse = _run([q], ks, vs, kv_split=1, kv_interleave=2)
+    _check(out, lse, [q], ks, vs)
+
+
+def test_interleaved_kv_mode_partial_and_merge():
+    """The interleaved mode under the ring's PARTIAL_FIRST -> MERGE_FINAL sequence equals one shot."""
+    from hetu_dit_b200 import _C, kernels
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(31)
+    q = _mk((1, 300, 2, 128), torch.bfloat16, gen).to(dev)
+    k1, v1, k2, v2 = (_mk((1, n, 2, 128), torch.bfloat16, gen).to(dev) for n in (700, 700, 400, 400))
+    acc = torch.empty(1, 300, 2, 128, device=dev)
+    acc_lse = torch.empty(1, 2, 300, device=dev)
+    kernels.attn_fwd([q], [k1], [v1], mode=_C.ATTN_PARTIAL_FIRST, acc_out=acc, acc_lse=acc_lse, kv_interleave=2)
+    out, lse = kernels.attn_fwd([q], [k2], [v2], mode=_C.ATTN_MERGE_FINAL, acc_out=acc, acc_lse=acc_lse,
+                                return_lse=True, kv_interleave=2)
+    torch.cuda.synchronize()
+    assert _C.device_status(0, clear=True)[0] == 0
+    _check(out, lse, [q.cpu()], [k1.cpu(), k2.cpu()], [v1.cpu(), v2.cpu()])
+
+
+@pytest.mark.parametrize("kv_split,kv_interleave", [(1, 1), (1, 2), (2, 1)])
+def test_result_scatter_from_the_epilogue(kv_split, kv_interleave):
+    """The attention epilogue (or the split-KV merge pass) stores each result row into the buffer of the rank
+    that owns it: joint rows to every destination, image rows of owner u to destination u -- bit-identical to
+    the plain call followed by the copy, for the paired, the interleaved and the split-KV launch."""
+    from hetu_dit_b200 import _C, kernels
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(41)
+    B, H, D, U, S, J = 2, 2, 128, 4, 96, 100
+    jq, iq = _mk((B, J, H, D), torch.bfloat16, gen).to(dev), _mk((B, U * S, H, D), torch.bfloat16, gen).to(dev)
+    k, v = _mk((B, 900, H, D), torch.bfloat16, gen).to(dev), _mk((B, 900, H, D), torch.bfloat16, gen).to(dev)
+    plain = kernels.attn_fwd([jq, iq], [k], [v], kv_split=kv_split, kv_interleave=kv_interleave)
+    # destinations are wider than the slice written (2 * H heads), as the peers' gathered output buffers are
+    bufs = [torch.zeros(B, J + S, 2 * H, D, device=dev, dtype=torch.bfloat16) for _ in range(U)]
+    dst = kernels.RawDst([x[:, :, H:].data_ptr() for x in bufs], bufs[0].stride()[:3])
+    kernels.attn_fwd([jq, iq], [k], [v], kv_split=kv_split, kv_interleave=kv_interleave, out_dsts=dst,
+                     q_rows_per_dst=[0, S], q_dst_row0=[0, J])
+    torch.cuda.synchronize()
+    assert _C.device_status(0, clear=True)[0] == 0
+    for u in range(U):
+        assert torch.equal(bufs[u][:, :J, H:], plain[:, :J])
+        assert torch.equal(bufs[u][:, J:, H:], plain[:, J + u * S:J + (u + 1) * S])
+        assert bufs[u][:, :, :H].abs().max().item() == 0
+    _check(plain, None, [jq.cpu(), iq.cpu()], [k.cpu()], [v.cpu()])

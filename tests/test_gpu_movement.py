@@ -105,6 +105,37 @@ def test_norm_rope_matches_oracle(D, dtype):
         assert (diff == 0).float().mean().item() > 0.99
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_layer_norm_rope_matches_torch(D):
+    """LayerNorm over the head dimension (the QK norm of the CogVideoX shape) + rotary embedding on the rows
+    past the text prefix, against torch's layer_norm on the same 16-bit inputs."""
+    from hetu_dit_b200 import kernels
+    gen = torch.Generator().manual_seed(3 * D)
+    B, S, H, S_txt = 2, 61, 3, 9
+    dtype = torch.bfloat16
+    q = torch.randn(B, S, H, D, generator=gen).to(dtype)
+    k = torch.randn(B, S, H, D, generator=gen).to(dtype)
+    w = (1 + 0.1 * torch.randn(D, generator=gen)).to(dtype)
+    bias = (0.1 * torch.randn(D, generator=gen)).to(dtype)
+    ang = torch.rand(S - S_txt, D // 2, generator=gen) * 6.28
+    cos = torch.cos(ang).repeat_interleave(2, -1).contiguous()
+    sin = torch.sin(ang).repeat_interleave(2, -1).contiguous()
+
+    def want(x):
+        y = torch.nn.functional.layer_norm(x.float(), (D,), w.float(), bias.float(), 1e-6).to(dtype)
+        rot = oa.apply_rotary_emb(y[:, S_txt:].transpose(1, 2), cos, sin).transpose(1, 2)
+        return torch.cat([y[:, :S_txt], rot.to(dtype)], 1)
+
+    qd, kd = q.to(DEV), k.to(DEV)
+    kernels.qk_norm_rope([(qd, w.to(DEV), 2, True, bias.to(DEV)), (kd, w.to(DEV), 2, True, bias.to(DEV))], eps=1e-6,
+                         cos=cos.to(DEV), sin=sin.to(DEV), rope_seq_start=S_txt)
+    torch.cuda.synchronize()
+    for got, ref in ((qd, want(q)), (kd, want(k))):
+        diff = (got.cpu().float() - ref.float()).abs()
+        assert diff.max().item() <= 2 * 2 ** -8 * ref.float().abs().max().item()
+        assert (diff == 0).float().mean().item() > 0.97
+
+
 def test_rope_golden(golden_dir):
     """apply_rotary_emb outputs recorded from the reference function."""
     from hetu_dit_b200 import kernels

@@ -102,6 +102,26 @@ def test_flux_single_stage_patches_with_stale_kv():
     reset_cache_manager()
 
 
+def call(worker, method, *args, **kwargs):
+    """By-name call with the reference's positional / keyword arguments, as its executor makes it."""
+    from hetu_dit_b200.worker.worker import run_worker_method
+    return run_worker_method(worker, method, *args, **kwargs)
+
+
+def diffuse(worker, cfg, lat, prompt, pooled, steps, both=False):
+    """execute_diffusion_stage(encode_stage_results, engine_config, input_config, model_class, task_id): returns
+    the latents on the worker that owns the result. Under sequence parallelism without PipeFusion the reference
+    returns them on the first diffusion rank only; `both` asks every rank in turn so that each can check."""
+    from hetu_dit_b200.config import InputConfig
+    enc = {"prompt_embeds": prompt, "pooled_prompt_embeds": pooled, "latents": lat}
+    inp = InputConfig(height=512, width=256, num_inference_steps=steps)
+    if both:
+        cfg.diffusion_stage_ranks = [worker.rank]
+    results, latents = call(worker, "execute_diffusion_stage", enc, cfg, inp, None, task_id="t0")
+    assert results["after"] >= results["before"] and results["inner_results"]["running_task"] == "t0"
+    return latents
+
+
 def _flux_worker_case(rank, world, port, errq):
     """Two PipeFusion stages of the Flux-shaped model through the worker plan API: stage 0 holds the double
     blocks, stage 1 the single blocks, which re-use the text stream that arrives with patch 0."""
@@ -133,10 +153,10 @@ def _flux_worker_case(rank, world, port, errq):
         cfg.parallel_config.pp_config.pp_degree = 2
         cfg.parallel_config.pp_config.num_pipeline_patch = 4
         cfg.runtime_config.warmup_steps = 1
-        w.switch_parallel_env(cfg, [0, 1])
-        w.hotspa_model()
+        call(w, "switch_parallel_env", 2, [0, 1], cfg)
+        call(w, "hotspa_model", cfg)
         assert sorted(w.cache.cache) == ([0, 1] if rank == 0 else [2, 3, 4])
-        out = w.execute_diffusion_stage(lat.to(dev), prompt.to(dev), pooled.to(dev), 4, height=512, width=256)
+        out = diffuse(w, cfg, lat, prompt, pooled, 4)
         if rank == 1:
             want = opf.denoise_flux(sd, shape, lat, prompt, pooled, 4, 3.5, [128] * 4, 1, (32, 16), stage_starts=(0, 2))
             cos, rel = oa.cosine_and_max_rel(out.cpu(), want)
@@ -196,10 +216,10 @@ def _worker_case(rank, world, port, errq):
         cfg.parallel_config.pp_config.pp_degree = 2
         cfg.parallel_config.pp_config.num_pipeline_patch = 4
         cfg.runtime_config.warmup_steps = 1
-        w.switch_parallel_env(cfg, [0, 1])
-        stats = w.hotspa_model()
+        call(w, "switch_parallel_env", 2, [0, 1], cfg)
+        stats = call(w, "hotspa_model", cfg)
         assert stats["from_peers"] == 0 and sorted(w.cache.cache) == ([0, 1] if rank == 0 else [2, 3])
-        out = w.execute_diffusion_stage(lat.to(dev), prompt.to(dev), pooled.to(dev), 4, height=512, width=256)
+        out = diffuse(w, cfg, lat, prompt, pooled, 4)
         want = opf.denoise(sd, shape, lat, prompt, pooled, 4, 4.0, [128] * 4, 1, (32, 16))
         if rank == 1:
             cos, rel = oa.cosine_and_max_rel(out.cpu(), want)
@@ -211,18 +231,19 @@ def _worker_case(rank, world, port, errq):
         cfg1 = EngineConfig()
         cfg1.parallel_config.pp_config.num_pipeline_patch = 4
         cfg1.runtime_config.warmup_steps = 1
-        w.switch_parallel_env(cfg1, [rank])
-        stats = w.hotspa_model()
+        call(w, "switch_parallel_env", 1, [rank], engine_config=cfg1)
+        stats = call(w, "hotspa_model", engine_config=cfg1)
         assert stats["from_peers"] > 0 and stats["from_cpu"] == 0, stats
         assert sorted(w.cache.cache) == [0, 1, 2, 3]
         for i, blk in enumerate(w.transformer.transformer_blocks):
             ref = model.transformer_blocks[i].state_dict()
             for k, v in blk.state_dict().items():
                 assert torch.equal(v.cpu(), ref[k]), (i, k)
-        out = w.execute_diffusion_stage(lat.to(dev), prompt.to(dev), pooled.to(dev), 4, height=512, width=256)
+        out = diffuse(w, cfg1, lat, prompt, pooled, 4)
         cos, rel = oa.cosine_and_max_rel(out.cpu(), want)
         assert cos >= 0.999 and rel <= 5e-2, ("solo", cos, rel)
-        assert w.get_worker_state()["stage"] == "idle"
+        state = call(w, "get_worker_state")
+        assert state["running_task"] is None and state["running_stage"] is None and state["rank"] == rank
 
         # plan C: Ulysses degree 2 over both GPUs, 4 patches of which every rank holds one half; nothing to
         # migrate (both ranks hold all blocks). The whole latents come back on both ranks (end-of-denoise
@@ -231,11 +252,11 @@ def _worker_case(rank, world, port, errq):
         cfg2.parallel_config.sp_config.ulysses_degree = 2
         cfg2.parallel_config.pp_config.num_pipeline_patch = 4
         cfg2.runtime_config.warmup_steps = 1
-        w.switch_parallel_env(cfg2, [0, 1])
-        stats = w.hotspa_model()
+        call(w, "switch_parallel_env", 2, [0, 1], cfg2)
+        stats = call(w, "hotspa_model", cfg2)
         assert stats["from_peers"] == 0 and stats["from_cpu"] == 0, stats
         from hetu_dit_b200.core.distributed.runtime_state import get_runtime_state
-        out = w.execute_diffusion_stage(lat.to(dev), prompt.to(dev), pooled.to(dev), 4, height=512, width=256)
+        out = diffuse(w, cfg2, lat, prompt, pooled, 4, both=True)
         assert get_runtime_state().pp_patches_token_num == [64] * 4
         want_sp = opf.denoise(sd, shape, lat, prompt, pooled, 4, 4.0, [128] * 4, 1, (32, 16), ulysses=2)
         cos, rel = oa.cosine_and_max_rel(out.cpu(), want_sp)
@@ -243,9 +264,9 @@ def _worker_case(rank, world, port, errq):
         # and without patches the sequence-parallel result is the plain one
         cfg3 = EngineConfig()
         cfg3.parallel_config.sp_config.ulysses_degree = 2
-        w.switch_parallel_env(cfg3, [0, 1])
-        w.hotspa_model()
-        out = w.execute_diffusion_stage(lat.to(dev), prompt.to(dev), pooled.to(dev), 2, height=512, width=256)
+        call(w, "switch_parallel_env", 2, [0, 1], cfg3)
+        call(w, "hotspa_model", cfg3)
+        out = diffuse(w, cfg3, lat, prompt, pooled, 2, both=True)
         want_full = opf.denoise(sd, shape, lat, prompt, pooled, 2, 4.0, [512], 0, (32, 16))
         cos, rel = oa.cosine_and_max_rel(out.cpu(), want_full)
         assert cos >= 0.999 and rel <= 5e-2, ("ulysses2 unpatched", cos, rel)
@@ -264,6 +285,81 @@ def test_worker_plan_switch_and_migration_two_gpus():
     errq = ctx.SimpleQueue()
     try:
         mp.spawn(_worker_case, args=(2, 29811, errq), nprocs=2, join=True)
+    except Exception:
+        msgs = []
+        while not errq.empty():
+            msgs.append(errq.get())
+        pytest.fail("\n".join(msgs) or "worker failed")
+
+
+def _pp_sp_case(rank, world, port, errq):
+    """PipeFusion (2 stages, 4 patches, 1 warm-up step) combined with Ulysses degree 2 on four GPUs through the
+    worker plan API -- the combination the serving trace uses -- then a switch to Ulysses 4 without PipeFusion."""
+    import traceback
+    try:
+        import os
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from hetu_dit_b200.config import EngineConfig
+        from hetu_dit_b200.core.distributed import parallel_state as ps
+        from hetu_dit_b200.core.distributed.runtime_state import ModelGeometry
+        from hetu_dit_b200.model_executor.pipelines.pipeline_sd3_shaped import SD3ShapedPipeline
+        from hetu_dit_b200.worker.worker import Worker
+        from oracle import attention as oa
+        from oracle import pipefusion as opf
+
+        def exchange(obj):
+            out = [None] * world
+            dist.all_gather_object(out, obj)
+            return out
+
+        shape, model, lat, prompt, pooled = _tiny()
+        sd = {k: v.float() for k, v in model.state_dict().items()}
+        w = Worker(rank, world, exchange=exchange, heap_bytes=128 << 20, arena_bytes=64 << 20)
+        w.init_static_env()
+        w.init_instance_model(model, ModelGeometry(4, 64), lambda t: SD3ShapedPipeline(t, guidance_scale=4.0))
+        cfg = EngineConfig()
+        cfg.parallel_config.pp_config.pp_degree = 2
+        cfg.parallel_config.pp_config.num_pipeline_patch = 4
+        cfg.parallel_config.sp_config.ulysses_degree = 2
+        cfg.runtime_config.warmup_steps = 1
+        call(w, "switch_parallel_env", 4, [0, 1, 2, 3], cfg)
+        call(w, "hotspa_model", cfg)
+        # rank order is tp-sp-pp: ranks 0, 1 are stage 0 (the two Ulysses ranks), ranks 2, 3 stage 1
+        assert ps.get_pipeline_parallel_rank() == rank // 2 and ps.get_ulysses_parallel_rank() == rank % 2
+        assert sorted(w.cache.cache) == ([0, 1] if rank < 2 else [2, 3])
+        out = diffuse(w, cfg, lat, prompt, pooled, 4)
+        want = opf.denoise(sd, shape, lat, prompt, pooled, 4, 4.0, [128] * 4, 1, (32, 16), ulysses=2)
+        if rank >= 2:
+            cos, rel = oa.cosine_and_max_rel(out.cpu(), want)
+            assert cos >= 0.999 and rel <= 5e-2, ("pp2 x ulysses2", cos, rel)
+        else:
+            assert out is None
+        cfg2 = EngineConfig()
+        cfg2.parallel_config.sp_config.ulysses_degree = 4
+        call(w, "switch_parallel_env", 4, [0, 1, 2, 3], cfg2)
+        stats = call(w, "hotspa_model", cfg2)
+        assert stats["from_cpu"] == 0 and sorted(w.cache.cache) == [0, 1, 2, 3], stats
+        out = diffuse(w, cfg2, lat, prompt, pooled, 2, both=True)
+        want_full = opf.denoise(sd, shape, lat, prompt, pooled, 2, 4.0, [512], 0, (32, 16))
+        cos, rel = oa.cosine_and_max_rel(out.cpu(), want_full)
+        assert cos >= 0.999 and rel <= 5e-2, ("ulysses4", cos, rel)
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errq.put(f"rank {rank}:\n{traceback.format_exc()}")
+        raise
+
+
+def test_worker_pipefusion_with_sequence_parallelism_four_gpus():
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    try:
+        mp.spawn(_pp_sp_case, args=(4, 29815, errq), nprocs=4, join=True)
     except Exception:
         msgs = []
         while not errq.empty():

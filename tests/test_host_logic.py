@@ -30,11 +30,24 @@ def test_library_exports_every_declared_symbol():
     assert _C.lib().hdit_version() >= 100
 
 
-def test_ctypes_structs_match_header_layout():
+def test_ctypes_structs_match_header_layout(tmp_path):
+    """The ctypes mirrors have the size (and a few probed field offsets) the C compiler gives include/hdit.h."""
+    import subprocess
     from hetu_dit_b200 import _C
-    assert ctypes.sizeof(_C.Seg) == 40
-    assert ctypes.sizeof(_C.CopyPiece) == 72
-    assert ctypes.sizeof(_C.AttnArgs) == 32 + 40 * 22 + 8 + 24 + 32
+    src = tmp_path / "sizes.c"
+    src.write_text(
+        '#include <stdio.h>\n#include <stddef.h>\n#include "hdit.h"\n'
+        'int main(void) { printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(hdit_seg), sizeof(hdit_copy_piece), '
+        'sizeof(hdit_attn_args), sizeof(hdit_norm_rope_tensor), sizeof(hdit_norm_rope_args), '
+        'offsetof(hdit_attn_args, n_out_dst), offsetof(hdit_attn_args, q_dst_row0), '
+        'offsetof(hdit_norm_rope_tensor, dst)); return 0; }\n')
+    exe = tmp_path / "sizes"
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    want = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
+    got = [ctypes.sizeof(_C.Seg), ctypes.sizeof(_C.CopyPiece), ctypes.sizeof(_C.AttnArgs),
+           ctypes.sizeof(_C.NormRopeTensor), ctypes.sizeof(_C.NormRopeArgs), _C.AttnArgs.n_out_dst.offset,
+           _C.AttnArgs.q_dst_row0.offset, _C.NormRopeTensor.dst.offset]
+    assert got == want
 
 
 def test_no_cpu_path():
@@ -365,13 +378,75 @@ def test_flux_pipeline_stage_split_and_first_token(monkeypatch):
     pipe.stage_sliced = True                      # the worker's block cache already placed this stage's blocks
     assert pipe._stage_blocks() == (pipe.model.transformer_blocks, pipe.model.single_transformer_blocks)
 
+    # rotary rows: the whole table with the first token's row, or -- a whole-image step under sequence
+    # parallelism with several patches -- a local table of the text rows followed by this rank's rows
+    tab = torch.arange(10 + 640, dtype=torch.float32)[:, None].repeat(1, 4)
+    pipe.model._rope = lambda s_txt, grid, device: (tab, -tab)
+    pipe.grid = (20, 32)
     monkeypatch.setattr(mod.ps, "get_sequence_parallel_world_size", lambda: 1)
-    assert pipe._first_token() == 0
+    assert pipe._rope_and_first_token(10, "cpu")[1] == 0
     rt.patch_mode, rt.pipeline_patch_idx = True, 1
-    assert pipe._first_token() == 128
+    assert pipe._rope_and_first_token(10, "cpu")[1] == 128
     rt.patch_mode = False
     monkeypatch.setattr(mod.ps, "get_sequence_parallel_world_size", lambda: 2)
-    with pytest.raises(NotImplementedError):
-        pipe._first_token()
+    (cos, sin), first = pipe._rope_and_first_token(10, torch.device("cpu"))
+    rows = list(range(10)) + list(range(10, 74)) + list(range(138, 202))
+    assert first == 0 and cos[:, 0].tolist() == [float(r) for r in rows] and torch.equal(sin, -cos)
     rt.pp_patches_token_start_end_idx_global = [[256, 512]]
-    assert pipe._first_token() == 256
+    assert pipe._rope_and_first_token(10, "cpu")[1] == 256
+
+
+def test_worker_plan_api_signatures_match_the_reference():
+    """The executor calls worker methods by name with positional / keyword arguments
+    (executor/gpu_executor.py:176-220 of the reference), so the parameter lists are part of the boundary:
+    switch_parallel_env (worker/worker.py:480-482), hotspa_model (:1571, a coroutine), execute_diffusion_stage
+    (:1009-1016), execute_encode_diffusion_stage (:1185-1191), get_worker_state (:1527)."""
+    import inspect
+    from hetu_dit_b200.worker.worker import Worker, run_worker_method
+
+    def params(fn):
+        return [p for p in inspect.signature(fn).parameters if p != "self"]
+
+    assert params(Worker.switch_parallel_env) == ["world_size", "ranks", "engine_config"]
+    assert params(Worker.hotspa_model) == ["engine_config"] and inspect.iscoroutinefunction(Worker.hotspa_model)
+    assert params(Worker.execute_diffusion_stage) == ["encode_stage_results", "engine_config", "input_config",
+                                                      "model_class", "task_id"]
+    assert params(Worker.execute_encode_diffusion_stage) == ["engine_config", "input_config", "model_class", "task_id"]
+    assert params(Worker.get_worker_state) == []
+    for name in ("init_static_env", "init_instance_model", "rpc_find_sources"):
+        assert callable(getattr(Worker, name))
+
+    class Stub:
+        def sync(self, a, b=2):
+            return a + b
+
+        async def coro(self, engine_config=None):
+            return ("awaited", engine_config)
+
+    assert run_worker_method(Stub(), "sync", 1, b=5) == 6
+    assert run_worker_method(Stub(), "coro", engine_config="cfg") == ("awaited", "cfg")
+
+
+def test_set_activate_groups_with_the_reference_call_forms():
+    """ParallelGroups.set_activate_*(degree, ranks, group_ranks) as worker.py:493-556 of the reference calls
+    them, for a plan on ranks {1, 3, 4, 6} of 8 with ulysses 2 x pp 2: same groups as activate_plan."""
+    from hetu_dit_b200.core.distributed import parallel_state as ps
+    from hetu_dit_b200.core.distributed.utils import RankGenerator
+    ranks = [1, 3, 4, 6]
+    for me in ranks:
+        a = ps.ParallelGroups(me, 8, None)
+        a.activate_plan(ranks, ulysses=2, pp=2)
+        b = ps.ParallelGroups(me, 8, None)
+        rank_map = {i: r for i, r in enumerate(sorted(ranks))}
+        gen = RankGenerator(tp=1, sp=2, pp=2, cfg=1, dp=1, order="tp-sp-pp-cfg-dp")
+        mapped = lambda axis: [[rank_map[r] for r in g] for g in gen.get_ranks(axis)]
+        b.set_activate_world_group(len(ranks), ranks, [ranks])
+        b.set_activate_tp_group(degree=4, ranks=ranks, group_ranks=mapped("tp"))
+        b.set_activate_sp_group(degree=4, ranks=ranks, group_ranks=mapped("sp"), ulysses_degree=2, ring_degree=1)
+        b.set_activate_pp_group(degree=4, ranks=ranks, group_ranks=mapped("pp"))
+        b.set_activate_cfg_group(degree=4, ranks=ranks, group_ranks=mapped("cfg"))
+        b.set_activate_dp_group(degree=4, ranks=ranks, group_ranks=mapped("dp"))
+        for axis in ("world", "tp", "sp", "pp", "cfg", "dp"):
+            assert a.group(axis).ranks == b.group(axis).ranks, (me, axis)
+        assert a.group("sp").ulysses_group.ranks == b.group("sp").ulysses_group.ranks
+    ps.destroy_model_parallel()

@@ -62,6 +62,50 @@ def test_split_static_matches_plain_entry_point_twice():
         cos, rel = oa.cosine_and_max_rel(out_new, out_ref)
         assert cos >= 0.9999 and rel <= 2e-2, (call, cos, rel)
         assert (lse_new - lse_ref).abs().max().item() <= 2e-3
+        # and against the CPU oracle of the whole (unsplit) attention
+        want, want_lse = oa.attention_with_lse(q.cpu(), torch.cat([t.cpu() for t in ks], 1),
+                                               torch.cat([t.cpu() for t in vs], 1))
+        cos, rel = oa.cosine_and_max_rel(out_new.cpu(), want)
+        assert cos >= 0.9999 and rel <= 2e-2, ("oracle", call, cos, rel)
+        assert (lse_new.cpu() - want_lse).abs().max().item() <= 2e-3
+
+
+@pytest.mark.parametrize("B,sq,H,D", [(1, 4096, 16, 128), (1, 2048, 64, 64)])
+def test_split_static_at_its_documented_limit(B, sq, H, D):
+    """Exactly the largest problems the static array holds: 8 Mi accumulator elements (4096 x 16 x 128) and
+    128 Ki log-sum-exp entries (2048 x 64 at head_dim 64, which is also 8 Mi accumulator elements). Checked
+    against the ordinary entry point everywhere and against the CPU oracle on a subset of heads and rows."""
+    from hetu_dit_b200 import _C
+    from oracle import attention as oa
+    lib = _C.lib()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    assert B * sq * H * D == 8 << 20 and B * H * sq <= 128 << 10
+    gen = torch.Generator(device=dev).manual_seed(7 + D)
+
+    def mk(n):
+        return torch.randn(B, n, H, D, generator=gen, device=dev, dtype=torch.float32).bfloat16()
+
+    q = mk(sq)
+    lens = (300, 129)
+    ks, vs = [mk(n) for n in lens], [mk(n) for n in lens]
+    out_ref = torch.empty(B, sq, H, D, dtype=torch.bfloat16, device=dev)
+    lse_ref = torch.empty(B, H, sq, dtype=torch.float32, device=dev)
+    out_new = torch.full_like(out_ref, float("nan"))
+    lse_new = torch.full_like(lse_ref, float("nan"))
+    _C.check(lib.hdit_attn_fwd(ctypes.byref(_args(_C, [q], ks, vs, out_ref, lse_ref))))
+    _C.check(lib.hdit_attn_fwd_split_static(ctypes.byref(_args(_C, [q], ks, vs, out_new, lse_new)), 1))
+    torch.cuda.synchronize()
+    assert _C.device_status(0, clear=True)[0] == 0
+    cos, rel = oa.cosine_and_max_rel(out_new, out_ref)
+    assert cos >= 0.9999 and rel <= 2e-2, (cos, rel)
+    assert (lse_new - lse_ref).abs().max().item() <= 2e-3
+    hs, rows = [0, H - 1], slice(sq - 257, sq)   # the last rows and heads sit at the end of the static array
+    want, want_lse = oa.attention_with_lse(q[:, rows][:, :, hs].cpu(), torch.cat([t[:, :, hs].cpu() for t in ks], 1),
+                                           torch.cat([t[:, :, hs].cpu() for t in vs], 1))
+    cos, rel = oa.cosine_and_max_rel(out_new[:, rows][:, :, hs].cpu(), want)
+    assert cos >= 0.9999 and rel <= 2e-2, ("oracle", cos, rel)
+    assert (lse_new[:, hs][:, :, rows].cpu() - want_lse).abs().max().item() <= 2e-3
 
 
 def test_split_static_rejects_oversize_and_bad_split():
