@@ -404,26 +404,12 @@ def run_gpu(args):
             ms = t.item()
         return ms / n
 
-    def capture():
-        """The step as one CUDA graph (None when capture fails: the eager path stays valid)."""
-        if args.no_graph:
-            return None, None
-        try:
-            side = torch.cuda.Stream(device=dev)
-            side.wait_stream(torch.cuda.current_stream(dev))
-            with torch.cuda.stream(side):
-                step(resident)
-            torch.cuda.current_stream(dev).wait_stream(side)
-            barrier()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                out = step(resident)
-            barrier()
-            return g, out
-        except Exception as e:
-            print(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); timing eager launches",
-                  file=sys.stderr)
-            return None, None
+    def graphed(inp):
+        """The step through the product's own CUDA-graph replay (ShapedDiT.forward_graphed): captured on the first
+        call, replayed afterwards."""
+        lat = inp["latent"][:, tok0:tok0 + s_loc] if index_dev is None else inp["latent"].index_select(1, index_dev)
+        return model.forward_graphed(lat, inp["text"], inp["pooled"], inp["t"], inp["g"], grid=band, token_offset=tok0,
+                                     full_grid=grid, token_index=index_dev)
 
     with torch.no_grad():
         for _ in range(max(args.warmup, 3)):
@@ -447,10 +433,11 @@ def run_gpu(args):
 
         # (2) the timed region proper: the same step captured once in a CUDA graph and replayed, which
         #     takes the Python / launch overhead of ~1.5 k kernels per step off the critical path
-        graph, out_static = capture()
-        run_step = graph.replay if graph is not None else (lambda: step(resident))
+        use_graph = not args.no_graph
+        run_step = (lambda: graphed(resident)) if use_graph else (lambda: step(resident))
         for _ in range(2):
             run_step()
+        barrier()
         with ClockSampler(local_rank) as clk:
             ms_step = timed(run_step, args.steps)
 
@@ -458,14 +445,8 @@ def run_gpu(args):
         out_host = torch.empty((1, s_loc, shape.token_in), dtype=torch.bfloat16).pin_memory()
 
         def e2e_step():
-            if graph is not None:
-                for k, v in host.items():
-                    resident[k].copy_(v, non_blocking=True)
-                graph.replay()
-                out_host.copy_(out_static, non_blocking=True)
-            else:
-                inp = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
-                out_host.copy_(step(inp), non_blocking=True)
+            inp = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+            out_host.copy_((graphed if use_graph else step)(inp), non_blocking=True)
 
         for _ in range(2):
             e2e_step()
@@ -475,15 +456,11 @@ def run_gpu(args):
         #     handed to the USP operators as joint tensors (the reference's layout), timed the same way
         ms_replicated = None
         if world > 1 and shape.block_kind == "mmdit" and model.shard_text and S_TXT % world == 0:
-            del graph
             model.shard_text = False
-            for _ in range(2):
-                step(resident)
-            graph2, _ = capture()
-            run2 = graph2.replay if graph2 is not None else (lambda: step(resident))
-            for _ in range(2):
-                run2()
-            ms_replicated = timed(run2, args.steps)
+            for _ in range(3):
+                run_step()
+            barrier()
+            ms_replicated = timed(run_step, args.steps)
             model.shard_text = True
     status = _C.device_status(local_rank, clear=True)
     if status[0] != 0:
@@ -520,7 +497,7 @@ def run_gpu(args):
                    "parallelism": f"ulysses{U}xring{R}" if world > 1 else "single",
                    "text_stream": text_layout,
                    "l2": "weights and activations exceed the 126 MB L2; no explicit flush",
-                   "cuda_graph": graph is not None if world == 1 or ms_replicated is None else True,
+                   "cuda_graph": use_graph,
                    "ms_per_step_eager_launches": ms_eager,
                    "ms_per_step_replicated_text": ms_replicated,
                    "step_flops": step_flops,

@@ -12,7 +12,7 @@ Ulysses groups are consecutive ranks and ring groups have stride `ulysses`.
 A plan may sit on any sorted subset of the node's ranks: position i of the
 sorted list plays local rank i (worker.py:507 `rank_map`).
 """
-from itertools import combinations
+from itertools import combinations, count
 from typing import Dict, List, Optional, Sequence, Tuple
 
 from .peer import PeerGroup, PeerHeap
@@ -27,6 +27,7 @@ class _ProcessGroupSlots:
 
 
 PROCESS_GROUP = _ProcessGroupSlots
+_PLAN_EPOCHS = count(1)  # process-wide, so that an epoch value is never seen twice
 
 
 def seq_parallel_rank_lists(sp_ulysses_degree: int, sp_ring_degree: int, world_size: int, ranks: Sequence[int],
@@ -79,6 +80,7 @@ class ParallelGroups:
         self.degrees: Dict[str, int] = dict(tp=1, ulysses=1, ring=1, pp=1, cfg=1, dp=1)
         self._groups: Dict[str, PeerGroup] = {}
         self._pp_coordinator = None
+        self.plan_epoch = next(_PLAN_EPOCHS)  # new value whenever a group is re-bound: captured CUDA graphs of older plans are void
         self.activate_plan(list(range(world_size)) if world_size == 1 else [rank])
 
     # -- enumeration the reference uses to size its communicator pool -------------------
@@ -118,6 +120,7 @@ class ParallelGroups:
         lut = sorted(ranks)
         n = len(lut)
         sp = ulysses * ring
+        self.plan_epoch = next(_PLAN_EPOCHS)
         if tp * sp * pp * cfg * dp != n:
             raise ValueError(f"degrees tp={tp} sp={sp} pp={pp} cfg={cfg} dp={dp} do not multiply to {n} ranks")
         if self.rank not in lut:
@@ -152,6 +155,7 @@ class ParallelGroups:
     def set_activate_world_group(self, degree=None, ranks=None, group_ranks=None):
         if ranks is None:            # one-argument form: set_activate_world_group(ranks)
             degree, ranks = None, degree
+        self.plan_epoch = next(_PLAN_EPOCHS)
         self.rank_map = sorted(ranks)
         self._groups["world"] = PeerGroup(self.rank_map, self.rank, self.heap)
         self.activate_world_groups = [list(g) for g in (group_ranks or [self.rank_map])]
@@ -162,6 +166,7 @@ class ParallelGroups:
             members, ulysses_degree, ring_degree = list(degree), ranks, group_ranks
         else:
             members = self._mine(ranks, group_ranks)
+        self.plan_epoch = next(_PLAN_EPOCHS)
         upg, rpg = set_seq_parallel_pg(ulysses_degree, ring_degree, self.rank, len(members), list(members),
                                        heap=self.heap)
         self._groups["sp"] = SequenceParallelGroup(sorted(members), self.rank, self.heap, upg, rpg)
@@ -173,6 +178,7 @@ class ParallelGroups:
             members = list(degree)
         else:
             members = self._mine(ranks, group_ranks)
+        self.plan_epoch = next(_PLAN_EPOCHS)
         self._groups[axis] = PeerGroup(members, self.rank, self.heap)
         self.degrees[axis] = len(members)
         if axis == "pp":

@@ -514,6 +514,29 @@ class ShapedDiT(nn.Module):
             shift, scale = self.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
         return self.proj_out(kernels.ln_modulate(hidden.contiguous(), shift, scale))
 
+    def forward_graphed(self, latent_tokens, text_embeds, pooled, timestep, guidance=None, grid=None,
+                        token_offset: int = 0, full_grid: Optional[Tuple[int, ...]] = None,
+                        token_index: Optional[torch.Tensor] = None):
+        """forward() replayed from a CUDA graph that is captured on the first call with these shapes under the
+        active plan (see step_graph.StepGraphCache). The result is the graph's output buffer: use it before the
+        next call with the same shapes. Every rank of a sequence-parallel plan must make the same calls."""
+        from ..step_graph import StepGraphCache
+        cache = self.__dict__.setdefault("_step_graphs", StepGraphCache())
+        if guidance is None:
+            guidance = torch.ones_like(timestep)
+        key = ("step", tuple(latent_tokens.shape), tuple(text_embeds.shape), latent_tokens.dtype, bool(self.shard_text),
+               tuple(grid) if grid is not None else None, int(token_offset),
+               tuple(full_grid) if full_grid is not None else None,
+               None if token_index is None else (int(token_index.numel()), token_index.data_ptr()))
+
+        def fn(lat, txt, pl, t, g):
+            # token_index is read by the replayed graph: the caller keeps that tensor alive and unchanged (it is
+            # part of the key by address)
+            return self.forward(lat, txt, pl, t, g, grid=grid, token_offset=token_offset, full_grid=full_grid,
+                                token_index=token_index)
+
+        return cache.run(key, fn, latent_tokens, text_embeds, pooled, timestep, guidance)
+
     def _modulations_ahead(self, temb):
         """Every block's adaLN vectors depend only on the timestep embedding, and each is a matrix-vector
         product that streams its weight once from HBM (6.4 GB per step at the Flux shape) while the blocks'

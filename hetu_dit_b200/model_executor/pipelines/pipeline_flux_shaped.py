@@ -88,4 +88,4 @@ class FluxShapedPipeline(SD3ShapedPipeline):
         return hidden_states, encoder_hidden_states
 
     def _backbone_forward(self, latents, encoder_hidden_states, pooled, t):
-        return self._transformer(latents, encoder_hidden_states, pooled, t.expand(latents.shape[0]))
+        return self._stage(latents, encoder_hidden_states, pooled, t.expand(latents.shape[0]).contiguous())

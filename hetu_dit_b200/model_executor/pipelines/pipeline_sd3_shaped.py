@@ -54,6 +54,24 @@ class SD3ShapedPipeline:
         # True when model.transformer_blocks already holds only this stage's blocks (the worker's block
         # cache placed them); False when the model is whole and the stage's slice is taken here.
         self.stage_sliced = False
+        # Replay the whole-image step from a CUDA graph where the step is one self-contained launch sequence:
+        # a single pipeline stage without pipeline patches (sequence parallelism included). PipeFusion stages
+        # and patched steps run eagerly: their hand-offs and stale-KV updates depend on per-patch host state.
+        self.use_cuda_graph = True
+        self._graphs = None
+
+    def _stage(self, hidden_states, encoder_hidden_states, pooled, timestep):
+        """_transformer(), through a captured CUDA graph when the step qualifies (see use_cuda_graph)."""
+        rt = get_runtime_state()
+        if not (self.use_cuda_graph and hidden_states.is_cuda and ps.get_pipeline_parallel_world_size() == 1
+                and rt.num_pipeline_patch == 1 and not rt.patch_mode):
+            return self._transformer(hidden_states, encoder_hidden_states, pooled, timestep)
+        from ..step_graph import StepGraphCache
+        if self._graphs is None:
+            self._graphs = StepGraphCache()
+        key = ("stage", tuple(hidden_states.shape), tuple(encoder_hidden_states.shape), hidden_states.dtype,
+               tuple(self.grid), float(self.guidance_scale))
+        return self._graphs.run(key, self._transformer, hidden_states, encoder_hidden_states, pooled, timestep)
 
     # ------------------------------------------------------------------ one stage of the backbone
     def _stage_blocks(self):
@@ -124,8 +142,8 @@ class SD3ShapedPipeline:
     def _backbone_forward(self, latents, encoder_hidden_states, pooled, t):
         if ps.is_pipeline_first_stage():
             latents = torch.cat([latents] * 2)  # unconditional + conditional through one batch
-        timestep = t.expand(latents.shape[0])
-        noise_pred, encoder_hidden_states = self._transformer(latents, encoder_hidden_states, pooled, timestep)
+        timestep = t.expand(latents.shape[0]).contiguous()
+        noise_pred, encoder_hidden_states = self._stage(latents, encoder_hidden_states, pooled, timestep)
         if ps.is_pipeline_last_stage():
             uncond, text = noise_pred.chunk(2)
             latents = uncond + self.guidance_scale * (text - uncond)

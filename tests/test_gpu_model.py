@@ -195,3 +195,58 @@ def test_full_size_flux_block_row_subset():
         hr = hr + mod[5][:, None] * osd._ff(sd, "b.ff", osd._mod(F.layer_norm(hr, (d,), eps=1e-6), mod[3], mod[4]))
     cos, rel = oa.cosine_and_max_rel(h[:, rows.to(DEV)].cpu(), hr)
     assert cos >= 0.9999 and rel <= 2e-2, (cos, rel)
+
+
+def test_graph_replay_matches_eager_bit_for_bit():
+    """ShapedDiT.forward_graphed: the captured step replayed twice with fresh inputs equals the eager step bit
+    for bit, and a second shape gets its own graph."""
+    from hetu_dit_b200 import _C
+    from hetu_dit_b200.model_executor.models.shaped_dit import ShapedDiT
+    shape, grid = tiny_shape("flux")
+    model = ShapedDiT(shape).to(DEV).init_weights(seed=5, std=0.05).bfloat16()
+    with torch.no_grad():
+        for seed in (0, 1, 2):
+            lat, txt, pooled, t, g = (x.to(DEV) for x in _inputs(shape, grid[0] * grid[1], 33, seed=seed))
+            eager = model(lat, txt, pooled, t, g, grid=grid).clone()
+            got = model.forward_graphed(lat, txt, pooled, t, g, grid=grid)
+            torch.cuda.synchronize()
+            assert torch.equal(got, eager), seed
+        lat, txt, pooled, t, g = (x.to(DEV) for x in _inputs(shape, 10 * 12, 20, seed=3))
+        assert torch.equal(model.forward_graphed(lat, txt, pooled, t, g, grid=(10, 12)),
+                           model(lat, txt, pooled, t, g, grid=(10, 12)))
+    cache = model.__dict__["_step_graphs"]
+    assert cache.captures == 2 and cache.replays == 4
+    assert _C.device_status(0, clear=True)[0] == 0
+
+
+def test_pipeline_whole_image_steps_replay_from_a_graph():
+    """The SD3-shaped pipeline without pipeline patches replays its stage forward from a CUDA graph: same latents
+    as with the graph switched off, bit for bit, over several steps and two requests."""
+    from hetu_dit_b200.config import EngineConfig
+    from hetu_dit_b200.core.distributed import parallel_state as ps
+    from hetu_dit_b200.core.distributed.runtime_state import ModelGeometry, initialize_runtime_state, reset_runtime_state
+    from hetu_dit_b200.core.resource_manager.cache_manager import reset_cache_manager
+    from hetu_dit_b200.model_executor.models.shaped_dit import DiTShape, ShapedDiT
+    from hetu_dit_b200.model_executor.pipelines.pipeline_sd3_shaped import SD3ShapedPipeline
+    ps.destroy_model_parallel()
+    reset_cache_manager()
+    shape = DiTShape("sd3-tiny", 3, 0, 256, 4, 64, 64, 128, 96, False, None, False)
+    model = ShapedDiT(shape).to(DEV).init_weights(seed=11, std=0.05).bfloat16()
+    rt = initialize_runtime_state(ModelGeometry(4, 64), EngineConfig())
+    rt.set_input_parameters(height=512, width=256, batch_size=1, num_inference_steps=3)
+    pipe = SD3ShapedPipeline(model, guidance_scale=4.0)
+    outs = {}
+    for use_graph in (False, True):
+        pipe.use_cuda_graph = use_graph
+        for req in range(2):
+            gen = torch.Generator().manual_seed(40 + req)
+            lat = torch.randn(1, 32 * 16, 64, generator=gen).bfloat16().to(DEV)
+            prompt = torch.randn(2, 19, 128, generator=gen).bfloat16().to(DEV)
+            pooled = torch.randn(2, 96, generator=gen).bfloat16().to(DEV)
+            outs[(use_graph, req)] = pipe.diffusion_stage(lat, prompt, pooled, 3).clone()
+    torch.cuda.synchronize()
+    for req in range(2):
+        assert torch.equal(outs[(True, req)], outs[(False, req)]), req
+    assert pipe._graphs.captures == 1 and pipe._graphs.replays == 6
+    reset_runtime_state()
+    reset_cache_manager()
