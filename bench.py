@@ -291,12 +291,14 @@ def parity_check(cfg_name, rank, world, plan, dev, ps, dist):
         return outs + [y.float()]
 
     pg.activate_plan([rank])
+    model.register_cache()
     solo = run(0, _n_tokens(grid), None, grid, _n_tokens(grid))
     worst_cos, worst_rel = 1.0, 0.0
     layouts = []
     if world > 1:
         U, R = plan
         pg.activate_plan(list(range(world)), ulysses=U, ring=R)
+        model.register_cache()
         tok0, n, index, band = _shard_tokens(CONFIGS[cfg_name]["shard"], grid, rank, world)
         rows = torch.arange(tok0, tok0 + n, device=dev) if index is None else index.to(dev)
         for shard_text in ((True, False) if shape.block_kind == "mmdit" and s_txt % world == 0 else (False,)):
@@ -371,8 +373,7 @@ def run_gpu(args):
         model = M.ShapedDiT(shape)
     torch.set_default_dtype(torch.float32)
     model.init_weights(seed=0, std=0.02)
-    if shape.block_kind == "mmdit" and shape.n_single and shape.text_first:
-        model.register_cache()
+    model.register_cache()
     model.shard_text = not args.replicated_text
     host = {k: v.pin_memory() for k, v in _inputs(shape, S_IMG, S_TXT).items()}
     tok0, s_loc, index, band = _shard_tokens(cfg["shard"], grid, rank, world)

@@ -145,6 +145,9 @@ struct alignas(64) AttnKernelParams {
 #ifndef HDIT_ATTN_POLY8
 #define HDIT_ATTN_POLY8 0
 #endif
+#ifndef HDIT_ATTN_SPLIT_P
+#define HDIT_ATTN_SPLIT_P 0  // 1: head_dim 64 keeps P in TMEM columns of its own (see Cfg::kSplitP); measured slower
+#endif
 #ifndef HDIT_ATTN_LATE_KWAIT
 #define HDIT_ATTN_LATE_KWAIT 1  // 1: poll the next K block between P V and Q K^T instead of before the hand-over
 #endif
@@ -167,6 +170,14 @@ struct Cfg {
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kColS = 0;      // + t * 128
   static constexpr uint32_t kColO = 256;    // + t * D
+  // head_dim 64 leaves 128 TMEM columns free. With HDIT_ATTN_SPLIT_P, P gets columns of its own there instead of
+  // overwriting S, so the next Q K^T of a tile may run as soon as the softmax threads have *read* S, which cuts
+  // the S -> P -> P V -> Q K^T chain. Measured on B200 it is slower than the aliased layout (499 vs 596 TFLOP/s at
+  // 24 heads x 4429 tokens): both softmax groups then run in phase and contend for the special-function unit,
+  // where the aliased schedule keeps them half a block apart. Off by default.
+  static constexpr bool kSplitP = (D == 64) && (HDIT_ATTN_SPLIT_P != 0);
+  static constexpr uint32_t kColP = kSplitP ? 384 : kColS;  // + t * 64 when split, + t * 128 when aliased on S
+  static constexpr uint32_t kStrideP = kSplitP ? 64 : 128;
 };
 
 struct KvCursor {
@@ -257,7 +268,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
   uint64_t* p_ready = s_full + 2;                // [2]
   uint64_t* o_done = p_ready + 2;                // [2]
   uint64_t* merge_bar = o_done + 2;              // [1] interleaved mode: half 1's partial result is in smem
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(merge_bar + 1);
+  uint64_t* s_free = merge_bar + 1;              // [2] split-P: the softmax threads have read S into registers
+  uint64_t* pv_done = s_free + 2;                // [2] split-P: P V is done (P may be overwritten, O is stable)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -294,6 +307,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 4);  // one arrival per softmax warp
       mbar_init(&o_done[i], 1);
+      mbar_init(&s_free[i], 4);
+      mbar_init(&pv_done[i], 1);
     }
     mbar_init(merge_bar, 4);
     for (int i = 0; i < C::kStagesK; ++i) {
@@ -410,7 +425,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         };
         auto issue_pv = [&](int t, int stage, bool accumulate) {
           const uint32_t d_tmem = tmem_base + C::kColO + t * D;
-          const uint32_t a_tmem = tmem_base + C::kColS + t * 128;
+          const uint32_t a_tmem = tmem_base + C::kColP + t * C::kStrideP;
           const uint64_t b0 = v_desc0 + static_cast<uint32_t>((stage * C::kTileBytes) >> 4);
 #pragma unroll
           for (int kk = 0; kk < kBlockN / 16; ++kk) {
@@ -460,6 +475,36 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
           g_attn_trace_mma[0][63][1] = static_cast<long long>(ns);
         }
 #endif
+        if constexpr (C::kSplitP) {
+          // P has its own columns: per round, first the next Q K^T of every half (needs only that the softmax
+          // threads have read the current S), then the P V of every half as its P arrives.
+          for (int i = 0; i < n_iter && ok; ++i) {
+            for (int t = 0; t <= last_t && ok; ++t) {
+              const int j = il ? 2 * i + t : i;
+              const int jn = j + blk_step;
+              if (j >= nblk || jn >= nblk) continue;
+              if (il || t == 0) wait(&k_full[k_stage(jn)], k_phase(jn), W_MMA_KFULL, jn);
+              wait(&s_free[t], i & 1, W_MMA_PREADY, 1000 + i * 2 + t);
+              if (!ok) break;
+              tc_fence_after();
+              issue_qk(t, k_stage(jn));
+              tc_commit(&s_full[t]);
+              if (il || t == last_t) tc_commit(&k_empty[k_stage(jn)]);
+            }
+            for (int t = 0; t <= last_t && ok; ++t) {
+              const int j = il ? 2 * i + t : i;
+              if (j >= nblk) break;
+              if (il || t == 0) wait(&v_full[v_stage(j)], v_phase(j), W_MMA_VFULL, j);
+              wait(&p_ready[t], i & 1, W_MMA_PREADY, i * 2 + t);
+              if (!ok) break;
+              tc_fence_after();
+              issue_pv(t, v_stage(j), i > 0);
+              tc_commit(&pv_done[t]);
+              if (j + blk_step >= nblk) tc_commit(&o_done[t]);
+              if (il || t == last_t) tc_commit(&v_empty[v_stage(j)]);
+            }
+          }
+        } else
         for (int i = 0; i < n_iter && ok; ++i) {
           for (int t = 0; t <= last_t && ok; ++t) {
             // half t's i-th KV block and the one after it
@@ -515,6 +560,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     if (active) {
       const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
       const uint32_t tm_s = tmem_base + lane_base + C::kColS + t * 128;
+      const uint32_t tm_p = tmem_base + lane_base + C::kColP + t * C::kStrideP;
       const uint32_t tm_o = tmem_base + lane_base + C::kColO + t * D;
       const float scale_log2 = p.scale_log2;
       float m_run = -INFINITY;   // maximum the stored P and O are scaled against (log2 units)
@@ -552,6 +598,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         for (int c = 0; c < 4; ++c) tmem_ld32(tm_s + c * 32, s[c]);
         tc_wait_ld();
         HDIT_TRACE_SM(2);
+        if constexpr (C::kSplitP) {
+          // S is in registers: the issuer may overwrite it with the next block's scores
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s_free[t]);
+        }
 
 #if defined(HDIT_ATTN_PROBE) && HDIT_ATTN_PROBE == 2
         // timing probe (wrong results): S is read and P written, but nothing is computed
@@ -573,13 +625,27 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
               if (c * 32 + i >= valid) s[c][i] = 0xff800000u;  // -inf
         }
 
+        // split-P: the previous P V of this half must be done before its P is overwritten or O is rescaled. The
+        // wait sits as late as possible (before the first P store / inside the rare rescale), so that the P V
+        // runs under this block's load and maximum passes.
+        bool pv_waited = !C::kSplitP || j == 0;
+        auto wait_pv_done = [&]() {
+          if (pv_waited) return;
+          pv_waited = true;
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(&pv_done[t], (j - 1) & 1, abort_flag, kSpinLimit))) {
+            report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_SM_ODONE, 100 + j * 2 + t);
+            ok = false;
+          }
+          tc_fence_after();
+        };
         // Rescale the running state to a larger maximum (rare: only when it grows by more than 2^8).
         auto rescale_to = [&](bool grow, float m_new) {
           const float alpha = grow ? ex2_approx(m_run - m_new) : 1.0f;
           if (grow) m_run = m_new;
           l_run *= alpha;
           if (j > 0) {
-            // O(t) is stable here: the commit that raised s_full covered the previous P V.
+            // O(t) is stable here: the commit that raised s_full covered the previous P V (split-P: wait for it)
+            wait_pv_done();
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
               uint32_t o[32];
@@ -624,7 +690,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
               pk[i >> 1] = pack2<FP16>(p0.x, p0.y);
               pk[(i >> 1) + 1] = pack2<FP16>(p1.x, p1.y);
             }
-            tmem_st16(tm_s + c * 16, pk);
+            if (c == 0) wait_pv_done();
+            tmem_st16(tm_p + c * 16, pk);
           }
           raw_max = fmaxf(mx0, mx1);
           return (acc0.x + acc0.y) + (acc1.x + acc1.y);
@@ -668,6 +735,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
           m_pend = fmaxf(m_run, m_blk);
         }
         HDIT_TRACE_SM(4);
+        if (!ok) break;
         tc_wait_st();
         tc_fence_before();
         // one arrival per warp: 128 arrivals on one barrier word would serialise on the S -> P -> MMA path
@@ -1171,9 +1239,9 @@ int attn_fwd_impl(const hdit_attn_args* a, int n_split, float* split_out, float*
     const long long ctas_pair = static_cast<long long>(kp.n_pairs) * a->heads * a->batch;
     const long long ctas_il = static_cast<long long>(kp.n_tiles) * a->heads * a->batch;
     // measured at 3 heads x 4608 tokens, head_dim 128: an interleaved iteration (two KV blocks, each ring
-    // effectively half as deep) costs 1.56 paired blocks; about 6 blocks' worth of fixed cost per CTA
+    // effectively half as deep) costs 1.12 paired blocks; about 6 blocks' worth of fixed cost per CTA
     const double t_pair = static_cast<double>((ctas_pair + kSmCount - 1) / kSmCount) * (nblk + 6.0);
-    const double t_il = static_cast<double>((ctas_il + kSmCount - 1) / kSmCount) * ((nblk + 1) / 2 * 1.56 + 6.0);
+    const double t_il = static_cast<double>((ctas_il + kSmCount - 1) / kSmCount) * ((nblk + 1) / 2 * 1.12 + 6.0);
     if (a->kv_interleave == 2 || t_il * 1.05 < t_pair) {
       kp.interleave = 1;
       kp.n_pairs = kp.n_tiles;

@@ -186,7 +186,7 @@ def _interleave_cost(q_tiles, kv_blocks, batch, heads):
     """Cost (in KV blocks of one paired CTA) of running one query tile per CTA with the KV blocks interleaved
     over its two halves; the constants are the library's own (csrc/attn_sm100.cu)."""
     ctas_il = q_tiles * heads * batch
-    return -(-ctas_il // _SM_COUNT) * ((kv_blocks + 1) // 2 * 1.56 + 6.0)
+    return -(-ctas_il // _SM_COUNT) * ((kv_blocks + 1) // 2 * 1.12 + 6.0)
 
 
 def _pick_kv_split(q_segs, k_segs, batch, heads, kv_interleave=0):

@@ -121,7 +121,7 @@ class JointAttnProcessor:
         ranges = [_prologue_range(i0, i0 + S_img, attn.norm_q, attn.norm_k, rope, text_rows + token_offset),
                   _prologue_range(t0, t0 + S_txt, attn.norm_added_q, attn.norm_added_k,
                                   rope if attn.rope_on_text else None, text_offset)]
-        out = self._ops.get(hetuDiTLongContextAttention)(attn, q, k, v, dropout_p=0.0, causal=False,
+        out = self._ops.get(hetuDiTLongContextAttention)(_cache_key(attn), q, k, v, dropout_p=0.0, causal=False,
                                                          qk_prologue=sorted(ranges, key=lambda r: r[0]))
         out = out.reshape(B, S_txt + S_img, attn.heads * attn.head_dim)
         return attn.to_out[0](out[:, i0:i0 + S_img]), attn.to_add_out(out[:, t0:t0 + S_txt])
@@ -143,7 +143,7 @@ class JointAttnProcessor:
 
         if ps.get_sequence_parallel_world_size() > 1:
             cls = hetuDiTFluxLongContextAttention if strategy == "front" else hetuDiTJointLongContextAttention
-            out = self._ops.get(cls)(attn, q, k, v, dropout_p=0.0, causal=False, joint_tensor_query=tq,
+            out = self._ops.get(cls)(_cache_key(attn), q, k, v, dropout_p=0.0, causal=False, joint_tensor_query=tq,
                                      joint_tensor_key=tk, joint_tensor_value=tv, joint_strategy=strategy)
         else:
             k, v = get_cache_manager().update_and_get_kv_cache(new_kv=[k, v], layer=attn, slice_dim=1,
@@ -195,7 +195,7 @@ class SingleAttnProcessor:
             text_rows = int(text_total) if attn.rope_on_text else 0
             ranges = [_prologue_range(t_lo, t_hi, attn.norm_q, attn.norm_k, rope_txt, text_offset),
                       _prologue_range(i_lo, i_hi, attn.norm_q, attn.norm_k, rope, text_rows + token_offset)]
-            ctx = self._ops.get(hetuDiTLongContextAttention)(attn, q, k, v, dropout_p=0.0, causal=False,
+            ctx = self._ops.get(hetuDiTLongContextAttention)(_cache_key(attn), q, k, v, dropout_p=0.0, causal=False,
                                                              qk_prologue=sorted(ranges, key=lambda r: r[0]))
             return ctx.reshape(B, S, attn.heads * attn.head_dim)
         text_rows = S_txt if attn.rope_on_text else 0
@@ -209,7 +209,7 @@ class SingleAttnProcessor:
         if sp > 1:
             strategy = "front" if front else "rear"
             cls = hetuDiTFluxLongContextAttention if front else hetuDiTJointLongContextAttention
-            out = self._ops.get(cls)(attn, q[:, i_lo:i_hi], k[:, i_lo:i_hi], v[:, i_lo:i_hi], dropout_p=0.0,
+            out = self._ops.get(cls)(_cache_key(attn), q[:, i_lo:i_hi], k[:, i_lo:i_hi], v[:, i_lo:i_hi], dropout_p=0.0,
                                      causal=False, joint_tensor_query=q[:, t_lo:t_hi], joint_tensor_key=k[:, t_lo:t_hi],
                                      joint_tensor_value=v[:, t_lo:t_hi], joint_strategy=strategy)
         elif _cached(attn) and S_txt:
@@ -253,6 +253,13 @@ class CogVideoXAttnProcessor:
 
 def _cached(attn) -> bool:
     return ("attn", attn) in get_cache_manager().cache
+
+
+def _cache_key(attn):
+    """What the processors hand to the USP operators as the layer that owns a stale-KV buffer: the layer itself
+    for the image models, None for the video models (the reference passes attn=None there,
+    attention_processor.py:1117, 1496, so they never touch the KV cache)."""
+    return attn if getattr(attn, "stale_kv", True) else None
 
 
 # names of the reference's processors that these stand in for

@@ -53,6 +53,8 @@ class DiTShape:
     qk_norm_kind: str = "rms"            # "rms" or "layer" (LayerNorm with weight and bias over head_dim)
     block_kind: str = "mmdit"            # "mmdit": double (+ single) stream blocks; "cogvideox": n_double CogVideoX blocks
     temb_dim: Optional[int] = None       # width of the timestep embedding; None = hidden
+    stale_kv: bool = True                # attention layers keep a PipeFusion stale-KV buffer (image models); the
+                                         # reference's video processors pass attn=None and never do
 
     def __post_init__(self):
         if self.text_first is None:
@@ -74,10 +76,11 @@ FLUX_DEV = DiTShape("flux.1-dev", 19, 38, 3072, 24, 128, 64, 4096, 768, True, (1
 # 42 blocks, 48 x 64 heads, patch 2x2x2 over a 16-channel latent (128 features per token), text front, rotary
 # embedding on the video rows only, no pooled text vector, 512-wide timestep embedding
 COGVIDEOX_5B = DiTShape("cogvideox-1.5-5b", 42, 0, 3072, 48, 64, 128, 4096, 0, True, (16, 24, 24), False,
-                        text_first=True, rope_on_text=False, qk_norm_kind="layer", block_kind="cogvideox", temb_dim=512)
+                        text_first=True, rope_on_text=False, qk_norm_kind="layer", block_kind="cogvideox", temb_dim=512,
+                        stale_kv=False)
 # 20 double + 40 single blocks, 24 x 128 heads, patch 1x2x2 (64 features per token), text rear
 HUNYUAN_VIDEO = DiTShape("hunyuanvideo", 20, 40, 3072, 24, 128, 64, 4096, 768, True, (16, 56, 56), True,
-                         text_first=False, rope_on_text=False)
+                         text_first=False, rope_on_text=False, stale_kv=False)
 
 
 def timestep_embedding(t: torch.Tensor, dim: int = 256, max_period: float = 10000.0) -> torch.Tensor:
@@ -156,6 +159,7 @@ class Attention(nn.Module):
         d = shape.hidden
         self.heads, self.head_dim = shape.heads, shape.head_dim
         self.text_first, self.rope_on_text = bool(shape.text_first), bool(shape.rope_on_text)
+        self.stale_kv = bool(shape.stale_kv)
         norm_cls = LayerNormWeight if shape.qk_norm_kind == "layer" else RMSNormWeight
         self.to_q, self.to_k, self.to_v = nn.Linear(d, d), nn.Linear(d, d), nn.Linear(d, d)
         self.norm_q = norm_cls(shape.head_dim) if shape.qk_norm else None
@@ -396,6 +400,8 @@ class ShapedDiT(nn.Module):
         hetu_dit/model_executor/diffusion_executor/models/base_model.py:162-178). Call after a plan switch."""
         from ...core.distributed import parallel_state as ps
         from ...core.resource_manager.cache_manager import get_cache_manager
+        if not self.shape.stale_kv:
+            return
         kind = "sequence_parallel_attn_cache" if ps.get_sequence_parallel_world_size() > 1 else "naive_cache"
         for m in self.modules():
             if isinstance(m, Attention):
