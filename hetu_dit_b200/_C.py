@@ -155,6 +155,10 @@ def _declare(lib):
     lib.hdit_gate_residual.argtypes = [ctypes.c_int32] + [ctypes.c_void_p] * 4 + [ctypes.c_int64] * 7 + [ctypes.c_void_p]
     lib.hdit_gelu_tanh.restype = ctypes.c_int
     lib.hdit_gelu_tanh.argtypes = [ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int64] * 4 + [ctypes.c_void_p]
+    lib.hdit_cfg_euler_step.restype = ctypes.c_int
+    lib.hdit_cfg_euler_step.argtypes = [ctypes.c_int32] + [ctypes.c_void_p] * 5 + [ctypes.c_int64, ctypes.c_float,
+                                                                                 ctypes.c_void_p, ctypes.c_int32,
+                                                                                 ctypes.c_void_p]
     lib.hdit_heap_alloc.restype = ctypes.c_int
     lib.hdit_heap_alloc.argtypes = [ctypes.c_int64, ctypes.POINTER(ctypes.c_void_p)]
     lib.hdit_heap_free.restype = ctypes.c_int

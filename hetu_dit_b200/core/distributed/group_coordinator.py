@@ -101,12 +101,13 @@ class PipelineGroupCoordinator:
         words += [0] * (_HEADER_BYTES // 8 - len(words))
         return torch.tensor(words, dtype=torch.int64, device=t.device)
 
-    def _push(self, tensor: torch.Tensor, name: str, segment_idx: int):
+    def _slot(self, tensor: torch.Tensor, name: str, segment_idx: int):
+        """(payload address in the successor's inbox, header piece or None) of message (name, segment_idx)."""
         key = (name, segment_idx)
         nbytes = tensor.numel() * tensor.element_size()
         dst_base = self.heap.peer_ptr(self.next_rank, self.inbox_offset)
         slot = self._send_slot.get(key)
-        pieces = []
+        header = None
         if slot is None or slot[1] != tensor.shape or slot[2] != tensor.dtype:
             if slot is not None:
                 raise RuntimeError(f"message {key} changed shape without reset_buffer()")
@@ -117,12 +118,32 @@ class PipelineGroupCoordinator:
             self._send_slot[key] = (off, tensor.shape, tensor.dtype)
             self.send_shape.setdefault(name, {})[segment_idx] = tensor.shape
             hdr = self._header(tensor)
-            pieces.append((hdr.data_ptr(), dst_base + off, 1, 0, 0, 1, 0, 0, _HEADER_BYTES))
+            header = (hdr.data_ptr(), dst_base + off, 1, 0, 0, 1, 0, 0, _HEADER_BYTES)
+            self._keep_alive = hdr  # until the copy below has been enqueued behind it on the same stream
         else:
             off = slot[0]
+        return dst_base + off + _HEADER_BYTES, header
+
+    def _push(self, tensor: torch.Tensor, name: str, segment_idx: int):
+        nbytes = tensor.numel() * tensor.element_size()
+        dst, header = self._slot(tensor, name, segment_idx)
+        pieces = [header] if header is not None else []
         if nbytes:
-            pieces.append((tensor.data_ptr(), dst_base + off + _HEADER_BYTES, 1, 0, 0, 1, 0, 0, nbytes))
+            pieces.append((tensor.data_ptr(), dst, 1, 0, 0, 1, 0, 0, nbytes))
         kernels.copy_pieces(pieces, tensor.device)
+        self.heap.signal(self.next_rank, _CHANNEL)
+
+    def reserve_send(self, like: torch.Tensor, name: str = "latent", segment_idx: int = -1) -> int:
+        """For a producer kernel that writes the message itself: the address in the successor's inbox where the
+        payload of a tensor shaped like `like` belongs (the header goes out now if this is the first message of
+        the slot). The caller's kernel stores the payload there and then calls commit_send()."""
+        dst, header = self._slot(like, name or "latent", segment_idx)
+        if header is not None:
+            kernels.copy_pieces([header], like.device)
+        return dst
+
+    def commit_send(self):
+        """Publishes the message whose payload a kernel has stored at the address reserve_send() returned."""
         self.heap.signal(self.next_rank, _CHANNEL)
 
     def pipeline_isend(self, tensor: torch.Tensor, name: str = "latent", segment_idx: int = -1) -> None:

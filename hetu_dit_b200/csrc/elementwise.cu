@@ -275,6 +275,78 @@ bool misaligned(const void* p, int64_t stride) { return (reinterpret_cast<uintpt
 }  // namespace
 }  // namespace hdit
 
+namespace hdit {
+namespace {
+
+// Classifier-free guidance + flow-matching Euler step of a latent patch in one pass, with an optional second
+// destination (the next pipeline stage's inbox). Rounding follows the eager sequence it replaces: the guidance
+// combine runs in the 16-bit type, one rounding per operation (difference, scaled difference, sum); the step runs
+// in fp32 on the rounded prediction and is rounded once.
+template <bool FP16>
+__global__ void __launch_bounds__(256) cfg_euler_step_kernel(const uint16_t* __restrict__ uncond,
+                                                            const uint16_t* __restrict__ cond,
+                                                            const uint16_t* __restrict__ sample, uint16_t* __restrict__ out,
+                                                            uint16_t* __restrict__ out2, long long n_vec, float guidance,
+                                                            const float* __restrict__ sigmas, int step) {
+  const float dt = sigmas[step + 1] - sigmas[step];
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+    const uint4 u4 = reinterpret_cast<const uint4*>(uncond)[i];
+    const uint4 s4 = reinterpret_cast<const uint4*>(sample)[i];
+    uint4 c4 = u4;
+    if (cond != nullptr) c4 = reinterpret_cast<const uint4*>(cond)[i];
+    const uint16_t* u = reinterpret_cast<const uint16_t*>(&u4);
+    const uint16_t* c = reinterpret_cast<const uint16_t*>(&c4);
+    const uint16_t* sm = reinterpret_cast<const uint16_t*>(&s4);
+    uint4 o4;
+    uint16_t* o = reinterpret_cast<uint16_t*>(&o4);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float pred = ew_to_f<FP16>(u[k]);
+      if (cond != nullptr) {
+        const float d = ew_to_f<FP16>(ew_from_f<FP16>(ew_to_f<FP16>(c[k]) - pred));
+        const float m = ew_to_f<FP16>(ew_from_f<FP16>(guidance * d));
+        pred = ew_to_f<FP16>(ew_from_f<FP16>(pred + m));
+      }
+      o[k] = ew_from_f<FP16>(__fadd_rn(ew_to_f<FP16>(sm[k]), __fmul_rn(dt, pred)));
+    }
+    reinterpret_cast<uint4*>(out)[i] = o4;
+    if (out2 != nullptr) reinterpret_cast<uint4*>(out2)[i] = o4;
+  }
+}
+
+}  // namespace
+}  // namespace hdit
+
+extern "C" int hdit_cfg_euler_step(int32_t dtype, const void* uncond, const void* cond, const void* sample, void* out,
+                                   void* out_peer, int64_t n_elems, float guidance_scale, const float* sigmas,
+                                   int32_t step_index, void* stream) {
+  using namespace hdit;
+  if (dtype != HDIT_BF16 && dtype != HDIT_FP16) return set_error(HDIT_ERR_BAD_ARG, "dtype must be bf16 or fp16");
+  if (uncond == nullptr || sample == nullptr || out == nullptr || sigmas == nullptr || n_elems < 0 || step_index < 0)
+    return set_error(HDIT_ERR_BAD_ARG, "null pointer or negative size");
+  if (n_elems == 0) return HDIT_OK;
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(uncond) | reinterpret_cast<uintptr_t>(cond) |
+                         reinterpret_cast<uintptr_t>(sample) | reinterpret_cast<uintptr_t>(out) |
+                         reinterpret_cast<uintptr_t>(out_peer);
+  if ((bits & 15) != 0 || n_elems % 8 != 0)
+    return set_error(HDIT_ERR_SHAPE, "pointers must be 16-byte aligned and n_elems a multiple of 8");
+  const long long n_vec = n_elems / 8;
+  long long blocks = (n_vec + 255) / 256;
+  if (blocks > 148LL * 8) blocks = 148LL * 8;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == HDIT_FP16)
+    cfg_euler_step_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const uint16_t*>(uncond), static_cast<const uint16_t*>(cond), static_cast<const uint16_t*>(sample),
+        static_cast<uint16_t*>(out), static_cast<uint16_t*>(out_peer), n_vec, guidance_scale, sigmas, step_index);
+  else
+    cfg_euler_step_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const uint16_t*>(uncond), static_cast<const uint16_t*>(cond), static_cast<const uint16_t*>(sample),
+        static_cast<uint16_t*>(out), static_cast<uint16_t*>(out_peer), n_vec, guidance_scale, sigmas, step_index);
+  HDIT_CUDA_OK(cudaGetLastError());
+  return HDIT_OK;
+}
+
 extern "C" int hdit_ln_modulate(int32_t dtype, const void* x, const void* shift, const void* scale, void* out,
                                 int64_t rows, int64_t dim, int64_t rows_per_batch, int64_t x_row_stride,
                                 int64_t out_row_stride, int64_t mod_batch_stride, float eps, void* stream) {

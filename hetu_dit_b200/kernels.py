@@ -431,3 +431,29 @@ def gelu_tanh(x, out=None):
                                          _stream_ptr(x.device)))
     _count()
     return out
+
+
+def cfg_euler_step(noise_pred, sample, sigmas, step_index, guidance_scale, cfg=True, out=None, out_peer_ptr=None):
+    """sample + (sigmas[i + 1] - sigmas[i]) * guided(noise_pred) in one pass. noise_pred is (2 * B, ...) =
+    [unconditional; conditional] when cfg is set (guided = uncond + scale * (cond - uncond)), else (B, ...) taken as
+    it is; sample and the result are (B, ...), contiguous, 16-bit. sigmas: fp32 device tensor. out_peer_ptr: raw
+    device address (e.g. the next pipeline stage's inbox slot) that receives a second copy of the result."""
+    _require_cuda(sample)
+    if not (noise_pred.is_contiguous() and sample.is_contiguous()):
+        raise ValueError("noise_pred and sample must be contiguous")
+    n = sample.numel()
+    if noise_pred.numel() != (2 * n if cfg else n):
+        raise ValueError("noise_pred does not match sample")
+    if sigmas.dtype != torch.float32 or not sigmas.is_cuda or not 0 <= step_index < sigmas.numel() - 1:
+        raise ValueError("sigmas must be a float32 device tensor with step_index + 1 in range")
+    if out is None:
+        out = torch.empty_like(sample)
+    es = noise_pred.element_size()
+    uncond = noise_pred.data_ptr()
+    cond = uncond + n * es if cfg else None
+    with torch.cuda.device(sample.device):
+        _C.check(_C.lib().hdit_cfg_euler_step(_DTYPE_CODE[sample.dtype], uncond, cond, sample.data_ptr(), out.data_ptr(),
+                                              out_peer_ptr, n, float(guidance_scale), sigmas.data_ptr(), int(step_index),
+                                              _stream_ptr(sample.device)))
+    _count()
+    return out

@@ -87,5 +87,7 @@ class FluxShapedPipeline(SD3ShapedPipeline):
             hidden_states = m.proj_out(kernels.ln_modulate(hidden_states.contiguous(), shift, scale))
         return hidden_states, encoder_hidden_states
 
-    def _backbone_forward(self, latents, encoder_hidden_states, pooled, t):
+    cfg_batch = False  # guidance-distilled: one batch element, the guidance scale is an embedding
+
+    def _backbone_forward(self, latents, encoder_hidden_states, pooled, t, guide: bool = True):
         return self._stage(latents, encoder_hidden_states, pooled, t.expand(latents.shape[0]).contiguous())

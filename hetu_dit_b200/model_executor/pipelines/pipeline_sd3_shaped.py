@@ -20,6 +20,7 @@ from typing import List, Optional, Tuple
 import torch
 import torch.nn.functional as F
 
+from ... import kernels
 from ...core.distributed import parallel_state as ps
 from ...core.distributed.runtime_state import get_runtime_state
 from ..models.shaped_dit import ShapedDiT, _modulate, timestep_embedding
@@ -59,6 +60,8 @@ class SD3ShapedPipeline:
         # and patched steps run eagerly: their hand-offs and stale-KV updates depend on per-patch host state.
         self.use_cuda_graph = True
         self._graphs = None
+        # guidance + scheduler step (+ wrap-around send) of the last stage as one kernel; False = the eager chain
+        self.fused_step = True
 
     def _stage(self, hidden_states, encoder_hidden_states, pooled, timestep):
         """_transformer(), through a captured CUDA graph when the step qualifies (see use_cuda_graph)."""
@@ -139,17 +142,45 @@ class SD3ShapedPipeline:
         return torch.cat([part[:, starts[p]:starts[p + 1]] for p in range(rt.num_pipeline_patch) for part in parts],
                          dim=1)
 
-    def _backbone_forward(self, latents, encoder_hidden_states, pooled, t):
+    cfg_batch = True  # unconditional + conditional halves go through the backbone as one batch of two
+
+    def _backbone_forward(self, latents, encoder_hidden_states, pooled, t, guide: bool = True):
+        """guide=False leaves the last stage's prediction as the two-batch (uncond, cond) tensor: the caller fuses
+        the guidance into the scheduler step (_guided_step)."""
         if ps.is_pipeline_first_stage():
             latents = torch.cat([latents] * 2)  # unconditional + conditional through one batch
         timestep = t.expand(latents.shape[0]).contiguous()
         noise_pred, encoder_hidden_states = self._stage(latents, encoder_hidden_states, pooled, timestep)
-        if ps.is_pipeline_last_stage():
+        if ps.is_pipeline_last_stage() and guide:
             uncond, text = noise_pred.chunk(2)
             latents = uncond + self.guidance_scale * (text - uncond)
         else:
             latents = noise_pred
         return latents, encoder_hidden_states
+
+    def _guided_step(self, noise_pred, last_latents, i, send_as=None):
+        """Last stage: classifier-free guidance + scheduler step of one (patch of the) latents in a single kernel
+        (csrc/elementwise.cu), which also stores the result into the first stage's inbox when `send_as` =
+        (name, segment index) names the wrap-around message -- the eager chain and the separate send copy of
+        the reference (pipeline_stable_diffusion_3.py:1585-1631, 1703-1713) become one launch plus a flag."""
+        if not (self.fused_step and noise_pred.is_cuda and noise_pred.is_contiguous() and last_latents.is_contiguous()
+                and last_latents.numel() % 8 == 0):
+            if self.cfg_batch:
+                uncond, text = noise_pred.chunk(2)
+                noise_pred = uncond + self.guidance_scale * (text - uncond)
+            out = self._scheduler_step(noise_pred, last_latents, i)
+            if send_as is not None:
+                ps.get_pp_group().pipeline_isend(out, name=send_as[0], segment_idx=send_as[1])
+            return out
+        peer = None
+        pp = ps.get_pp_group() if send_as is not None else None
+        if pp is not None:
+            peer = pp.reserve_send(last_latents, send_as[0], send_as[1])
+        out = kernels.cfg_euler_step(noise_pred, last_latents, self.sigmas, i, self.guidance_scale, cfg=self.cfg_batch,
+                                     out_peer_ptr=peer)
+        if pp is not None:
+            pp.commit_send()
+        return out
 
     def _scheduler_step(self, noise_pred, last_latents, i):
         """Flow-matching Euler step in fp32; the step index is the caller's, so it advances once per
@@ -176,15 +207,13 @@ class SD3ShapedPipeline:
                 if not first:
                     encoder_hidden_states = pp.pipeline_recv(0, "encoder_hidden_states")
             latents, encoder_hidden_states = self._backbone_forward(
-                latents, prompt_embeds if first else encoder_hidden_states, pooled, self.sigmas[i:i + 1])
+                latents, prompt_embeds if first else encoder_hidden_states, pooled, self.sigmas[i:i + 1], guide=not last)
+            sends = pp_world > 1 and not (sync_only and last and k == len(steps) - 1)
             if last:
-                latents = self._scheduler_step(latents, last_timestep_latents, i)
-            if sync_only and last and k == len(steps) - 1:
-                pass
-            elif pp_world > 1:
+                latents = self._guided_step(latents, last_timestep_latents, i, ("latent", -1) if sends else None)
+            elif sends:
                 pp.pipeline_send(latents)
-                if not last:
-                    pp.pipeline_send(encoder_hidden_states, name="encoder_hidden_states")
+                pp.pipeline_send(encoder_hidden_states, name="encoder_hidden_states")
         return latents
 
     # ------------------------------------------------------------------ patch pipeline
@@ -245,11 +274,11 @@ class SD3ShapedPipeline:
                     patch_latents[p] = pp.get_pipeline_recv_data(idx=p)
                 patch_latents[p], next_encoder_hidden_states = self._backbone_forward(
                     patch_latents[p], prompt_embeds if first else last_encoder_hidden_states, pooled,
-                    self.sigmas[i:i + 1])
+                    self.sigmas[i:i + 1], guide=not last)
                 if last:
-                    patch_latents[p] = self._scheduler_step(patch_latents[p], last_patch_latents[p], i)
-                    if pp_world > 1 and k != len(steps) - 1:
-                        pp.pipeline_isend(patch_latents[p], segment_idx=p)
+                    sends = pp_world > 1 and k != len(steps) - 1
+                    patch_latents[p] = self._guided_step(patch_latents[p], last_patch_latents[p].contiguous(), i,
+                                                         ("latent", p) if sends else None)
                 elif pp_world > 1:
                     if p == 0:
                         pp.pipeline_isend(next_encoder_hidden_states, name="encoder_hidden_states")

@@ -359,6 +359,23 @@ HDIT_API int hdit_gate_residual(int32_t dtype, const void* x, const void* gate, 
 HDIT_API int hdit_gelu_tanh(int32_t dtype, const void* x, void* out, int64_t rows, int64_t dim, int64_t x_row_stride,
                             int64_t out_row_stride, void* stream);
 
+/*
+ * Classifier-free guidance and the flow-matching Euler step of one latent patch, fused:
+ *   pred = uncond + guidance_scale * (cond - uncond)        (16-bit arithmetic, one rounding per operation)
+ *   out  = sample + (sigmas[step_index + 1] - sigmas[step_index]) * pred    (fp32, rounded once)
+ * cond == NULL skips the guidance (uncond is the prediction). `sigmas` is a device array, so the call does not
+ * depend on host state and can be replayed from a CUDA graph with the step index baked in. out_peer (optional) gets
+ * the same result: with the next pipeline stage's inbox slot as out_peer this is also the wrap-around send of the
+ * new latent patch. All pointers 16-byte aligned, n_elems a multiple of 8.
+ *
+ * Replaces, in the reference, the eager chain of pipeline_stable_diffusion_3.py:1703-1713 (chunk, sub, mul, add)
+ * and schedulers/scheduling_flow_match_euler_discrete.py:22-129 (upcast, mul, add, downcast) that runs per patch on
+ * the last pipeline stage (:1585-1611), plus the isend of the result (:1625-1631).
+ */
+HDIT_API int hdit_cfg_euler_step(int32_t dtype, const void* uncond, const void* cond, const void* sample, void* out,
+                                 void* out_peer, int64_t n_elems, float guidance_scale, const float* sigmas,
+                                 int32_t step_index, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -290,8 +290,9 @@ def test_oracle_flux_pipefusion_is_consistent_with_the_plain_step():
 
 def test_kv_split_choice_follows_the_wave_model():
     """The wrapper's split-KV choice is pure host arithmetic: split when the grid leaves most SMs idle or
-    spills a little over a wave, never for grids that fill the GPU or for short KV ranges."""
-    from hetu_dit_b200.kernels import _pick_kv_split
+    spills a little over a wave, never for grids that fill the GPU or for short KV ranges -- and not where the
+    library's own interleaved mode (one query tile per CTA, no merge pass) is cheaper still."""
+    from hetu_dit_b200.kernels import _interleave_cost, _pick_kv_split
 
     class T:
         def __init__(self, s, d):
@@ -300,14 +301,25 @@ def test_kv_split_choice_follows_the_wave_model():
     def pick(batch, heads, d, s):
         return _pick_kv_split([T(s, d)], [T(s, d)], batch, heads)
 
-    assert pick(1, 3, 128, 4608) == 2       # Ulysses 8 of 24 heads: 54 CTAs on 148 SMs
-    assert pick(1, 6, 128, 4608) == 1       # 108 CTAs: two half-length waves cost what one wave costs
-    assert pick(1, 24, 128, 4608) == 1      # the single-GPU grid
-    assert pick(1, 3, 128, 17776) == 2      # 210 CTAs = 1.4 waves -> 3 half-length waves
+    def pick_no_il(batch, heads, d, s):
+        return _pick_kv_split([T(s, d)], [T(s, d)], batch, heads, kv_interleave=1)
+
+    # with the interleaved mode forbidden: the split-KV wave model alone
+    assert pick_no_il(1, 3, 128, 4608) == 2     # Ulysses 8 of 24 heads: 54 CTAs on 148 SMs
+    assert pick_no_il(1, 6, 128, 4608) == 1     # 108 CTAs: two half-length waves cost what one wave costs
+    assert pick_no_il(1, 24, 128, 4608) == 1    # the single-GPU grid
+    assert pick_no_il(1, 3, 128, 17776) == 2    # 210 CTAs = 1.4 waves -> 3 half-length waves
+    assert pick_no_il(1, 6, 128, 17776) == 1
+    assert pick_no_il(2, 3, 128, 377) == 1      # 3 KV blocks: nothing to split
+    assert _pick_kv_split([T(512, 128), T(4096, 128)], [T(4608, 128)], 1, 3, kv_interleave=1) == 2
+    # left to the library: 54 CTAs become 108 interleaved ones (measured 48 us against 59 us for the split)
+    assert pick(1, 3, 128, 4608) == 1
+    assert pick(1, 24, 128, 4608) == 1
     assert pick(1, 6, 128, 17776) == 1
-    assert pick(2, 3, 128, 377) == 1        # 3 KV blocks: nothing to split
-    # two query segments count their tiles separately, like the kernel's grid does
-    assert _pick_kv_split([T(512, 128), T(4096, 128)], [T(4608, 128)], 1, 3) == 2
+    # the interleaved cost model in wave units: 12 heads (216 pairs = 2 waves) pay off, 6 and 24 heads do not
+    paired = lambda heads, blocks=36: -(-18 * heads // 148) * (blocks + 6.0)
+    assert _interleave_cost(36, 36, 1, 12) < paired(12) and _interleave_cost(36, 36, 1, 3) < paired(3)
+    assert _interleave_cost(36, 36, 1, 6) > paired(6) and _interleave_cost(36, 36, 1, 24) > paired(24)
 
 
 @pytest.mark.parametrize("sp,n_patch,height", [(2, 4, 64), (4, 2, 64), (2, 3, 48), (1, 4, 64)])
