@@ -69,6 +69,11 @@ class AttnArgs(ctypes.Structure):
         ("out_dst", ctypes.c_void_p * 8),
         ("q_rows_per_dst", ctypes.c_int64 * HDIT_MAX_Q_SEG),
         ("q_dst_row0", ctypes.c_int64 * HDIT_MAX_Q_SEG),
+        ("n_wait", ctypes.c_int32),
+        ("reserved1", ctypes.c_int32),
+        ("wait_slots", ctypes.c_void_p * 8),
+        ("wait_epoch", ctypes.c_void_p),
+        ("wait_spins", ctypes.c_int64),
     ]
 
 
@@ -121,6 +126,17 @@ class NormRopeArgs(ctypes.Structure):
         ("rope_row0", ctypes.c_int64),
         ("t", NormRopeTensor * 3),
         ("stream", ctypes.c_void_p),
+        ("range2_start", ctypes.c_int64),
+        ("range2_norm_weight", ctypes.c_void_p * 3),
+        ("range2_norm_bias", ctypes.c_void_p * 3),
+        ("range2_do_rope", ctypes.c_int32 * 3),
+        ("reserved0", ctypes.c_int32),
+        ("range2_rope_row0", ctypes.c_int64),
+        ("n_signal", ctypes.c_int32),
+        ("signal_me", ctypes.c_int32),
+        ("signal_slots", ctypes.c_void_p * 8),
+        ("epoch_counter", ctypes.c_void_p),
+        ("ticket", ctypes.c_void_p),
     ]
 
 

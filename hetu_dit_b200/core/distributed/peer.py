@@ -22,6 +22,9 @@ _P2P_BASE = _BARRIER_SLOTS      # then 8 x 8 x 16 point-to-point sequence counte
 _EPOCH_BASE = _P2P_BASE + 8 * 8 * 16  # then one barrier epoch counter per rank subset (device-side)
 _P2P_SENT_BASE = _EPOCH_BASE + 256    # then, per link and channel, how many messages this rank has signalled ...
 _P2P_EXPECT_BASE = _P2P_SENT_BASE + 8 * 8 * 16  # ... and how many it has waited for (device-side, graph-replayable)
+_FOLD_BASE = _P2P_EXPECT_BASE + 8 * 8 * 16  # then, per rank subset, 8 arrival flags of the folded exchange barrier,
+_FOLD_EPOCH_BASE = _FOLD_BASE + _BARRIER_SLOTS  # its epoch counter (device-side) ...
+_FOLD_TICKET_BASE = _FOLD_EPOCH_BASE + 256      # ... and the ticket word of the signalling kernel
 DEFAULT_MAX_SPINS = 20_000_000  # about two seconds of polling
 
 
@@ -142,6 +145,27 @@ class PeerHeap:
         with torch.cuda.device(self.device):
             stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
             _C.check(_C.lib().hdit_peer_barrier(peer_slots, my_slots, n, me, 0, counter, max_spins, stream))
+
+    def folded_barrier(self, ranks: Sequence[int]):
+        """(FlagSignal, FlagWait) of a barrier whose signalling half runs in the tail of a producer kernel and
+        whose waiting half runs in the head of the consumer kernel (both of this library): the producer's last
+        CTA bumps this rank's flag in every peer's heap, the consumer polls the flags the peers bump here. Only
+        "the producers' stores are visible to the consumer" is guaranteed -- unlike barrier(), it does not hold
+        this rank back until the peers have arrived."""
+        from ... import kernels
+        ranks = list(ranks)
+        me = ranks.index(self.rank)
+        mask = 0
+        for r in ranks:
+            mask |= 1 << (r % MAX_RANKS_PER_NODE)
+        row = _FOLD_BASE + mask * MAX_RANKS_PER_NODE
+        epoch = self._flag_ptr(self.rank, _FOLD_EPOCH_BASE + mask)
+        ticket = self._flag_ptr(self.rank, _FOLD_TICKET_BASE + mask)
+        sig = kernels.FlagSignal([None if i == me else self._flag_ptr(r, row + me) for i, r in enumerate(ranks)], me,
+                                 epoch, ticket)
+        wait = kernels.FlagWait([None if i == me else self._flag_ptr(self.rank, row + i) for i in range(len(ranks))],
+                                epoch, self.max_spins)
+        return sig, wait
 
     def p2p_flag_index(self, src: int, dst: int, channel: int) -> int:
         return _P2P_BASE + ((src % 8) * 8 + (dst % 8)) * 16 + channel

@@ -58,13 +58,19 @@ class _UlyssesExchange:
         g.barrier()
         return outs
 
-    def gather_heads_fused(self, query, key, value, prologue):
+    def gather_heads_fused(self, query, key, value, prologue, fold_barrier: bool = False):
         """gather_heads for Q, K and V with the per-head RMSNorm and the rotary embedding of Q and K applied on
         the way: the kernel that normalises and rotates a row stores each head slice straight into the peer
         that attends it, so the projections' output is read once and nothing is written locally.
 
         prologue: [(row_lo, row_hi, q_norm_weight, k_norm_weight, eps, (cos, sin) or None, rope_row0)], row
-        ranges that tile [0, S_loc) -- one launch per range (ranges differ in norm weights or rotary rows)."""
+        ranges that tile [0, S_loc). One or two ranges (text rows and image rows differ in norm weights and rotary
+        rows) go out in ONE launch; more than two fall back to one launch per range.
+
+        fold_barrier: instead of the flag barrier kernel after the exchange, the exchange kernel's last CTA
+        signals the peers and the consumer (the attention kernel's loader) waits for the peers' signals: returns
+        (q, k, v, FlagWait) -- the caller must hand the FlagWait to the attention call that reads q, k, v, and
+        nothing else may read them before."""
         g, U, me = self.group, self.group.world_size, self.group.rank_in_group
         B, S, H, D = query.shape
         if H % U != 0:
@@ -80,15 +86,36 @@ class _UlyssesExchange:
             buf, off = self.heap.alloc((B, U * S, H // U, D), t.dtype, name=f"usp_{tag}_{(B, S, H, D)}_{t.dtype}")
             outs.append(buf)
             dsts.append(kernels.RawDst([self.heap.peer_ptr(r, off) for r in g.ranks], buf.stride()[:3]))
-        for lo, hi, wq, wk, eps, rope, row0 in prologue:
-            if hi <= lo:
-                continue
-            cos, sin = rope if rope is not None else (None, None)
-            kernels.qk_norm_rope([(query[:, lo:hi], wq, wq is not None, rope is not None),
-                                  (key[:, lo:hi], wk, wk is not None, rope is not None),
-                                  (value[:, lo:hi], None, False, False)],
+        signal = wait = None
+        if fold_barrier:
+            signal, wait = self.heap.folded_barrier(g.ranks)
+        ranges = [r for r in prologue if r[1] > r[0]]
+        same = len(ranges) == 2 and ranges[0][4] == ranges[1][4] and \
+            (ranges[0][5] is None or ranges[1][5] is None or ranges[0][5][0] is ranges[1][5][0]) and \
+            (ranges[0][2] is None) == (ranges[1][2] is None)
+        if len(ranges) == 1 or same:
+            lo, hi, wq, wk, eps, rope, row0 = ranges[0]
+            table = rope if rope is not None else (ranges[1][5] if same else None)
+            cos, sin = table if table is not None else (None, None)
+            range2 = None
+            if same:
+                lo2, _, wq2, wk2, _, rope2, row0_2 = ranges[1]
+                range2 = (lo2, [(wq2, rope2 is not None), (wk2, rope2 is not None), (None, False)], row0_2)
+            kernels.qk_norm_rope([(query, wq, wq is not None, rope is not None),
+                                  (key, wk, wk is not None, rope is not None),
+                                  (value, None, False, False)],
                                  eps=eps, cos=cos, sin=sin, rope_seq_start=0, rope_row0=row0, dsts=dsts,
-                                 dst_seq_offset=me * S + lo)
+                                 dst_seq_offset=me * S, range2=range2, signal=signal)
+        else:
+            for i, (lo, hi, wq, wk, eps, rope, row0) in enumerate(ranges):
+                cos, sin = rope if rope is not None else (None, None)
+                kernels.qk_norm_rope([(query[:, lo:hi], wq, wq is not None, rope is not None),
+                                      (key[:, lo:hi], wk, wk is not None, rope is not None),
+                                      (value[:, lo:hi], None, False, False)],
+                                     eps=eps, cos=cos, sin=sin, rope_seq_start=0, rope_row0=row0, dsts=dsts,
+                                     dst_seq_offset=me * S + lo, signal=signal if i == len(ranges) - 1 else None)
+        if fold_barrier:
+            return outs + [wait]
         g.barrier()
         return outs
 
@@ -179,12 +206,20 @@ class hetuDiTLongContextAttention(torch.nn.Module):
         self.ring_pg = ps.PROCESS_GROUP.RING_PG
         self.ulysses_pg = ps.PROCESS_GROUP.ULYSSES_PG
 
+    def _kv_hook_runs(self, attn) -> bool:
+        """Whether the stale-KV update will launch work on the gathered K / V before attention does."""
+        if attn is None or not self.use_kv_cache:
+            return False
+        from ...distributed.runtime_state import get_runtime_state, runtime_state_is_initialized
+        return runtime_state_is_initialized() and get_runtime_state().num_pipeline_patch > 1
+
     def _run(self, attn, query, key, value, joint_k, joint_v, joint_strategy, dropout_p, softmax_scale, causal,
              window_size, alibi_slopes, deterministic, return_attn_probs, joint_q=None, qk_prologue=None):
         """joint_q stays its own query segment. The reference concatenates it into every rank's query before
         the all-to-all, so each Ulysses rank attends U identical copies of the text queries; here the
         replicated rows are attended once per head slice and their context rows are sent to all peers."""
         U = 1 if self.ulysses_pg is None else self.ulysses_pg.world_size
+        wait_flags = None
         if U > 1:
             r = self.ulysses_pg.rank_in_group
             if joint_k is not None:
@@ -195,7 +230,12 @@ class hetuDiTLongContextAttention(torch.nn.Module):
                     joint_q = joint_q[..., hpr * r:hpr * (r + 1), :]
             xchg = _UlyssesExchange(self.ulysses_pg)
             if qk_prologue is not None:
-                query, key, value = xchg.gather_heads_fused(query, key, value, qk_prologue)
+                # The barrier after the exchange folds into the kernels on either side of it when attention is
+                # the first (and only) reader of the gathered tensors: no ring pull and no stale-KV update.
+                fold = (self.ring_pg is None or self.ring_pg.world_size == 1) and not self._kv_hook_runs(attn)
+                res = xchg.gather_heads_fused(query, key, value, qk_prologue, fold_barrier=fold)
+                query, key, value = res[:3]
+                wait_flags = res[3] if fold else None
             else:
                 query, key, value = xchg.gather_heads([query, key, value], ["q", "k", "v"])
         elif qk_prologue is not None:
@@ -218,7 +258,7 @@ class hetuDiTLongContextAttention(torch.nn.Module):
                                 return_attn_probs=return_attn_probs, group=self.ring_pg,
                                 attn_layer=attn if self.use_kv_cache else None, joint_tensor_key=joint_k,
                                 joint_tensor_value=joint_v, joint_strategy=joint_strategy, joint_tensor_query=joint_q,
-                                out_scatter=scatter)
+                                out_scatter=scatter, wait_flags=wait_flags)
         if U > 1:
             xchg.finish()
             return out_buf

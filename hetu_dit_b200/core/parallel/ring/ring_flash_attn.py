@@ -52,7 +52,7 @@ def _publish(heap, t: torch.Tensor, tag: str) -> torch.Tensor:
 def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                             softmax_scale, dropout_p=0, causal=True, window_size=(-1, -1), alibi_slopes=None,
                             deterministic=False, attn_layer=None, joint_tensor_key=None, joint_tensor_value=None,
-                            joint_strategy="none", joint_tensor_query=None, out_scatter=None):
+                            joint_strategy="none", joint_tensor_query=None, out_scatter=None, wait_flags=None):
     """(out in q.dtype, lse (B, H, Sq) fp32) for this rank's queries against the whole ring's K/V.
 
     joint_tensor_query (not in the reference's signature): joint queries kept as their own segment
@@ -61,7 +61,10 @@ def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor,
 
     out_scatter (not in the reference's signature): dict(dsts=RawDst, q=(rows per destination, first row),
     joint=(...)) -- the launch that produces the final result stores its rows into these destination buffers
-    (the Ulysses reverse all-to-all from the attention epilogue) and `out` is returned as None."""
+    (the Ulysses reverse all-to-all from the attention epilogue) and `out` is returned as None.
+
+    wait_flags (a kernels.FlagWait, ring of one only): the attention kernel waits for these peer flags before it
+    loads q, k, v (the barrier after the Ulysses head exchange, folded into the consumer)."""
     if joint_strategy not in _SUPPORTED_JOINT:
         raise ValueError(
             f"joint_strategy: {joint_strategy} not supprted. supported joint strategy: {_SUPPORTED_JOINT}")
@@ -92,8 +95,11 @@ def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor,
             ks, vs = [k, joint_tensor_key], [v, joint_tensor_value]
         elif joint_strategy == "front":
             ks, vs = [joint_tensor_key, k], [joint_tensor_value, v]
-        res = kernels.attn_fwd(q_segs, ks, vs, softmax_scale=softmax_scale, return_lse=True, **scatter_kw)
+        res = kernels.attn_fwd(q_segs, ks, vs, softmax_scale=softmax_scale, return_lse=True, wait_flags=wait_flags,
+                               **scatter_kw)
         return (None, res) if out_scatter is not None else res
+    if wait_flags is not None:
+        raise ValueError("wait_flags need a ring of one: the ring pull reads K / V before attention does")
 
     heap = process_group.heap
     if heap is None:
@@ -149,7 +155,7 @@ def ring_flash_attn_forward(process_group: Optional[PeerGroup], q: torch.Tensor,
 def ring_flash_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
                          alibi_slopes=None, deterministic=False, return_attn_probs=False, group=None, attn_layer=None,
                          joint_tensor_key=None, joint_tensor_value=None, joint_strategy="none", joint_tensor_query=None,
-                         out_scatter=None):
+                         out_scatter=None, wait_flags=None):
     """Forward only (inference): returns out, or (out, lse, None) when return_attn_probs is set."""
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** (-0.5)
@@ -158,5 +164,6 @@ def ring_flash_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=Fals
                                        window_size=window_size, alibi_slopes=alibi_slopes, deterministic=False,
                                        attn_layer=attn_layer, joint_tensor_key=joint_tensor_key,
                                        joint_tensor_value=joint_tensor_value, joint_strategy=joint_strategy,
-                                       joint_tensor_query=joint_tensor_query, out_scatter=out_scatter)
+                                       joint_tensor_query=joint_tensor_query, out_scatter=out_scatter,
+                                       wait_flags=wait_flags)
     return out if not return_attn_probs else (out, lse, None)

@@ -92,6 +92,7 @@ enum Where : int {
   W_MMA_PREADY = 6,
   W_SM_SFULL = 7,
   W_SM_ODONE = 8,
+  W_PEER_FLAGS = 9,
 };
 
 struct alignas(64) AttnKernelParams {
@@ -128,6 +129,11 @@ struct alignas(64) AttnKernelParams {
   void* dst[8];
   long long seg_rows_per_dst[HDIT_MAX_Q_SEG];  // 0 = rows of the segment go to every destination
   long long seg_dst_row0[HDIT_MAX_Q_SEG];
+  // peers' arrival flags to wait for before the first load (n_wait == 0: none)
+  int n_wait;
+  const int32_t* wait_slot[8];
+  const int32_t* wait_epoch;
+  unsigned wait_spins;
 };
 
 // Tuning switches (compile-time so that variants can be measured against each other). The defaults are what
@@ -338,7 +344,30 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (warp == 8) {
       // =========================== TMA producer ===========================
-      if (lane == 0) {
+      bool inputs_ready = true;
+      if (p.n_wait > 0) {
+        // Q, K and V were stored into this rank's buffers by its Ulysses peers: wait (bounded) until each of them
+        // has published the epoch this rank's own exchange kernel advanced to, one lane per peer. The loads below
+        // go through the async proxy, hence the proxy fence after the acquire.
+        const int32_t epoch = *p.wait_epoch;
+        bool seen = true;
+        if (lane < p.n_wait && p.wait_slot[lane] != nullptr) {
+          seen = false;
+          for (unsigned i = 0; i < p.wait_spins; ++i) {
+            int32_t v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p.wait_slot[lane]) : "memory");
+            if (v - epoch >= 0) {
+              seen = true;
+              break;
+            }
+            __nanosleep(32);
+          }
+          if (!seen) report_failure(p.status, abort_flag, HDIT_ERR_PEER_TIMEOUT, W_PEER_FLAGS, lane);
+        }
+        inputs_ready = __all_sync(0xffffffffu, seen);
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
+      if (lane == 0 && inputs_ready) {
         for (int s = 0; s < p.n_q_seg; ++s) tma_prefetch_desc(&p.q_map[s]);
         for (int s = 0; s < p.n_kv_seg; ++s) {
           tma_prefetch_desc(&p.k_map[s]);
@@ -1231,6 +1260,16 @@ int attn_fwd_impl(const hdit_attn_args* a, int n_split, float* split_out, float*
     kp.n_dst = sc.n_dst = a->n_out_dst;
     sc.q_len0 = kp.q_len[0];
     for (int i = 0; i < a->n_out_dst; ++i) kp.dst[i] = sc.dst[i] = a->out_dst[i];
+  }
+
+  if (a->n_wait < 0 || a->n_wait > 8) return set_error(HDIT_ERR_BAD_ARG, "n_wait must be 0..8");
+  if (a->n_wait > 0) {
+    if (a->wait_epoch == nullptr) return set_error(HDIT_ERR_BAD_ARG, "wait_epoch is null");
+    kp.n_wait = a->n_wait;
+    for (int i = 0; i < a->n_wait; ++i) kp.wait_slot[i] = a->wait_slots[i];
+    kp.wait_epoch = a->wait_epoch;
+    const long long spins = a->wait_spins > 0 ? a->wait_spins : 20000000LL;
+    kp.wait_spins = static_cast<unsigned>(spins > 0xffffffffLL ? 0xffffffffLL : spins);
   }
 
   // Interleaved mode (one Q tile per CTA, its two halves on the even and odd KV blocks): taken when it cuts

@@ -47,7 +47,23 @@ struct NormRopeParams {
   const float* sin_tab;
   long long rope_seq_start;  // tokens below this index are not rotated
   long long rope_row0;       // table row of token rope_seq_start
+  // second row range: tokens >= range2_start take these norm weights / rotary rows instead (seq = none)
+  long long range2_start;
+  const void* weight2[kMaxTensors];
+  const void* bias2[kMaxTensors];
+  int do_rope2[kMaxTensors];
+  long long rope_row0_2;
+  // after the last CTA: publish the next epoch to the peers' flag slots (0 = no signal)
+  int n_signal;
+  int signal_me;
+  int32_t* signal_slot[kMaxDst];
+  int32_t* epoch_counter;
+  unsigned int* ticket;
 };
+
+__device__ __forceinline__ void nr_st_release_sys(int32_t* p, int32_t v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 template <bool FP16>
 __device__ __forceinline__ float to_f(uint16_t v) {
@@ -77,10 +93,14 @@ __global__ void __launch_bounds__(512) norm_rope_kernel(const __grid_constant__ 
   for (long long tok = blockIdx.x; tok < n_tok; tok += gridDim.x) {
     const int b = static_cast<int>(tok / p.seq);
     const int s = static_cast<int>(tok - static_cast<long long>(b) * p.seq);
-    const bool rotate = t.do_rope && s >= p.rope_seq_start;
+    const bool r2 = s >= p.range2_start;
+    const bool rotate = r2 ? (p.do_rope2[blockIdx.y] != 0) : (t.do_rope && s >= p.rope_seq_start);
+    const void* const weight = r2 ? p.weight2[blockIdx.y] : t.weight;
+    const void* const bias = r2 ? p.bias2[blockIdx.y] : t.bias;
     float cs[8], sn[8];
     if (rotate) {
-      const long long trow = (s - p.rope_seq_start + p.rope_row0) * D + part * 8;
+      const long long trow = (r2 ? (s - p.range2_start + p.rope_row0_2) : (s - p.rope_seq_start + p.rope_row0)) * D +
+                             part * 8;
       const float4 c0 = *reinterpret_cast<const float4*>(p.cos_tab + trow);
       const float4 c1 = *reinterpret_cast<const float4*>(p.cos_tab + trow + 4);
       const float4 s0 = *reinterpret_cast<const float4*>(p.sin_tab + trow);
@@ -124,14 +144,14 @@ __global__ void __launch_bounds__(512) norm_rope_kernel(const __grid_constant__ 
         float w[8], bb[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) w[i] = 1.f, bb[i] = 0.f;
-        if (t.weight != nullptr) {
-          const uint4 wraw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(t.weight) + part * 8);
+        if (weight != nullptr) {
+          const uint4 wraw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(weight) + part * 8);
           const uint16_t* wp = reinterpret_cast<const uint16_t*>(&wraw);
 #pragma unroll
           for (int i = 0; i < 8; ++i) w[i] = to_f<FP16>(wp[i]);
         }
-        if (t.bias != nullptr) {
-          const uint4 braw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(t.bias) + part * 8);
+        if (bias != nullptr) {
+          const uint4 braw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(bias) + part * 8);
           const uint16_t* bp = reinterpret_cast<const uint16_t*>(&braw);
 #pragma unroll
           for (int i = 0; i < 8; ++i) bb[i] = to_f<FP16>(bp[i]);
@@ -145,8 +165,8 @@ __global__ void __launch_bounds__(512) norm_rope_kernel(const __grid_constant__ 
 #pragma unroll
         for (int off = TPR / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
         const float rstd = rsqrtf(ss * (1.0f / D) + p.eps);
-        if (t.weight != nullptr) {
-          const uint4 wraw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(t.weight) + part * 8);
+        if (weight != nullptr) {
+          const uint4 wraw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(weight) + part * 8);
           const uint16_t* w = reinterpret_cast<const uint16_t*>(&wraw);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -176,6 +196,33 @@ __global__ void __launch_bounds__(512) norm_rope_kernel(const __grid_constant__ 
         uint16_t* dst = static_cast<uint16_t*>(t.dst[d_idx]) + b * t.ds_b + (s + t.dst_seq_offset) * t.ds_s +
                         hh * t.ds_h + part * 8;
         *reinterpret_cast<uint4*>(dst) = outv;
+      }
+    }
+  }
+  if (p.n_signal > 0) {
+    // The CTA that finishes last tells every peer that this rank's rows have landed in its buffers: the epoch
+    // lives in device memory (a replayed CUDA graph advances it by itself), the ticket goes back to zero for
+    // the next launch. Writes of the other threads are ordered before the ticket by the barrier + fence.
+    __shared__ unsigned int last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const unsigned int total = gridDim.x * gridDim.y;
+      last = (atomicAdd(p.ticket, 1u) == total - 1) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (last && threadIdx.x < 32) {
+      int32_t epoch = 0;
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+        epoch = *p.epoch_counter + 1;
+        *p.epoch_counter = epoch;
+        *p.ticket = 0;
+      }
+      epoch = __shfl_sync(0xffffffffu, epoch, 0);
+      if (threadIdx.x < p.n_signal && static_cast<int>(threadIdx.x) != p.signal_me) {
+        __threadfence_system();
+        nr_st_release_sys(p.signal_slot[threadIdx.x], epoch);
       }
     }
   }
@@ -233,8 +280,9 @@ extern "C" int hdit_qk_norm_rope(const hdit_norm_rope_args* a) {
     if (a->cos == nullptr || a->sin == nullptr) return set_error(HDIT_ERR_BAD_ARG, "rope requested without cos/sin tables");
     if ((reinterpret_cast<uintptr_t>(a->cos) & 15) || (reinterpret_cast<uintptr_t>(a->sin) & 15))
       return set_error(HDIT_ERR_SHAPE, "cos/sin tables must be 16-byte aligned");
+    const long long first_end = (a->range2_start > 0 && a->range2_start < a->seq) ? a->range2_start : a->seq;
     if (a->rope_seq_start < 0 || a->rope_row0 < 0 ||
-        (a->seq > a->rope_seq_start && a->rope_row0 + (a->seq - a->rope_seq_start) > a->rope_rows))
+        (first_end > a->rope_seq_start && a->rope_row0 + (first_end - a->rope_seq_start) > a->rope_rows))
       return set_error(HDIT_ERR_SHAPE, "rope table of %lld rows does not cover tokens [%lld, %d)",
                        (long long)a->rope_rows, (long long)a->rope_seq_start, a->seq);
   }
@@ -248,6 +296,38 @@ extern "C" int hdit_qk_norm_rope(const hdit_norm_rope_args* a) {
   p.sin_tab = a->sin;
   p.rope_seq_start = a->rope_seq_start;
   p.rope_row0 = a->rope_row0;
+  p.range2_start = (a->range2_start > 0 && a->range2_start < a->seq) ? a->range2_start : a->seq;
+  if (p.range2_start < a->seq) {
+    bool rope2 = false;
+    for (int i = 0; i < a->n_tensors; ++i) {
+      p.weight2[i] = a->range2_norm_weight[i];
+      p.bias2[i] = a->range2_norm_bias[i];
+      p.do_rope2[i] = a->range2_do_rope[i];
+      rope2 |= a->range2_do_rope[i] != 0;
+      if ((reinterpret_cast<uintptr_t>(p.weight2[i]) | reinterpret_cast<uintptr_t>(p.bias2[i])) & 15)
+        return set_error(HDIT_ERR_SHAPE, "tensor %d: second-range norm weight / bias must be 16-byte aligned", i);
+    }
+    p.rope_row0_2 = a->range2_rope_row0;
+    if (rope2) {
+      if (a->cos == nullptr || a->sin == nullptr) return set_error(HDIT_ERR_BAD_ARG, "rope requested without cos/sin tables");
+      if (a->range2_rope_row0 < 0 || a->range2_rope_row0 + (a->seq - p.range2_start) > a->rope_rows)
+        return set_error(HDIT_ERR_SHAPE, "rope table of %lld rows does not cover the second range", (long long)a->rope_rows);
+    }
+  }
+  if (a->n_signal < 0 || a->n_signal > kMaxDst) return set_error(HDIT_ERR_BAD_ARG, "n_signal must be 0..8");
+  if (a->n_signal > 0) {
+    if (a->epoch_counter == nullptr || a->ticket == nullptr || a->signal_me < 0 || a->signal_me >= a->n_signal)
+      return set_error(HDIT_ERR_BAD_ARG, "signal needs an epoch counter, a ticket word and this rank's index");
+    for (int i = 0; i < a->n_signal; ++i) {
+      if (i != a->signal_me && a->signal_slots[i] == nullptr)
+        return set_error(HDIT_ERR_NOT_INITIALISED, "signal slot of peer %d is null", i);
+      p.signal_slot[i] = a->signal_slots[i];
+    }
+    p.n_signal = a->n_signal;
+    p.signal_me = a->signal_me;
+    p.epoch_counter = a->epoch_counter;
+    p.ticket = reinterpret_cast<unsigned int*>(a->ticket);
+  }
 
   const int tpr = a->head_dim / 8;
   int threads = a->heads * tpr;

@@ -74,6 +74,7 @@ def attn_fwd(
     out_dsts=None,
     q_rows_per_dst=None,
     q_dst_row0=None,
+    wait_flags=None,
 ):
     """softmax(Q K^T * scale) V over segment lists, (B, S, H, D) layout.
 
@@ -94,6 +95,9 @@ def attn_fwd(
     r // q_rows_per_dst[s] at row q_dst_row0[s] + r % q_rows_per_dst[s], or to every destination at row
     q_dst_row0[s] + r when q_rows_per_dst[s] is 0. With the Ulysses peers' output buffers as destinations this
     is the reverse all-to-all done by the attention epilogue. Returns None (or the lse) in that case.
+
+    wait_flags (a FlagWait): flags in this rank's memory that the peers' exchange kernels bump; the kernel's
+    loader waits for them before its first load (the barrier after the head exchange, folded into attention).
     """
     q0 = q_segs[0]
     if not q0.is_cuda:
@@ -150,6 +154,12 @@ def attn_fwd(
             raise ValueError("acc_lse must be contiguous (B, H, Sq)")
         a.acc_out = acc_out.data_ptr()
         a.acc_lse = acc_lse.data_ptr()
+    if wait_flags is not None:
+        a.n_wait = len(wait_flags.slots)
+        for i, ptr in enumerate(wait_flags.slots):
+            a.wait_slots[i] = ptr
+        a.wait_epoch = wait_flags.epoch_ptr
+        a.wait_spins = int(wait_flags.max_spins)
     a.stream = _stream_ptr(q0.device)
     n_split = 1
     if mode == _C.ATTN_FINAL:
@@ -298,6 +308,23 @@ def kv_scatter(kv_cache, new_k, new_v, token_start):
     _count()
 
 
+class FlagSignal:
+    """Where an exchange kernel publishes "my rows have landed": for every peer the address (in that peer's
+    memory) of the flag this rank bumps (None at this rank's own index), this rank's index, and the device
+    addresses of this rank's epoch counter and ticket word."""
+
+    def __init__(self, slots, me, epoch_ptr, ticket_ptr):
+        self.slots, self.me, self.epoch_ptr, self.ticket_ptr = list(slots), int(me), int(epoch_ptr), int(ticket_ptr)
+
+
+class FlagWait:
+    """The matching wait: the flags in this rank's memory that the peers bump (None at this rank's own index)
+    and the device address of the epoch they must reach."""
+
+    def __init__(self, slots, epoch_ptr, max_spins=20_000_000):
+        self.slots, self.epoch_ptr, self.max_spins = list(slots), int(epoch_ptr), int(max_spins)
+
+
 class RawDst:
     """Destinations given as raw device addresses (e.g. mapped peer memory) plus (b, s, h) strides in elements."""
 
@@ -309,13 +336,17 @@ class RawDst:
 
 
 def qk_norm_rope(tensors, *, eps=1e-6, cos=None, sin=None, rope_seq_start=0, rope_row0=0, dsts=None,
-                 dst_seq_offset=0):
+                 dst_seq_offset=0, range2=None, signal=None):
     """Fused RMSNorm + RoPE (+ head scatter) over up to three (B, S, H, D) tensors.
 
     tensors: list of (x, norm_weight or None, do_norm, do_rope[, norm_bias]). do_norm: False / 0 = none,
     True / 1 = RMSNorm, 2 = LayerNorm over the head dimension (weight and bias optional). dsts: None for
     in-place, or a list (one entry per tensor) of lists of destination tensors (B, S_dst, H/n_dst, D); all
     tensors share n_dst.
+
+    range2 = (start, [(norm_weight, do_rope[, norm_bias]) per tensor], rope_row0): rows [start, S) take these norm
+    weights and rotary rows instead (the norm kind stays the tensor's). signal (a FlagSignal): the kernel's last
+    CTA tells the peers that this rank's rows have landed (see FlagWait / attn_fwd's wait_flags).
     """
     x0 = tensors[0][0]
     B, S, H, D = x0.shape
@@ -352,6 +383,20 @@ def qk_norm_rope(tensors, *, eps=1e-6, cos=None, sin=None, rope_seq_start=0, rop
             o0 = outs[0]
             t.dst_stride_b, t.dst_stride_s, t.dst_stride_h = o0.stride(0), o0.stride(1), o0.stride(2)
         t.dst_seq_offset = int(dst_seq_offset)
+    if range2 is not None:
+        start, per_tensor, row0_2 = range2
+        a.range2_start = int(start)
+        a.range2_rope_row0 = int(row0_2)
+        for i, ent in enumerate(per_tensor):
+            w, do_rope, *rest = ent
+            a.range2_norm_weight[i] = w.data_ptr() if w is not None else None
+            a.range2_norm_bias[i] = rest[0].data_ptr() if rest and rest[0] is not None else None
+            a.range2_do_rope[i] = int(bool(do_rope))
+    if signal is not None:
+        a.n_signal, a.signal_me = len(signal.slots), signal.me
+        for i, ptr in enumerate(signal.slots):
+            a.signal_slots[i] = ptr
+        a.epoch_counter, a.ticket = signal.epoch_ptr, signal.ticket_ptr
     a.stream = _stream_ptr(x0.device)
     with torch.cuda.device(x0.device):
         _C.check(_C.lib().hdit_qk_norm_rope(ctypes.byref(a)))

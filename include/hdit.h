@@ -138,6 +138,16 @@ typedef struct hdit_attn_args {
   void* out_dst[8];
   int64_t q_rows_per_dst[HDIT_MAX_Q_SEG];
   int64_t q_dst_row0[HDIT_MAX_Q_SEG];
+  /* Optional: before its first load every CTA waits (bounded by wait_spins polls, default about 2 s; on expiry
+   * HDIT_ERR_PEER_TIMEOUT, where = 9, iteration = silent peer) until each non-NULL wait_slots[p] -- a flag in this
+   * rank's memory that peer p bumps, see hdit_norm_rope_args.signal_slots -- has reached *wait_epoch. This is the
+   * waiting half of the barrier between the Ulysses head exchange and attention, folded into the consumer.
+   * n_wait = 0: off. */
+  int32_t n_wait;
+  int32_t reserved1;
+  const int32_t* wait_slots[8];
+  const int32_t* wait_epoch;
+  int64_t wait_spins;
 } hdit_attn_args;
 
 HDIT_API int hdit_attn_fwd(const hdit_attn_args* args);
@@ -232,6 +242,25 @@ typedef struct hdit_norm_rope_args {
   int64_t rope_row0;
   hdit_norm_rope_tensor t[3];
   void* stream;
+  /* Optional second row range in the same launch: tokens [range2_start, seq) take these norm weights / biases,
+   * rotate (or not) per tensor, and use table row (s - range2_start + range2_rope_row0); tokens below it follow
+   * the fields above. range2_start <= 0 or >= seq: none. (Text and image rows of a joint sequence differ in
+   * their norm weights and rotary rows; one launch covers both.) */
+  int64_t range2_start;
+  const void* range2_norm_weight[3];
+  const void* range2_norm_bias[3];
+  int32_t range2_do_rope[3];
+  int32_t reserved0;
+  int64_t range2_rope_row0;
+  /* Optional: when every CTA has stored its rows, the last one publishes the next epoch of `epoch_counter` (a
+   * device int32 of this rank, advanced by the kernel) with release / system scope to signal_slots[p] for every
+   * p != signal_me -- the signalling half of hdit_peer_barrier folded into the kernel that performs the Ulysses
+   * head exchange. `ticket` is a zero-initialised device word the launches of one stream share. n_signal = 0: off. */
+  int32_t n_signal;
+  int32_t signal_me;
+  int32_t* signal_slots[8];
+  int32_t* epoch_counter;
+  int32_t* ticket;
 } hdit_norm_rope_args;
 
 HDIT_API int hdit_qk_norm_rope(const hdit_norm_rope_args* args);

@@ -226,3 +226,67 @@ def test_cfg_euler_step_matches_the_eager_chain_bit_for_bit(dtype, cfg):
     got = kernels.cfg_euler_step(pred, sample, sigmas, step, scale, cfg=cfg, out_peer_ptr=peer.data_ptr())
     torch.cuda.synchronize()
     assert torch.equal(got, want) and torch.equal(peer, want)
+
+
+def test_norm_rope_two_row_ranges_in_one_launch_and_folded_signal():
+    """One launch over [text; image] rows with their own norm weights and rotary rows equals two launches, bit
+    for bit; and the launch's last CTA publishes the next epoch to the peers' flags (here: flags in local memory
+    standing in for two peers), advancing the device-side epoch counter once per launch."""
+    from hetu_dit_b200 import kernels
+    gen = torch.Generator().manual_seed(23)
+    B, S, H, D, T = 2, 90, 4, 128, 26
+    dtype = torch.bfloat16
+    q = torch.randn(B, S, H, D, generator=gen).to(dtype).to(DEV)
+    k = torch.randn(B, S, H, D, generator=gen).to(dtype).to(DEV)
+    v = torch.randn(B, S, H, D, generator=gen).to(dtype).to(DEV)
+    w = [(1 + 0.1 * torch.randn(D, generator=gen)).to(dtype).to(DEV) for _ in range(4)]
+    ang = torch.rand(200, D // 2, generator=gen) * 6.28
+    cos = torch.cos(ang).repeat_interleave(2, -1).contiguous().to(DEV)
+    sin = torch.sin(ang).repeat_interleave(2, -1).contiguous().to(DEV)
+
+    def outs():
+        return [torch.zeros(B, S + 5, H, D, dtype=dtype, device=DEV) for _ in range(3)]
+
+    two = outs()
+    kernels.qk_norm_rope([(q[:, :T], w[0], True, True), (k[:, :T], w[1], True, True), (v[:, :T], None, False, False)],
+                         cos=cos, sin=sin, rope_row0=7, dsts=[[o] for o in two], dst_seq_offset=5)
+    kernels.qk_norm_rope([(q[:, T:], w[2], True, True), (k[:, T:], w[3], True, True), (v[:, T:], None, False, False)],
+                         cos=cos, sin=sin, rope_row0=100, dsts=[[o] for o in two], dst_seq_offset=5 + T)
+    flags = torch.zeros(64, dtype=torch.int32, device=DEV)   # [0..2]: peers' slots, [8]: epoch counter, [9]: ticket
+    base = flags.data_ptr()
+    signal = kernels.FlagSignal([base + 0, None, base + 8], 1, base + 32, base + 36)
+    for launch in (1, 2):
+        one = outs()
+        kernels.qk_norm_rope([(q, w[0], True, True), (k, w[1], True, True), (v, None, False, False)], cos=cos, sin=sin,
+                             rope_row0=7, dsts=[[o] for o in one], dst_seq_offset=5,
+                             range2=(T, [(w[2], True), (w[3], True), (None, False)], 100), signal=signal)
+        torch.cuda.synchronize()
+        for a, b in zip(one, two):
+            assert torch.equal(a, b)
+        f = flags.cpu().tolist()
+        assert f[0] == launch and f[2] == launch and f[1] == 0 and f[8] == launch and f[9] == 0, f[:10]
+
+
+def test_attention_waits_for_peer_flags_and_reports_a_silent_peer():
+    """The attention kernel's loader waits for the flags its peers bump: with the flags at the awaited epoch the
+    result is the ordinary one; with a flag that nothing sets the bounded wait runs out, the kernel reports
+    HDIT_ERR_PEER_TIMEOUT (where = 9, the silent peer's index) and returns -- the context stays usable."""
+    from hetu_dit_b200 import _C, kernels
+    gen = torch.Generator().manual_seed(29)
+    q, k, v = (torch.randn(1, 200, 2, 64, generator=gen).bfloat16().to(DEV) for _ in range(3))
+    want = kernels.attn_fwd([q], [k], [v])
+    flags = torch.zeros(16, dtype=torch.int32, device=DEV)
+    flags[0], flags[2], flags[8] = 5, 6, 5     # peers 0 and 2 have reached epoch 5 (one is already ahead)
+    base = flags.data_ptr()
+    wait = kernels.FlagWait([base + 0, None, base + 8], base + 32, max_spins=20000)
+    got = kernels.attn_fwd([q], [k], [v], wait_flags=wait)
+    torch.cuda.synchronize()
+    assert _C.device_status(0, clear=True)[0] == 0 and torch.equal(got, want)
+    flags[2] = 4                               # peer 2 has not arrived
+    kernels.attn_fwd([q], [k], [v], wait_flags=wait)
+    torch.cuda.synchronize()
+    code, _, where, who = _C.device_status(0, clear=True)
+    assert (code, where, who) == (_C.HDIT_ERR_PEER_TIMEOUT, 9, 2)
+    assert torch.equal(kernels.attn_fwd([q], [k], [v]), want)   # the next launch is unaffected
+    torch.cuda.synchronize()
+    assert _C.device_status(0, clear=True)[0] == 0
