@@ -188,15 +188,17 @@ def test_split_kv_matches_single_launch(D, dtype, n_split):
 
 def test_split_kv_auto_small_grid():
     """The shape one rank sees after the Ulysses exchange at degree 8 of a 24-head model: 3 heads of the whole
-    sequence. The wrapper picks a split by itself; strided output (heads of a wider buffer) is honoured."""
+    sequence. Left alone, the library fills the GPU by itself (interleaved mode, or a KV split when that mode is
+    forbidden); strided output (heads of a wider buffer) is honoured either way."""
     from hetu_dit_b200 import kernels
     gen = torch.Generator().manual_seed(77)
     q, k, v = (_mk((1, 2400, 3, 128), torch.bfloat16, gen) for _ in range(3))
-    assert kernels._pick_kv_split([q], [k], 1, 3) > 1
-    wide = torch.zeros(1, 2400, 6, 128, dtype=torch.bfloat16, device="cuda:0")
-    out, lse = _run([q], [k], [v], out=wide[:, :, 3:])
-    _check(out, lse, [q], [k], [v])
-    assert wide[:, :, :3].abs().max().item() == 0
+    assert kernels._pick_kv_split([q], [k], 1, 3, kv_interleave=1) > 1
+    for interleave in (0, 1):
+        wide = torch.zeros(1, 2400, 6, 128, dtype=torch.bfloat16, device="cuda:0")
+        out, lse = _run([q], [k], [v], out=wide[:, :, 3:], kv_interleave=interleave)
+        _check(out, lse, [q], [k], [v])
+        assert wide[:, :, :3].abs().max().item() == 0
 
 
 def test_split_kv_argument_errors():
