@@ -180,6 +180,12 @@ class _UlyssesExchange:
 
 class hetuDiTLongContextAttention(torch.nn.Module):
     ring_impl_type_supported_kv_cache = ["basic"]
+    # Fold the barrier between the head exchange and attention into those two kernels (signal from the exchange
+    # kernel's last CTA, wait in the attention kernel's loader) instead of a one-warp barrier kernel. Off: measured
+    # on the Flux-shaped step at Ulysses 2 it costs 43.6 ms against 39.9 ms per step -- while it waits, the
+    # attention grid holds every SM, which starves the GEMMs the blocks run beside attention on a second stream;
+    # the one-warp kernel waits for free. It pays where nothing runs beside attention.
+    fold_exchange_barrier = False
 
     def __init__(self, scatter_idx: int = 2, gather_idx: int = 1, ring_impl_type: str = "basic",
                  use_pack_qkv: bool = False, use_kv_cache: bool = False) -> None:
@@ -230,9 +236,10 @@ class hetuDiTLongContextAttention(torch.nn.Module):
                     joint_q = joint_q[..., hpr * r:hpr * (r + 1), :]
             xchg = _UlyssesExchange(self.ulysses_pg)
             if qk_prologue is not None:
-                # The barrier after the exchange folds into the kernels on either side of it when attention is
+                # The barrier after the exchange can fold into the kernels on either side of it when attention is
                 # the first (and only) reader of the gathered tensors: no ring pull and no stale-KV update.
-                fold = (self.ring_pg is None or self.ring_pg.world_size == 1) and not self._kv_hook_runs(attn)
+                fold = self.fold_exchange_barrier and (self.ring_pg is None or self.ring_pg.world_size == 1) and \
+                    not self._kv_hook_runs(attn)
                 res = xchg.gather_heads_fused(query, key, value, qk_prologue, fold_barrier=fold)
                 query, key, value = res[:3]
                 wait_flags = res[3] if fold else None
