@@ -58,7 +58,7 @@ class PipelineGroupCoordinator:
                 raise RuntimeError("PipeFusion across ranks needs the peer heap")
             # First allocation after a plan switch on every stage -> same offset everywhere. At most
             # half of the heap, so the sequence-parallel buffers of the same plan still fit.
-            inbox_bytes = min(inbox_bytes, (self.heap.nbytes // 2) // 4096 * 4096)
+            inbox_bytes = min(inbox_bytes, (self.heap._limit // 2) // 4096 * 4096)
             self.inbox_bytes = inbox_bytes
             self.inbox, self.inbox_offset = self.heap.alloc((inbox_bytes,), torch.uint8, name="pp_inbox")
         self.reset_buffer()

@@ -45,6 +45,7 @@ class PeerHeap:
         self.nbytes = int(nbytes)
         self.rank, self.world_size, self.device = rank, world_size, torch.device(device)
         self._cursor = FLAG_BYTES
+        self._limit = self.nbytes   # allocations end here; reserve_tail() lowers it
         self.max_spins = DEFAULT_MAX_SPINS  # default bound of every device-side wait; a plan may raise it
         self._named: Dict[str, tuple] = {}
         self._epochs: Dict[int, int] = {}
@@ -77,6 +78,15 @@ class PeerHeap:
         self._named.clear()
         self._flip.clear()
 
+    def reserve_tail(self, nbytes: int) -> int:
+        """Sets `nbytes` at the top of the heap aside for good (it survives reset()) and returns its offset. Every
+        rank must make the same reservations in the same order, before the plans start to allocate."""
+        nbytes = (int(nbytes) + 255) // 256 * 256
+        if self._cursor + nbytes > self._limit:
+            raise MemoryError("peer heap too small for this reservation")
+        self._limit -= nbytes
+        return self._limit
+
     def alloc(self, shape: Sequence[int], dtype: torch.dtype, name: Optional[str] = None):
         """(tensor, offset): a zero-copy view of `shape` at a 256-byte aligned heap offset. A `name`
         makes the buffer persistent: asking again with the same name, shape and dtype returns it."""
@@ -91,8 +101,8 @@ class PeerHeap:
             n *= s
         nbytes = n * torch.empty((), dtype=dtype).element_size()
         off = (self._cursor + 255) // 256 * 256
-        if off + nbytes > self.nbytes:
-            raise MemoryError(f"peer heap exhausted: need {nbytes} bytes at offset {off} of {self.nbytes}")
+        if off + nbytes > self._limit:
+            raise MemoryError(f"peer heap exhausted: need {nbytes} bytes at offset {off} of {self._limit}")
         self._cursor = off + nbytes
         t = self._bytes[off:off + nbytes].view(dtype).view(shape)
         if name is not None:

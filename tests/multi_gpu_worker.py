@@ -232,3 +232,32 @@ def barrier_timeout_case(rank, world, port, errq):
     except Exception:
         errq.put(f"rank {rank}:\n{traceback.format_exc()}")
         raise
+
+
+def handoff_case(rank, world, port, errq):
+    """Stage hand-off of latents to a "decode" rank over the peer heap: bit-exact, repeated (the slot is re-used),
+    surviving a plan switch (heap reset) in between, several shapes and dtypes."""
+    try:
+        dist, ps, heap, dev = _setup(rank, world, port)
+        from hetu_dit_b200.core.distributed.handoff import StageHandoff
+        ho = StageHandoff(heap, slot_bytes=4 << 20)
+        ps.initialize_model_parallel(sequence_parallel_degree=world, ulysses_degree=world)
+        decode = world - 1
+        shapes = [((1, 16, 64, 64), torch.bfloat16), ((2, 16, 24, 40), torch.float16), ((1, 16, 5, 12, 20), torch.float32)]
+        for rnd, (shape, dtype) in enumerate(shapes):
+            gen = torch.Generator().manual_seed(500 + rnd)
+            want = torch.randn(shape, generator=gen).to(dtype)
+            if rank == 0:
+                ho.send(decode, want.to(dev))
+            if rank == decode:
+                got = ho.recv(0)
+                assert got.dtype == dtype and tuple(got.shape) == shape and torch.equal(got.cpu(), want), rnd
+            heap.check()
+            dist.barrier()
+            heap.reset()                       # a plan switch drops the activation buffers, not the slots
+            heap.alloc((1024,), torch.uint8, name="after_reset")
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errq.put(f"rank {rank}:\n{traceback.format_exc()}")
+        raise

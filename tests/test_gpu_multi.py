@@ -63,3 +63,8 @@ def test_group_all_gather(world):
 def test_barrier_timeout_is_reported_not_hung():
     from tests.multi_gpu_worker import barrier_timeout_case
     _spawn(barrier_timeout_case, 2)
+
+
+def test_stage_handoff_to_decode_rank():
+    from tests.multi_gpu_worker import handoff_case
+    _spawn(handoff_case, 2)
