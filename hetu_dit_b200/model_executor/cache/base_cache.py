@@ -266,8 +266,11 @@ class BaseBlockCache:
                 dst[:, p.dest_offset:p.dest_offset + span].copy_(src[:, p.abs_start_idx:p.abs_end_idx], non_blocking=True)
             p.status = "done"
 
-    def _reuse_overlap(self, plan: DataReconstructionPlan, old_block: nn.Module, old_tp: Tuple[float, float]):
-        """Device copies of the part of the target range the previously cached slice already holds."""
+    def _reuse_overlap(self, plan: DataReconstructionPlan, old_block: nn.Module, old_tp: Tuple[float, float],
+                       cpu_block: Optional[nn.Module] = None):
+        """Device copies of the part of the target range the previously cached slice already holds. The unsplit
+        sizes come from the CPU master block when it is given (always, from adjust_pipeline); a slice whose shape
+        disagrees with its range raises instead of being copied at a wrong offset."""
         boxes = []
         for name, sub in plan.skeleton_block.named_modules():
             if not isinstance(sub, nn.Linear):
@@ -282,9 +285,17 @@ class BaseBlockCache:
                 tensors.append(("bias", 0))
             for tname, d in tensors:
                 new_t, old_t = getattr(sub, tname).data, getattr(old, tname).data
-                full = _full_size(new_t, old_t, d, plan.target_tp_range, old_tp, self)
+                if cpu_block is not None:
+                    full = getattr(_resolve(cpu_block, name), tname).shape[d if new_t.dim() > 1 else 0]
+                else:
+                    full = _full_size(new_t, old_t, d, plan.target_tp_range, old_tp, self)
                 lo, hi = self.range_to_indices(plan.target_tp_range, full)
                 o_lo, o_hi = self.range_to_indices(old_tp, full)
+                dd = d if new_t.dim() > 1 else 0
+                if new_t.shape[dd] != hi - lo or old_t.shape[dd] != o_hi - o_lo:
+                    raise RuntimeError(
+                        f"{name}.{tname}: slices of {old_t.shape[dd]} / {new_t.shape[dd]} along dim {dd} do not match "
+                        f"the ranges {old_tp} / {plan.target_tp_range} of a dimension of {full}")
                 k_lo, k_hi = max(lo, o_lo), min(hi, o_hi)
                 if k_hi <= k_lo:
                     continue
@@ -356,7 +367,7 @@ class BaseBlockCache:
             plan = plans[idx]
             plan.skeleton_block = self._create_skeleton_block(idx, cpu_full_transformer, target_tp, slice_bias)
             if cached is not None:
-                self._reuse_overlap(plan, cached[0], cached[1])
+                self._reuse_overlap(plan, cached[0], cached[1], self.get_cpu_block_for_index(cpu_full_transformer, idx))
             for p in plan.pieces:
                 if p.status == "sourced":
                     dst = getattr(_resolve(plan.skeleton_block, p.layer_path), p.tensor_type).data

@@ -270,6 +270,41 @@ def _worker_case(rank, world, port, errq):
         want_full = opf.denoise(sd, shape, lat, prompt, pooled, 2, 4.0, [512], 0, (32, 16))
         cos, rel = oa.cosine_and_max_rel(out.cpu(), want_full)
         assert cos >= 0.999 and rel <= 5e-2, ("ulysses2 unpatched", cos, rel)
+
+        # plans D and E: a tensor-parallel re-slice in which each rank pulls from the slice its peer is replacing
+        # at the same time. D (2 pipeline stages, at most 2 cached blocks) leaves blocks 0-1 whole on rank 0 and
+        # 2-3 whole on rank 1. E (tensor parallel 2) makes rank 0 cut its blocks down to the first half of the
+        # rows / columns -- releasing the whole tensors -- while rank 1 pulls the second half of those very
+        # tensors, and vice versa. The released memory must not be re-used before the peer's pull has run.
+        w.cache.max_num_cached_blocks = 2
+        cfg4 = EngineConfig()
+        cfg4.parallel_config.pp_config.pp_degree = 2
+        call(w, "switch_parallel_env", 2, [0, 1], cfg4)
+        call(w, "hotspa_model", cfg4)
+        assert sorted(w.cache.cache) == ([0, 1] if rank == 0 else [2, 3])
+        w.cache.max_num_cached_blocks = 1 << 30
+        cfg5 = EngineConfig()
+        cfg5.parallel_config.tp_config.tp_degree = 2
+        call(w, "switch_parallel_env", 2, [0, 1], cfg5)
+        stats = call(w, "hotspa_model", cfg5)
+        assert stats["from_peers"] > 0 and stats["from_cpu"] == 0, stats
+        tp = (0.0, 0.5) if rank == 0 else (0.5, 1.0)
+        for i, blk in enumerate(w.transformer.transformer_blocks):
+            assert w.cache.cache[i][1] == tp
+            for name, sub in blk.named_modules():
+                if not isinstance(sub, torch.nn.Linear):
+                    continue
+                ref = dict(model.transformer_blocks[i].named_modules())[name]
+                kind = w.cache.choose_tp_split_type(name)
+                if kind is None:
+                    assert torch.equal(sub.weight.cpu(), ref.weight), (i, name)
+                    continue
+                dim = 0 if kind == "row" else 1
+                lo, hi = w.cache.range_to_indices(tp, ref.weight.shape[dim])
+                want_w = ref.weight[lo:hi] if dim == 0 else ref.weight[:, lo:hi]
+                assert torch.equal(sub.weight.cpu(), want_w), (i, name, kind)
+                if kind == "row" and ref.bias is not None:
+                    assert torch.equal(sub.bias.cpu(), ref.bias[lo:hi]), (i, name, "bias")
         dist.barrier()
         dist.destroy_process_group()
     except Exception:
