@@ -563,6 +563,182 @@ def gen_usp(ref):
             print(f"usp_{name}.npz written")
 
 
+# ----------------------------------------------------------------------------- PipeFusion schedule order
+PIPEFUSION_CASES = [
+    # (pipeline stages, patches, denoising steps, warm-up steps)
+    (2, 2, 3, 1), (2, 4, 4, 1), (2, 4, 3, 0), (3, 3, 4, 1), (4, 4, 3, 1), (4, 8, 4, 2), (2, 4, 2, 2), (1, 1, 3, 1),
+    (4, 2, 3, 1),
+]
+
+
+def _lift_method_undecorated(path, name, cls, namespace):
+    with open(path) as f:
+        tree = ast.parse(f.read())
+    node = _find(tree, name, cls)
+    node.decorator_list = []
+    ns = dict(namespace)
+    exec(compile(ast.Module(body=[node], type_ignores=[]), path, "exec"), ns)
+    return ns[name]
+
+
+def gen_pipefusion_order(ref):
+    """Runs the reference's _sync_pipeline / _init_async_pipeline / _async_pipeline
+    (model_executor/pipelines/pipeline_stable_diffusion_3.py:1352-1678) for every stage of a few pipeline shapes
+    with a recording stand-in for the pipeline group, the backbone and the scheduler, and writes per stage the
+    order of receives, queue operations, forwards, scheduler steps and sends."""
+    from typing import Callable, Dict, List, Optional
+    path = os.path.join(ref, "hetu_dit/model_executor/pipelines/pipeline_stable_diffusion_3.py")
+    cases = []
+    for (stages, n_patch, n_steps, warmup) in PIPEFUSION_CASES:
+        for stage in range(stages):
+            events = []
+            patch_h = 2
+
+            class Group:
+                def pipeline_recv(self, idx=-1, name="latent"):
+                    events.append(["recv", name or "latent", idx])
+                    return torch.zeros(1, 4, patch_h * n_patch, 4) if (name or "latent") == "latent" else "text"
+
+                def pipeline_send(self, tensor, name="latent", segment_idx=-1):
+                    events.append(["send", name, segment_idx])
+
+                pipeline_isend = pipeline_send
+
+                def add_pipeline_recv_task(self, idx=-1, name="latent"):
+                    events.append(["add_recv_task", name or "latent", idx])
+
+                def recv_next(self):
+                    events.append(["recv_next"])
+
+                def get_pipeline_recv_data(self, idx=-1, name="latent"):
+                    events.append(["get", name, idx])
+                    return torch.zeros(1, 4, patch_h, 4) if name == "latent" else "text"
+
+            class State:
+                num_pipeline_patch = n_patch
+                pp_patches_height = [patch_h] * n_patch
+                pp_patches_start_idx_local = [patch_h * i for i in range(n_patch + 1)]
+                runtime_config = _NS(warmup_steps=warmup)
+                pipeline_patch_idx = 0
+
+                def set_patched_mode(self, patch_mode):
+                    events.append(["patched_mode", bool(patch_mode)])
+                    self.pipeline_patch_idx = 0
+
+                def next_patch(self):
+                    self.pipeline_patch_idx = (self.pipeline_patch_idx + 1) % n_patch
+
+            state, group = State(), Group()
+            prompt = "prompt"
+
+            class Pipe:
+                interrupt = False
+                scheduler = _NS(order=1)
+
+                def _init_sync_pipeline(self, latents):
+                    events.append(["patched_mode", False])  # what the reference's _init_sync_pipeline does first
+                    state.pipeline_patch_idx = 0
+                    return latents
+
+                def _backbone_forward(self, latents, encoder_hidden_states, pooled_prompt_embeds, t):
+                    events.append(["forward", state.pipeline_patch_idx, int(t),
+                                   "prompt" if encoder_hidden_states is prompt else "received"])
+                    return latents, "text"
+
+                def _scheduler_step(self, noise_pred, last, t):
+                    events.append(["step", int(t)])
+                    return noise_pred
+
+            ns = {
+                "torch": torch, "List": List, "Optional": Optional, "Callable": Callable, "Dict": Dict,
+                "logger": logging.getLogger("golden"), "XLA_AVAILABLE": False,
+                "get_runtime_state": lambda: state, "get_pp_group": lambda: group,
+                "is_pipeline_first_stage": lambda: stage == 0, "is_pipeline_last_stage": lambda: stage == stages - 1,
+                "get_pipeline_parallel_world_size": lambda: stages, "get_sequence_parallel_world_size": lambda: 1,
+                "get_sp_group": lambda: None,
+            }
+            for name in ("_sync_pipeline", "_init_async_pipeline", "_async_pipeline"):
+                setattr(Pipe, name, _lift_method_undecorated(path, name, "hetuDiTStableDiffusion3Pipeline", ns))
+            pipe = Pipe()
+            bar = _NS(update=lambda: None)
+            latents = torch.zeros(1, 4, patch_h * n_patch, 4)
+            timesteps = list(range(n_steps))
+            # the entry point's branch (pipeline_stable_diffusion_3.py:372-411)
+            if n_patch > 1 and n_steps > warmup:
+                latents = pipe._sync_pipeline(latents=latents, prompt_embeds=prompt, pooled_prompt_embeds=None,
+                                              timesteps=timesteps[:warmup], num_warmup_steps=0, progress_bar=bar)
+                pipe._async_pipeline(latents=latents, prompt_embeds=prompt, pooled_prompt_embeds=None,
+                                     timesteps=timesteps[warmup:], num_warmup_steps=0, progress_bar=bar)
+            else:
+                pipe._sync_pipeline(latents=latents, prompt_embeds=prompt, pooled_prompt_embeds=None,
+                                    timesteps=timesteps, num_warmup_steps=0, progress_bar=bar, sync_only=True)
+            cases.append({"stages": stages, "stage": stage, "num_pipeline_patch": n_patch, "steps": n_steps,
+                          "warmup": warmup, "events": events})
+    with open(os.path.join(HERE, "pipefusion_order.json"), "w") as f:
+        json.dump(cases, f, separators=(",", ":"))
+    print("pipefusion_order.json written:", len(cases), "cases")
+
+
+# ----------------------------------------------------------------------------- position-embedding rows per rank
+def _runs(idx):
+    """Maximal contiguous runs [start, end) of an increasing-by-one-within-run index list."""
+    runs = []
+    for v in idx:
+        if runs and runs[-1][1] == v:
+            runs[-1][1] = v + 1
+        else:
+            runs.append([v, v + 1])
+    return runs
+
+
+def gen_pos_embed_rows(ref):
+    """Runs the reference's patch-embedding wrapper forward
+    (model_executor/diffusion_executor/layers/embeddings.py:31-112) on a stand-in module whose projection is the
+    identity on zeros and whose position table holds its own row numbers, with the patch metadata the reference's
+    _calc_patches_metadata computes, and writes which table rows each rank adds: whole-image mode and every patch
+    of patch mode."""
+    log = logging.getLogger("golden")
+    rs_path = os.path.join(ref, "hetu_dit/core/distributed/runtime_state.py")
+    em_path = os.path.join(ref, "hetu_dit/model_executor/diffusion_executor/layers/embeddings.py")
+    cases = []
+    for (h, w, vae, patch, npp, sp) in [(1024, 1024, 8, 2, 4, 1), (1024, 1024, 8, 2, 4, 2), (1024, 1024, 8, 2, 4, 4),
+                                        (512, 512, 8, 2, 2, 2), (1152, 896, 8, 2, 3, 2), (1024, 2048, 8, 2, 4, 2),
+                                        (768, 768, 8, 2, 1, 1), (1024, 1024, 8, 2, 1, 8), (1536, 1536, 8, 2, 8, 1)]:
+        for rank in range(sp):
+            meta, _ = lift(rs_path, "_calc_patches_metadata", cls="DiTRuntimeState", namespace={
+                "get_sequence_parallel_world_size": lambda sp=sp: sp,
+                "get_sequence_parallel_rank": lambda rank=rank: rank, "logger": log})
+            state = _NS(backbone_patch_size=patch, vae_scale_factor=vae,
+                        input_config=_NS(height=h, width=w),
+                        parallel_config=_NS(pp_config=_NS(num_pipeline_patch=npp)), patch_mode=False,
+                        pipeline_patch_idx=0)
+            meta(state)
+            gh, gw = h // vae // patch, w // vae // patch
+            table = torch.arange(gh * gw, dtype=torch.float32).reshape(1, gh * gw, 1)
+            module = _NS(patch_size=patch, pos_embed_max_size=None, proj=lambda x: x, flatten=False, layer_norm=False,
+                         pos_embed=table, height=gh, width=gw)
+            fwd, _ = lift(em_path, "forward", cls="hetuDiTPatchEmbedWrapper",
+                          namespace={"get_runtime_state": lambda: state, "torch": torch})
+            wrapper = _NS(module=module)
+            rec = {"height": h, "width": w, "vae": vae, "patch": patch, "num_pipeline_patch": state.num_pipeline_patch,
+                   "sp_world": sp, "sp_rank": rank,
+                   "bounds": [list(b) for b in state.pp_patches_token_start_end_idx_global]}
+            n_local = sum(e - s for s, e in state.pp_patches_token_start_end_idx_global)
+            # the wrapper reads the latent width in pixels from the last dimension
+            rows = fwd(wrapper, torch.zeros(1, n_local, w // vae))[0, :, 0].long().tolist()
+            rec["whole_image_rows"] = _runs(rows)
+            state.patch_mode = True
+            rec["patch_rows"] = []
+            for p in range(state.num_pipeline_patch):
+                state.pipeline_patch_idx = p
+                s, e = state.pp_patches_token_start_end_idx_global[p]
+                rec["patch_rows"].append(_runs(fwd(wrapper, torch.zeros(1, e - s, w // vae))[0, :, 0].long().tolist()))
+            cases.append(rec)
+    with open(os.path.join(HERE, "pos_embed_rows.json"), "w") as f:
+        json.dump(cases, f, separators=(",", ":"))
+    print("pos_embed_rows.json written:", len(cases), "cases")
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="root of a Hetu-DiT checkout")
@@ -576,3 +752,7 @@ if __name__ == "__main__":
         gen_rope(a.reference)
     if a.only in ("", "usp"):
         gen_usp(a.reference)
+    if a.only in ("", "pos_embed_rows"):
+        gen_pos_embed_rows(a.reference)
+    if a.only in ("", "pipefusion_order"):
+        gen_pipefusion_order(a.reference)

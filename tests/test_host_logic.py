@@ -462,3 +462,132 @@ def test_set_activate_groups_with_the_reference_call_forms():
             assert a.group(axis).ranks == b.group(axis).ranks, (me, axis)
         assert a.group("sp").ulysses_group.ranks == b.group("sp").ulysses_group.ranks
     ps.destroy_model_parallel()
+
+
+# ----------------------------------------------------------------------------- PipeFusion schedule order
+def _pipefusion_cases():
+    import json
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "pipefusion_order.json")) as f:
+        return json.load(f)
+
+
+@pytest.mark.parametrize("case", _pipefusion_cases(),
+                         ids=lambda c: f"pp{c['stages']}s{c['stage']}m{c['num_pipeline_patch']}n{c['steps']}w{c['warmup']}")
+def test_pipefusion_schedule_order_matches_reference(case, monkeypatch):
+    """Every stage's order of receives, receive-queue operations, forwards (patch index, step, text source),
+    scheduler steps and sends through the warm-up and the patch pipeline is the one the reference's
+    _sync_pipeline / _init_async_pipeline / _async_pipeline produce
+    (model_executor/pipelines/pipeline_stable_diffusion_3.py:1352-1678, run with recording stand-ins by
+    tests/golden/make_golden.py)."""
+    import types
+    from hetu_dit_b200.model_executor.pipelines import pipeline_sd3_shaped as mod
+    stages, stage, n_patch = case["stages"], case["stage"], case["num_pipeline_patch"]
+    events, tokens = [], 4
+
+    class Group:
+        def pipeline_recv(self, idx=-1, name="latent"):
+            events.append(["recv", name or "latent", idx])
+            return torch.zeros(1, tokens * n_patch, 8)
+
+        def pipeline_send(self, tensor, name="latent", segment_idx=-1):
+            events.append(["send", name, segment_idx])
+
+        pipeline_isend = pipeline_send
+
+        def add_pipeline_recv_task(self, idx=-1, name="latent"):
+            events.append(["add_recv_task", name or "latent", idx])
+
+        def recv_next(self):
+            events.append(["recv_next"])
+
+        def get_pipeline_recv_data(self, idx=-1, name="latent"):
+            events.append(["get", name, idx])
+            return torch.zeros(1, tokens, 8)
+
+    class State:
+        ready = False
+        num_pipeline_patch = n_patch
+        pp_patches_token_num = [tokens] * n_patch
+        runtime_config = types.SimpleNamespace(warmup_steps=case["warmup"])
+        pipeline_patch_idx = 0
+
+        def set_patched_mode(self, patch_mode):
+            events.append(["patched_mode", bool(patch_mode)])
+            self.pipeline_patch_idx = 0
+
+        def next_patch(self):
+            self.pipeline_patch_idx = (self.pipeline_patch_idx + 1) % n_patch
+
+    state, group = State(), Group()
+    fake_ps = types.SimpleNamespace(
+        get_pp_group=lambda: group, is_pipeline_first_stage=lambda: stage == 0,
+        is_pipeline_last_stage=lambda: stage == stages - 1, get_pipeline_parallel_world_size=lambda: stages,
+        get_sequence_parallel_world_size=lambda: 1)
+    monkeypatch.setattr(mod, "ps", fake_ps)
+    monkeypatch.setattr(mod, "get_runtime_state", lambda: state)
+    monkeypatch.setattr(mod, "flow_match_sigmas", lambda n, device=None: torch.arange(n + 1, dtype=torch.float32))
+    prompt = torch.zeros(2, 3, 8)
+
+    pipe = object.__new__(mod.SD3ShapedPipeline)
+
+    def backbone(latents, encoder_hidden_states, pooled, t, guide=True):
+        assert guide == (stage != stages - 1)  # the last stage leaves guidance to the fused step
+        events.append(["forward", state.pipeline_patch_idx, int(t),
+                       "prompt" if encoder_hidden_states is prompt else "received"])
+        return latents, torch.zeros(2, 3, 8)
+
+    def guided_step(noise_pred, last_latents, i, send_as=None):
+        events.append(["step", int(i)])
+        if send_as is not None:
+            events.append(["send", send_as[0], send_as[1]])
+        return noise_pred
+
+    pipe._backbone_forward = backbone
+    pipe._guided_step = guided_step
+    out = pipe.diffusion_stage(torch.zeros(1, tokens * n_patch, 8), prompt, None, case["steps"])
+    assert (out is not None) == (stage == stages - 1)
+    assert events[-1] == ["patched_mode", False]  # the entry point leaves the runtime state unpatched
+    assert events[:-1] == case["events"]
+
+
+# ----------------------------------------------------------------------------- position rows per rank
+def _pos_cases():
+    import json
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "pos_embed_rows.json")) as f:
+        return json.load(f)
+
+
+@pytest.mark.parametrize("case", _pos_cases(),
+                         ids=lambda c: f"{c['height']}x{c['width']}m{c['num_pipeline_patch']}sp{c['sp_world']}r{c['sp_rank']}")
+def test_position_rows_match_reference_patch_embed(case, monkeypatch):
+    """The rows of the position table a rank adds to its tokens -- whole-image mode and every patch of patch
+    mode -- are the rows the reference's patch-embedding wrapper slices
+    (model_executor/diffusion_executor/layers/embeddings.py:90-112), run on a table of row numbers by
+    tests/golden/make_golden.py."""
+    import types
+    from hetu_dit_b200.model_executor.pipelines import pipeline_sd3_shaped as mod
+    cell = case["vae"] * case["patch"]
+    gh, gw = case["height"] // cell, case["width"] // cell
+    state = types.SimpleNamespace(pp_patches_token_start_end_idx_global=[tuple(b) for b in case["bounds"]],
+                                  patch_mode=False, pipeline_patch_idx=0)
+    monkeypatch.setattr(mod, "get_runtime_state", lambda: state)
+    monkeypatch.setattr(mod, "ps", types.SimpleNamespace(get_sequence_parallel_world_size=lambda: case["sp_world"]))
+    pipe = object.__new__(mod.SD3ShapedPipeline)
+    pipe.grid = (gh, gw)
+    pipe.model = types.SimpleNamespace(
+        _sincos_pos=lambda h, w, device, dtype: torch.arange(h * w, dtype=torch.float32).reshape(1, h * w, 1))
+
+    def rows(n):
+        return pipe._positions(n, "cpu", torch.float32)[0, :, 0].long().tolist()
+
+    def flat(runs):
+        return [i for s, e in runs for i in range(s, e)]
+
+    n_local = sum(e - s for s, e in case["bounds"])
+    assert rows(n_local) == flat(case["whole_image_rows"])
+    state.patch_mode = True
+    for p, runs in enumerate(case["patch_rows"]):
+        state.pipeline_patch_idx = p
+        assert rows(case["bounds"][p][1] - case["bounds"][p][0]) == flat(runs)
+    with pytest.raises(ValueError):
+        pipe._positions(n_local + 1, "cpu", torch.float32)
