@@ -140,6 +140,35 @@ class NormRopeArgs(ctypes.Structure):
     ]
 
 
+class GemmArgs(ctypes.Structure):
+    _fields_ = [
+        ("dtype", ctypes.c_int32),
+        ("epilogue", ctypes.c_int32),
+        ("m", ctypes.c_int64),
+        ("n", ctypes.c_int64),
+        ("k", ctypes.c_int64),
+        ("a", ctypes.c_void_p),
+        ("lda", ctypes.c_int64),
+        ("w", ctypes.c_void_p),
+        ("ldw", ctypes.c_int64),
+        ("bias", ctypes.c_void_p),
+        ("out", ctypes.c_void_p),
+        ("ldo", ctypes.c_int64),
+        ("residual", ctypes.c_void_p),
+        ("ldr", ctypes.c_int64),
+        ("gate", ctypes.c_void_p),
+        ("gate_batch_stride", ctypes.c_int64),
+        ("rows_per_batch", ctypes.c_int64),
+        ("tile_n", ctypes.c_int32),
+        ("max_ctas", ctypes.c_int32),
+        ("stream", ctypes.c_void_p),
+        ("tile_m", ctypes.c_int32),
+        ("reserved0", ctypes.c_int32),
+    ]
+
+
+GEMM_BIAS, GEMM_BIAS_GELU_TANH, GEMM_BIAS_GATE_RESIDUAL = 0, 1, 2
+
 _lib = None
 _lock = threading.Lock()
 
@@ -175,6 +204,8 @@ def _declare(lib):
     lib.hdit_cfg_euler_step.argtypes = [ctypes.c_int32] + [ctypes.c_void_p] * 5 + [ctypes.c_int64, ctypes.c_float,
                                                                                  ctypes.c_void_p, ctypes.c_int32,
                                                                                  ctypes.c_void_p]
+    lib.hdit_linear_fused.restype = ctypes.c_int
+    lib.hdit_linear_fused.argtypes = [ctypes.POINTER(GemmArgs)]
     lib.hdit_heap_alloc.restype = ctypes.c_int
     lib.hdit_heap_alloc.argtypes = [ctypes.c_int64, ctypes.POINTER(ctypes.c_void_p)]
     lib.hdit_heap_free.restype = ctypes.c_int

@@ -1,5 +1,6 @@
 """Tensor-level entry points over the C ABI (torch is used for device memory and streams only)."""
 import ctypes
+import os
 
 import torch
 
@@ -476,6 +477,77 @@ def gelu_tanh(x, out=None):
                                          _stream_ptr(x.device)))
     _count()
     return out
+
+
+def linear_fused(x, weight, bias=None, epilogue="bias", residual=None, gate=None, out=None, tile_n=0, max_ctas=0,
+                 tile_m=0):
+    """epilogue(x @ weight.T + bias) in one tensor-core kernel (csrc/gemm_sm100.cu). x (B, S, K) or (rows, K) with
+    evenly strided rows, weight (N, K) as torch.nn.Linear stores it. epilogue: "bias" (a plain linear layer),
+    "gelu_tanh", or "gate_residual" = residual + gate[:, None, :] * linear(x) with gate (B, N) and residual of the
+    output's shape. `out` may be a column block of a wider buffer, or `residual` itself."""
+    _require_cuda(x)
+    if x.dim() == 2:
+        res3 = residual.unsqueeze(0) if residual is not None else None
+        out3 = out.unsqueeze(0) if out is not None else None
+        return linear_fused(x.unsqueeze(0), weight, bias, epilogue, res3, gate, out3, tile_n, max_ctas, tile_m)[0]
+    rows, k, _, xs = _rows_view(x)
+    n = weight.shape[0]
+    if weight.dim() != 2 or weight.shape[1] != k or weight.stride(1) != 1 or weight.dtype != x.dtype:
+        raise ValueError("weight must be (N, K), K-contiguous, of x's dtype")
+    if out is None:
+        out = torch.empty(tuple(x.shape[:-1]) + (n,), dtype=x.dtype, device=x.device)
+    rows_o, n_o, _, os_ = _rows_view(out)
+    if (rows_o, n_o) != (rows, n):
+        raise ValueError("out does not match (rows, N)")
+    a = _C.GemmArgs()
+    a.dtype = _DTYPE_CODE[x.dtype]
+    a.epilogue = {"bias": _C.GEMM_BIAS, "gelu_tanh": _C.GEMM_BIAS_GELU_TANH,
+                  "gate_residual": _C.GEMM_BIAS_GATE_RESIDUAL}[epilogue]
+    a.m, a.n, a.k = rows, n, k
+    a.a, a.lda = x.data_ptr(), xs
+    a.w, a.ldw = weight.data_ptr(), weight.stride(0)
+    if bias is not None:
+        if bias.numel() != n or not bias.is_contiguous() or bias.dtype != x.dtype:
+            raise ValueError("bias must be N contiguous elements of x's dtype")
+        a.bias = bias.data_ptr()
+    a.out, a.ldo = out.data_ptr(), os_
+    if epilogue == "gate_residual":
+        rows_r, n_r, _, rs = _rows_view(residual)
+        if (rows_r, n_r) != (rows, n):
+            raise ValueError("residual does not match (rows, N)")
+        if gate.dim() != 2 or gate.shape[1] != n or gate.stride(1) != 1 or rows % gate.shape[0] != 0:
+            raise ValueError("gate must be (B, N) with rows a multiple of B")
+        a.residual, a.ldr = residual.data_ptr(), rs
+        a.gate, a.gate_batch_stride = gate.data_ptr(), gate.stride(0)
+        a.rows_per_batch = rows // gate.shape[0]
+    a.tile_n, a.max_ctas, a.tile_m = tile_n, max_ctas, tile_m
+    with torch.cuda.device(x.device):
+        a.stream = _stream_ptr(x.device)
+        _C.check(_C.lib().hdit_linear_fused(ctypes.byref(a)))
+    _count()
+    return out
+
+
+# Whether linear_tail() runs the fused tensor-core kernel (True) or the library GEMM followed by the one-pass
+# tail kernel (False). HDIT_FUSED_LINEAR=0/1 overrides the default.
+FUSED_LINEAR = os.environ.get("HDIT_FUSED_LINEAR", "0") == "1"
+
+
+def linear_tail(linear, x, epilogue, residual=None, gate=None, out=None):
+    """A torch.nn.Linear followed by its elementwise tail ("gelu_tanh", or "gate_residual" = residual +
+    gate[:, None] * linear(x)), as one kernel when FUSED_LINEAR is set and the layouts allow it (rows evenly
+    strided across the batch), else as the library GEMM plus hdit_gelu_tanh / hdit_gate_residual."""
+    fusable = (FUSED_LINEAR and x.is_cuda and x.dim() == 3 and _even_rows(x) and not torch.is_grad_enabled()
+               and (out is None or _even_rows(out)) and (residual is None or _even_rows(residual))
+               and (gate is None or gate.stride(-1) == 1))
+    if fusable:
+        return linear_fused(x, linear.weight, linear.bias, epilogue, residual=residual, gate=gate, out=out)
+    y = linear(x)
+    if epilogue == "gelu_tanh":
+        return gelu_tanh(y, out=y if out is None else out)
+    if epilogue == "gate_residual":
+        return gate_residual(residual, gate, y, out=out)
+    raise ValueError(epilogue)
 
 
 def cfg_euler_step(noise_pred, sample, sigmas, step_index, guidance_scale, cfg=True, out=None, out_peer_ptr=None):

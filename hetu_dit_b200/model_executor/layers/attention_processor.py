@@ -66,6 +66,13 @@ def _project_into(buf, row0, x, linear):
         buf[:, row0:row0 + S] = linear(x)
 
 
+def _out_proj(linear, x, tail):
+    """Output projection; tail = (residual, gate) folds the block's gated residual addition into it."""
+    if tail is None:
+        return linear(x)
+    return kernels.linear_tail(linear, x, "gate_residual", residual=tail[0], gate=tail[1])
+
+
 class _Operators:
     """Lazily built USP operators of one attention layer, rebuilt when the SP degree changes (the reference
     re-creates them in worker.py:1848-1983 on a plan switch)."""
@@ -104,7 +111,8 @@ class JointAttnProcessor:
         ops = list(self._ops._ops.values())
         return ops[0] if ops else None
 
-    def _sharded_text(self, attn, hidden_states, encoder_hidden_states, rope, text_total, token_offset, text_offset):
+    def _sharded_text(self, attn, hidden_states, encoder_hidden_states, rope, text_total, token_offset, text_offset,
+                      tails=(None, None)):
         B, S_img, _ = hidden_states.shape
         S_txt = encoder_hidden_states.shape[1]
         t0, i0 = (0, S_txt) if attn.text_first else (S_img, 0)
@@ -124,16 +132,19 @@ class JointAttnProcessor:
         out = self._ops.get(hetuDiTLongContextAttention)(_cache_key(attn), q, k, v, dropout_p=0.0, causal=False,
                                                          qk_prologue=sorted(ranges, key=lambda r: r[0]))
         out = out.reshape(B, S_txt + S_img, attn.heads * attn.head_dim)
-        return attn.to_out[0](out[:, i0:i0 + S_img]), attn.to_add_out(out[:, t0:t0 + S_txt])
+        return (_out_proj(attn.to_out[0], out[:, i0:i0 + S_img], tails[0]),
+                _out_proj(attn.to_add_out, out[:, t0:t0 + S_txt], tails[1]))
 
     def __call__(self, attn, hidden_states, encoder_hidden_states=None, image_rotary_emb=None, text_len=None,
-                 token_offset: int = 0, text_offset=None):
+                 token_offset: int = 0, text_offset=None, tails=(None, None)):
+        """tails = ((residual, gate) | None for the image stream, the same for the text stream): the stream's
+        result is residual + gate[:, None] * projected attention output instead of the projected output."""
         strategy = "front" if attn.text_first else "rear"
         B, S_img, _ = hidden_states.shape
         S_txt = encoder_hidden_states.shape[1]
         if text_offset is not None and ps.get_sequence_parallel_world_size() > 1:
             return self._sharded_text(attn, hidden_states, encoder_hidden_states, image_rotary_emb,
-                                      int(text_len or S_txt), token_offset, text_offset)
+                                      int(text_len or S_txt), token_offset, text_offset, tails)
         q, k, v = (_heads(p(hidden_states), attn) for p in (attn.to_q, attn.to_k, attn.to_v))
         tq, tk, tv = (_heads(p(encoder_hidden_states), attn) for p in (attn.add_q_proj, attn.add_k_proj, attn.add_v_proj))
         text_rows = S_txt if attn.rope_on_text else 0
@@ -157,7 +168,7 @@ class JointAttnProcessor:
             img, txt = out[:, :S_img], out[:, S_img:]
         else:
             txt, img = out[:, :S_txt], out[:, S_txt:]
-        return attn.to_out[0](img), attn.to_add_out(txt)
+        return _out_proj(attn.to_out[0], img, tails[0]), _out_proj(attn.to_add_out, txt, tails[1])
 
 
 class SingleAttnProcessor:

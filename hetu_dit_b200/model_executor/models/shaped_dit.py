@@ -117,8 +117,7 @@ class _GELUProj(nn.Module):
         self.proj = nn.Linear(d_in, d_out)
 
     def forward(self, x):
-        y = self.proj(x)
-        return kernels.gelu_tanh(y, out=y)
+        return kernels.linear_tail(self.proj, x, "gelu_tanh")
 
 
 class FeedForward(nn.Module):
@@ -126,10 +125,13 @@ class FeedForward(nn.Module):
         super().__init__()
         self.net = nn.ModuleList([_GELUProj(dim, dim * mult), nn.Identity(), nn.Linear(dim * mult, dim)])
 
-    def forward(self, x):
-        for m in self.net:
-            x = m(x)
-        return x
+    def forward(self, x, residual=None, gate=None):
+        """residual / gate given: returns residual + gate[:, None] * mlp(x) (the gated residual addition that
+        follows the MLP in an adaLN-Zero block rides on the second linear layer)."""
+        x = self.net[1](self.net[0](x))
+        if residual is None:
+            return self.net[2](x)
+        return kernels.linear_tail(self.net[2], x, "gate_residual", residual=residual, gate=gate)
 
 
 class RMSNormWeight(nn.Module):
@@ -241,24 +243,29 @@ class JointBlock(nn.Module):
         # LayerNorm + modulation and gate + residual are one fused pass each (csrc/elementwise.cu)
         h = kernels.ln_modulate(hidden, mod[0], mod[1])
         c = kernels.ln_modulate(context, cmod[0], cmod[1])
+        sp = ps.get_sequence_parallel_world_size() > 1 and hidden.is_cuda
+        # with fused linear layers the gated residual of the image stream rides on the attention's output
+        # projection (and the text stream's too, unless its tail runs on the branch stream below)
+        fuse = kernels.FUSED_LINEAR and hidden.is_cuda
+        tails = ((hidden, mod[2]) if fuse else None, (context, cmod[2]) if fuse and not sp else None)
         a_img, a_txt = self.attn(h, encoder_hidden_states=c, image_rotary_emb=rope, token_offset=token_offset,
-                                 text_len=text_total, text_offset=text_offset)
-        if ps.get_sequence_parallel_world_size() > 1 and hidden.is_cuda:
+                                 text_len=text_total, text_offset=text_offset, tails=tails)
+        if sp:
             # the text stream's tail is independent of the image stream's: under sequence parallelism its
             # GEMMs have few rows and stream their weights, so they run beside the image stream's
             with _Branch(hidden.device) as br:
                 ctx_in = context
                 context = kernels.gate_residual(ctx_in, cmod[2], a_txt)
-                context = kernels.gate_residual(context, cmod[5],
-                                                self.ff_context(kernels.ln_modulate(context, cmod[3], cmod[4])))
-            hidden = kernels.gate_residual(hidden, mod[2], a_img)
-            hidden = kernels.gate_residual(hidden, mod[5], self.ff(kernels.ln_modulate(hidden, mod[3], mod[4])))
+                context = self.ff_context(kernels.ln_modulate(context, cmod[3], cmod[4]), residual=context,
+                                          gate=cmod[5])
+            hidden = a_img if fuse else kernels.gate_residual(hidden, mod[2], a_img)
+            hidden = self.ff(kernels.ln_modulate(hidden, mod[3], mod[4]), residual=hidden, gate=mod[5])
             br.join()
             return hidden, context
-        hidden = kernels.gate_residual(hidden, mod[2], a_img)
-        hidden = kernels.gate_residual(hidden, mod[5], self.ff(kernels.ln_modulate(hidden, mod[3], mod[4])))
-        context = kernels.gate_residual(context, cmod[2], a_txt)
-        context = kernels.gate_residual(context, cmod[5], self.ff_context(kernels.ln_modulate(context, cmod[3], cmod[4])))
+        hidden = a_img if fuse else kernels.gate_residual(hidden, mod[2], a_img)
+        hidden = self.ff(kernels.ln_modulate(hidden, mod[3], mod[4]), residual=hidden, gate=mod[5])
+        context = a_txt if fuse else kernels.gate_residual(context, cmod[2], a_txt)
+        context = self.ff_context(kernels.ln_modulate(context, cmod[3], cmod[4]), residual=context, gate=cmod[5])
         return hidden, context
 
 
@@ -286,21 +293,20 @@ class SingleBlock(nn.Module):
             # no concatenated copy
             B, S, d = x.shape
             buf = torch.empty((B, S, 5 * d), dtype=x.dtype, device=x.device)
-            kernels.gelu_tanh(self.proj_mlp(h), out=buf[..., d:])
+            kernels.linear_tail(self.proj_mlp, h, "gelu_tanh", out=buf[..., d:])
             self.attn(h, image_rotary_emb=rope, text_len=text_len, token_offset=token_offset, out=buf[..., :d])
-            return kernels.gate_residual(x, gate, self.proj_out(buf))
+            return kernels.linear_tail(self.proj_out, buf, "gate_residual", residual=x, gate=gate)
         # MLP branch beside the attention: its GEMM fills the SMs that the head-sharded attention grid leaves
         # free and the time the two peer exchanges spend waiting on flags
         B, S, d = x.shape
         buf = torch.empty((B, S, 5 * d), dtype=x.dtype, device=x.device)
         with _Branch(x.device) as br:
-            mlp = self.proj_mlp(h)
-            kernels.gelu_tanh(mlp, out=buf[..., d:])
+            kernels.linear_tail(self.proj_mlp, h, "gelu_tanh", out=buf[..., d:])
         a = self.attn(h, image_rotary_emb=rope, text_len=text_len, token_offset=token_offset, text_offset=text_offset,
                       text_total=text_total)
         buf[..., :d].copy_(a)
         br.join()
-        return kernels.gate_residual(x, gate, self.proj_out(buf))
+        return kernels.linear_tail(self.proj_out, buf, "gate_residual", residual=x, gate=gate)
 
 
 class CogVideoXBlock(nn.Module):

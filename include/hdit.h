@@ -405,6 +405,51 @@ HDIT_API int hdit_cfg_euler_step(int32_t dtype, const void* uncond, const void* 
                                  void* out_peer, int64_t n_elems, float guidance_scale, const float* sigmas,
                                  int32_t step_index, void* stream);
 
+/*
+ * Linear layer with a fused tail:  out[r, :] = tail(a[r, :] . w^T + bias)  for a (m, k) and w (n, k), both with k
+ * contiguous (the layout torch.nn.Linear stores), 16-bit storage, fp32 accumulation on the tensor cores
+ * (tcgen05.mma, accumulators in tensor memory), the bias added in fp32 and the sum rounded to the storage type
+ * once -- the value an unfused linear layer writes -- before the tail:
+ *   HDIT_GEMM_BIAS               : nothing more
+ *   HDIT_GEMM_BIAS_GELU_TANH     : GELU, tanh approximation (as hdit_gelu_tanh)
+ *   HDIT_GEMM_BIAS_GATE_RESIDUAL : residual[r, :] + gate[r / rows_per_batch, :] * value (as hdit_gate_residual)
+ * Row strides (lda, ldw, ldo, ldr, gate_batch_stride) in elements, multiples of 8; pointers 16-byte aligned; n and k
+ * multiples of 8; m, n, k ragged against the tile sizes are handled. `out` may alias `residual`. bias may be NULL.
+ * tile_m x tile_n: output tile of one CTA, 128 x 256, 128 x 128 or 256 x 256; 0 lets the library choose by the
+ * number of waves. max_ctas: 0 = one persistent CTA per SM.
+ *
+ * In the reference these are the torch.nn.Linear layers of the blocks it wraps followed by eager elementwise
+ * kernels: the MLP of hetuDiTFeedForwardWrapper.forward (layers/feedforward.py:73-78: linear, GELU, linear) and the
+ * output projections and gated residual additions around hetuDiTAttentionWrapper.forward
+ * (layers/attention_processor.py:207-449).
+ */
+enum { HDIT_GEMM_BIAS = 0, HDIT_GEMM_BIAS_GELU_TANH = 1, HDIT_GEMM_BIAS_GATE_RESIDUAL = 2 };
+
+typedef struct hdit_gemm_args {
+  int32_t dtype;     /* HDIT_BF16 / HDIT_FP16 */
+  int32_t epilogue;  /* HDIT_GEMM_* */
+  int64_t m, n, k;
+  const void* a;
+  int64_t lda;
+  const void* w;
+  int64_t ldw;
+  const void* bias; /* n elements or NULL */
+  void* out;
+  int64_t ldo;
+  const void* residual; /* (m, n), HDIT_GEMM_BIAS_GATE_RESIDUAL only */
+  int64_t ldr;
+  const void* gate; /* (m / rows_per_batch, n) */
+  int64_t gate_batch_stride;
+  int64_t rows_per_batch;
+  int32_t tile_n;
+  int32_t max_ctas;
+  void* stream;
+  int32_t tile_m;
+  int32_t reserved0;
+} hdit_gemm_args;
+
+HDIT_API int hdit_linear_fused(const hdit_gemm_args* args);
+
 #ifdef __cplusplus
 }
 #endif

@@ -37,16 +37,18 @@ def test_ctypes_structs_match_header_layout(tmp_path):
     src = tmp_path / "sizes.c"
     src.write_text(
         '#include <stdio.h>\n#include <stddef.h>\n#include "hdit.h"\n'
-        'int main(void) { printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(hdit_seg), sizeof(hdit_copy_piece), '
+        'int main(void) { printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(hdit_seg), sizeof(hdit_copy_piece), '
         'sizeof(hdit_attn_args), sizeof(hdit_norm_rope_tensor), sizeof(hdit_norm_rope_args), '
         'offsetof(hdit_attn_args, n_out_dst), offsetof(hdit_attn_args, q_dst_row0), '
-        'offsetof(hdit_norm_rope_tensor, dst)); return 0; }\n')
+        'offsetof(hdit_norm_rope_tensor, dst), sizeof(hdit_gemm_args), offsetof(hdit_gemm_args, stream)); '
+        'return 0; }\n')
     exe = tmp_path / "sizes"
     subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
     want = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
     got = [ctypes.sizeof(_C.Seg), ctypes.sizeof(_C.CopyPiece), ctypes.sizeof(_C.AttnArgs),
            ctypes.sizeof(_C.NormRopeTensor), ctypes.sizeof(_C.NormRopeArgs), _C.AttnArgs.n_out_dst.offset,
-           _C.AttnArgs.q_dst_row0.offset, _C.NormRopeTensor.dst.offset]
+           _C.AttnArgs.q_dst_row0.offset, _C.NormRopeTensor.dst.offset, ctypes.sizeof(_C.GemmArgs),
+           _C.GemmArgs.stream.offset]
     assert got == want
 
 
@@ -63,6 +65,14 @@ def test_argument_checks_without_gpu():
     a = _C.AttnArgs()
     a.dtype, a.head_dim, a.batch, a.heads, a.n_q_seg, a.n_kv_seg = _C.HDIT_BF16, 96, 1, 1, 1, 1
     assert _C.lib().hdit_attn_fwd(ctypes.byref(a)) == _C.HDIT_ERR_SHAPE
+    g = _C.GemmArgs()
+    g.dtype, g.m, g.n, g.k = _C.HDIT_BF16, 16, 12, 64  # n not a multiple of 8
+    g.a = g.w = g.out = 256
+    g.lda = g.ldw = 64
+    g.ldo = 16
+    assert _C.lib().hdit_linear_fused(ctypes.byref(g)) == _C.HDIT_ERR_SHAPE
+    g.n, g.epilogue = 16, 7
+    assert _C.lib().hdit_linear_fused(ctypes.byref(g)) == _C.HDIT_ERR_BAD_ARG
     a.head_dim, a.n_kv_seg = 64, 11
     assert _C.lib().hdit_attn_fwd(ctypes.byref(a)) == _C.HDIT_ERR_SHAPE
     assert b"n_kv_seg" in _C.lib().hdit_last_error()
