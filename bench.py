@@ -498,7 +498,7 @@ def run_gpu(args):
                    "parallelism": f"ulysses{U}xring{R}" if world > 1 else "single",
                    "text_stream": text_layout,
                    "l2": "weights and activations exceed the 126 MB L2; no explicit flush",
-                   "cuda_graph": use_graph,
+                   "cuda_graph": use_graph, "fused_linear": bool(kernels.FUSED_LINEAR),
                    "ms_per_step_eager_launches": ms_eager,
                    "ms_per_step_replicated_text": ms_replicated,
                    "step_flops": step_flops,
@@ -588,6 +588,29 @@ def run_kernel_case(args):
         fn = lambda: kernels.gate_residual(x, gate, y, out=out)
         work = 3.0 * x.numel() * 2
         unit = "GB/s"
+    elif kind in ("linear", "linearlib"):
+        # linear:<rows>:<n>:<k>:<bias|gelu_tanh|gate_residual>[:<tile_m>x<tile_n>] -- the fused tensor-core kernel;
+        # linearlib:... the library GEMM followed by the one-pass tail kernel it replaces
+        parts = arg.split(":")
+        M, N, K = (int(v) for v in parts[:3])
+        epi = parts[3] if len(parts) > 3 else "bias"
+        tm, tn = (int(v) for v in parts[4].split("x")) if len(parts) > 4 else (0, 0)
+        x = torch.randn(1, M, K, device=dev, dtype=torch.bfloat16)
+        lin = torch.nn.Linear(K, N, device=dev, dtype=torch.bfloat16)
+        res = torch.randn(1, M, N, device=dev, dtype=torch.bfloat16)
+        gate = torch.randn(1, N, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(1, M, N, device=dev, dtype=torch.bfloat16)
+        if kind == "linear":
+            fn = lambda: kernels.linear_fused(x, lin.weight, lin.bias, epi, residual=res, gate=gate, out=out, tile_m=tm,
+                                              tile_n=tn)
+        elif epi == "gelu_tanh":
+            fn = lambda: kernels.gelu_tanh(lin(x), out=out)
+        elif epi == "gate_residual":
+            fn = lambda: kernels.gate_residual(res, gate, lin(x), out=out)
+        else:
+            fn = lambda: lin(x)
+        work = 2.0 * M * N * K
+        unit = "TFLOP/s"
     else:
         raise SystemExit(f"unknown kernel case {args.kernel_case}")
     for _ in range(3):
@@ -786,7 +809,9 @@ def main():
                     help="wrap one extra eager step in cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--kernel-case", default="",
                     help="one kernel instead of the step: attn:<batch>, attnheads:<heads> (attnheads1: no KV split), "
-                         "copy:<MiB>, normrope:<batch>, lnmod:<batch>, gate:<batch>, usp:<flux|cogvideox|hunyuan>")
+                         "copy:<MiB>, normrope:<batch>, lnmod:<batch>, gate:<batch>, "
+                         "linear:<rows>:<n>:<k>:<tail>[:<tile_m>x<tile_n>], linearlib:<rows>:<n>:<k>:<tail>, "
+                         "usp:<flux|cogvideox|hunyuan>")
     args = ap.parse_args()
     if args.kernel_case.startswith("usp:"):
         run_usp_case(args)

@@ -163,7 +163,7 @@ class GemmArgs(ctypes.Structure):
         ("max_ctas", ctypes.c_int32),
         ("stream", ctypes.c_void_p),
         ("tile_m", ctypes.c_int32),
-        ("reserved0", ctypes.c_int32),
+        ("cta_pair", ctypes.c_int32),
     ]
 
 

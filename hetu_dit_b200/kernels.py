@@ -480,7 +480,7 @@ def gelu_tanh(x, out=None):
 
 
 def linear_fused(x, weight, bias=None, epilogue="bias", residual=None, gate=None, out=None, tile_n=0, max_ctas=0,
-                 tile_m=0):
+                 tile_m=0, cta_pair=0):
     """epilogue(x @ weight.T + bias) in one tensor-core kernel (csrc/gemm_sm100.cu). x (B, S, K) or (rows, K) with
     evenly strided rows, weight (N, K) as torch.nn.Linear stores it. epilogue: "bias" (a plain linear layer),
     "gelu_tanh", or "gate_residual" = residual + gate[:, None, :] * linear(x) with gate (B, N) and residual of the
@@ -489,7 +489,7 @@ def linear_fused(x, weight, bias=None, epilogue="bias", residual=None, gate=None
     if x.dim() == 2:
         res3 = residual.unsqueeze(0) if residual is not None else None
         out3 = out.unsqueeze(0) if out is not None else None
-        return linear_fused(x.unsqueeze(0), weight, bias, epilogue, res3, gate, out3, tile_n, max_ctas, tile_m)[0]
+        return linear_fused(x.unsqueeze(0), weight, bias, epilogue, res3, gate, out3, tile_n, max_ctas, tile_m, cta_pair)[0]
     rows, k, _, xs = _rows_view(x)
     n = weight.shape[0]
     if weight.dim() != 2 or weight.shape[1] != k or weight.stride(1) != 1 or weight.dtype != x.dtype:
@@ -520,7 +520,7 @@ def linear_fused(x, weight, bias=None, epilogue="bias", residual=None, gate=None
         a.residual, a.ldr = residual.data_ptr(), rs
         a.gate, a.gate_batch_stride = gate.data_ptr(), gate.stride(0)
         a.rows_per_batch = rows // gate.shape[0]
-    a.tile_n, a.max_ctas, a.tile_m = tile_n, max_ctas, tile_m
+    a.tile_n, a.max_ctas, a.tile_m, a.cta_pair = tile_n, max_ctas, tile_m, cta_pair
     with torch.cuda.device(x.device):
         a.stream = _stream_ptr(x.device)
         _C.check(_C.lib().hdit_linear_fused(ctypes.byref(a)))
@@ -529,8 +529,17 @@ def linear_fused(x, weight, bias=None, epilogue="bias", residual=None, gate=None
 
 
 # Whether linear_tail() runs the fused tensor-core kernel (True) or the library GEMM followed by the one-pass
-# tail kernel (False). HDIT_FUSED_LINEAR=0/1 overrides the default.
+# tail kernel (False). Off by default: measured inside the whole step the fused kernel is 1 to 3 % behind
+# (Flux-shaped 69.5 against 68.1-69.1 ms, SD3-shaped 12.32 against 12.00 ms per step) although alone it matches
+# the pair of kernels it replaces -- without multicast loads it moves more operand bytes from L2 per flop than
+# the library's kernels, and under the power cap that costs clock. HDIT_FUSED_LINEAR=1 turns it on.
 FUSED_LINEAR = os.environ.get("HDIT_FUSED_LINEAR", "0") == "1"
+# The fused kernel is used between these row counts. Below, the library's split-K GEMMs fill the GPU better than
+# whole output tiles do (measured at 576 to 2304 rows: the fused kernel takes 1.2x to 2x the library GEMM + tail
+# kernel). Above (video-length sequences) the kernel sits at the power cap for long: measured 0.8x to 0.97x of
+# the library path at 18 k rows.
+FUSED_LINEAR_MIN_ROWS = int(os.environ.get("HDIT_FUSED_LINEAR_MIN_ROWS", "4096"))
+FUSED_LINEAR_MAX_ROWS = int(os.environ.get("HDIT_FUSED_LINEAR_MAX_ROWS", "12288"))
 
 
 def linear_tail(linear, x, epilogue, residual=None, gate=None, out=None):
@@ -538,6 +547,7 @@ def linear_tail(linear, x, epilogue, residual=None, gate=None, out=None):
     gate[:, None] * linear(x)), as one kernel when FUSED_LINEAR is set and the layouts allow it (rows evenly
     strided across the batch), else as the library GEMM plus hdit_gelu_tanh / hdit_gate_residual."""
     fusable = (FUSED_LINEAR and x.is_cuda and x.dim() == 3 and _even_rows(x) and not torch.is_grad_enabled()
+               and FUSED_LINEAR_MIN_ROWS <= x.shape[0] * x.shape[1] <= FUSED_LINEAR_MAX_ROWS
                and (out is None or _even_rows(out)) and (residual is None or _even_rows(residual))
                and (gate is None or gate.stride(-1) == 1))
     if fusable:

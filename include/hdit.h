@@ -415,8 +415,9 @@ HDIT_API int hdit_cfg_euler_step(int32_t dtype, const void* uncond, const void* 
  *   HDIT_GEMM_BIAS_GATE_RESIDUAL : residual[r, :] + gate[r / rows_per_batch, :] * value (as hdit_gate_residual)
  * Row strides (lda, ldw, ldo, ldr, gate_batch_stride) in elements, multiples of 8; pointers 16-byte aligned; n and k
  * multiples of 8; m, n, k ragged against the tile sizes are handled. `out` may alias `residual`. bias may be NULL.
- * tile_m x tile_n: output tile of one CTA, 128 x 256, 128 x 128 or 256 x 256; 0 lets the library choose by the
- * number of waves. max_ctas: 0 = one persistent CTA per SM.
+ * tile_m x tile_n: output tile of one CTA, 128 x 256, 128 x 128 or 256 x 256; cta_pair = 2 makes two CTAs of a
+ * cluster (an SM pair) share 256 x 256 tiles with tcgen05.mma.cta_group::2, each loading half of the W tile. Zeros
+ * let the library choose by the number of waves. max_ctas: 0 = one persistent CTA per SM.
  *
  * In the reference these are the torch.nn.Linear layers of the blocks it wraps followed by eager elementwise
  * kernels: the MLP of hetuDiTFeedForwardWrapper.forward (layers/feedforward.py:73-78: linear, GELU, linear) and the
@@ -445,7 +446,7 @@ typedef struct hdit_gemm_args {
   int32_t max_ctas;
   void* stream;
   int32_t tile_m;
-  int32_t reserved0;
+  int32_t cta_pair; /* 0 = choose, 1 = never, 2 = always: two CTAs of a cluster share 256 x 256 tiles */
 } hdit_gemm_args;
 
 HDIT_API int hdit_linear_fused(const hdit_gemm_args* args);

@@ -38,16 +38,18 @@ def _inputs(B, S, K, N, dtype, seed):
     return x, w, b, res, gate
 
 
-TILES = [(0, 0), (128, 128), (128, 256), (256, 256)]
+# (tile_m, tile_n, cta_pair): 0 = the library chooses; cta_pair 2 = two CTAs share a 256 x 256 tile
+TILES = [(0, 0, 0), (128, 128, 1), (128, 256, 1), (256, 256, 1), (0, 0, 2)]
 
 
 @pytest.mark.parametrize("epilogue", ["bias", "gelu_tanh", "gate_residual"])
-@pytest.mark.parametrize("tile", TILES, ids=lambda t: f"tile{t[0]}x{t[1]}")
+@pytest.mark.parametrize("tile", TILES, ids=lambda t: f"tile{t[0]}x{t[1]}pair{t[2]}")
 @pytest.mark.parametrize("B,S,K,N", [(1, 128, 64, 256), (1, 300, 200, 264), (2, 333, 1024, 1160), (1, 576, 3072, 3072)])
 def test_linear_fused_matches_unfused_chain(B, S, K, N, tile, epilogue):
     from hetu_dit_b200 import kernels
     x, w, b, res, gate = _inputs(B, S, K, N, torch.bfloat16, B * 1000 + S + K + N)
-    got = kernels.linear_fused(x, w, b, epilogue=epilogue, residual=res, gate=gate, tile_m=tile[0], tile_n=tile[1])
+    got = kernels.linear_fused(x, w, b, epilogue=epilogue, residual=res, gate=gate, tile_m=tile[0], tile_n=tile[1],
+                               cta_pair=tile[2])
     torch.cuda.synchronize()
     _check(got, _want(x, w, b, epilogue, res, gate))
 
@@ -56,10 +58,10 @@ def test_linear_fused_many_tiles_per_cta_and_long_k():
     """Few persistent CTAs walk many tiles: both accumulators and every ring stage are re-used many times."""
     from hetu_dit_b200 import kernels
     x, w, b, res, gate = _inputs(1, 1100, 4160, 1544, torch.bfloat16, 7)
-    for tile_m, tile_n in TILES[1:]:
-        for ctas in (1, 3, 7):
+    for tile_m, tile_n, pair in TILES[1:]:
+        for ctas in (2, 3, 7):
             got = kernels.linear_fused(x, w, b, epilogue="gate_residual", residual=res, gate=gate, tile_m=tile_m,
-                                       tile_n=tile_n, max_ctas=ctas)
+                                       tile_n=tile_n, max_ctas=ctas, cta_pair=pair)
             torch.cuda.synchronize()
             _check(got, _want(x, w, b, "gate_residual", res, gate))
 
@@ -67,8 +69,9 @@ def test_linear_fused_many_tiles_per_cta_and_long_k():
 def test_linear_fused_fp16_no_bias_strided_and_in_place():
     from hetu_dit_b200 import kernels
     x, w, b, res, gate = _inputs(2, 200, 512, 384, torch.float16, 11)
-    got = kernels.linear_fused(x, w, None, epilogue="bias")
-    _check(got, _want(x, w, None, "bias"))
+    for pair in (1, 2):
+        got = kernels.linear_fused(x, w, None, epilogue="bias", cta_pair=pair)
+        _check(got, _want(x, w, None, "bias"))
     # the result lands in a column block of a wider buffer; rows of x are a column block too
     wide_in = torch.zeros(2, 200, 512 + 64, dtype=torch.float16, device=DEV)
     wide_in[..., 64:] = x
@@ -94,6 +97,8 @@ def test_linear_fused_two_dim_and_argument_errors():
         kernels.linear_fused(x[..., :60], w[:, :60].contiguous(), b)  # k not a multiple of 8
     with pytest.raises(_C.HditError):
         kernels.linear_fused(x, w, b, tile_n=64)
+    with pytest.raises(_C.HditError):
+        kernels.linear_fused(x, w, b, tile_n=128, cta_pair=2)
     with pytest.raises(ValueError):
         kernels.linear_fused(x, w[:, :64], b)
 
@@ -111,9 +116,11 @@ def test_linear_fused_flux_mlp_shapes():
     b2 = torch.randn(d, device=DEV, generator=gen).to(torch.bfloat16)
     gate = torch.randn(1, d, device=DEV, generator=gen).to(torch.bfloat16)
     buf = torch.randn(1, 4608, 5 * d, device=DEV, generator=gen).to(torch.bfloat16)
-    kernels.linear_fused(x, w1, b1, epilogue="gelu_tanh", out=buf[..., d:])
-    out = kernels.linear_fused(buf, w2, b2, epilogue="gate_residual", residual=x, gate=gate)
-    torch.cuda.synchronize()
     rows = torch.arange(0, 4608, 37, device=DEV)
-    _check(buf[:, rows, d:], _want(x[:, rows], w1, b1, "gelu_tanh"))
-    _check(out[:, rows], _want(buf[:, rows], w2, b2, "gate_residual", x[:, rows], gate))
+    for pair in (1, 2):
+        buf[..., d:].zero_()
+        kernels.linear_fused(x, w1, b1, epilogue="gelu_tanh", out=buf[..., d:], cta_pair=pair)
+        out = kernels.linear_fused(buf, w2, b2, epilogue="gate_residual", residual=x, gate=gate, cta_pair=pair)
+        torch.cuda.synchronize()
+        _check(buf[:, rows, d:], _want(x[:, rows], w1, b1, "gelu_tanh"))
+        _check(out[:, rows], _want(buf[:, rows], w2, b2, "gate_residual", x[:, rows], gate))

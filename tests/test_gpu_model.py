@@ -63,8 +63,19 @@ def hook_block_outputs(model, s_txt):
     return outs, handles
 
 
+@pytest.fixture
+def fused_linear(request, monkeypatch):
+    """Runs the test with the blocks' linear layers + tails as separate kernels (False) or fused (True)."""
+    from hetu_dit_b200 import kernels
+    monkeypatch.setattr(kernels, "FUSED_LINEAR", bool(request.param))
+    monkeypatch.setattr(kernels, "FUSED_LINEAR_MIN_ROWS", 0)
+    monkeypatch.setattr(kernels, "FUSED_LINEAR_MAX_ROWS", 1 << 40)
+    return bool(request.param)
+
+
+@pytest.mark.parametrize("fused_linear", [False, True], indirect=True, ids=["unfused", "fused_linear"])
 @pytest.mark.parametrize("kind", ["flux", "sd3", "cogvideox", "hunyuan"])
-def test_tiny_model_step(kind):
+def test_tiny_model_step(kind, fused_linear):
     """One step of a tiny model of each shape: every block's output and the final output against the fp32
     oracle, cosine >= 0.9999 and max |a-b| / max |b| <= 2e-2 per block; the per-element relative error over the
     elements above 1 % of the block's largest magnitude is bounded too."""
