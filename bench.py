@@ -353,7 +353,8 @@ def run_gpu(args):
             dist.all_gather_object(out, b)
             return out
 
-        heap = PeerHeap((1 << 30) if args.config in ("flux", "sd3") else (3 << 30), rank, world, dev, gather)
+        # exchange buffers of the video shapes: (tokens, heads / U, 128) x {q, k, v, out} x two generations
+        heap = PeerHeap((1 << 30) if args.config in ("flux", "sd3") else (8 << 30), rank, world, dev, gather)
     ps.init_distributed_environment(rank, world, heap)
 
     parity = None
@@ -541,6 +542,14 @@ def run_kernel_case(args):
         q, k, v = (torch.randn(B, S_IMG + S_TXT, 24, 128, device=dev, dtype=torch.bfloat16) for _ in range(3))
         fn = lambda: kernels.attn_fwd([q], [k], [v])
         work = 4.0 * B * (S_IMG + S_TXT) ** 2 * 24 * 128
+        unit = "TFLOP/s"
+    elif kind == "attn64":
+        # the SD3-shaped attention: 4096 image + 154 text tokens (padded to 160 rows of storage), 24 heads of 64,
+        # `arg` batch entries (2 = the classifier-free-guidance batch)
+        B = int(arg or 2)
+        q, k, v = (torch.randn(B, 4096 + 154, 24, 64, device=dev, dtype=torch.bfloat16) for _ in range(3))
+        fn = lambda: kernels.attn_fwd([q], [k], [v])
+        work = 4.0 * B * (4096 + 154) ** 2 * 24 * 64
         unit = "TFLOP/s"
     elif kind in ("attnheads", "attnheads1"):
         # the shape one rank attends after the Ulysses exchange: `arg` of the 24 heads, all 4608 tokens.
@@ -808,7 +817,7 @@ def main():
     ap.add_argument("--profile-one-step", action="store_true",
                     help="wrap one extra eager step in cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--kernel-case", default="",
-                    help="one kernel instead of the step: attn:<batch>, attnheads:<heads> (attnheads1: no KV split), "
+                    help="one kernel instead of the step: attn:<batch>, attn64:<batch>, attnheads:<heads> (attnheads1: no KV split), "
                          "copy:<MiB>, normrope:<batch>, lnmod:<batch>, gate:<batch>, "
                          "linear:<rows>:<n>:<k>:<tail>[:<tile_m>x<tile_n>], linearlib:<rows>:<n>:<k>:<tail>, "
                          "usp:<flux|cogvideox|hunyuan>")

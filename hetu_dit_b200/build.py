@@ -62,6 +62,20 @@ def build(force=False, verbose=False):
     return LIB_PATH
 
 
+def build_microbench(force=False):
+    """The stand-alone tcgen05 microbenchmark (csrc/microbench): a binary next to its source, not part of the library."""
+    src = os.path.join(CSRC, "microbench", "tcgen05_issue.cu")
+    exe = src[:-3]
+    deps = [src, os.path.join(CSRC, "ptx_sm100.cuh")]
+    if not force and os.path.exists(exe) and all(os.path.getmtime(d) <= os.path.getmtime(exe) for d in deps):
+        return exe
+    nvcc = os.environ.get("NVCC", "nvcc")
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-o", exe, src],
+                   check=True, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    return exe
+
+
 if __name__ == "__main__":
     build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    build_microbench(force="--force" in sys.argv)
     print(LIB_PATH)

@@ -528,25 +528,27 @@ def linear_fused(x, weight, bias=None, epilogue="bias", residual=None, gate=None
     return out
 
 
-# Whether linear_tail() runs the fused tensor-core kernel (True) or the library GEMM followed by the one-pass
-# tail kernel (False). Off by default: measured inside the whole step the fused kernel is 1 to 3 % behind
-# (Flux-shaped 69.5 against 68.1-69.1 ms, SD3-shaped 12.32 against 12.00 ms per step) although alone it matches
-# the pair of kernels it replaces -- without multicast loads it moves more operand bytes from L2 per flop than
-# the library's kernels, and under the power cap that costs clock. HDIT_FUSED_LINEAR=1 turns it on.
-FUSED_LINEAR = os.environ.get("HDIT_FUSED_LINEAR", "0") == "1"
-# The fused kernel is used between these row counts. Below, the library's split-K GEMMs fill the GPU better than
+# Whether linear_tail() may run the fused tensor-core kernel (csrc/gemm_sm100.cu) instead of the library GEMM
+# followed by the one-pass tail kernel, and for which tails. Measured inside the whole step (same box, alternating
+# runs): fusing the GELU wins (Flux-shaped 68.3-68.8 against 68.9-69.3 ms, SD3-shaped 11.77 against 11.99 ms per
+# step); fusing the gated residuals as well loses (69.5 against 68.1-69.1 ms, 12.32 against 12.00 ms) although alone
+# it ties the pair of kernels it replaces -- without multicast loads the kernel moves more operand bytes from L2 per
+# flop than the library's, and under the power cap that costs clock. So only the GELU is fused by default.
+# HDIT_FUSED_LINEAR=0 turns the fused kernel off, HDIT_FUSED_LINEAR_TAILS=gelu_tanh,gate_residual fuses both tails.
+FUSED_LINEAR = os.environ.get("HDIT_FUSED_LINEAR", "1") == "1"
+FUSED_LINEAR_TAILS = set(os.environ.get("HDIT_FUSED_LINEAR_TAILS", "gelu_tanh").split(","))
+# The fused kernel is used from this row count on. Below, the library's split-K GEMMs fill the GPU better than
 # whole output tiles do (measured at 576 to 2304 rows: the fused kernel takes 1.2x to 2x the library GEMM + tail
-# kernel). Above (video-length sequences) the kernel sits at the power cap for long: measured 0.8x to 0.97x of
-# the library path at 18 k rows.
+# kernel).
 FUSED_LINEAR_MIN_ROWS = int(os.environ.get("HDIT_FUSED_LINEAR_MIN_ROWS", "4096"))
-FUSED_LINEAR_MAX_ROWS = int(os.environ.get("HDIT_FUSED_LINEAR_MAX_ROWS", "12288"))
+FUSED_LINEAR_MAX_ROWS = int(os.environ.get("HDIT_FUSED_LINEAR_MAX_ROWS", str(1 << 40)))
 
 
 def linear_tail(linear, x, epilogue, residual=None, gate=None, out=None):
     """A torch.nn.Linear followed by its elementwise tail ("gelu_tanh", or "gate_residual" = residual +
     gate[:, None] * linear(x)), as one kernel when FUSED_LINEAR is set and the layouts allow it (rows evenly
     strided across the batch), else as the library GEMM plus hdit_gelu_tanh / hdit_gate_residual."""
-    fusable = (FUSED_LINEAR and x.is_cuda and x.dim() == 3 and _even_rows(x) and not torch.is_grad_enabled()
+    fusable = (FUSED_LINEAR and epilogue in FUSED_LINEAR_TAILS and x.is_cuda and x.dim() == 3 and _even_rows(x) and not torch.is_grad_enabled()
                and FUSED_LINEAR_MIN_ROWS <= x.shape[0] * x.shape[1] <= FUSED_LINEAR_MAX_ROWS
                and (out is None or _even_rows(out)) and (residual is None or _even_rows(residual))
                and (gate is None or gate.stride(-1) == 1))

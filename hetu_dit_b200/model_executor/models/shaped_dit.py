@@ -246,7 +246,7 @@ class JointBlock(nn.Module):
         sp = ps.get_sequence_parallel_world_size() > 1 and hidden.is_cuda
         # with fused linear layers the gated residual of the image stream rides on the attention's output
         # projection (and the text stream's too, unless its tail runs on the branch stream below)
-        fuse = kernels.FUSED_LINEAR and hidden.is_cuda
+        fuse = kernels.FUSED_LINEAR and "gate_residual" in kernels.FUSED_LINEAR_TAILS and hidden.is_cuda
         tails = ((hidden, mod[2]) if fuse else None, (context, cmod[2]) if fuse and not sp else None)
         a_img, a_txt = self.attn(h, encoder_hidden_states=c, image_rotary_emb=rope, token_offset=token_offset,
                                  text_len=text_total, text_offset=text_offset, tails=tails)

@@ -198,6 +198,14 @@ class Worker:
         rt.set_input_parameters(height=input_config.height, width=input_config.width,
                                 batch_size=input_config.batch_size or 1,
                                 num_inference_steps=input_config.num_inference_steps)
+        # A text length the previous request did not have changes the shape of the text-stream message between
+        # pipeline stages: every stage forgets its inbox layout here, between the same two requests.
+        text_shape = tuple(prompt_embeds.shape)
+        if text_shape != getattr(self, "_last_text_shape", None):
+            pp = ps.get_pp_group_or_none()
+            if pp is not None:
+                pp.reset_buffer()
+            self._last_text_shape = text_shape
         out = self.pipeline.diffusion_stage(latents, prompt_embeds, pooled, input_config.num_inference_steps)
         torch.cuda.synchronize(self.device)
         self.heap.check()
