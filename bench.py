@@ -24,7 +24,7 @@ import torch  # noqa: E402
 
 METRIC, UNIT = "denoise_step_tokens_per_s", "tokens/s"
 
-# The BASELINE configurations: shape, latent token grid, text tokens, and the sequence-parallel plan per GPU
+# The benchmark configurations: shape, latent token grid, text tokens, and the sequence-parallel plan per GPU
 # count as (ulysses, ring). "flux" is the default (the configuration the headline metric is quoted on).
 CONFIGS = {
     "flux": dict(shape="FLUX_DEV", grid=(64, 64), s_txt=512, plans={1: (1, 1), 2: (2, 1), 4: (4, 1), 8: (8, 1)},
@@ -645,7 +645,7 @@ USP_CASES = {
 
 
 def run_usp_case(args):
-    """Operator-level timing of one USP attention layer at a BASELINE config's shape under torchrun:
+    """Operator-level timing of one USP attention layer at the shape of one of the benchmark configurations under torchrun:
     `usp:<flux|cogvideox|hunyuan>`. Prints ms per layer (max over ranks), TFLOP/s per GPU, and the share of
     the layer that is not attention compute (exchange, barriers, copies)."""
     import torch.distributed as dist
@@ -717,7 +717,7 @@ def run_usp_case(args):
 
 
 def run_trace(args):
-    """BASELINE's serving-trace configuration on N GPUs: SD3-medium-shaped model, seeded Poisson arrivals at 2
+    """The serving-trace configuration on N GPUs: SD3-medium-shaped model, seeded Poisson arrivals at 2
     requests/s, four resolutions, text length 77..333, 20 steps per request, PipeFusion with 4 patches and one
     warm-up step, the plan (PipeFusion degree x Ulysses degree) taken from a fixed table per resolution and every
     change of plan made through the worker plan API with parameter-slice migration. Prints mean / p95 request
@@ -785,10 +785,12 @@ def run_trace(args):
                 "data": "synthetic",
                 "config": {"workload": "SD3-medium-shaped serving trace: Poisson arrivals 2 req/s (seed 0), 20 steps, "
                                        "resolutions 512/768/1024/1536 squared, text 77..333 tokens, CFG batch 2, "
-                                       "PipeFusion 4 patches, 1 warm-up step, FIFO admission, plan per resolution "
+                                       "PipeFusion 4 patches, 1 warm-up step, FIFO admission (a request occupies "
+                                       "pp x sp GPUs; requests on disjoint GPUs overlap), plan per resolution "
                                        "from a fixed table, plan switches through the worker API",
                            "requests": n_req, "requests_in_full_trace": 2000,
-                           "arrivals": "virtual clock; service times measured on the GPUs (max over ranks)",
+                           "arrivals": "virtual clock; service times measured on the GPUs one request at a time "
+                                       "(max over ranks)",
                            "slo": "latency <= 5 x single-GPU latency of the same resolution"},
                 "trace": res, "wall_s": wall, "gpu_launches": kernels.launch_count(), "clocks": clk.summary()}
         print(json.dumps(line), flush=True)
@@ -803,7 +805,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="flux", choices=sorted(CONFIGS) + ["trace"],
-                    help="which BASELINE configuration to run (default: the Flux.1-dev-shaped step); `trace` is "
+                    help="which benchmark configuration to run (default: the Flux.1-dev-shaped step); `trace` is "
                          "the serving trace of the SD3-medium-shaped model")
     ap.add_argument("--trace-requests", type=int, default=200,
                     help="--config trace: how many of the 2000 requests of the trace to run")

@@ -188,6 +188,12 @@ class PipelineGroupCoordinator:
             raise ValueError("No more tasks to receive")
         self.receiving_tasks.append(self.recv_tasks_queue.pop(0))
 
+    def pop_received(self, idx: int = -1, name: str = "latent") -> None:
+        """The bookkeeping half of get_pipeline_recv_data(): the wait itself is part of a replayed CUDA graph."""
+        assert len(self.receiving_tasks) > 0, "No tasks to receive, call add_pipeline_recv_task first"
+        got_name, got_idx = self.receiving_tasks.pop(0)
+        assert got_name == (name or "latent") and got_idx == idx, "Received tensor does not match the requested"
+
     def get_pipeline_recv_data(self, idx: int = -1, name: str = "latent") -> torch.Tensor:
         assert len(self.receiving_tasks) > 0, "No tasks to receive, call add_pipeline_recv_task first"
         got_name, got_idx = self.receiving_tasks.pop(0)

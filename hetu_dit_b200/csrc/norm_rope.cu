@@ -80,8 +80,13 @@ __device__ __forceinline__ uint16_t from_f(float f) {
     return __bfloat16_as_ushort(__float2bfloat16_rn(f));
 }
 
+// Resident CTAs per SM the register allocation aims for (bytes in flight per SM = CTAs x threads x 32).
+#ifndef HDIT_NR_MIN_CTAS
+#define HDIT_NR_MIN_CTAS 3
+#endif
+
 template <int D, bool FP16>
-__global__ void __launch_bounds__(512) norm_rope_kernel(const __grid_constant__ NormRopeParams p) {
+__global__ void __launch_bounds__(512, HDIT_NR_MIN_CTAS) norm_rope_kernel(const __grid_constant__ NormRopeParams p) {
   constexpr int TPR = D / 8;  // threads per (token, head) row
   const NormRopeTensor& t = p.t[blockIdx.y];
   const int rows_per_iter = blockDim.x / TPR;
@@ -90,112 +95,132 @@ __global__ void __launch_bounds__(512) norm_rope_kernel(const __grid_constant__ 
   const int heads_per_dst = p.heads / p.n_dst;
   const long long n_tok = static_cast<long long>(p.batch) * p.seq;
 
-  for (long long tok = blockIdx.x; tok < n_tok; tok += gridDim.x) {
-    const int b = static_cast<int>(tok / p.seq);
-    const int s = static_cast<int>(tok - static_cast<long long>(b) * p.seq);
-    const bool r2 = s >= p.range2_start;
-    const bool rotate = r2 ? (p.do_rope2[blockIdx.y] != 0) : (t.do_rope && s >= p.rope_seq_start);
-    const void* const weight = r2 ? p.weight2[blockIdx.y] : t.weight;
-    const void* const bias = r2 ? p.bias2[blockIdx.y] : t.bias;
-    float cs[8], sn[8];
-    if (rotate) {
-      const long long trow = (r2 ? (s - p.range2_start + p.rope_row0_2) : (s - p.rope_seq_start + p.rope_row0)) * D +
-                             part * 8;
-      const float4 c0 = *reinterpret_cast<const float4*>(p.cos_tab + trow);
-      const float4 c1 = *reinterpret_cast<const float4*>(p.cos_tab + trow + 4);
-      const float4 s0 = *reinterpret_cast<const float4*>(p.sin_tab + trow);
-      const float4 s1 = *reinterpret_cast<const float4*>(p.sin_tab + trow + 4);
-      cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
-      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+  // Two tokens per pass: both 16-byte loads of a thread are issued before either is used, which doubles the
+  // bytes in flight per resident thread (the kernel is latency-bound: one short dependent chain per load).
+  for (long long tok0 = blockIdx.x; tok0 < n_tok; tok0 += 2LL * gridDim.x) {
+    const long long toks[2] = {tok0, tok0 + gridDim.x};
+    const int n_here = toks[1] < n_tok ? 2 : 1;
+    int bb_[2], ss_[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const long long tk = j < n_here ? toks[j] : toks[0];
+      bb_[j] = static_cast<int>(tk / p.seq);
+      ss_[j] = static_cast<int>(tk - static_cast<long long>(bb_[j]) * p.seq);
     }
     // All threads of a warp run the same number of iterations (heads is padded up), so the
     // shuffles below are always executed by full warps.
     for (int h0 = 0; h0 < p.heads; h0 += rows_per_iter) {
       const int h = h0 + row_in_blk;
       const bool live = h < p.heads;
-      uint4 raw = make_uint4(0, 0, 0, 0);
-      if (live) {
-        const uint16_t* src = static_cast<const uint16_t*>(t.x) + b * t.xs_b + s * t.xs_s + h * t.xs_h + part * 8;
-        raw = *reinterpret_cast<const uint4*>(src);
+      uint4 raws[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        raws[j] = make_uint4(0, 0, 0, 0);
+        if (live && j < n_here) {
+          const uint16_t* src =
+              static_cast<const uint16_t*>(t.x) + bb_[j] * t.xs_b + ss_[j] * t.xs_s + h * t.xs_h + part * 8;
+          raws[j] = *reinterpret_cast<const uint4*>(src);
+        }
       }
-      const uint16_t* e = reinterpret_cast<const uint16_t*>(&raw);
-      float f[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = to_f<FP16>(e[i]);
+      for (int j = 0; j < 2; ++j) {
+        if (j >= n_here) break;  // uniform over the CTA
+        const int b = bb_[j], s = ss_[j];
+        const bool r2 = s >= p.range2_start;
+        const bool rotate = r2 ? (p.do_rope2[blockIdx.y] != 0) : (t.do_rope && s >= p.rope_seq_start);
+        const void* const weight = r2 ? p.weight2[blockIdx.y] : t.weight;
+        const void* const bias = r2 ? p.bias2[blockIdx.y] : t.bias;
+        float cs[8], sn[8];
+        if (rotate) {
+          const long long trow =
+              (r2 ? (s - p.range2_start + p.rope_row0_2) : (s - p.rope_seq_start + p.rope_row0)) * D + part * 8;
+          const float4 c0 = *reinterpret_cast<const float4*>(p.cos_tab + trow);
+          const float4 c1 = *reinterpret_cast<const float4*>(p.cos_tab + trow + 4);
+          const float4 s0 = *reinterpret_cast<const float4*>(p.sin_tab + trow);
+          const float4 s1 = *reinterpret_cast<const float4*>(p.sin_tab + trow + 4);
+          cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+          sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+        }
+        const uint4 raw = raws[j];
+        const uint16_t* e = reinterpret_cast<const uint16_t*>(&raw);
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = to_f<FP16>(e[i]);
 
-      if (t.do_norm == 2) {
-        // LayerNorm over the head dimension (CogVideoX-style QK norm): fp32 throughout, one rounding,
-        // as torch's layer_norm does for 16-bit inputs
-        float sum = 0.f;
+        if (t.do_norm == 2) {
+          // LayerNorm over the head dimension (CogVideoX-style QK norm): fp32 throughout, one rounding,
+          // as torch's layer_norm does for 16-bit inputs
+          float sum = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sum += f[i];
+          for (int i = 0; i < 8; ++i) sum += f[i];
 #pragma unroll
-        for (int off = TPR / 2; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-        const float mean = sum * (1.0f / D);
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          f[i] -= mean;
-          ss = fmaf(f[i], f[i], ss);
-        }
-#pragma unroll
-        for (int off = TPR / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-        const float rstd = rsqrtf(ss * (1.0f / D) + p.eps);
-        float w[8], bb[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) w[i] = 1.f, bb[i] = 0.f;
-        if (weight != nullptr) {
-          const uint4 wraw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(weight) + part * 8);
-          const uint16_t* wp = reinterpret_cast<const uint16_t*>(&wraw);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) w[i] = to_f<FP16>(wp[i]);
-        }
-        if (bias != nullptr) {
-          const uint4 braw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(bias) + part * 8);
-          const uint16_t* bp = reinterpret_cast<const uint16_t*>(&braw);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) bb[i] = to_f<FP16>(bp[i]);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = to_f<FP16>(from_f<FP16>(fmaf(f[i] * rstd, w[i], bb[i])));
-      } else if (t.do_norm) {
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
-#pragma unroll
-        for (int off = TPR / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-        const float rstd = rsqrtf(ss * (1.0f / D) + p.eps);
-        if (weight != nullptr) {
-          const uint4 wraw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(weight) + part * 8);
-          const uint16_t* w = reinterpret_cast<const uint16_t*>(&wraw);
+          for (int off = TPR / 2; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+          const float mean = sum * (1.0f / D);
+          float ss = 0.f;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const float y = to_f<FP16>(from_f<FP16>(__fmul_rn(f[i], rstd)));
-            f[i] = to_f<FP16>(from_f<FP16>(__fmul_rn(y, to_f<FP16>(w[i]))));
+            f[i] -= mean;
+            ss = fmaf(f[i], f[i], ss);
           }
-        } else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] = to_f<FP16>(from_f<FP16>(__fmul_rn(f[i], rstd)));
+          for (int off = TPR / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+          const float rstd = rsqrtf(ss * (1.0f / D) + p.eps);
+          float w[8], bb[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w[i] = 1.f, bb[i] = 0.f;
+          if (weight != nullptr) {
+            const uint4 wraw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(weight) + part * 8);
+            const uint16_t* wp = reinterpret_cast<const uint16_t*>(&wraw);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = to_f<FP16>(wp[i]);
+          }
+          if (bias != nullptr) {
+            const uint4 braw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(bias) + part * 8);
+            const uint16_t* bp = reinterpret_cast<const uint16_t*>(&braw);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) bb[i] = to_f<FP16>(bp[i]);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = to_f<FP16>(from_f<FP16>(fmaf(f[i] * rstd, w[i], bb[i])));
+        } else if (t.do_norm) {
+          float ss = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+#pragma unroll
+          for (int off = TPR / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+          const float rstd = rsqrtf(ss * (1.0f / D) + p.eps);
+          if (weight != nullptr) {
+            const uint4 wraw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(weight) + part * 8);
+            const uint16_t* w = reinterpret_cast<const uint16_t*>(&wraw);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float y = to_f<FP16>(from_f<FP16>(__fmul_rn(f[i], rstd)));
+              f[i] = to_f<FP16>(from_f<FP16>(__fmul_rn(y, to_f<FP16>(w[i]))));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = to_f<FP16>(from_f<FP16>(__fmul_rn(f[i], rstd)));
+          }
         }
-      }
-      if (rotate) {
+        if (rotate) {
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-          const float a = f[i], c = f[i + 1];
-          f[i] = __fadd_rn(__fmul_rn(a, cs[i]), __fmul_rn(-c, sn[i]));
-          f[i + 1] = __fadd_rn(__fmul_rn(c, cs[i + 1]), __fmul_rn(a, sn[i + 1]));
+          for (int i = 0; i < 8; i += 2) {
+            const float a = f[i], c = f[i + 1];
+            f[i] = __fadd_rn(__fmul_rn(a, cs[i]), __fmul_rn(-c, sn[i]));
+            f[i + 1] = __fadd_rn(__fmul_rn(c, cs[i + 1]), __fmul_rn(a, sn[i + 1]));
+          }
         }
-      }
-      if (live) {
-        uint4 outv;
-        uint16_t* o = reinterpret_cast<uint16_t*>(&outv);
+        if (live) {
+          uint4 outv;
+          uint16_t* o = reinterpret_cast<uint16_t*>(&outv);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = from_f<FP16>(f[i]);
-        const int d_idx = h / heads_per_dst;
-        const int hh = h - d_idx * heads_per_dst;
-        uint16_t* dst = static_cast<uint16_t*>(t.dst[d_idx]) + b * t.ds_b + (s + t.dst_seq_offset) * t.ds_s +
-                        hh * t.ds_h + part * 8;
-        *reinterpret_cast<uint4*>(dst) = outv;
+          for (int i = 0; i < 8; ++i) o[i] = from_f<FP16>(f[i]);
+          const int d_idx = h / heads_per_dst;
+          const int hh = h - d_idx * heads_per_dst;
+          uint16_t* dst = static_cast<uint16_t*>(t.dst[d_idx]) + b * t.ds_b + (s + t.dst_seq_offset) * t.ds_s +
+                          hh * t.ds_h + part * 8;
+          *reinterpret_cast<uint4*>(dst) = outv;
+        }
       }
     }
   }
@@ -335,7 +360,8 @@ extern "C" int hdit_qk_norm_rope(const hdit_norm_rope_args* a) {
   if (threads > 512) threads = 512;
   const long long n_tok = static_cast<long long>(a->batch) * a->seq;
   const long long cap = 148LL * 32;  // short blocks (one 16-byte load per thread per token): many resident CTAs
-  dim3 grid(static_cast<unsigned>(n_tok < cap ? n_tok : cap), static_cast<unsigned>(a->n_tensors));
+  const long long want = (n_tok + 1) / 2;  // a CTA takes two tokens per pass
+  dim3 grid(static_cast<unsigned>(want < cap ? want : cap), static_cast<unsigned>(a->n_tensors));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
   const bool fp16 = a->dtype == HDIT_FP16;
   if (a->head_dim == 128) {

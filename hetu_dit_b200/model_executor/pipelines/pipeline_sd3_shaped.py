@@ -45,6 +45,11 @@ def stage_block_range(total_blocks: int, pp_rank: int, pp_world: int,
 
 
 class SD3ShapedPipeline:
+    use_cuda_graph = True    # see __init__
+    fused_step = True
+    _patch_pool = None       # memory pool shared by the per-patch CUDA graphs
+    _live_patch_graphs = None
+
     def __init__(self, model: ShapedDiT, guidance_scale: float = 5.0, grid: Tuple[int, int] = (128, 128)):
         self.model = model
         self.shape = model.shape
@@ -60,6 +65,8 @@ class SD3ShapedPipeline:
         # and patched steps run eagerly: their hand-offs and stale-KV updates depend on per-patch host state.
         self.use_cuda_graph = True
         self._graphs = None
+        self._patch_pool = None
+        self._live_patch_graphs = None
         # guidance + scheduler step (+ wrap-around send) of the last stage as one kernel; False = the eager chain
         self.fused_step = True
 
@@ -158,13 +165,15 @@ class SD3ShapedPipeline:
             latents = noise_pred
         return latents, encoder_hidden_states
 
-    def _guided_step(self, noise_pred, last_latents, i, send_as=None):
+    def _guided_step(self, noise_pred, last_latents, i, send_as=None, sigmas=None, out=None):
         """Last stage: classifier-free guidance + scheduler step of one (patch of the) latents in a single kernel
         (csrc/elementwise.cu), which also stores the result into the first stage's inbox when `send_as` =
         (name, segment index) names the wrap-around message -- the eager chain and the separate send copy of
         the reference (pipeline_stable_diffusion_3.py:1585-1631, 1703-1713) become one launch plus a flag."""
         if not (self.fused_step and noise_pred.is_cuda and noise_pred.is_contiguous() and last_latents.is_contiguous()
                 and last_latents.numel() % 8 == 0):
+            if sigmas is not None or out is not None:
+                raise RuntimeError("a captured patch step needs the fused guidance + scheduler kernel")
             if self.cfg_batch:
                 uncond, text = noise_pred.chunk(2)
                 noise_pred = uncond + self.guidance_scale * (text - uncond)
@@ -176,8 +185,8 @@ class SD3ShapedPipeline:
         pp = ps.get_pp_group() if send_as is not None else None
         if pp is not None:
             peer = pp.reserve_send(last_latents, send_as[0], send_as[1])
-        out = kernels.cfg_euler_step(noise_pred, last_latents, self.sigmas, i, self.guidance_scale, cfg=self.cfg_batch,
-                                     out_peer_ptr=peer)
+        out = kernels.cfg_euler_step(noise_pred, last_latents, self.sigmas if sigmas is None else sigmas, i,
+                                     self.guidance_scale, cfg=self.cfg_batch, out=out, out_peer_ptr=peer)
         if pp is not None:
             pp.commit_send()
         return out
@@ -251,49 +260,109 @@ class SD3ShapedPipeline:
         pp = ps.get_pp_group() if pp_world > 1 else None
         patch_latents = self._init_async_pipeline(len(steps), latents, rt.runtime_config.warmup_steps)
         n_patch = rt.num_pipeline_patch
-        last_patch_latents = [None] * n_patch if last else None
-        last_encoder_hidden_states = None
-        first_async_recv = True
+        n_steps = len(steps)
+        st = {"last_patch": [None] * n_patch if last else None, "text": None, "first_recv": True}
+
+        def receives(k, p, host_only):
+            """Messages patch p of step k starts from. host_only: only the receive-queue bookkeeping (the waits and
+            copies themselves are part of a replayed graph)."""
+            if last:
+                st["last_patch"][p] = patch_latents[p]  # the sample of this step: the previous step's result
+            if pp_world == 1 or (first and k == 0):
+                return
+            if st["first_recv"]:
+                if not first and p == 0:
+                    pp.recv_next()
+                pp.recv_next()
+                st["first_recv"] = False
+            if not first and p == 0:
+                if host_only:
+                    pp.pop_received(idx=p, name="encoder_hidden_states")
+                else:
+                    # private copy: the text stream serves every patch of this step, while the
+                    # sender may refill the inbox slot as soon as patch 0 has gone round the ring
+                    st["text"] = pp.get_pipeline_recv_data(idx=p, name="encoder_hidden_states").clone()
+            if host_only:
+                pp.pop_received(idx=p)
+            else:
+                patch_latents[p] = pp.get_pipeline_recv_data(idx=p)
+
+        def posts(k, p):
+            """The reference posts its next receives here; with pushed messages only the order is recorded."""
+            if pp_world == 1 or (first and k == 0):
+                pass
+            elif k == n_steps - 1 and p == n_patch - 1:
+                pass
+            elif first:
+                pp.recv_next()
+            else:
+                if p == n_patch - 1:
+                    pp.recv_next()
+                pp.recv_next()
+
+        def compute(k, p, i, t, sigmas=None, step_index=None, out=None):
+            """Forward of patch p through this stage and what follows it: the guided scheduler step (+ wrap-around
+            send) on the last stage, the hand-over to the next stage elsewhere."""
+            patch_latents[p], next_text = self._backbone_forward(
+                patch_latents[p], prompt_embeds if first else st["text"], pooled, t, guide=not last)
+            if last:
+                sends = pp_world > 1 and k != n_steps - 1
+                patch_latents[p] = self._guided_step(
+                    patch_latents[p], st["last_patch"][p].contiguous(), i if step_index is None else step_index,
+                    ("latent", p) if sends else None, sigmas=sigmas, out=out)
+            elif pp_world > 1:
+                if p == 0:
+                    pp.pipeline_isend(next_text, name="encoder_hidden_states")
+                pp.pipeline_isend(patch_latents[p], segment_idx=p)
+
+        # Steps 2 .. n - 2 of the patch pipeline enqueue the same launches per patch: they are captured once per
+        # patch (at step 2, when every message has been seen once and all lazy set-up is done) and replayed. The
+        # first two steps and the last one (no wrap-around send) run eagerly.
+        graphed = (self.use_cuda_graph and self.fused_step and pp_world > 1 and latents.is_cuda and n_steps >= 4
+                   and rt.runtime_config.warmup_steps > 0)
+        graphs = [None] * n_patch
+        if graphed:
+            dev = latents.device
+            t_static = torch.zeros(1, dtype=self.sigmas.dtype, device=dev)
+            sig_pair = torch.zeros(2, dtype=self.sigmas.dtype, device=dev)
+            static_last = [None] * n_patch
+            if self._patch_pool is None:
+                self._patch_pool = torch.cuda.graph_pool_handle()
         for k, i in enumerate(steps):
+            replay = graphed and 2 <= k <= n_steps - 2
+            if replay:
+                t_static.copy_(self.sigmas[i:i + 1])
+                sig_pair.copy_(self.sigmas[i:i + 2])
             for p in range(n_patch):
-                if last:
-                    last_patch_latents[p] = patch_latents[p]
-                if pp_world == 1 or (first and k == 0):
-                    pass
+                if not replay:
+                    receives(k, p, host_only=False)
+                    compute(k, p, i, self.sigmas[i:i + 1])
+                elif graphs[p] is None:
+                    if last:
+                        # the sample the scheduler step updates in place from now on
+                        static_last[p] = patch_latents[p].contiguous().clone()
+                        patch_latents[p] = static_last[p]
+                    cur = torch.cuda.current_stream(dev)
+                    side = torch.cuda.Stream(device=dev)
+                    side.wait_stream(cur)
+                    with torch.cuda.stream(side):
+                        g = torch.cuda.CUDAGraph()
+                        g.capture_begin(pool=self._patch_pool)
+                        try:
+                            receives(k, p, host_only=False)
+                            compute(k, p, i, t_static, sigmas=sig_pair, step_index=0,
+                                    out=static_last[p] if last else None)
+                        finally:
+                            g.capture_end()
+                    cur.wait_stream(side)
+                    graphs[p] = g
+                    g.replay()
                 else:
-                    if first_async_recv:
-                        if not first and p == 0:
-                            pp.recv_next()
-                        pp.recv_next()
-                        first_async_recv = False
-                    if not first and p == 0:
-                        # private copy: the text stream serves every patch of this step, while the
-                        # sender may refill the inbox slot as soon as patch 0 has gone round the ring
-                        last_encoder_hidden_states = pp.get_pipeline_recv_data(
-                            idx=p, name="encoder_hidden_states").clone()
-                    patch_latents[p] = pp.get_pipeline_recv_data(idx=p)
-                patch_latents[p], next_encoder_hidden_states = self._backbone_forward(
-                    patch_latents[p], prompt_embeds if first else last_encoder_hidden_states, pooled,
-                    self.sigmas[i:i + 1], guide=not last)
-                if last:
-                    sends = pp_world > 1 and k != len(steps) - 1
-                    patch_latents[p] = self._guided_step(patch_latents[p], last_patch_latents[p].contiguous(), i,
-                                                         ("latent", p) if sends else None)
-                elif pp_world > 1:
-                    if p == 0:
-                        pp.pipeline_isend(next_encoder_hidden_states, name="encoder_hidden_states")
-                    pp.pipeline_isend(patch_latents[p], segment_idx=p)
-                if pp_world == 1 or (first and k == 0):
-                    pass
-                elif k == len(steps) - 1 and p == n_patch - 1:
-                    pass
-                elif first:
-                    pp.recv_next()
-                else:
-                    if p == n_patch - 1:
-                        pp.recv_next()
-                    pp.recv_next()
+                    receives(k, p, host_only=True)
+                    graphs[p].replay()
+                posts(k, p)
                 rt.next_patch()
+        self._live_patch_graphs = graphs  # until the next request: the replays may still be running
         return torch.cat(patch_latents, dim=1) if last else None
 
     # ------------------------------------------------------------------ entry point

@@ -11,6 +11,12 @@ resets the heap, so graphs are keyed by the plan epoch and dropped when it chang
 
 All ranks of a plan must call run() with the same key sequence (they do: the pipelines are SPMD), because the
 capture call itself runs the step once for real (warm-up) and once more on first replay.
+
+Captures go through CUDAGraph.capture_begin / capture_end on a side stream with one memory pool shared by all
+graphs of the cache: the torch.cuda.graph context manager would synchronise the device, run the garbage
+collector and empty the allocator cache on every capture, which costs more than the step it captures when every
+request brings a new text length. Sharing the pool is safe because the graphs of a cache never run concurrently
+and their static inputs and outputs stay referenced (only dead temporaries are reused between graphs).
 """
 from typing import Callable, Dict, Hashable, Tuple
 
@@ -26,6 +32,7 @@ class StepGraphCache:
         self.max_entries = max_entries
         self.captures = 0
         self.replays = 0
+        self._pool = None
 
     def clear(self):
         self._entries.clear()
@@ -48,11 +55,16 @@ class StepGraphCache:
             side = torch.cuda.Stream(device=dev)
             side.wait_stream(cur)
             with torch.cuda.stream(side):
-                fn(*static)  # warm-up: lazy set-up, heap buffers, allocator pools
+                fn(*static)  # warm-up: lazy set-up, heap buffers of this shape, library workspaces
+                if self._pool is None:
+                    self._pool = torch.cuda.graph_pool_handle()
+                graph = torch.cuda.CUDAGraph()
+                graph.capture_begin(pool=self._pool)
+                try:
+                    out = fn(*static)
+                finally:
+                    graph.capture_end()
             cur.wait_stream(side)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                out = fn(*static)
             ent = self._entries[key] = (graph, static, out)
             self.captures += 1
         else:

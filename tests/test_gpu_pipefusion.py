@@ -226,6 +226,19 @@ def _worker_case(rank, world, port, errq):
             assert cos >= 0.999 and rel <= 5e-2, ("pp2", cos, rel)
         else:
             assert out is None
+        # Eight steps: steps 2..5 of the patch pipeline are captured per patch and replayed from CUDA graphs. The
+        # result must be the eager one bit for bit (same kernels, same order), twice in a row (the second request
+        # captures anew over the same inbox and stale-KV buffers), and match the oracle.
+        want8 = opf.denoise(sd, shape, lat, prompt, pooled, 8, 4.0, [128] * 4, 1, (32, 16))
+        outs8 = []
+        for graph in (False, True, True):
+            w.pipeline.use_cuda_graph = graph
+            outs8.append(diffuse(w, cfg, lat, prompt, pooled, 8))
+        w.pipeline.use_cuda_graph = True
+        if rank == 1:
+            cos, rel = oa.cosine_and_max_rel(outs8[0].cpu(), want8)
+            assert cos >= 0.999 and rel <= 5e-2, ("pp2 eight steps", cos, rel)
+            assert torch.equal(outs8[0], outs8[1]) and torch.equal(outs8[1], outs8[2]), "graph replay differs from eager"
 
         # plan B: two independent single-GPU plans; each rank pulls the blocks it lacks from its peer
         cfg1 = EngineConfig()

@@ -5,6 +5,7 @@ import json
 import os
 import re
 
+import numpy as np
 import pytest
 import torch
 
@@ -546,7 +547,7 @@ def test_pipefusion_schedule_order_matches_reference(case, monkeypatch):
                        "prompt" if encoder_hidden_states is prompt else "received"])
         return latents, torch.zeros(2, 3, 8)
 
-    def guided_step(noise_pred, last_latents, i, send_as=None):
+    def guided_step(noise_pred, last_latents, i, send_as=None, **_):
         events.append(["step", int(i)])
         if send_as is not None:
             events.append(["send", send_as[0], send_as[1]])
@@ -601,3 +602,17 @@ def test_position_rows_match_reference_patch_embed(case, monkeypatch):
         assert rows(case["bounds"][p][1] - case["bounds"][p][0]) == flat(runs)
     with pytest.raises(ValueError):
         pipe._positions(n_local + 1, "cpu", torch.float32)
+
+
+def test_trace_admission_on_disjoint_gpus():
+    """The serving trace's virtual clock: one request at a time against requests that occupy part of the node
+    and overlap on disjoint GPUs; first-in-first-out start order in both."""
+    from hetu_dit_b200.serving.trace_driver import simulate_fifo, simulate_fifo_gpus
+    arrivals, service = [0.0, 0.1, 0.2, 0.3], [1.0, 1.0, 1.0, 1.0]
+    np.testing.assert_allclose(simulate_fifo(arrivals, service), [1.0, 1.9, 2.8, 3.7])
+    # every request takes the whole node: the same as one server
+    np.testing.assert_allclose(simulate_fifo_gpus(arrivals, service, [4, 4, 4, 4], 4), [1.0, 1.9, 2.8, 3.7])
+    # half the node each: two at a time
+    np.testing.assert_allclose(simulate_fifo_gpus(arrivals, service, [2, 2, 2, 2], 4), [1.0, 1.0, 1.8, 1.8])
+    # a whole-node request in the middle holds back the small ones behind it (no overtaking)
+    np.testing.assert_allclose(simulate_fifo_gpus(arrivals, service, [1, 4, 1, 1], 4), [1.0, 1.9, 2.8, 2.7])
