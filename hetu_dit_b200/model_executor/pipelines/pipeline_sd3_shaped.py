@@ -326,8 +326,8 @@ class SD3ShapedPipeline:
             t_static = torch.zeros(1, dtype=self.sigmas.dtype, device=dev)
             sig_pair = torch.zeros(2, dtype=self.sigmas.dtype, device=dev)
             static_last = [None] * n_patch
-            if self._patch_pool is None:
-                self._patch_pool = torch.cuda.graph_pool_handle()
+            # one pool for this request's graphs (a pool whose graphs are all gone must not be captured into again)
+            self._patch_pool = torch.cuda.graph_pool_handle()
         for k, i in enumerate(steps):
             replay = graphed and 2 <= k <= n_steps - 2
             if replay:

@@ -36,6 +36,7 @@ class StepGraphCache:
 
     def clear(self):
         self._entries.clear()
+        self._pool = None  # a pool whose graphs are all gone must not be captured into again
 
     def run(self, key: Hashable, fn: Callable, *inputs):
         """fn(*inputs) through a CUDA graph captured on first use of `key`. Tensor inputs are copied into the
@@ -43,12 +44,14 @@ class StepGraphCache:
         the same key). Non-tensor inputs must be part of `key`."""
         epoch = ps.get_parallel_groups().plan_epoch
         if epoch != self._epoch:
-            self._entries.clear()
+            self.clear()
             self._epoch = epoch
         ent = self._entries.get(key)
         if ent is None:
             if len(self._entries) >= self.max_entries:
                 self._entries.pop(next(iter(self._entries)))
+            if not self._entries:
+                self._pool = None
             dev = next(x.device for x in inputs if isinstance(x, torch.Tensor))
             static = [x.clone() if isinstance(x, torch.Tensor) else x for x in inputs]
             cur = torch.cuda.current_stream(dev)
