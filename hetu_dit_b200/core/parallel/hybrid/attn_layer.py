@@ -13,6 +13,7 @@ against the consumers, the tcgen05 attention kernel runs on the gathered
 tensors (joint text K/V as an extra segment, never concatenated), and the
 context rows are stored back into their owners' output buffers the same way.
 """
+import os
 from typing import Optional
 
 import torch
@@ -185,7 +186,7 @@ class hetuDiTLongContextAttention(torch.nn.Module):
     # on the Flux-shaped step at Ulysses 2 it costs 43.6 ms against 39.9 ms per step -- while it waits, the
     # attention grid holds every SM, which starves the GEMMs the blocks run beside attention on a second stream;
     # the one-warp kernel waits for free. It pays where nothing runs beside attention.
-    fold_exchange_barrier = False
+    fold_exchange_barrier = os.environ.get("HDIT_FOLD_EXCHANGE_BARRIER", "0") == "1"
 
     def __init__(self, scatter_idx: int = 2, gather_idx: int = 1, ring_impl_type: str = "basic",
                  use_pack_qkv: bool = False, use_kv_cache: bool = False) -> None:
