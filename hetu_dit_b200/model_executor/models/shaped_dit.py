@@ -609,7 +609,7 @@ class ShapedDiT(nn.Module):
         def groups_of(m):
             return [m] if torch.is_tensor(m[0]) else list(m)
 
-        rows, structure = [], {}
+        rows = []
         for slot, i in enumerate(range(me, n_items, world)):
             m = blocks[i].modulation(silu) if i < len(blocks) else self.norm_out.linear(silu).chunk(2, dim=-1)
             rows.append(torch.cat([t for g in groups_of(m) for t in g], dim=-1))
