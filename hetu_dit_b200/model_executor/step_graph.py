@@ -9,8 +9,10 @@ What makes this safe here: every buffer the exchange kernels use lives at a fixe
 the kernels themselves, and the attention wrapper's scratch comes from the graph's private pool. A plan switch
 resets the heap, so graphs are keyed by the plan epoch and dropped when it changes.
 
-All ranks of a plan must call run() with the same key sequence (they do: the pipelines are SPMD), because the
-capture call itself runs the step once for real (warm-up) and once more on first replay.
+The first call with a key runs the step eagerly and returns that result: it doubles as the warm-up every capture
+needs (lazy set-up, heap buffers of that shape, library workspaces), so no step is executed only to be thrown
+away, and a key that never comes back costs nothing extra. The second call captures and replays. All ranks of a
+plan must call run() with the same key sequence (they do: the pipelines are SPMD).
 
 Captures go through CUDAGraph.capture_begin / capture_end on a side stream with one memory pool shared by all
 graphs of the cache: the torch.cuda.graph context manager would synchronise the device, run the garbage
@@ -18,7 +20,7 @@ collector and empty the allocator cache on every capture, which costs more than 
 request brings a new text length. Sharing the pool is safe because the graphs of a cache never run concurrently
 and their static inputs and outputs stay referenced (only dead temporaries are reused between graphs).
 """
-from typing import Callable, Dict, Hashable, Tuple
+from typing import Callable, Dict, Hashable, Optional, Tuple
 
 import torch
 
@@ -27,7 +29,8 @@ from ..core.distributed import parallel_state as ps
 
 class StepGraphCache:
     def __init__(self, max_entries: int = 32):
-        self._entries: Dict[Hashable, Tuple[torch.cuda.CUDAGraph, list, object]] = {}
+        # key -> None (seen once, ran eagerly) or (graph, static inputs, static output)
+        self._entries: Dict[Hashable, Optional[Tuple[torch.cuda.CUDAGraph, list, object]]] = {}
         self._epoch = -1
         self.max_entries = max_entries
         self.captures = 0
@@ -39,27 +42,29 @@ class StepGraphCache:
         self._pool = None  # a pool whose graphs are all gone must not be captured into again
 
     def run(self, key: Hashable, fn: Callable, *inputs):
-        """fn(*inputs) through a CUDA graph captured on first use of `key`. Tensor inputs are copied into the
-        graph's static input buffers; the result is the graph's static output (valid until the next run() with
-        the same key). Non-tensor inputs must be part of `key`."""
+        """fn(*inputs): eagerly on the first use of `key`, through a CUDA graph captured on its second use from
+        then on. Tensor inputs are copied into the graph's static input buffers; a replayed result is the graph's
+        static output (valid until the next run() with the same key). Non-tensor inputs must be part of `key`."""
         epoch = ps.get_parallel_groups().plan_epoch
         if epoch != self._epoch:
             self.clear()
             self._epoch = epoch
-        ent = self._entries.get(key)
-        if ent is None:
+        ent = self._entries.get(key, False)
+        if ent is False:
+            # first use: the eager step is the warm-up; remember that the key has been seen
             if len(self._entries) >= self.max_entries:
                 self._entries.pop(next(iter(self._entries)))
-            if not self._entries:
-                self._pool = None
+            self._entries[key] = None
+            return fn(*inputs)
+        if ent is None:
             dev = next(x.device for x in inputs if isinstance(x, torch.Tensor))
             static = [x.clone() if isinstance(x, torch.Tensor) else x for x in inputs]
             cur = torch.cuda.current_stream(dev)
             side = torch.cuda.Stream(device=dev)
             side.wait_stream(cur)
             with torch.cuda.stream(side):
-                fn(*static)  # warm-up: lazy set-up, heap buffers of this shape, library workspaces
-                if self._pool is None:
+                if self._pool is None or not any(e is not None for e in self._entries.values()):
+                    # no live graph holds the pool any more (all evicted): it must not be captured into again
                     self._pool = torch.cuda.graph_pool_handle()
                 graph = torch.cuda.CUDAGraph()
                 graph.capture_begin(pool=self._pool)

@@ -222,11 +222,13 @@ def test_graph_replay_matches_eager_bit_for_bit():
             got = model.forward_graphed(lat, txt, pooled, t, g, grid=grid)
             torch.cuda.synchronize()
             assert torch.equal(got, eager), seed
-        lat, txt, pooled, t, g = (x.to(DEV) for x in _inputs(shape, 10 * 12, 20, seed=3))
-        assert torch.equal(model.forward_graphed(lat, txt, pooled, t, g, grid=(10, 12)),
-                           model(lat, txt, pooled, t, g, grid=(10, 12)))
+        for seed in (3, 4):
+            lat, txt, pooled, t, g = (x.to(DEV) for x in _inputs(shape, 10 * 12, 20, seed=seed))
+            assert torch.equal(model.forward_graphed(lat, txt, pooled, t, g, grid=(10, 12)),
+                               model(lat, txt, pooled, t, g, grid=(10, 12)))
     cache = model.__dict__["_step_graphs"]
-    assert cache.captures == 2 and cache.replays == 4
+    # per shape: the first call runs eagerly (and is the warm-up), the second captures, every later one replays
+    assert cache.captures == 2 and cache.replays == 3
     assert _C.device_status(0, clear=True)[0] == 0
 
 
@@ -258,6 +260,6 @@ def test_pipeline_whole_image_steps_replay_from_a_graph():
     torch.cuda.synchronize()
     for req in range(2):
         assert torch.equal(outs[(True, req)], outs[(False, req)]), req
-    assert pipe._graphs.captures == 1 and pipe._graphs.replays == 6
+    assert pipe._graphs.captures == 1 and pipe._graphs.replays == 5
     reset_runtime_state()
     reset_cache_manager()
