@@ -45,7 +45,7 @@ def test_single_stage_patches_with_stale_kv():
     sd = {k: v.float().cpu() for k, v in gpu_model.state_dict().items()}
     want = opf.denoise(sd, shape, lat, prompt, pooled, 4, 4.0, [128] * 4, 1, (32, 16))
     cos, rel = oa.cosine_and_max_rel(got.cpu(), want)
-    assert cos >= 0.999 and rel <= 5e-2, (cos, rel)
+    _close(cos, rel)
     # the stale K/V matters: the result is closer to the patched oracle than to the un-patched one
     full = opf.denoise(sd, shape, lat, prompt, pooled, 4, 4.0, [512], 1, (32, 16))
     g = got.cpu().float()
@@ -94,12 +94,23 @@ def test_flux_single_stage_patches_with_stale_kv():
     sd = {k: v.float().cpu() for k, v in gpu_model.state_dict().items()}
     want = opf.denoise_flux(sd, shape, lat, prompt, pooled, 4, 3.5, [128] * 4, 1, (32, 16))
     cos, rel = oa.cosine_and_max_rel(got.cpu(), want)
-    assert cos >= 0.999 and rel <= 5e-2, (cos, rel)
+    _close(cos, rel)
     full = opf.denoise_flux(sd, shape, lat, prompt, pooled, 4, 3.5, [512], 1, (32, 16))
     g = got.cpu().float()
     assert (g - want).abs().mean() < (g - full).abs().mean()
     reset_runtime_state()
     reset_cache_manager()
+
+
+# Final latents after 4 to 8 denoising steps with guidance against the fp32 oracle: cosine and max |a - b| / max |b|.
+# The per-step bound (0.9999, 2e-2) is held by the model-level tests; several 16-bit steps compound, measured here
+# 0.99990 to 0.999995 and 0.006 to 0.015.
+COS_MIN, MAX_REL = 0.9998, 2e-2
+
+
+def _close(cos, rel, tag=""):
+    print(f"parity {tag}: cosine {cos:.6f} max_rel {rel:.4f}")
+    assert cos >= COS_MIN and rel <= MAX_REL, (tag, cos, rel)
 
 
 def call(worker, method, *args, **kwargs):
@@ -160,7 +171,7 @@ def _flux_worker_case(rank, world, port, errq):
         if rank == 1:
             want = opf.denoise_flux(sd, shape, lat, prompt, pooled, 4, 3.5, [128] * 4, 1, (32, 16), stage_starts=(0, 2))
             cos, rel = oa.cosine_and_max_rel(out.cpu(), want)
-            assert cos >= 0.999 and rel <= 5e-2, ("flux pp2", cos, rel)
+            _close(cos, rel, "flux pp2")
         else:
             assert out is None
         dist.barrier()
@@ -223,7 +234,7 @@ def _worker_case(rank, world, port, errq):
         want = opf.denoise(sd, shape, lat, prompt, pooled, 4, 4.0, [128] * 4, 1, (32, 16))
         if rank == 1:
             cos, rel = oa.cosine_and_max_rel(out.cpu(), want)
-            assert cos >= 0.999 and rel <= 5e-2, ("pp2", cos, rel)
+            _close(cos, rel, "pp2")
         else:
             assert out is None
         # Eight steps: steps 2..5 of the patch pipeline are captured per patch and replayed from CUDA graphs. The
@@ -237,7 +248,7 @@ def _worker_case(rank, world, port, errq):
         w.pipeline.use_cuda_graph = True
         if rank == 1:
             cos, rel = oa.cosine_and_max_rel(outs8[0].cpu(), want8)
-            assert cos >= 0.999 and rel <= 5e-2, ("pp2 eight steps", cos, rel)
+            _close(cos, rel, "pp2 eight steps")
             assert torch.equal(outs8[0], outs8[1]) and torch.equal(outs8[1], outs8[2]), "graph replay differs from eager"
 
         # plan B: two independent single-GPU plans; each rank pulls the blocks it lacks from its peer
@@ -254,7 +265,7 @@ def _worker_case(rank, world, port, errq):
                 assert torch.equal(v.cpu(), ref[k]), (i, k)
         out = diffuse(w, cfg1, lat, prompt, pooled, 4)
         cos, rel = oa.cosine_and_max_rel(out.cpu(), want)
-        assert cos >= 0.999 and rel <= 5e-2, ("solo", cos, rel)
+        _close(cos, rel, "solo")
         state = call(w, "get_worker_state")
         assert state["running_task"] is None and state["running_stage"] is None and state["rank"] == rank
 
@@ -273,7 +284,7 @@ def _worker_case(rank, world, port, errq):
         assert get_runtime_state().pp_patches_token_num == [64] * 4
         want_sp = opf.denoise(sd, shape, lat, prompt, pooled, 4, 4.0, [128] * 4, 1, (32, 16), ulysses=2)
         cos, rel = oa.cosine_and_max_rel(out.cpu(), want_sp)
-        assert cos >= 0.999 and rel <= 5e-2, ("ulysses2", cos, rel)
+        _close(cos, rel, "ulysses2")
         # and without patches the sequence-parallel result is the plain one
         cfg3 = EngineConfig()
         cfg3.parallel_config.sp_config.ulysses_degree = 2
@@ -282,7 +293,7 @@ def _worker_case(rank, world, port, errq):
         out = diffuse(w, cfg3, lat, prompt, pooled, 2, both=True)
         want_full = opf.denoise(sd, shape, lat, prompt, pooled, 2, 4.0, [512], 0, (32, 16))
         cos, rel = oa.cosine_and_max_rel(out.cpu(), want_full)
-        assert cos >= 0.999 and rel <= 5e-2, ("ulysses2 unpatched", cos, rel)
+        _close(cos, rel, "ulysses2 unpatched")
 
         # plans D and E: a tensor-parallel re-slice in which each rank pulls from the slice its peer is replacing
         # at the same time. D (2 pipeline stages, at most 2 cached blocks) leaves blocks 0-1 whole on rank 0 and
@@ -381,7 +392,7 @@ def _pp_sp_case(rank, world, port, errq):
         want = opf.denoise(sd, shape, lat, prompt, pooled, 4, 4.0, [128] * 4, 1, (32, 16), ulysses=2)
         if rank >= 2:
             cos, rel = oa.cosine_and_max_rel(out.cpu(), want)
-            assert cos >= 0.999 and rel <= 5e-2, ("pp2 x ulysses2", cos, rel)
+            _close(cos, rel, "pp2 x ulysses2")
         else:
             assert out is None
         cfg2 = EngineConfig()
@@ -392,7 +403,7 @@ def _pp_sp_case(rank, world, port, errq):
         out = diffuse(w, cfg2, lat, prompt, pooled, 2, both=True)
         want_full = opf.denoise(sd, shape, lat, prompt, pooled, 2, 4.0, [512], 0, (32, 16))
         cos, rel = oa.cosine_and_max_rel(out.cpu(), want_full)
-        assert cos >= 0.999 and rel <= 5e-2, ("ulysses4", cos, rel)
+        _close(cos, rel, "ulysses4")
         dist.barrier()
         dist.destroy_process_group()
     except Exception:
