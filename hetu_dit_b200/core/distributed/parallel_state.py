@@ -83,6 +83,10 @@ class ParallelGroups:
         self.plan_epoch = next(_PLAN_EPOCHS)  # new value whenever a group is re-bound: captured CUDA graphs of older plans are void
         self.activate_plan(list(range(world_size)) if world_size == 1 else [rank])
 
+    def void_captured_graphs(self):
+        """New plan epoch without a new plan: addresses that captured CUDA graphs hold are no longer valid."""
+        self.plan_epoch = next(_PLAN_EPOCHS)
+
     # -- enumeration the reference uses to size its communicator pool -------------------
     def _generate_rank_combinations(self, world_size: int, base_num: int = 0) -> List[List[int]]:
         out = []

@@ -78,6 +78,20 @@ class PeerHeap:
         self._named.clear()
         self._flip.clear()
 
+    def mark(self):
+        """The allocation state right now, for rewind()."""
+        return self._cursor, frozenset(self._named)
+
+    def rewind(self, mark):
+        """Forget every buffer allocated since mark() (a request of a new shape on the same plan: exchange
+        buffers are named by shape, and a bump allocator can only give memory back from its end). Every rank of
+        the plan must rewind between the same two requests; CUDA graphs that captured the forgotten buffers'
+        addresses are void afterwards."""
+        cursor, names = mark
+        self._cursor = cursor
+        for name in [n for n in self._named if n not in names]:
+            del self._named[name]
+
     def reserve_tail(self, nbytes: int) -> int:
         """Sets `nbytes` at the top of the heap aside for good (it survives reset()) and returns its offset. Every
         rank must make the same reservations in the same order, before the plans start to allocate."""

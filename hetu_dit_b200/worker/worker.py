@@ -119,6 +119,8 @@ class Worker:
         # inbox by its own inbox offset, so every stage must carve it from the same place.
         if pc.pp_degree > 1:
             ps.get_pp_group()
+        self._heap_mark = self.heap.mark()
+        self._last_request_shape = None
 
     def rpc_find_sources(self, pieces) -> List[int]:
         """uids of the pieces this worker's cache can serve; none while it is re-slicing itself."""
@@ -198,14 +200,20 @@ class Worker:
         rt.set_input_parameters(height=input_config.height, width=input_config.width,
                                 batch_size=input_config.batch_size or 1,
                                 num_inference_steps=input_config.num_inference_steps)
-        # A text length the previous request did not have changes the shape of the text-stream message between
-        # pipeline stages: every stage forgets its inbox layout here, between the same two requests.
-        text_shape = tuple(prompt_embeds.shape)
-        if text_shape != getattr(self, "_last_text_shape", None):
+        # A request shape (resolution, batch, text length) the previous request did not have: the exchange buffers in
+        # the peer heap are named by shape, so the heap goes back to where the plan left it (else a long trace of
+        # many shapes fills it), the CUDA graphs that hold the old buffers' addresses are dropped, and every
+        # pipeline stage forgets its inbox layout (the text-stream message changes size) -- on every rank of the
+        # plan, between the same two requests.
+        request_shape = (input_config.height, input_config.width, input_config.batch_size or 1, tuple(prompt_embeds.shape))
+        if request_shape != getattr(self, "_last_request_shape", None):
+            if getattr(self, "_last_request_shape", None) is not None and getattr(self, "_heap_mark", None) is not None:
+                self.heap.rewind(self._heap_mark)
+                ps.get_parallel_groups().void_captured_graphs()
             pp = ps.get_pp_group_or_none()
             if pp is not None:
                 pp.reset_buffer()
-            self._last_text_shape = text_shape
+            self._last_request_shape = request_shape
         out = self.pipeline.diffusion_stage(latents, prompt_embeds, pooled, input_config.num_inference_steps)
         torch.cuda.synchronize(self.device)
         self.heap.check()

@@ -290,3 +290,22 @@ def test_attention_waits_for_peer_flags_and_reports_a_silent_peer():
     assert torch.equal(kernels.attn_fwd([q], [k], [v]), want)   # the next launch is unaffected
     torch.cuda.synchronize()
     assert _C.device_status(0, clear=True)[0] == 0
+
+
+def test_peer_heap_mark_and_rewind():
+    """Buffers allocated after mark() go away on rewind() and the same names come back at the same offsets;
+    buffers from before the mark stay where they are."""
+    from hetu_dit_b200.core.distributed.peer import PeerHeap
+    heap = PeerHeap(8 << 20, 0, 1, torch.device(DEV))
+    inbox, off_inbox = heap.alloc((1024,), torch.uint8, name="pp_inbox")
+    mark = heap.mark()
+    a, off_a = heap.alloc((4, 256), torch.bfloat16, name="usp_q_a")
+    b, off_b = heap.alloc((1000,), torch.float32, name="usp_k_a")
+    assert heap.alloc((4, 256), torch.bfloat16, name="usp_q_a")[1] == off_a
+    heap.rewind(mark)
+    c, off_c = heap.alloc((8, 256), torch.bfloat16, name="usp_q_b")     # another shape takes the space
+    assert off_c == off_a and c.data_ptr() == a.data_ptr()
+    assert heap.alloc((1024,), torch.uint8, name="pp_inbox")[1] == off_inbox
+    heap.rewind(mark)
+    assert heap.alloc((4, 256), torch.bfloat16, name="usp_q_a")[1] == off_a
+    assert heap.alloc((1000,), torch.float32, name="usp_k_a")[1] == off_b
