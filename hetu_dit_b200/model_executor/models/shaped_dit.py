@@ -185,6 +185,9 @@ class Attention(nn.Module):
 
 
 _BRANCH_STREAMS = {}
+# Run a double block's text-stream tail beside the image-stream tail on one GPU too (under sequence parallelism it
+# always does): HDIT_BRANCH_TEXT_TAIL=1.
+BRANCH_TEXT_TAIL_ALWAYS = os.environ.get("HDIT_BRANCH_TEXT_TAIL", "0") == "1"
 
 
 class _Branch:
@@ -244,7 +247,7 @@ class JointBlock(nn.Module):
         # LayerNorm + modulation and gate + residual are one fused pass each (csrc/elementwise.cu)
         h = kernels.ln_modulate(hidden, mod[0], mod[1])
         c = kernels.ln_modulate(context, cmod[0], cmod[1])
-        sp = ps.get_sequence_parallel_world_size() > 1 and hidden.is_cuda
+        sp = (ps.get_sequence_parallel_world_size() > 1 or BRANCH_TEXT_TAIL_ALWAYS) and hidden.is_cuda
         # with fused linear layers the gated residual of the image stream rides on the attention's output
         # projection (and the text stream's too, unless its tail runs on the branch stream below)
         fuse = kernels.FUSED_LINEAR and "gate_residual" in kernels.FUSED_LINEAR_TAILS and hidden.is_cuda
