@@ -80,6 +80,13 @@ __device__ __forceinline__ uint16_t from_f(float f) {
     return __bfloat16_as_ushort(__float2bfloat16_rn(f));
 }
 
+// Grid size per SM. A CTA that handles a single pair of tokens lives for one load round trip, and the launch
+// and retirement of thousands of such CTAs is what the kernel then spends its time on; a few CTAs per SM that
+// loop over many token pairs keep their loads in flight back to back.
+#ifndef HDIT_NR_CTAS_PER_SM
+#define HDIT_NR_CTAS_PER_SM 32
+#endif
+
 // Resident CTAs per SM the register allocation aims for (bytes in flight per SM = CTAs x threads x 32). Measured at
 // the Flux shape (4608 tokens, 24 x 128, Q and K): 2 -> 46.5 us, 3 (40 registers, small spills) -> 50.1 us.
 #ifndef HDIT_NR_MIN_CTAS
@@ -360,7 +367,7 @@ extern "C" int hdit_qk_norm_rope(const hdit_norm_rope_args* a) {
   threads = (threads + 31) / 32 * 32;
   if (threads > 512) threads = 512;
   const long long n_tok = static_cast<long long>(a->batch) * a->seq;
-  const long long cap = 148LL * 32;  // short blocks (one 16-byte load per thread per token): many resident CTAs
+  const long long cap = 148LL * HDIT_NR_CTAS_PER_SM;
   const long long want = (n_tok + 1) / 2;  // a CTA takes two tokens per pass
   dim3 grid(static_cast<unsigned>(want < cap ? want : cap), static_cast<unsigned>(a->n_tensors));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
