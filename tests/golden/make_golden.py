@@ -14,6 +14,13 @@ inputs and outputs are written out:
   rope.npz           apply_rotary_emb on seeded inputs
   usp_<case>.npz     hetuDiT*LongContextAttention / ring attention / KV cache on
                      CPU `gloo` ranks, fp32
+  pipefusion_order.json  per pipeline stage, the order of receives, receive-queue
+                     operations, forwards, scheduler steps and sends that the SD3
+                     pipeline's _sync_pipeline / _init_async_pipeline / _async_pipeline
+                     produce with recording stand-ins (--only pipefusion_order)
+  pos_embed_rows.json  which rows of the position table the patch-embedding wrapper
+                     adds on every sequence-parallel rank, whole image and per
+                     pipeline patch (--only pos_embed_rows)
 
 The reference imports packages that are not installed here (diffusers, ray,
 yunchang, flash_attn on CPU). Those imports are satisfied with stubs defined
