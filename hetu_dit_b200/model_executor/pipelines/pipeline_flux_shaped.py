@@ -24,6 +24,11 @@ from .pipeline_sd3_shaped import SD3ShapedPipeline, stage_block_range
 
 
 class FluxShapedPipeline(SD3ShapedPipeline):
+    # the reference's Flux pipeline labels the text-stream message differently in its two loops
+    # (pipeline_flux.py:475,526 against :756,606,668)
+    sync_text_message = "encoder_hidden_state"
+    async_text_message = "encoder_hidden_states"
+
     def __init__(self, model: ShapedDiT, guidance_scale: float = 3.5, grid=(64, 64)):
         if model.shape.rope_axes is None or model.guidance_embed is None:
             raise ValueError("FluxShapedPipeline needs a model with rotary positions and a guidance embedding")

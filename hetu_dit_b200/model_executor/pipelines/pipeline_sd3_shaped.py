@@ -45,6 +45,10 @@ def stage_block_range(total_blocks: int, pp_rank: int, pp_world: int,
 
 
 class SD3ShapedPipeline:
+    # label of the text-stream message between pipeline stages, in the whole-image steps and in the patch steps
+    # (pipeline_stable_diffusion_3.py:1395,1438 and :1502,1560,1632)
+    sync_text_message = "encoder_hidden_states"
+    async_text_message = "encoder_hidden_states"
     use_cuda_graph = True    # see __init__
     fused_step = True
     _patch_pool = None       # memory pool shared by the per-patch CUDA graphs
@@ -214,7 +218,7 @@ class SD3ShapedPipeline:
             else:
                 latents = pp.pipeline_recv()
                 if not first:
-                    encoder_hidden_states = pp.pipeline_recv(0, "encoder_hidden_states")
+                    encoder_hidden_states = pp.pipeline_recv(0, self.sync_text_message)
             latents, encoder_hidden_states = self._backbone_forward(
                 latents, prompt_embeds if first else encoder_hidden_states, pooled, self.sigmas[i:i + 1], guide=not last)
             sends = pp_world > 1 and not (sync_only and last and k == len(steps) - 1)
@@ -222,7 +226,7 @@ class SD3ShapedPipeline:
                 latents = self._guided_step(latents, last_timestep_latents, i, ("latent", -1) if sends else None)
             elif sends:
                 pp.pipeline_send(latents)
-                pp.pipeline_send(encoder_hidden_states, name="encoder_hidden_states")
+                pp.pipeline_send(encoder_hidden_states, name=self.sync_text_message)
         return latents
 
     # ------------------------------------------------------------------ patch pipeline
@@ -246,7 +250,7 @@ class SD3ShapedPipeline:
         recv_timesteps = num_timesteps - 1 if first else num_timesteps
         for _ in range(recv_timesteps):
             if not first:
-                pp.add_pipeline_recv_task(0, "encoder_hidden_states")
+                pp.add_pipeline_recv_task(0, self.async_text_message)
             for patch_idx in range(rt.num_pipeline_patch):
                 pp.add_pipeline_recv_task(patch_idx)
         return patch_latents
@@ -277,11 +281,11 @@ class SD3ShapedPipeline:
                 st["first_recv"] = False
             if not first and p == 0:
                 if host_only:
-                    pp.pop_received(idx=p, name="encoder_hidden_states")
+                    pp.pop_received(idx=p, name=self.async_text_message)
                 else:
                     # private copy: the text stream serves every patch of this step, while the
                     # sender may refill the inbox slot as soon as patch 0 has gone round the ring
-                    st["text"] = pp.get_pipeline_recv_data(idx=p, name="encoder_hidden_states").clone()
+                    st["text"] = pp.get_pipeline_recv_data(idx=p, name=self.async_text_message).clone()
             if host_only:
                 pp.pop_received(idx=p)
             else:
@@ -312,7 +316,7 @@ class SD3ShapedPipeline:
                     ("latent", p) if sends else None, sigmas=sigmas, out=out)
             elif pp_world > 1:
                 if p == 0:
-                    pp.pipeline_isend(next_text, name="encoder_hidden_states")
+                    pp.pipeline_isend(next_text, name=self.async_text_message)
                 pp.pipeline_isend(patch_latents[p], segment_idx=p)
 
         # Steps 2 .. n - 2 of the patch pipeline enqueue the same launches per patch: they are captured once per

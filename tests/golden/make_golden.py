@@ -589,98 +589,122 @@ def _lift_method_undecorated(path, name, cls, namespace):
 
 
 def gen_pipefusion_order(ref):
-    """Runs the reference's _sync_pipeline / _init_async_pipeline / _async_pipeline
-    (model_executor/pipelines/pipeline_stable_diffusion_3.py:1352-1678) for every stage of a few pipeline shapes
-    with a recording stand-in for the pipeline group, the backbone and the scheduler, and writes per stage the
-    order of receives, queue operations, forwards, scheduler steps and sends."""
+    """Runs the reference's _sync_pipeline / _init_async_pipeline / _async_pipeline of the SD3 pipeline
+    (model_executor/pipelines/pipeline_stable_diffusion_3.py:1352-1678) and of the Flux pipeline
+    (pipelines/pipeline_flux.py:428-760) for every stage of a few pipeline shapes with a recording stand-in for the
+    pipeline group, the backbone and the scheduler, and writes per stage the order of receives, queue operations,
+    forwards, scheduler steps and sends."""
     from typing import Callable, Dict, List, Optional
-    path = os.path.join(ref, "hetu_dit/model_executor/pipelines/pipeline_stable_diffusion_3.py")
+    families = {
+        "sd3": ("hetu_dit/model_executor/pipelines/pipeline_stable_diffusion_3.py", "hetuDiTStableDiffusion3Pipeline"),
+        "flux": ("hetu_dit/model_executor/pipelines/pipeline_flux.py", "hetuDiTFluxPipeline"),
+    }
     cases = []
-    for (stages, n_patch, n_steps, warmup) in PIPEFUSION_CASES:
-        for stage in range(stages):
-            events = []
-            patch_h = 2
+    for family, (rel, cls) in families.items():
+        path = os.path.join(ref, rel)
+        for (stages, n_patch, n_steps, warmup) in PIPEFUSION_CASES:
+            for stage in range(stages):
+                events = []
+                patch_h = 2      # SD3: latent rows per patch; Flux: tokens per patch
+                flux = family == "flux"
 
-            class Group:
-                def pipeline_recv(self, idx=-1, name="latent"):
-                    events.append(["recv", name or "latent", idx])
-                    return torch.zeros(1, 4, patch_h * n_patch, 4) if (name or "latent") == "latent" else "text"
+                def whole():
+                    return torch.zeros(1, patch_h * n_patch, 4) if flux else torch.zeros(1, 4, patch_h * n_patch, 4)
 
-                def pipeline_send(self, tensor, name="latent", segment_idx=-1):
-                    events.append(["send", name, segment_idx])
+                def one_patch():
+                    return torch.zeros(1, patch_h, 4) if flux else torch.zeros(1, 4, patch_h, 4)
 
-                pipeline_isend = pipeline_send
+                class Group:
+                    def pipeline_recv(self, idx=-1, name="latent"):
+                        events.append(["recv", name or "latent", idx])
+                        return whole() if (name or "latent") == "latent" else "text"
 
-                def add_pipeline_recv_task(self, idx=-1, name="latent"):
-                    events.append(["add_recv_task", name or "latent", idx])
+                    def pipeline_send(self, tensor, name="latent", segment_idx=-1):
+                        events.append(["send", name, segment_idx])
 
-                def recv_next(self):
-                    events.append(["recv_next"])
+                    pipeline_isend = pipeline_send
 
-                def get_pipeline_recv_data(self, idx=-1, name="latent"):
-                    events.append(["get", name, idx])
-                    return torch.zeros(1, 4, patch_h, 4) if name == "latent" else "text"
+                    def add_pipeline_recv_task(self, idx=-1, name="latent"):
+                        events.append(["add_recv_task", name or "latent", idx])
 
-            class State:
-                num_pipeline_patch = n_patch
-                pp_patches_height = [patch_h] * n_patch
-                pp_patches_start_idx_local = [patch_h * i for i in range(n_patch + 1)]
-                runtime_config = _NS(warmup_steps=warmup)
-                pipeline_patch_idx = 0
+                    def recv_next(self):
+                        events.append(["recv_next"])
 
-                def set_patched_mode(self, patch_mode):
-                    events.append(["patched_mode", bool(patch_mode)])
-                    self.pipeline_patch_idx = 0
+                    def get_pipeline_recv_data(self, idx=-1, name="latent"):
+                        events.append(["get", name, idx])
+                        return one_patch() if name == "latent" else "text"
 
-                def next_patch(self):
-                    self.pipeline_patch_idx = (self.pipeline_patch_idx + 1) % n_patch
+                class State:
+                    num_pipeline_patch = n_patch
+                    pp_patches_height = [patch_h] * n_patch
+                    pp_patches_token_num = [patch_h] * n_patch
+                    pp_patches_start_idx_local = [patch_h * i for i in range(n_patch + 1)]
+                    pp_patches_token_start_idx_local = [patch_h * i for i in range(n_patch + 1)]
+                    pp_patches_token_start_end_idx_global = [(patch_h * i, patch_h * (i + 1)) for i in range(n_patch)]
+                    runtime_config = _NS(warmup_steps=warmup)
+                    pipeline_patch_idx = 0
 
-            state, group = State(), Group()
-            prompt = "prompt"
+                    def set_patched_mode(self, patch_mode):
+                        events.append(["patched_mode", bool(patch_mode)])
+                        self.pipeline_patch_idx = 0
 
-            class Pipe:
-                interrupt = False
-                scheduler = _NS(order=1)
+                    def next_patch(self):
+                        self.pipeline_patch_idx = (self.pipeline_patch_idx + 1) % n_patch
 
-                def _init_sync_pipeline(self, latents):
-                    events.append(["patched_mode", False])  # what the reference's _init_sync_pipeline does first
-                    state.pipeline_patch_idx = 0
-                    return latents
+                state, group = State(), Group()
+                prompt = "prompt"
 
-                def _backbone_forward(self, latents, encoder_hidden_states, pooled_prompt_embeds, t):
-                    events.append(["forward", state.pipeline_patch_idx, int(t),
-                                   "prompt" if encoder_hidden_states is prompt else "received"])
-                    return latents, "text"
+                class Pipe:
+                    interrupt = False
+                    scheduler = _NS(order=1)
 
-                def _scheduler_step(self, noise_pred, last, t):
-                    events.append(["step", int(t)])
-                    return noise_pred
+                    def _backbone_forward(self, latents, encoder_hidden_states, pooled_prompt_embeds, t, **_):
+                        events.append(["forward", state.pipeline_patch_idx, int(t),
+                                       "prompt" if encoder_hidden_states is prompt else "received"])
+                        return latents, "text"
 
-            ns = {
-                "torch": torch, "List": List, "Optional": Optional, "Callable": Callable, "Dict": Dict,
-                "logger": logging.getLogger("golden"), "XLA_AVAILABLE": False,
-                "get_runtime_state": lambda: state, "get_pp_group": lambda: group,
-                "is_pipeline_first_stage": lambda: stage == 0, "is_pipeline_last_stage": lambda: stage == stages - 1,
-                "get_pipeline_parallel_world_size": lambda: stages, "get_sequence_parallel_world_size": lambda: 1,
-                "get_sp_group": lambda: None,
-            }
-            for name in ("_sync_pipeline", "_init_async_pipeline", "_async_pipeline"):
-                setattr(Pipe, name, _lift_method_undecorated(path, name, "hetuDiTStableDiffusion3Pipeline", ns))
-            pipe = Pipe()
-            bar = _NS(update=lambda: None)
-            latents = torch.zeros(1, 4, patch_h * n_patch, 4)
-            timesteps = list(range(n_steps))
-            # the entry point's branch (pipeline_stable_diffusion_3.py:372-411)
-            if n_patch > 1 and n_steps > warmup:
-                latents = pipe._sync_pipeline(latents=latents, prompt_embeds=prompt, pooled_prompt_embeds=None,
-                                              timesteps=timesteps[:warmup], num_warmup_steps=0, progress_bar=bar)
-                pipe._async_pipeline(latents=latents, prompt_embeds=prompt, pooled_prompt_embeds=None,
-                                     timesteps=timesteps[warmup:], num_warmup_steps=0, progress_bar=bar)
-            else:
-                pipe._sync_pipeline(latents=latents, prompt_embeds=prompt, pooled_prompt_embeds=None,
-                                    timesteps=timesteps, num_warmup_steps=0, progress_bar=bar, sync_only=True)
-            cases.append({"stages": stages, "stage": stage, "num_pipeline_patch": n_patch, "steps": n_steps,
-                          "warmup": warmup, "events": events})
+                    def _scheduler_step(self, noise_pred, last, t):
+                        events.append(["step", int(t)])
+                        return noise_pred
+
+                if flux:
+                    def _init_sync(self, latents, latent_image_ids):
+                        events.append(["patched_mode", False])  # what the reference's _init_sync_pipeline does first
+                        state.pipeline_patch_idx = 0
+                        return latents, latent_image_ids
+                else:
+                    def _init_sync(self, latents):
+                        events.append(["patched_mode", False])
+                        state.pipeline_patch_idx = 0
+                        return latents
+                Pipe._init_sync_pipeline = _init_sync
+
+                ns = {
+                    "torch": torch, "List": List, "Optional": Optional, "Callable": Callable, "Dict": Dict,
+                    "logger": logging.getLogger("golden"), "XLA_AVAILABLE": False,
+                    "get_runtime_state": lambda: state, "get_pp_group": lambda: group,
+                    "is_pipeline_first_stage": lambda: stage == 0, "is_pipeline_last_stage": lambda: stage == stages - 1,
+                    "get_pipeline_parallel_world_size": lambda: stages, "get_sequence_parallel_world_size": lambda: 1,
+                    "get_sp_group": lambda: None,
+                }
+                for name in ("_sync_pipeline", "_init_async_pipeline", "_async_pipeline"):
+                    setattr(Pipe, name, _lift_method_undecorated(path, name, cls, ns))
+                pipe = Pipe()
+                bar = _NS(update=lambda: None)
+                latents = whole()
+                timesteps = list(range(n_steps))
+                extra = dict(text_ids=None, latent_image_ids=torch.zeros(patch_h * n_patch, 3), guidance=None) if flux else {}
+                # the entry point's branch (pipeline_stable_diffusion_3.py:372-411, pipeline_flux.py:346-390)
+                if n_patch > 1 and n_steps > warmup:
+                    latents = pipe._sync_pipeline(latents=latents, prompt_embeds=prompt, pooled_prompt_embeds=None,
+                                                  timesteps=timesteps[:warmup], num_warmup_steps=0, progress_bar=bar, **extra)
+                    pipe._async_pipeline(latents=latents, prompt_embeds=prompt, pooled_prompt_embeds=None,
+                                         timesteps=timesteps[warmup:], num_warmup_steps=0, progress_bar=bar, **extra)
+                else:
+                    pipe._sync_pipeline(latents=latents, prompt_embeds=prompt, pooled_prompt_embeds=None,
+                                        timesteps=timesteps, num_warmup_steps=0, progress_bar=bar, sync_only=True, **extra)
+                cases.append({"pipeline": family, "stages": stages, "stage": stage, "num_pipeline_patch": n_patch,
+                              "steps": n_steps, "warmup": warmup, "events": events})
     with open(os.path.join(HERE, "pipefusion_order.json"), "w") as f:
         json.dump(cases, f, separators=(",", ":"))
     print("pipefusion_order.json written:", len(cases), "cases")

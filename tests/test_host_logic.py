@@ -483,14 +483,15 @@ def _pipefusion_cases():
 
 
 @pytest.mark.parametrize("case", _pipefusion_cases(),
-                         ids=lambda c: f"pp{c['stages']}s{c['stage']}m{c['num_pipeline_patch']}n{c['steps']}w{c['warmup']}")
+                         ids=lambda c: f"{c['pipeline']}pp{c['stages']}s{c['stage']}m{c['num_pipeline_patch']}n{c['steps']}w{c['warmup']}")
 def test_pipefusion_schedule_order_matches_reference(case, monkeypatch):
     """Every stage's order of receives, receive-queue operations, forwards (patch index, step, text source),
     scheduler steps and sends through the warm-up and the patch pipeline is the one the reference's
-    _sync_pipeline / _init_async_pipeline / _async_pipeline produce
-    (model_executor/pipelines/pipeline_stable_diffusion_3.py:1352-1678, run with recording stand-ins by
-    tests/golden/make_golden.py)."""
+    _sync_pipeline / _init_async_pipeline / _async_pipeline produce, for its SD3 pipeline
+    (model_executor/pipelines/pipeline_stable_diffusion_3.py:1352-1678) and its Flux pipeline
+    (pipelines/pipeline_flux.py:428-760), run with recording stand-ins by tests/golden/make_golden.py."""
     import types
+    from hetu_dit_b200.model_executor.pipelines import pipeline_flux_shaped
     from hetu_dit_b200.model_executor.pipelines import pipeline_sd3_shaped as mod
     stages, stage, n_patch = case["stages"], case["stage"], case["num_pipeline_patch"]
     events, tokens = [], 4
@@ -539,7 +540,8 @@ def test_pipefusion_schedule_order_matches_reference(case, monkeypatch):
     monkeypatch.setattr(mod, "flow_match_sigmas", lambda n, device=None: torch.arange(n + 1, dtype=torch.float32))
     prompt = torch.zeros(2, 3, 8)
 
-    pipe = object.__new__(mod.SD3ShapedPipeline)
+    cls = pipeline_flux_shaped.FluxShapedPipeline if case["pipeline"] == "flux" else mod.SD3ShapedPipeline
+    pipe = object.__new__(cls)
 
     def backbone(latents, encoder_hidden_states, pooled, t, guide=True):
         assert guide == (stage != stages - 1)  # the last stage leaves guidance to the fused step
