@@ -27,7 +27,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ... import kernels
-from .peer import DEFAULT_MAX_SPINS, PeerGroup
+from .peer import PeerGroup
 
 _HEADER_BYTES = 256
 _MAGIC = 0x48444954  # "HDIT"
