@@ -597,6 +597,7 @@ int launch_gemm(GemmParams& kp, const hdit_gemm_args* a, cudaStream_t stream) {
   kp.m_tiles = static_cast<int>((a->m + C::kTileRows - 1) / C::kTileRows);
   kp.n_tiles = static_cast<int>((a->n + BN - 1) / BN);
   const long long tiles = static_cast<long long>(kp.m_tiles) * kp.n_tiles;
+  if (tiles > 0x7fffffffLL) return set_error(HDIT_ERR_TOO_LARGE, "more than 2^31 output tiles");
   long long ctas = a->max_ctas > 0 ? a->max_ctas : sm_count();
   {
     // band height: a wave of `units` tiles should read about as many A bytes as W bytes
@@ -663,6 +664,9 @@ extern "C" int hdit_linear_fused(const hdit_gemm_args* a) {
   if (a->epilogue == HDIT_GEMM_BIAS_GATE_RESIDUAL) {
     if (a->residual == nullptr || a->gate == nullptr || a->rows_per_batch <= 0)
       return set_error(HDIT_ERR_BAD_ARG, "the gated-residual epilogue needs residual, gate and rows_per_batch > 0");
+    if (a->rows_per_batch < 32 && a->rows_per_batch < a->m)
+      return set_error(HDIT_ERR_SHAPE, "the gated-residual epilogue needs at least 32 rows per batch entry "
+                                       "(a warp's 32 rows may span two entries, not more)");
     if (bad(a->residual, a->ldr) || bad(a->gate, a->gate_batch_stride) || a->ldr < a->n)
       return set_error(HDIT_ERR_SHAPE, "residual / gate need 16-byte aligned pointers and strides that are multiples of 8");
   }

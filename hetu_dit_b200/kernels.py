@@ -551,7 +551,7 @@ def linear_tail(linear, x, epilogue, residual=None, gate=None, out=None):
     fusable = (FUSED_LINEAR and epilogue in FUSED_LINEAR_TAILS and x.is_cuda and x.dim() == 3 and _even_rows(x) and not torch.is_grad_enabled()
                and FUSED_LINEAR_MIN_ROWS <= x.shape[0] * x.shape[1] <= FUSED_LINEAR_MAX_ROWS
                and (out is None or _even_rows(out)) and (residual is None or _even_rows(residual))
-               and (gate is None or gate.stride(-1) == 1))
+               and (gate is None or (gate.stride(-1) == 1 and (x.shape[0] == 1 or x.shape[1] >= 32))))
     if fusable:
         return linear_fused(x, linear.weight, linear.bias, epilogue, residual=residual, gate=gate, out=out)
     y = linear(x)

@@ -413,6 +413,7 @@ HDIT_API int hdit_cfg_euler_step(int32_t dtype, const void* uncond, const void* 
  *   HDIT_GEMM_BIAS               : nothing more
  *   HDIT_GEMM_BIAS_GELU_TANH     : GELU, tanh approximation (as hdit_gelu_tanh)
  *   HDIT_GEMM_BIAS_GATE_RESIDUAL : residual[r, :] + gate[r / rows_per_batch, :] * value (as hdit_gate_residual)
+ *                                  (rows_per_batch >= 32 unless there is a single batch entry)
  * Row strides (lda, ldw, ldo, ldr, gate_batch_stride) in elements, multiples of 8; pointers 16-byte aligned; n and k
  * multiples of 8; m, n, k ragged against the tile sizes are handled. `out` may alias `residual`. bias may be NULL.
  * tile_m x tile_n: output tile of one CTA, 128 x 256, 128 x 128 or 256 x 256; cta_pair = 2 makes two CTAs of a

@@ -74,6 +74,11 @@ def test_argument_checks_without_gpu():
     assert _C.lib().hdit_linear_fused(ctypes.byref(g)) == _C.HDIT_ERR_SHAPE
     g.n, g.epilogue = 16, 7
     assert _C.lib().hdit_linear_fused(ctypes.byref(g)) == _C.HDIT_ERR_BAD_ARG
+    # gated residual over batch entries of fewer than 32 rows: a warp's rows would span more than two entries
+    g.epilogue, g.m, g.rows_per_batch = _C.GEMM_BIAS_GATE_RESIDUAL, 64, 16
+    g.residual = g.gate = 256
+    g.ldr = g.gate_batch_stride = 16
+    assert _C.lib().hdit_linear_fused(ctypes.byref(g)) == _C.HDIT_ERR_SHAPE
     a.head_dim, a.n_kv_seg = 64, 11
     assert _C.lib().hdit_attn_fwd(ctypes.byref(a)) == _C.HDIT_ERR_SHAPE
     assert b"n_kv_seg" in _C.lib().hdit_last_error()
