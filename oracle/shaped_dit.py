@@ -70,16 +70,13 @@ def _qk(sd, prefix, x, H, D, norm_name, rope, row0, eps=1e-6):
     return y
 
 
-def joint_block(sd, p, hidden, context, temb, rope, H, D, order, kv_hook=None, row0=None, rope_on_text=True):
-    """kv_hook(k_img, v_img) -> (k_all, v_all): PipeFusion's stale-KV cache for the image tokens
-    (attention_processor.py:702-707); row0: rotary table row of the first image token; rope_on_text: the
-    table has rows for the text tokens (Flux) -- otherwise only the image / video rows are rotated."""
-    d = hidden.shape[-1]
-    mod = _lin(sd, p + ".norm1.linear", F.silu(temb)).chunk(6, dim=-1)
-    cmod = _lin(sd, p + ".norm1_context.linear", F.silu(temb)).chunk(6, dim=-1)
-    h = _mod(F.layer_norm(hidden, (d,), eps=1e-6), mod[0], mod[1])
-    c = _mod(F.layer_norm(context, (d,), eps=1e-6), cmod[0], cmod[1])
-    a = p + ".attn.module"
+def joint_attention(sd, a, h, c, rope, H, D, order, kv_hook=None, row0=None, rope_on_text=True):
+    """Joint attention of a double-stream block on the modulated streams h (image / video) and c (text), before the
+    output projections: (image rows, text rows), each (B, S, H*D). What the reference's processors return:
+    hetuDiTJointAttnProcessor2_0 (attention_processor.py:657-794; order "rear", no QK norm, no rotary table),
+    hetuDiTFluxAttnProcessor2_0 with encoder_hidden_states (:824-988; order "front", rotary rows for text and image),
+    hetuDiTHunyuanVideoAttnProcessor2_0 with add_q_proj (:1373-1534; order "rear", rotary rows for the video only)."""
+    d = h.shape[-1]
     S_txt, S_img = c.shape[1], h.shape[1]
     r0 = (S_txt if rope_on_text else 0) if row0 is None else row0
     q = _qk(sd, a, _lin(sd, a + ".to_q", h), H, D, "norm_q", rope, r0)
@@ -97,8 +94,22 @@ def joint_block(sd, p, hidden, context, temb, rope, H, D, order, kv_hook=None, r
     else:
         o = oa.sdpa(torch.cat([tq, q], 1), torch.cat([tk, k], 1), torch.cat([tv, v], 1))
         txt, img = o[:, :S_txt], o[:, S_txt:]
-    img = _lin(sd, a + ".to_out.0", img.reshape(img.shape[0], S_img, d))
-    txt = _lin(sd, a + ".to_add_out", txt.reshape(txt.shape[0], S_txt, d))
+    return img.reshape(img.shape[0], S_img, d), txt.reshape(txt.shape[0], S_txt, d)
+
+
+def joint_block(sd, p, hidden, context, temb, rope, H, D, order, kv_hook=None, row0=None, rope_on_text=True):
+    """kv_hook(k_img, v_img) -> (k_all, v_all): PipeFusion's stale-KV cache for the image tokens
+    (attention_processor.py:702-707); row0: rotary table row of the first image token; rope_on_text: the
+    table has rows for the text tokens (Flux) -- otherwise only the image / video rows are rotated."""
+    d = hidden.shape[-1]
+    mod = _lin(sd, p + ".norm1.linear", F.silu(temb)).chunk(6, dim=-1)
+    cmod = _lin(sd, p + ".norm1_context.linear", F.silu(temb)).chunk(6, dim=-1)
+    h = _mod(F.layer_norm(hidden, (d,), eps=1e-6), mod[0], mod[1])
+    c = _mod(F.layer_norm(context, (d,), eps=1e-6), cmod[0], cmod[1])
+    a = p + ".attn.module"
+    img, txt = joint_attention(sd, a, h, c, rope, H, D, order, kv_hook, row0, rope_on_text)
+    img = _lin(sd, a + ".to_out.0", img)
+    txt = _lin(sd, a + ".to_add_out", txt)
     hidden = hidden + mod[2][:, None] * img
     hidden = hidden + mod[5][:, None] * _ff(sd, p + ".ff", _mod(F.layer_norm(hidden, (d,), eps=1e-6), mod[3], mod[4]))
     context = context + cmod[2][:, None] * txt
@@ -107,21 +118,15 @@ def joint_block(sd, p, hidden, context, temb, rope, H, D, order, kv_hook=None, r
     return hidden, context
 
 
-def single_block(sd, p, x, temb, rope, H, D, text_len=None, row0=None, kv_hook=None, text_first=True,
-                 rope_on_text=True):
-    """x = [text; image] rows. text_len / row0: the first text_len rows take rotary rows [0, text_len), the
-    rest rows [row0, ...) (a patch of the image); kv_hook(k_img, v_img) -> (k_all, v_all) is PipeFusion's
-    stale-KV cache of the image tokens (attention_processor.py:898-917 of the reference).
-    text_first=False: x = [image; text] (HunyuanVideo single blocks, :1464-1468); rope_on_text=False: only the
-    image / video rows are rotated, from table row `row0` (default 0)."""
-    d = x.shape[-1]
-    shift, scale, gate = _lin(sd, p + ".norm.linear", F.silu(temb)).chunk(3, dim=-1)
-    h = _mod(F.layer_norm(x, (d,), eps=1e-6), shift, scale)
-    mlp = F.gelu(_lin(sd, p + ".proj_mlp", h), approximate="tanh")
-    a = p + ".attn.module"
+def single_attention(sd, a, h, rope, H, D, text_len=None, row0=None, kv_hook=None, text_first=True, rope_on_text=True):
+    """Attention of a single-stream block over the modulated joint rows h, before the output projection, (B, S, H*D):
+    hetuDiTFluxAttnProcessor2_0 without encoder_hidden_states (attention_processor.py:824-988; [text; image], rotary
+    rows for all) and hetuDiTHunyuanVideoAttnProcessor2_0 without add_q_proj (:1373-1534; [video; text], rotary rows
+    for the video only). text_len / row0 / kv_hook as in single_block()."""
+    d = h.shape[-1]
     if not (text_first and rope_on_text):
         assert kv_hook is None and text_len is not None
-        S = x.shape[1]
+        S = h.shape[1]
         t_lo, t_hi = (0, text_len) if text_first else (S - text_len, S)
         i_lo, i_hi = (text_len, S) if text_first else (0, S - text_len)
         ql, kl = _lin(sd, a + ".to_q", h), _lin(sd, a + ".to_k", h)
@@ -134,8 +139,7 @@ def single_block(sd, p, x, temb, rope, H, D, text_len=None, row0=None, kv_hook=N
         q = torch.cat([parts_q[i] for i in sorted(parts_q)], dim=1)
         k = torch.cat([parts_k[i] for i in sorted(parts_k)], dim=1)
         v = _heads(_lin(sd, a + ".to_v", h), H, D)
-        o = oa.sdpa(q, k, v).reshape(x.shape[0], x.shape[1], d)
-        return x + gate[:, None] * _lin(sd, p + ".proj_out", torch.cat([o, mlp], dim=-1))
+        return oa.sdpa(q, k, v).reshape(h.shape[0], h.shape[1], d)
     if text_len is None:
         q = _qk(sd, a, _lin(sd, a + ".to_q", h), H, D, "norm_q", rope, 0)
         k = _qk(sd, a, _lin(sd, a + ".to_k", h), H, D, "norm_k", rope, 0)
@@ -150,8 +154,36 @@ def single_block(sd, p, x, temb, rope, H, D, text_len=None, row0=None, kv_hook=N
     if kv_hook is not None:
         ki, vi = kv_hook(k[:, text_len:], v[:, text_len:])
         k, v = torch.cat([k[:, :text_len], ki], dim=1), torch.cat([v[:, :text_len], vi], dim=1)
-    o = oa.sdpa(q, k, v).reshape(x.shape[0], x.shape[1], d)
+    return oa.sdpa(q, k, v).reshape(h.shape[0], h.shape[1], d)
+
+
+def single_block(sd, p, x, temb, rope, H, D, text_len=None, row0=None, kv_hook=None, text_first=True,
+                 rope_on_text=True):
+    """x = [text; image] rows. text_len / row0: the first text_len rows take rotary rows [0, text_len), the
+    rest rows [row0, ...) (a patch of the image); kv_hook(k_img, v_img) -> (k_all, v_all) is PipeFusion's
+    stale-KV cache of the image tokens (attention_processor.py:898-917 of the reference).
+    text_first=False: x = [image; text] (HunyuanVideo single blocks, :1464-1468); rope_on_text=False: only the
+    image / video rows are rotated, from table row `row0` (default 0)."""
+    d = x.shape[-1]
+    shift, scale, gate = _lin(sd, p + ".norm.linear", F.silu(temb)).chunk(3, dim=-1)
+    h = _mod(F.layer_norm(x, (d,), eps=1e-6), shift, scale)
+    mlp = F.gelu(_lin(sd, p + ".proj_mlp", h), approximate="tanh")
+    o = single_attention(sd, p + ".attn.module", h, rope, H, D, text_len, row0, kv_hook, text_first, rope_on_text)
     return x + gate[:, None] * _lin(sd, p + ".proj_out", torch.cat([o, mlp], dim=-1))
+
+
+def cogvideox_attention(sd, a, x, S_txt, rope, H, D, row0=0):
+    """Attention of a CogVideoX block over the modulated rows x = [text; video], before the output projection,
+    (B, S, H*D): LayerNorm QK norm, rotary rows for the video only -- what hetuDiTCogVideoXAttnProcessor2_0 returns
+    (attention_processor.py:1022-1160)."""
+    d = x.shape[-1]
+    ql, kl = _lin(sd, a + ".to_q", x), _lin(sd, a + ".to_k", x)
+    q = torch.cat([_qk(sd, a, ql[:, :S_txt], H, D, "norm_q", None, 0),
+                   _qk(sd, a, ql[:, S_txt:], H, D, "norm_q", rope, row0)], dim=1)
+    k = torch.cat([_qk(sd, a, kl[:, :S_txt], H, D, "norm_k", None, 0),
+                   _qk(sd, a, kl[:, S_txt:], H, D, "norm_k", rope, row0)], dim=1)
+    v = _heads(_lin(sd, a + ".to_v", x), H, D)
+    return oa.sdpa(q, k, v).reshape(x.shape[0], x.shape[1], d)
 
 
 def cogvideox_block(sd, p, hidden, context, temb, rope, H, D, row0=0):
@@ -164,13 +196,7 @@ def cogvideox_block(sd, p, hidden, context, temb, rope, H, D, row0=0):
     x = torch.cat([_mod(F.layer_norm(context, (d,), eps=1e-6), m1[3], m1[4]),
                    _mod(F.layer_norm(hidden, (d,), eps=1e-6), m1[0], m1[1])], dim=1)
     a = p + ".attn1.module"
-    ql, kl = _lin(sd, a + ".to_q", x), _lin(sd, a + ".to_k", x)
-    q = torch.cat([_qk(sd, a, ql[:, :S_txt], H, D, "norm_q", None, 0),
-                   _qk(sd, a, ql[:, S_txt:], H, D, "norm_q", rope, row0)], dim=1)
-    k = torch.cat([_qk(sd, a, kl[:, :S_txt], H, D, "norm_k", None, 0),
-                   _qk(sd, a, kl[:, S_txt:], H, D, "norm_k", rope, row0)], dim=1)
-    v = _heads(_lin(sd, a + ".to_v", x), H, D)
-    o = _lin(sd, a + ".to_out.0", oa.sdpa(q, k, v).reshape(x.shape[0], x.shape[1], d))
+    o = _lin(sd, a + ".to_out.0", cogvideox_attention(sd, a, x, S_txt, rope, H, D, row0))
     hidden = hidden + m1[2][:, None] * o[:, S_txt:]
     context = context + m1[5][:, None] * o[:, :S_txt]
     x = torch.cat([_mod(F.layer_norm(context, (d,), eps=1e-6), m2[3], m2[4]),

@@ -14,6 +14,9 @@ inputs and outputs are written out:
   rope.npz           apply_rotary_emb on seeded inputs
   usp_<case>.npz     hetuDiT*LongContextAttention / ring attention / KV cache on
                      CPU `gloo` ranks, fp32
+  attn_processors.npz  the attention processors' __call__ (SD3, Flux double / single, CogVideoX,
+                     HunyuanVideo double / single) on a stand-in Attention module, fp32
+                     (--only attn_processors)
   pipefusion_order.json  per pipeline stage, the order of receives, receive-queue
                      operations, forwards, scheduler steps and sends that the SD3
                      pipeline's _sync_pipeline / _init_async_pipeline / _async_pipeline
@@ -770,6 +773,139 @@ def gen_pos_embed_rows(ref):
     print("pos_embed_rows.json written:", len(cases), "cases")
 
 
+# ----------------------------------------------------------------------------- attention processors
+def _find_class_anywhere(tree, cls):
+    for node in ast.walk(tree):
+        if isinstance(node, ast.ClassDef) and node.name == cls:
+            return node
+    raise KeyError(cls)
+
+
+def gen_attn_processors(ref):
+    """Runs the __call__ of the reference's attention processors
+    (model_executor/diffusion_executor/layers/attention_processor.py: hetuDiTJointAttnProcessor2_0 :657,
+    hetuDiTFluxAttnProcessor2_0 :824, hetuDiTCogVideoXAttnProcessor2_0 :1022, hetuDiTHunyuanVideoAttnProcessor2_0
+    :1373) on CPU in fp32 -- their scaled_dot_product_attention branch, one GPU, no pipeline patches -- with a
+    stand-in for the diffusers Attention module that holds seeded projections and QK norms, and writes inputs,
+    weights and outputs. The stand-in restates only diffusers' RMSNorm (x * rsqrt(mean(x^2) + eps) * weight)."""
+    from typing import Optional, Tuple, Union
+    import torch.nn as nn
+    import torch.nn.functional as F
+    path = os.path.join(ref, "hetu_dit/model_executor/diffusion_executor/layers/attention_processor.py")
+    with open(path) as f:
+        tree = ast.parse(f.read())
+    rope_fn, _ = lift(path, "apply_rotary_emb", namespace={"torch": torch, "Union": Union, "Tuple": Tuple})
+
+    class RMSNorm(nn.Module):
+        def __init__(self, dim, eps):
+            super().__init__()
+            self.weight, self.eps = nn.Parameter(torch.ones(dim)), eps
+
+        def forward(self, x):
+            return x * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + self.eps) * self.weight
+
+    state = _NS(max_condition_sequence_length=0, split_text_embed_in_sp=False, num_pipeline_patch=1)
+    cache = _NS(update_and_get_kv_cache=lambda new_kv, layer, slice_dim, layer_type: new_kv)
+    ns = {"torch": torch, "F": F, "Optional": Optional, "Attention": object, "HAS_LONG_CTX_ATTN": False,
+          "HAS_FLASH_ATTN": False, "get_sequence_parallel_world_size": lambda: 1,
+          "get_tensor_model_parallel_world_size": lambda: 1, "get_pipeline_parallel_world_size": lambda: 1,
+          "get_runtime_state": lambda: state, "get_cache_manager": lambda: cache, "apply_rotary_emb": rope_fn}
+
+    def call_of(cls):
+        node = next(n for n in _find_class_anywhere(tree, cls).body
+                    if isinstance(n, ast.FunctionDef) and n.name == "__call__")
+        scope = dict(ns)
+        exec(compile(ast.Module(body=[node], type_ignores=[]), path, "exec"), scope)
+        return scope["__call__"]
+
+    H, D, B, S_img, S_txt = 2, 16, 2, 10, 6
+    d = H * D
+    gen = torch.Generator().manual_seed(77)
+
+    def attn_module(norm, joint):
+        a = _NS(heads=H, is_cross_attention=False, spatial_norm=None, group_norm=None, norm_cross=False)
+        names = ["to_q", "to_k", "to_v"] + (["add_q_proj", "add_k_proj", "add_v_proj"] if joint else [])
+        for n in names:
+            lin = nn.Linear(d, d)
+            lin.weight.data = torch.randn(d, d, generator=gen) / d ** 0.5
+            lin.bias.data = torch.randn(d, generator=gen) * 0.1
+            setattr(a, n, lin)
+        if not joint:
+            a.add_q_proj = a.add_k_proj = a.add_v_proj = None
+        for n in ["norm_q", "norm_k"] + (["norm_added_q", "norm_added_k"] if joint else []):
+            if norm == "rms":
+                m = RMSNorm(D, 1e-6)
+                m.weight.data = torch.rand(D, generator=gen) + 0.5
+            elif norm == "layer":
+                m = nn.LayerNorm(D, eps=1e-6)
+                m.weight.data = torch.rand(D, generator=gen) + 0.5
+                m.bias.data = torch.randn(D, generator=gen) * 0.1
+            else:
+                m = None
+            setattr(a, n, m)
+        if not joint:
+            a.norm_added_q = a.norm_added_k = None
+        return a
+
+    def rope(rows):
+        ang = torch.rand(rows, D // 2, generator=gen) * 6.28
+        return torch.cos(ang).repeat_interleave(2, dim=-1), torch.sin(ang).repeat_interleave(2, dim=-1)
+
+    data = {"spec": np.array(json.dumps({"heads": H, "head_dim": D, "batch": B, "s_img": S_img, "s_txt": S_txt}))}
+
+    def record(case, a, inputs, outputs, rope_tab=None):
+        for n in ("to_q", "to_k", "to_v", "add_q_proj", "add_k_proj", "add_v_proj"):
+            m = getattr(a, n, None)
+            if m is not None:
+                data[f"{case}/{n}.weight"], data[f"{case}/{n}.bias"] = m.weight.detach().numpy(), m.bias.detach().numpy()
+        for n in ("norm_q", "norm_k", "norm_added_q", "norm_added_k"):
+            m = getattr(a, n, None)
+            if m is not None:
+                data[f"{case}/{n}.weight"] = m.weight.detach().numpy()
+                if getattr(m, "bias", None) is not None:
+                    data[f"{case}/{n}.bias"] = m.bias.detach().numpy()
+        for k, v in inputs.items():
+            data[f"{case}/in.{k}"] = v.numpy()
+        for k, v in outputs.items():
+            data[f"{case}/out.{k}"] = v.detach().numpy()
+        if rope_tab is not None:
+            data[f"{case}/cos"], data[f"{case}/sin"] = rope_tab[0].numpy(), rope_tab[1].numpy()
+
+    with torch.no_grad():
+        hid = torch.randn(B, S_img, d, generator=gen)
+        txt = torch.randn(B, S_txt, d, generator=gen)
+        # SD3: [image; text], no QK norm, no rotary embedding
+        a = attn_module(None, True)
+        img_o, txt_o = call_of("hetuDiTJointAttnProcessor2_0")(_NS(), a, hid, txt)
+        record("joint_sd3", a, {"hidden": hid, "encoder": txt}, {"image": img_o, "text": txt_o})
+        # Flux double block: [text; image], RMSNorm, rotary rows for text and image
+        a = attn_module("rms", True)
+        tab = rope(S_txt + S_img)
+        img_o, txt_o = call_of("hetuDiTFluxAttnProcessor2_0")(_NS(), a, hid, txt, None, tab)
+        record("flux_double", a, {"hidden": hid, "encoder": txt}, {"image": img_o, "text": txt_o}, tab)
+        # Flux single block: joint rows [text; image] come in as hidden_states
+        a = attn_module("rms", False)
+        state.max_condition_sequence_length = S_txt
+        joint = torch.cat([txt, hid], dim=1)
+        out = call_of("hetuDiTFluxAttnProcessor2_0")(_NS(), a, joint, None, None, tab)
+        record("flux_single", a, {"hidden": joint}, {"joint": out}, tab)
+        # CogVideoX: [text; video], LayerNorm QK norm, rotary rows for the video only
+        a = attn_module("layer", False)
+        tab_v = rope(S_img)
+        out = call_of("hetuDiTCogVideoXAttnProcessor2_0")(_NS(), a, hid, txt, None, tab_v)
+        record("cogvideox", a, {"hidden": hid, "encoder": txt}, {"joint": out}, tab_v)
+        # HunyuanVideo double block: [video; text], RMSNorm, rotary rows for the video only
+        a = attn_module("rms", True)
+        out = call_of("hetuDiTHunyuanVideoAttnProcessor2_0")(_NS(), a, hid, txt, None, tab_v)
+        record("hunyuan_double", a, {"hidden": hid, "encoder": txt}, {"joint": out}, tab_v)
+        # HunyuanVideo single block: [video; text] concatenated by the processor
+        a = attn_module("rms", False)
+        out = call_of("hetuDiTHunyuanVideoAttnProcessor2_0")(_NS(), a, hid, txt, None, tab_v)
+        record("hunyuan_single", a, {"hidden": hid, "encoder": txt}, {"joint": out}, tab_v)
+    np.savez_compressed(os.path.join(HERE, "attn_processors.npz"), **data)
+    print("attn_processors.npz written:", len(data), "arrays")
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="root of a Hetu-DiT checkout")
@@ -783,6 +919,8 @@ if __name__ == "__main__":
         gen_rope(a.reference)
     if a.only in ("", "usp"):
         gen_usp(a.reference)
+    if a.only in ("", "attn_processors"):
+        gen_attn_processors(a.reference)
     if a.only in ("", "pos_embed_rows"):
         gen_pos_embed_rows(a.reference)
     if a.only in ("", "pipefusion_order"):

@@ -178,3 +178,54 @@ def test_pipefusion_oracle_stale_kv_order_matches_the_reference_run():
     for r in range(U):
         q = torch.cat([d["fresh_q"][:, r * tok:(r + 1) * tok], d["jq"]], 1)      # "rear": [local; joint]
         torch.testing.assert_close(oa.sdpa(q, keys, vals), d[f"out_patch1_rank{r}"], rtol=2e-5, atol=2e-5)
+
+
+# ----------------------------------------------------------------------------- attention processors
+def _processor_case(name):
+    golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    with np.load(os.path.join(golden, "attn_processors.npz")) as f:
+        spec = json.loads(str(f["spec"]))
+        arrays = {k[len(name) + 1:]: torch.from_numpy(f[k]) for k in f.files if k.startswith(name + "/")}
+    sd = {"a." + k: v for k, v in arrays.items() if not k.startswith(("in.", "out.")) and k not in ("cos", "sin")}
+    rope = (arrays["cos"], arrays["sin"]) if "cos" in arrays else None
+    return spec, sd, arrays, rope
+
+
+def _close32(got, want):
+    assert got.shape == want.shape
+    assert (got - want).abs().max().item() <= 2e-5 * max(1.0, want.abs().max().item())
+
+
+def test_oracle_attention_matches_the_reference_processors():
+    """oracle/shaped_dit.py's attention of every block kind against what the reference's own attention processors
+    return on the same weights and inputs (fixtures recorded by tests/golden/make_golden.py from the processors'
+    __call__, CPU fp32): order of text and image rows, which rows are rotated, RMSNorm or LayerNorm QK norm."""
+    from oracle import shaped_dit as osd
+    # SD3: [image; text], no norm, no rotary table
+    spec, sd, x, rope = _processor_case("joint_sd3")
+    H, D = spec["heads"], spec["head_dim"]
+    img, txt = osd.joint_attention(sd, "a", x["in.hidden"], x["in.encoder"], None, H, D, "rear")
+    _close32(img, x["out.image"])
+    _close32(txt, x["out.text"])
+    # Flux double: [text; image], rotary rows for both
+    spec, sd, x, rope = _processor_case("flux_double")
+    img, txt = osd.joint_attention(sd, "a", x["in.hidden"], x["in.encoder"], rope, H, D, "front", rope_on_text=True)
+    _close32(img, x["out.image"])
+    _close32(txt, x["out.text"])
+    # Flux single: the joint rows [text; image]; with and without the text / image split of the rotary rows
+    spec, sd, x, rope = _processor_case("flux_single")
+    _close32(osd.single_attention(sd, "a", x["in.hidden"], rope, H, D), x["out.joint"])
+    _close32(osd.single_attention(sd, "a", x["in.hidden"], rope, H, D, text_len=spec["s_txt"]), x["out.joint"])
+    # CogVideoX: [text; video], LayerNorm QK norm, rotary rows for the video only
+    spec, sd, x, rope = _processor_case("cogvideox")
+    joint = torch.cat([x["in.encoder"], x["in.hidden"]], dim=1)
+    _close32(osd.cogvideox_attention(sd, "a", joint, spec["s_txt"], rope, H, D), x["out.joint"])
+    # HunyuanVideo double: [video; text], rotary rows for the video only
+    spec, sd, x, rope = _processor_case("hunyuan_double")
+    img, txt = osd.joint_attention(sd, "a", x["in.hidden"], x["in.encoder"], rope, H, D, "rear", rope_on_text=False)
+    _close32(torch.cat([img, txt], dim=1), x["out.joint"])
+    # HunyuanVideo single: the processor concatenates [video; text] itself
+    spec, sd, x, rope = _processor_case("hunyuan_single")
+    joint = torch.cat([x["in.hidden"], x["in.encoder"]], dim=1)
+    got = osd.single_attention(sd, "a", joint, rope, H, D, text_len=spec["s_txt"], text_first=False, rope_on_text=False)
+    _close32(got, x["out.joint"])
