@@ -17,6 +17,8 @@ inputs and outputs are written out:
   attn_processors.npz  the attention processors' __call__ (SD3, Flux double / single, CogVideoX,
                      HunyuanVideo double / single) on a stand-in Attention module, fp32
                      (--only attn_processors)
+  stage_split.json   which double / single blocks a pipeline stage keeps (_split_transformer_blocks)
+                     (--only stage_split)
   pipefusion_order.json  per pipeline stage, the order of receives, receive-queue
                      operations, forwards, scheduler steps and sends that the SD3
                      pipeline's _sync_pipeline / _init_async_pipeline / _async_pipeline
@@ -906,6 +908,51 @@ def gen_attn_processors(ref):
     print("attn_processors.npz written:", len(data), "arrays")
 
 
+# ----------------------------------------------------------------------------- pipeline stage split
+def gen_stage_split(ref):
+    """Runs the reference's _split_transformer_blocks
+    (model_executor/diffusion_executor/models/transformers/base_transformer.py:65-146) on a stand-in transformer with
+    numbered double and single blocks and writes, per (block counts, stages, stage, explicit per-stage counts), which
+    blocks the stage keeps and its after_flags."""
+    from typing import List
+    import torch.nn as nn
+    path = os.path.join(ref, "hetu_dit/model_executor/diffusion_executor/models/transformers/base_transformer.py")
+
+    class Block(nn.Module):
+        def __init__(self, i):
+            super().__init__()
+            self.i = i
+
+    cases = []
+    for (n_double, n_single, stages, counts) in [
+            (24, 0, 1, None), (24, 0, 2, None), (24, 0, 4, None), (24, 0, 5, None), (24, 0, 4, [3, 9, 6, 6]),
+            (19, 38, 2, None), (19, 38, 4, None), (19, 38, 8, None), (19, 38, 3, None), (19, 38, 4, [19, 10, 14, 14]),
+            (19, 38, 4, [5, 14, 19, 19]), (2, 3, 2, None), (2, 3, 5, None), (20, 40, 8, None), (42, 0, 8, None)]:
+        for stage in range(stages):
+            state = _NS(parallel_config=_NS(pp_config=_NS(attn_layer_num_for_pp=counts)))
+            ns = {"nn": nn, "List": List, "get_runtime_state": lambda state=state: state,
+                  "get_pipeline_parallel_rank": lambda stage=stage: stage,
+                  "get_pipeline_parallel_world_size": lambda stages=stages: stages,
+                  "StageInfo": lambda: _NS(after_flags={})}
+            fn, _ = lift(path, "_split_transformer_blocks", cls="hetuDiTDiffusionTransformerBaseWrapper", namespace=ns)
+            t = nn.Module()
+            t.transformer_blocks = nn.ModuleList([Block(i) for i in range(n_double)])
+            names = ["transformer_blocks"]
+            if n_single:
+                t.single_transformer_blocks = nn.ModuleList([Block(i) for i in range(n_single)])
+                names.append("single_transformer_blocks")
+            self = _NS()
+            fn(self, t, names)
+            cases.append({"n_double": n_double, "n_single": n_single, "stages": stages, "stage": stage,
+                          "attn_layer_num_for_pp": counts,
+                          "double": [b.i for b in t.transformer_blocks],
+                          "single": [b.i for b in t.single_transformer_blocks] if n_single else [],
+                          "after_flags": dict(self.stage_info.after_flags)})
+    with open(os.path.join(HERE, "stage_split.json"), "w") as f:
+        json.dump(cases, f, separators=(",", ":"))
+    print("stage_split.json written:", len(cases), "cases")
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="root of a Hetu-DiT checkout")
@@ -919,6 +966,8 @@ if __name__ == "__main__":
         gen_rope(a.reference)
     if a.only in ("", "usp"):
         gen_usp(a.reference)
+    if a.only in ("", "stage_split"):
+        gen_stage_split(a.reference)
     if a.only in ("", "attn_processors"):
         gen_attn_processors(a.reference)
     if a.only in ("", "pos_embed_rows"):

@@ -623,3 +623,25 @@ def test_trace_admission_on_disjoint_gpus():
     np.testing.assert_allclose(simulate_fifo_gpus(arrivals, service, [2, 2, 2, 2], 4), [1.0, 1.0, 1.8, 1.8])
     # a whole-node request in the middle holds back the small ones behind it (no overtaking)
     np.testing.assert_allclose(simulate_fifo_gpus(arrivals, service, [1, 4, 1, 1], 4), [1.0, 1.9, 2.8, 2.7])
+
+
+def test_stage_block_split_matches_reference():
+    """Which double / single blocks a pipeline stage holds: stage_block_range + the Flux pipeline's slicing against
+    the reference's _split_transformer_blocks (models/transformers/base_transformer.py:65-146), recorded by
+    tests/golden/make_golden.py for SD3-, Flux-, CogVideoX- and HunyuanVideo-sized block lists."""
+    import json
+    from hetu_dit_b200.model_executor.pipelines.pipeline_sd3_shaped import stage_block_range
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "stage_split.json")) as f:
+        cases = json.load(f)
+    assert len(cases) >= 60
+    for c in cases:
+        nd, ns = c["n_double"], c["n_single"]
+        lo, hi = stage_block_range(nd + ns, c["stage"], c["stages"], c["attn_layer_num_for_pp"])
+        double = list(range(min(lo, nd), min(hi, nd)))
+        single = list(range(max(lo - nd, 0), max(hi - nd, 0)))
+        assert double == c["double"] and single == c["single"], c
+        # after_flags: the stage holds the last block of that list
+        want_flags = {"transformer_blocks": bool(double) and double[-1] == nd - 1}
+        if ns:
+            want_flags["single_transformer_blocks"] = bool(single) and single[-1] == ns - 1
+        assert want_flags == c["after_flags"], c
