@@ -280,15 +280,18 @@ namespace {
 
 // Classifier-free guidance + flow-matching Euler step of a latent patch in one pass, with an optional second
 // destination (the next pipeline stage's inbox). Rounding follows the eager sequence it replaces: the guidance
-// combine runs in the 16-bit type, one rounding per operation (difference, scaled difference, sum); the step runs
-// in fp32 on the rounded prediction and is rounded once.
+// combine runs in the 16-bit type, one rounding per operation (difference, scaled difference, sum); the step keeps
+// the operation order of the reference's scheduler wrapper (prediction * sigma rounded to the 16-bit type; then in
+// fp32 denoised = sample - product, derivative = (sample - denoised) / sigma, sample + derivative * dt, each
+// operation rounded on its own) and is rounded to the 16-bit type once.
 template <bool FP16>
 __global__ void __launch_bounds__(256) cfg_euler_step_kernel(const uint16_t* __restrict__ uncond,
                                                             const uint16_t* __restrict__ cond,
                                                             const uint16_t* __restrict__ sample, uint16_t* __restrict__ out,
                                                             uint16_t* __restrict__ out2, long long n_vec, float guidance,
                                                             const float* __restrict__ sigmas, int step) {
-  const float dt = sigmas[step + 1] - sigmas[step];
+  const float sigma = sigmas[step];
+  const float dt = __fsub_rn(sigmas[step + 1], sigma);
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
     const uint4 u4 = reinterpret_cast<const uint4*>(uncond)[i];
@@ -308,7 +311,11 @@ __global__ void __launch_bounds__(256) cfg_euler_step_kernel(const uint16_t* __r
         const float m = ew_to_f<FP16>(ew_from_f<FP16>(guidance * d));
         pred = ew_to_f<FP16>(ew_from_f<FP16>(pred + m));
       }
-      o[k] = ew_from_f<FP16>(__fadd_rn(ew_to_f<FP16>(sm[k]), __fmul_rn(dt, pred)));
+      const float x = ew_to_f<FP16>(sm[k]);
+      const float product = ew_to_f<FP16>(ew_from_f<FP16>(__fmul_rn(pred, sigma)));
+      const float denoised = __fsub_rn(x, product);
+      const float derivative = __fdiv_rn(__fsub_rn(x, denoised), sigma);
+      o[k] = ew_from_f<FP16>(__fadd_rn(x, __fmul_rn(derivative, dt)));
     }
     reinterpret_cast<uint4*>(out)[i] = o4;
     if (out2 != nullptr) reinterpret_cast<uint4*>(out2)[i] = o4;

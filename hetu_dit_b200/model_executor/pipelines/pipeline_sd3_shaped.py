@@ -196,11 +196,18 @@ class SD3ShapedPipeline:
         return out
 
     def _scheduler_step(self, noise_pred, last_latents, i):
-        """Flow-matching Euler step in fp32; the step index is the caller's, so it advances once per
-        step however many patches the step has (the reference gates its scheduler's step counter on the
-        last patch, scheduling_flow_match_euler_discrete.py:119-124)."""
-        dt = self.sigmas[i + 1] - self.sigmas[i]
-        return (last_latents.float() + dt * noise_pred.float()).to(last_latents.dtype)
+        """Flow-matching Euler step with the operation order of the reference's scheduler wrapper
+        (scheduling_flow_match_euler_discrete.py:86-112, bit-identical to it on its own inputs): the product
+        prediction * sigma is rounded to the prediction's 16-bit type, the rest runs in fp32 --
+        denoised = sample - product, derivative = (sample - denoised) / sigma, result = sample + derivative * dt --
+        and is rounded once. The step index is the caller's, so it advances once per step however many patches the
+        step has (the reference gates its scheduler's step counter on the last patch, :119-124)."""
+        sigma, sigma_next = self.sigmas[i].float(), self.sigmas[i + 1].float()
+        sample = last_latents.float()
+        product = (noise_pred.float() * sigma).to(noise_pred.dtype).float()
+        denoised = sample - product
+        derivative = (sample - denoised) / sigma
+        return (sample + derivative * (sigma_next - sigma)).to(last_latents.dtype)
 
     # ------------------------------------------------------------------ warm-up: whole image per step
     def _sync_pipeline(self, latents, prompt_embeds, pooled, steps: List[int], sync_only: bool = False):

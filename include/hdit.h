@@ -391,7 +391,9 @@ HDIT_API int hdit_gelu_tanh(int32_t dtype, const void* x, void* out, int64_t row
 /*
  * Classifier-free guidance and the flow-matching Euler step of one latent patch, fused:
  *   pred = uncond + guidance_scale * (cond - uncond)        (16-bit arithmetic, one rounding per operation)
- *   out  = sample + (sigmas[step_index + 1] - sigmas[step_index]) * pred    (fp32, rounded once)
+ *   out  = sample + ((sample - (sample - round16(pred * sigma))) / sigma) * (sigmas[step_index + 1] - sigma),
+ *          sigma = sigmas[step_index]: the operation order of the reference's scheduler wrapper, fp32 with one
+ *          rounding per operation after the 16-bit product, the result rounded to the 16-bit type once
  * cond == NULL skips the guidance (uncond is the prediction). `sigmas` is a device array, so the call does not
  * depend on host state and can be replayed from a CUDA graph with the step index baked in. out_peer (optional) gets
  * the same result: with the next pipeline stage's inbox slot as out_peer this is also the wrap-around send of the

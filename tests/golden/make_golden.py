@@ -17,6 +17,8 @@ inputs and outputs are written out:
   attn_processors.npz  the attention processors' __call__ (SD3, Flux double / single, CogVideoX,
                      HunyuanVideo double / single) on a stand-in Attention module, fp32
                      (--only attn_processors)
+  scheduler_step.npz the flow-matching Euler scheduler wrapper's step() per patch: new sample and when the
+                     step index advances (--only scheduler_step)
   stage_split.json   which double / single blocks a pipeline stage keeps (_split_transformer_blocks)
                      (--only stage_split)
   pipefusion_order.json  per pipeline stage, the order of receives, receive-queue
@@ -953,6 +955,55 @@ def gen_stage_split(ref):
     print("stage_split.json written:", len(cases), "cases")
 
 
+# ----------------------------------------------------------------------------- scheduler step
+def gen_scheduler_step(ref):
+    """Runs the step() of the reference's flow-matching Euler scheduler wrapper
+    (model_executor/diffusion_executor/schedulers/scheduling_flow_match_euler_discrete.py:22-129) over the patches
+    of a few steps: the new sample per call and when the step index advances (after the last patch only, in patch
+    mode). Inputs are 16-bit as the pipelines pass them; the wrapper computes in fp32 and rounds once."""
+    from typing import Optional, Tuple, Union
+    path = os.path.join(ref, "hetu_dit/model_executor/diffusion_executor/schedulers/"
+                             "scheduling_flow_match_euler_discrete.py")
+    with open(path) as f:
+        tree = ast.parse(f.read())
+    node = next(n for n in _find_class_anywhere(tree, "hetuDiTFlowMatchEulerDiscreteSchedulerWrapper").body
+                if isinstance(n, ast.FunctionDef) and n.name == "step")
+    node.decorator_list = []
+    state = _NS(patch_mode=True, pipeline_patch_idx=0, num_pipeline_patch=4)
+    ns = {"torch": torch, "Optional": Optional, "Tuple": Tuple, "Union": Union,
+          "FlowMatchEulerDiscreteSchedulerOutput": lambda prev_sample: prev_sample,
+          "get_runtime_state": lambda: state,
+          "randn_tensor": lambda shape, dtype, device, generator: torch.zeros(shape, dtype=dtype, device=device)}
+    exec(compile(ast.Module(body=[node], type_ignores=[]), path, "exec"), ns)
+    step = ns["step"]
+    gen = torch.Generator().manual_seed(5)
+    n_steps = 6
+    s = torch.linspace(1.0, 1.0 / n_steps, n_steps, dtype=torch.float64)
+    sigmas = torch.cat([3.0 * s / (1 + 2.0 * s), torch.zeros(1, dtype=torch.float64)]).float()
+    data = {"sigmas": sigmas.numpy()}
+    calls = []
+    for dtype, tag in ((torch.bfloat16, "bf16"), (torch.float16, "fp16")):
+        sched = _NS(sigmas=sigmas, step_index=0, _step_index=0)
+        for mode, patches in ((False, 1), (True, 4)):
+            state.patch_mode, state.num_pipeline_patch = mode, patches
+            for it in range(2):
+                for p in range(patches):
+                    state.pipeline_patch_idx = p
+                    sched.step_index = sched._step_index
+                    mo = torch.randn(2, 24, 16, generator=gen).to(dtype)
+                    x = torch.randn(2, 24, 16, generator=gen).to(dtype)
+                    before = sched._step_index
+                    out = step(sched, mo, 0.5, x, return_dict=False)[0]
+                    k = f"{tag}/{len(calls)}"
+                    data[k + "/model_output"], data[k + "/sample"] = mo.float().numpy(), x.float().numpy()
+                    data[k + "/prev_sample"] = out.float().numpy()
+                    calls.append({"key": k, "dtype": tag, "step_index": before, "patch_mode": mode, "patch": p,
+                                  "patches": patches, "advanced": sched._step_index - before})
+    data["calls"] = np.array(json.dumps(calls))
+    np.savez_compressed(os.path.join(HERE, "scheduler_step.npz"), **data)
+    print("scheduler_step.npz written:", len(calls), "calls")
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="root of a Hetu-DiT checkout")
@@ -966,6 +1017,8 @@ if __name__ == "__main__":
         gen_rope(a.reference)
     if a.only in ("", "usp"):
         gen_usp(a.reference)
+    if a.only in ("", "scheduler_step"):
+        gen_scheduler_step(a.reference)
     if a.only in ("", "stage_split"):
         gen_stage_split(a.reference)
     if a.only in ("", "attn_processors"):

@@ -207,7 +207,8 @@ def test_gelu_tanh_matches_torch():
 @pytest.mark.parametrize("cfg", [True, False])
 def test_cfg_euler_step_matches_the_eager_chain_bit_for_bit(dtype, cfg):
     """Guidance combine + flow-matching Euler step in one kernel against the eager sequence it replaces (16-bit
-    guidance arithmetic with one rounding per operation, fp32 step rounded once), and the second destination."""
+    guidance arithmetic with one rounding per operation, the step in the reference scheduler's operation order), and
+    the second destination."""
     from hetu_dit_b200 import kernels
     gen = torch.Generator().manual_seed(17)
     n = (1, 384, 64)
@@ -220,8 +221,11 @@ def test_cfg_euler_step_matches_the_eager_chain_bit_for_bit(dtype, cfg):
         guided = uncond + scale * (text - uncond)
     else:
         guided = pred
-    dt = sigmas[step + 1] - sigmas[step]
-    want = (sample.float() + dt * guided.float()).to(dtype)
+    # the step in the operation order of the reference's scheduler wrapper (pinned against its recorded outputs in
+    # tests/test_host_logic.py::test_scheduler_step_matches_reference_wrapper)
+    sigma, x = sigmas[step], sample.float()
+    product = (guided.float() * sigma).to(dtype).float()
+    want = (x + ((x - (x - product)) / sigma) * (sigmas[step + 1] - sigma)).to(dtype)
     peer = torch.zeros_like(sample)
     got = kernels.cfg_euler_step(pred, sample, sigmas, step, scale, cfg=cfg, out_peer_ptr=peer.data_ptr())
     torch.cuda.synchronize()

@@ -645,3 +645,29 @@ def test_stage_block_split_matches_reference():
         if ns:
             want_flags["single_transformer_blocks"] = bool(single) and single[-1] == ns - 1
         assert want_flags == c["after_flags"], c
+
+
+def test_scheduler_step_matches_reference_wrapper():
+    """The flow-matching Euler step of the pipelines against the reference's scheduler wrapper
+    (schedulers/scheduling_flow_match_euler_discrete.py:22-129, recorded by tests/golden/make_golden.py): the same
+    16-bit result bit for bit (the wrapper rounds prediction * sigma to the prediction's type and forms
+    (sample - (sample - product)) / sigma in fp32; so do the pipelines and the fused kernel), and the step index
+    advances once per step -- after the last patch in patch mode -- which the pipelines get by indexing with the step
+    counter of their own loop."""
+    import json
+    from hetu_dit_b200.model_executor.pipelines import pipeline_sd3_shaped as mod
+    with np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "scheduler_step.npz")) as f:
+        calls = json.loads(str(f["calls"]))
+        data = {k: f[k] for k in f.files if k != "calls"}
+    pipe = object.__new__(mod.SD3ShapedPipeline)
+    pipe.sigmas = torch.from_numpy(data["sigmas"])
+    assert len(calls) >= 20
+    for c in calls:
+        dtype = torch.bfloat16 if c["dtype"] == "bf16" else torch.float16
+        mo = torch.from_numpy(data[c["key"] + "/model_output"]).to(dtype)
+        x = torch.from_numpy(data[c["key"] + "/sample"]).to(dtype)
+        want = torch.from_numpy(data[c["key"] + "/prev_sample"]).to(dtype)
+        got = pipe._scheduler_step(mo, x, c["step_index"])
+        assert got.dtype == dtype and torch.equal(got, want), c
+        # one advance per step: every call outside patch mode, the last patch only inside it
+        assert c["advanced"] == (1 if (not c["patch_mode"] or c["patch"] == c["patches"] - 1) else 0)
