@@ -73,6 +73,35 @@ def engine_config_for(pp: int, ulysses: int, patches: int = 4, warmup_steps: int
     return cfg
 
 
+def estimate_ddl(t_dict: Dict[int, float]) -> int:
+    """The reference's deadline for a request shape (hetu_dit/utils.py:267-288): with t_dict = {GPUs k: latency on
+    k GPUs}, k* the largest k whose speed-up over one GPU is at least 0.8 k, the deadline is
+    int(round(4 t_k*) * 1.1) + 2 seconds."""
+    t1 = t_dict[1]
+    best_k = 1
+    for k, tk in t_dict.items():
+        if (t1 / tk) / k >= 0.8 and k > best_k:
+            best_k = k
+    return int(round(t_dict[best_k] * 4) * 1.1) + 2
+
+
+def reference_deadlines(resolutions: Sequence[int], service: Sequence[float], gpus_needed: Sequence[int],
+                        single_gpu: Dict[int, float]) -> np.ndarray:
+    """Per request, estimate_ddl() over the latencies this run knows for its resolution: one GPU, and the GPUs of
+    the plan the table gave it (mean service time of that resolution)."""
+    by_res: Dict[int, Dict[int, list]] = {}
+    for r, s, k in zip(resolutions, service, gpus_needed):
+        by_res.setdefault(r, {}).setdefault(k, []).append(s)
+    ddl = {}
+    for r, per_k in by_res.items():
+        t = {1: single_gpu[r]}
+        for k, v in per_k.items():
+            if k != 1:
+                t[k] = float(np.mean(v))
+        ddl[r] = estimate_ddl(t)
+    return np.asarray([float(ddl[r]) for r in resolutions])
+
+
 def summarize(latencies: np.ndarray, deadlines: np.ndarray) -> Dict[str, float]:
     return {"mean_s": float(latencies.mean()), "p50_s": float(np.percentile(latencies, 50)),
             "p95_s": float(np.percentile(latencies, 95)), "max_s": float(latencies.max()),
@@ -197,8 +226,12 @@ class TraceDriver:
         deadlines = np.asarray([slo_factor * single_gpu[r.resolution] for r in trace])
         # requests are executed one at a time here; on the virtual clock those that fit side by side on disjoint
         # GPUs overlap. The one-request-at-a-time figures are kept beside them.
-        res = summarize(simulate_fifo_gpus(arrivals, service, need, self.world), deadlines)
+        lat = simulate_fifo_gpus(arrivals, service, need, self.world)
+        res = summarize(lat, deadlines)
         res["one_request_at_a_time"] = summarize(simulate_fifo(arrivals, service), deadlines)
+        # the same latencies against the reference's own deadline rule
+        ref_ddl = reference_deadlines([r.resolution for r in trace], service, need, single_gpu)
+        res["slo_attainment_reference_deadline"] = float((lat <= ref_ddl).mean())
         res.update(requests=len(trace), service_mean_s=float(np.mean(service)), switch_share=float(
             np.sum(switch_part) / max(np.sum(service), 1e-9)), single_gpu_latency_s=single_gpu, **self.stats)
         per_res = {}

@@ -144,6 +144,10 @@ def gen_bookkeeping(ref):
                              "groups": {tok: g.get_ranks(tok) for tok in ("tp", "sp", "pp", "cfg", "dp", "tp-sp")}})
     out["rank_generator"] = rg_cases
     mo = utils_ns["generate_masked_orthogonal_rank_groups"]
+    ddl_fn, _ = lift(os.path.join(ref, "hetu_dit/utils.py"), "estimate_ddl", namespace={})
+    out["estimate_ddl"] = [{"t": {str(k): v for k, v in t.items()}, "ddl": ddl_fn(t)} for t in (
+        {1: 0.144}, {1: 0.245, 4: 0.27}, {1: 0.45, 2: 0.37}, {1: 1.28, 4: 0.59}, {1: 1.28, 2: 0.75, 4: 0.59, 8: 0.5},
+        {1: 10.0, 2: 5.5, 4: 3.0, 8: 2.2}, {1: 10.0, 2: 7.0}, {1: 100.0, 2: 51.0, 4: 26.0, 8: 20.0}, {1: 0.6, 8: 0.09})]
     out["masked_orthogonal"] = [
         {"world": 24, "sizes": [2, 3, 4], "mask": m, "groups": mo(24, [2, 3, 4], m)}
         for m in ([False, True, False], [True, False, True], [True, True, True], [False, False, False])

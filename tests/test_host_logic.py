@@ -671,3 +671,18 @@ def test_scheduler_step_matches_reference_wrapper():
         assert got.dtype == dtype and torch.equal(got, want), c
         # one advance per step: every call outside patch mode, the last patch only inside it
         assert c["advanced"] == (1 if (not c["patch_mode"] or c["patch"] == c["patches"] - 1) else 0)
+
+
+def test_trace_deadline_rule_matches_reference():
+    """estimate_ddl of the serving-trace driver against the reference's (hetu_dit/utils.py:267-288, recorded in
+    bookkeeping.json), and the per-request deadlines the driver derives from it."""
+    import json
+    from hetu_dit_b200.serving.trace_driver import estimate_ddl, reference_deadlines
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "bookkeeping.json")) as f:
+        cases = json.load(f)["estimate_ddl"]
+    assert len(cases) >= 9
+    for c in cases:
+        assert estimate_ddl({int(k): v for k, v in c["t"].items()}) == c["ddl"], c
+    single = {512: 0.144, 1536: 1.28}
+    ddl = reference_deadlines([512, 1536, 512, 1536], [0.2, 0.6, 0.3, 0.58], [1, 4, 1, 4], single)
+    assert ddl.tolist() == [float(estimate_ddl({1: 0.144})), float(estimate_ddl({1: 1.28, 4: 0.59}))] * 2
