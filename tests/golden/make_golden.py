@@ -148,6 +148,19 @@ def gen_bookkeeping(ref):
     out["estimate_ddl"] = [{"t": {str(k): v for k, v in t.items()}, "ddl": ddl_fn(t)} for t in (
         {1: 0.144}, {1: 0.245, 4: 0.27}, {1: 0.45, 2: 0.37}, {1: 1.28, 4: 0.59}, {1: 1.28, 2: 0.75, 4: 0.59, 8: 0.5},
         {1: 10.0, 2: 5.5, 4: 3.0, 8: 2.2}, {1: 10.0, 2: 7.0}, {1: 100.0, 2: 51.0, 4: 26.0, 8: 20.0}, {1: 0.6, 8: 0.09})]
+    # --- worker plan API: parameter lists of the methods the executor calls by name -----------------------------
+    with open(os.path.join(ref, "hetu_dit/worker/worker.py")) as f:
+        wtree = ast.parse(f.read())
+    sigs = {}
+    for node in ast.walk(wtree):
+        if isinstance(node, ast.ClassDef) and node.name == "Worker":
+            for fn in node.body:
+                if isinstance(fn, (ast.FunctionDef, ast.AsyncFunctionDef)) and fn.name in (
+                        "switch_parallel_env", "hotspa_model", "execute_diffusion_stage",
+                        "execute_encode_diffusion_stage", "get_worker_state"):
+                    sigs[fn.name] = {"params": [a.arg for a in fn.args.args if a.arg != "self"],
+                                     "coroutine": isinstance(fn, ast.AsyncFunctionDef)}
+    out["worker_signatures"] = sigs
     out["masked_orthogonal"] = [
         {"world": 24, "sizes": [2, 3, 4], "mask": m, "groups": mo(24, [2, 3, 4], m)}
         for m in ([False, True, False], [True, False, True], [True, True, True], [False, False, False])

@@ -435,12 +435,16 @@ def test_worker_plan_api_signatures_match_the_reference():
     def params(fn):
         return [p for p in inspect.signature(fn).parameters if p != "self"]
 
-    assert params(Worker.switch_parallel_env) == ["world_size", "ranks", "engine_config"]
-    assert params(Worker.hotspa_model) == ["engine_config"] and inspect.iscoroutinefunction(Worker.hotspa_model)
-    assert params(Worker.execute_diffusion_stage) == ["encode_stage_results", "engine_config", "input_config",
-                                                      "model_class", "task_id"]
-    assert params(Worker.execute_encode_diffusion_stage) == ["engine_config", "input_config", "model_class", "task_id"]
-    assert params(Worker.get_worker_state) == []
+    # the parameter lists as they stand in the reference's source (read out of worker/worker.py by
+    # tests/golden/make_golden.py)
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "bookkeeping.json")) as f:
+        want = json.load(f)["worker_signatures"]
+    assert sorted(want) == ["execute_diffusion_stage", "execute_encode_diffusion_stage", "get_worker_state",
+                            "hotspa_model", "switch_parallel_env"]
+    for name, sig in want.items():
+        fn = getattr(Worker, name)
+        assert params(fn) == sig["params"], name
+        assert inspect.iscoroutinefunction(fn) == sig["coroutine"], name
     for name in ("init_static_env", "init_instance_model", "rpc_find_sources"):
         assert callable(getattr(Worker, name))
 
