@@ -161,6 +161,41 @@ def gen_bookkeeping(ref):
                     sigs[fn.name] = {"params": [a.arg for a in fn.args.args if a.arg != "self"],
                                      "coroutine": isinstance(fn, ast.AsyncFunctionDef)}
     out["worker_signatures"] = sigs
+    # --- operator / coordinator / cache surface: parameter names and literal defaults, as written in the source --
+    def surface(rel, wanted):
+        with open(os.path.join(ref, rel)) as f:
+            t = ast.parse(f.read())
+        got = {}
+        for node in ast.walk(t):
+            if isinstance(node, ast.ClassDef) and node.name in wanted:
+                for fn in node.body:
+                    if isinstance(fn, (ast.FunctionDef, ast.AsyncFunctionDef)) and fn.name in wanted[node.name]:
+                        args = [a.arg for a in fn.args.args if a.arg != "self"]
+                        defaults = {}
+                        for a, d in zip(args[len(args) - len(fn.args.defaults):], fn.args.defaults):
+                            try:
+                                defaults[a] = ast.literal_eval(d)
+                            except ValueError:
+                                defaults[a] = "<expression>"
+                        kwonly = [a.arg for a in fn.args.kwonlyargs]
+                        for a, d in zip(kwonly, fn.args.kw_defaults):
+                            if d is not None:
+                                try:
+                                    defaults[a] = ast.literal_eval(d)
+                                except ValueError:
+                                    defaults[a] = "<expression>"
+                        got[f"{node.name}.{fn.name}"] = {"params": args + kwonly, "defaults": defaults}
+        return got
+    api = {}
+    api.update(surface("hetu_dit/core/parallel/hybrid/attn_layer.py", {
+        "hetuDiTLongContextAttention": ["__init__", "forward"], "hetuDiTFluxLongContextAttention": ["__init__", "forward"],
+        "hetuDiTJointLongContextAttention": ["__init__", "forward"]}))
+    api.update(surface("hetu_dit/core/parallel/ulysses/attn_layer.py", {"hetuDiTUlyssesAttention": ["__init__", "forward"]}))
+    api.update(surface("hetu_dit/core/distributed/group_coordinator.py", {"PipelineGroupCoordinator": [
+        "pipeline_send", "pipeline_isend", "pipeline_recv", "add_pipeline_recv_task", "recv_next",
+        "get_pipeline_recv_data", "reset_buffer"]}))
+    api.update(surface("hetu_dit/core/resource_manager/cache_manager.py", {"CacheManager": ["update_and_get_kv_cache"]}))
+    out["api_surface"] = api
     out["masked_orthogonal"] = [
         {"world": 24, "sizes": [2, 3, 4], "mask": m, "groups": mo(24, [2, 3, 4], m)}
         for m in ([False, True, False], [True, False, True], [True, True, True], [False, False, False])

@@ -690,3 +690,33 @@ def test_trace_deadline_rule_matches_reference():
     single = {512: 0.144, 1536: 1.28}
     ddl = reference_deadlines([512, 1536, 512, 1536], [0.2, 0.6, 0.3, 0.58], [1, 4, 1, 4], single)
     assert ddl.tolist() == [float(estimate_ddl({1: 0.144})), float(estimate_ddl({1: 1.28, 4: 0.59}))] * 2
+
+
+def test_operator_coordinator_and_cache_surface_matches_reference():
+    """Parameter names, their order and their literal defaults of the USP operators, the pipeline group
+    coordinator and the stale-KV cache manager, as written in the reference's source (read out by
+    tests/golden/make_golden.py): a caller written against the reference binds the same arguments here. Parameters
+    this repository adds come after the reference's and have defaults."""
+    import inspect
+    import json
+    from hetu_dit_b200.core import parallel as P
+    from hetu_dit_b200.core.distributed.group_coordinator import PipelineGroupCoordinator
+    from hetu_dit_b200.core.resource_manager.cache_manager import CacheManager
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "bookkeeping.json")) as f:
+        want = json.load(f)["api_surface"]
+    assert len(want) == 14
+    owners = {"PipelineGroupCoordinator": PipelineGroupCoordinator, "CacheManager": CacheManager}
+    for key, sig in want.items():
+        cls_name, meth = key.split(".")
+        cls = owners.get(cls_name) or getattr(P, cls_name)
+        params = [p for p in inspect.signature(getattr(cls, meth)).parameters.values() if p.name != "self"]
+        positional = [p for p in params if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD, p.KEYWORD_ONLY)]
+        names = [p.name for p in positional]
+        assert names[:len(sig["params"])] == sig["params"], (key, names)
+        for p in positional[len(sig["params"]):]:
+            assert p.default is not p.empty, (key, p.name)          # additions never become required
+        by_name = {p.name: p for p in positional}
+        for name, default in sig["defaults"].items():
+            got = by_name[name].default
+            got = list(got) if isinstance(got, tuple) else got
+            assert got == default, (key, name, got, default)
