@@ -21,6 +21,9 @@ inputs and outputs are written out:
                      step index advances (--only scheduler_step)
   stage_split.json   which double / single blocks a pipeline stage keeps (_split_transformer_blocks)
                      (--only stage_split)
+  stage_forward.npz  forward() of the SD3 and Flux transformer wrappers for every stage of 1- to 4-stage
+                     pipelines on stand-in embedders / blocks / output layers, whole image and per patch
+                     (--only stage_forward)
   pipefusion_order.json  per pipeline stage, the order of receives, receive-queue
                      operations, forwards, scheduler steps and sends that the SD3
                      pipeline's _sync_pipeline / _init_async_pipeline / _async_pipeline
@@ -1056,6 +1059,139 @@ def gen_scheduler_step(ref):
     print("scheduler_step.npz written:", len(calls), "calls")
 
 
+# ----------------------------------------------------------------------------- stage forward of the transformer wrappers
+STAND_IN_HIDDEN = 8
+
+
+def stand_in_double(i, hidden, text, temb):
+    """Arithmetic of stand-in joint block i (repeated in tests/test_host_logic.py): both streams mix, so that a
+    wrong text source, block order or stage boundary changes the result."""
+    h = hidden * 1.5 + text.mean(1, keepdim=True) + temb[:, None] + (i + 1)
+    c = text * 0.5 + hidden.mean(1, keepdim=True) * 0.25 - (i + 1)
+    return h, c
+
+
+def stand_in_single(j, x, temb):
+    """Stand-in single block j on the joined rows: row-dependent, so that the join order matters."""
+    rows = torch.arange(x.shape[1], dtype=x.dtype)[None, :, None]
+    return x * 1.25 + rows * 0.01 * (j + 1) + temb[:, None]
+
+
+def stand_in_out_norm(hidden, temb):
+    x = torch.nn.functional.silu(temb)[:, None]
+    return torch.nn.functional.layer_norm(hidden, (hidden.shape[-1],), eps=1e-6) * (1 + 0.1 * x) + 0.2 * x
+
+
+def gen_stage_forward(ref):
+    """Runs forward() of the reference's SD3 and Flux transformer wrappers
+    (model_executor/diffusion_executor/models/transformers/transformer_sd3.py:43-198, transformer_flux.py:45-217) for
+    every stage of 1- to 4-stage pipelines, on stand-in embedders / blocks / output layers with the arithmetic above,
+    the block lists cut by the reference's own _split_transformer_blocks. Whole-image calls and patch-mode calls
+    (patches 0, 1, 2 in order: the SD3 wrapper keeps each block's text input of patch 0 and re-uses it for the later
+    patches). Written per call: the stage's inputs and outputs."""
+    from typing import Any, Dict, List, Optional, Union
+    import torch.nn as nn
+    base = os.path.join(ref, "hetu_dit/model_executor/diffusion_executor/models/transformers")
+    d = STAND_IN_HIDDEN
+
+    class Double(nn.Module):
+        def __init__(self, i):
+            super().__init__()
+            self.i = i
+
+        def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb=None):
+            h, c = stand_in_double(self.i, hidden_states, encoder_hidden_states, temb)
+            return c, h
+
+    class Single(nn.Module):
+        def __init__(self, j):
+            super().__init__()
+            self.j = j
+
+        def forward(self, hidden_states, temb, image_rotary_emb=None):
+            return stand_in_single(self.j, hidden_states, temb)
+
+    def temb_of(*a):                       # (timestep, pooled) or (timestep, guidance, pooled)
+        pooled = a[-1]
+        return 0.125 + 0.0625 * (len(a) == 3) + pooled.sum(-1, keepdim=True).expand(-1, d)
+
+    gen = torch.Generator().manual_seed(11)
+    data, calls = {}, []
+    for model, n_double, n_single, cls, fname in (("sd3", 5, 0, "hetuDiTSD3Transformer2DWrapper", "transformer_sd3.py"),
+                                                   ("flux", 3, 4, "hetuDiTFluxTransformer2DWrapper",
+                                                    "transformer_flux.py")):
+        for stages in (1, 2, 3, 4):
+            state = _NS(parallel_config=_NS(pp_config=_NS(attn_layer_num_for_pp=None)), patch_mode=False,
+                        pipeline_patch_idx=0)
+            wrappers = []
+            for stage in range(stages):
+                ns = {"nn": nn, "List": List, "get_runtime_state": lambda: state,
+                      "get_pipeline_parallel_rank": lambda stage=stage: stage,
+                      "get_pipeline_parallel_world_size": lambda stages=stages: stages,
+                      "StageInfo": lambda: _NS(after_flags={})}
+                split, _ = lift(os.path.join(base, "base_transformer.py"), "_split_transformer_blocks",
+                                cls="hetuDiTDiffusionTransformerBaseWrapper", namespace=ns)
+                t = nn.Module()
+                t.transformer_blocks = nn.ModuleList([Double(i) for i in range(n_double)])
+                names = ["transformer_blocks"]
+                if n_single:
+                    t.single_transformer_blocks = nn.ModuleList([Single(j) for j in range(n_single)])
+                    names.append("single_transformer_blocks")
+                w = _NS(training=False, gradient_checkpointing=False, config=_NS(patch_size=1), out_channels=d)
+                split(w, t, names)
+                w.transformer_blocks = t.transformer_blocks
+                w.single_transformer_blocks = t.single_transformer_blocks if n_single else []
+                w.encoder_hidden_states_cache = [None] * len(w.transformer_blocks)
+                w.pos_embed = (lambda h: h * 2.0 + 1.0) if model == "sd3" else (lambda ids: None)
+                w.x_embedder = lambda h: h * 2.0 + 1.0
+                w.context_embedder = lambda c: c * 3.0 - 1.0
+                w.time_text_embed = temb_of
+                w.norm_out = stand_in_out_norm
+                w.proj_out = lambda h: h * 7.0
+                w._get_patch_height_width = lambda: (1, 6)
+                fns = {"torch": torch, "Optional": Optional, "Dict": Dict, "Any": Any, "Union": Union,
+                       "Transformer2DModelOutput": lambda sample: sample, "USE_PEFT_BACKEND": False,
+                       "logger": logging.getLogger("ref"), "get_runtime_state": lambda: state,
+                       "is_pipeline_first_stage": lambda stage=stage: stage == 0,
+                       "is_pipeline_last_stage": lambda stage=stage, stages=stages: stage == stages - 1,
+                       "is_torch_version": lambda *a: True}
+                fwd = _lift_method_undecorated(os.path.join(base, fname), "forward", cls, fns)
+                wrappers.append((w, fwd))
+            pooled = torch.randn(2, 4, generator=gen, dtype=torch.float64) * 0.1
+            text0 = torch.randn(2, 3, d, generator=gen, dtype=torch.float64)
+            for mode, patches in (("whole", [None]), ("patch", [0, 1, 2])):
+                for patch in patches:
+                    state.patch_mode = mode == "patch"
+                    state.pipeline_patch_idx = patch or 0
+                    h = torch.randn(2, 6, d, generator=gen, dtype=torch.float64)
+                    c = text0 if not patch else text0 + 100.0       # later patches: the blocks must not read this
+                    for stage, (w, fwd) in enumerate(wrappers):
+                        kw = dict(hidden_states=h, encoder_hidden_states=c, pooled_projections=pooled,
+                                  timestep=torch.full((2,), 0.5, dtype=torch.float64), return_dict=False)
+                        if model == "flux":
+                            kw.update(img_ids=torch.zeros(6, 3), txt_ids=torch.zeros(3, 3),
+                                      guidance=torch.full((2,), 3.5, dtype=torch.float64))
+                        record = {}
+                        if stage == stages - 1:
+                            w.proj_out = lambda x, record=record: record.setdefault("tokens", x * 7.0)
+                        out_h, out_c = fwd(w, **kw)[0]
+                        if stage == stages - 1:
+                            out_h = record["tokens"]            # the token form, before the SD3 wrapper's unpatchify
+                        k = f"{model}/pp{stages}/{mode}{'' if patch is None else patch}/s{stage}"
+                        data[k + "/in_h"], data[k + "/in_c"] = h.numpy(), c.numpy()
+                        data[k + "/out_h"] = out_h.numpy()
+                        if out_c is not None:
+                            data[k + "/out_c"] = out_c.numpy()
+                        calls.append({"key": k, "model": model, "stages": stages, "stage": stage, "mode": mode,
+                                      "patch": patch, "n_double": n_double, "n_single": n_single,
+                                      "text_out": out_c is not None})
+                        h, c = out_h, (out_c if out_c is not None else c)
+            data[f"{model}/pp{stages}/pooled"] = pooled.numpy()
+    data["calls"] = np.array(json.dumps(calls))
+    np.savez_compressed(os.path.join(HERE, "stage_forward.npz"), **data)
+    print("stage_forward.npz written:", len(calls), "calls")
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="root of a Hetu-DiT checkout")
@@ -1071,6 +1207,8 @@ if __name__ == "__main__":
         gen_usp(a.reference)
     if a.only in ("", "scheduler_step"):
         gen_scheduler_step(a.reference)
+    if a.only in ("", "stage_forward"):
+        gen_stage_forward(a.reference)
     if a.only in ("", "stage_split"):
         gen_stage_split(a.reference)
     if a.only in ("", "attn_processors"):

@@ -720,3 +720,84 @@ def test_operator_coordinator_and_cache_surface_matches_reference():
             got = by_name[name].default
             got = list(got) if isinstance(got, tuple) else got
             assert got == default, (key, name, got, default)
+
+
+def _stage_forward_cases():
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "stage_forward.npz"))
+    import json
+    calls = json.loads(str(z["calls"]))
+    groups = {}
+    for c in calls:
+        groups.setdefault((c["model"], c["stages"]), []).append(c)
+    return z, groups
+
+
+@pytest.mark.parametrize("model,stages", [(m, s) for m in ("sd3", "flux") for s in (1, 2, 3, 4)])
+def test_stage_forward_matches_reference_transformer_wrappers(model, stages, monkeypatch):
+    """The stage forward of the two pipelines (_transformer) against forward() of the reference's SD3 and Flux
+    transformer wrappers (transformer_sd3.py:43-198, transformer_flux.py:45-217), which tests/golden/make_golden.py
+    ran on stand-in embedders, blocks and output layers: which stage embeds, which blocks a stage runs and in what
+    order, text rows joined in front of the image rows for the single blocks and split off again, the SD3 wrapper's
+    re-use of every block's text input of patch 0 for the later patches, output norm and projection on the last
+    stage only, and what a stage hands on. The stand-in arithmetic below repeats the generator's."""
+    import types
+    import torch.nn.functional as F
+    from hetu_dit_b200.model_executor.pipelines import pipeline_flux_shaped as fmod
+    from hetu_dit_b200.model_executor.pipelines import pipeline_sd3_shaped as smod
+    z, groups = _stage_forward_cases()
+    calls = groups[(model, stages)]
+    d = 8
+    n_double, n_single = calls[0]["n_double"], calls[0]["n_single"]
+
+    def double(i):
+        def f(hidden, text, temb, rope, tok0=0):
+            h = hidden * 1.5 + text.mean(1, keepdim=True) + temb[:, None] + (i + 1)
+            c = text * 0.5 + hidden.mean(1, keepdim=True) * 0.25 - (i + 1)
+            return h, c
+        return f
+
+    def single(j):
+        def f(x, temb, rope, s_txt, tok0=0):
+            rows = torch.arange(x.shape[1], dtype=x.dtype)[None, :, None]
+            return x * 1.25 + rows * 0.01 * (j + 1) + temb[:, None]
+        return f
+
+    ones = lambda e: torch.ones(e.shape[0], d, dtype=torch.float64)
+    m = types.SimpleNamespace(
+        time_embed=lambda e: 0.125 * ones(e), guidance_embed=lambda e: 0.0625 * ones(e),
+        pooled_embed=lambda p: p.sum(-1, keepdim=True).expand(-1, d),
+        x_embedder=lambda h: h * 2.0 + 1.0, context_embedder=lambda c: c * 3.0 - 1.0,
+        transformer_blocks=[double(i) for i in range(n_double)],
+        single_transformer_blocks=[single(j) for j in range(n_single)],
+        norm_out=types.SimpleNamespace(linear=lambda x: torch.cat([0.2 * x, 0.1 * x], dim=-1)),
+        proj_out=lambda h: h * 7.0)
+    cls = smod.SD3ShapedPipeline if model == "sd3" else fmod.FluxShapedPipeline
+    pipe = cls.__new__(cls)
+    pipe.model, pipe.stage_sliced, pipe.guidance_scale = m, False, 3.5
+    pipe.shape = types.SimpleNamespace(hidden=d)
+    pipe._positions = lambda n, device, dtype: 0.0
+    pipe._rope_and_first_token = lambda s_txt, device: (None, 0)
+    rt = types.SimpleNamespace(parallel_config=types.SimpleNamespace(pp_config=types.SimpleNamespace(
+        attn_layer_num_for_pp=None)), patch_mode=False, pipeline_patch_idx=0)
+    for mod in (smod, fmod):
+        monkeypatch.setattr(mod, "get_runtime_state", lambda: rt)
+    monkeypatch.setattr(fmod.kernels, "ln_modulate", lambda h, shift, scale: F.layer_norm(
+        h, (d,), eps=1e-6) * (1 + scale[:, None]) + shift[:, None])
+    monkeypatch.setattr(smod.ps, "get_pipeline_parallel_world_size", lambda: stages)
+    caches = [dict() for _ in range(stages)]
+    pooled = torch.from_numpy(z[f"{model}/pp{stages}/pooled"])
+    assert len(calls) == 4 * stages
+    for c in calls:
+        stage = c["stage"]
+        monkeypatch.setattr(smod.ps, "get_pipeline_parallel_rank", lambda stage=stage: stage)
+        monkeypatch.setattr(smod.ps, "is_pipeline_first_stage", lambda stage=stage: stage == 0)
+        monkeypatch.setattr(smod.ps, "is_pipeline_last_stage", lambda stage=stage: stage == stages - 1)
+        rt.patch_mode, rt.pipeline_patch_idx = c["mode"] == "patch", c["patch"] or 0
+        pipe.encoder_hidden_states_cache = caches[stage]            # one wrapper per stage in the reference
+        h_in, c_in = torch.from_numpy(z[c["key"] + "/in_h"]), torch.from_numpy(z[c["key"] + "/in_c"])
+        h, text = pipe._transformer(h_in, c_in, pooled, torch.full((2,), 0.5, dtype=torch.float64))
+        want = torch.from_numpy(z[c["key"] + "/out_h"])
+        assert h.shape == want.shape and torch.allclose(h, want, rtol=1e-12, atol=1e-12), c
+        if c["text_out"]:
+            want_c = torch.from_numpy(z[c["key"] + "/out_c"])
+            assert torch.allclose(text, want_c, rtol=1e-12, atol=1e-12), c
