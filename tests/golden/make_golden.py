@@ -164,6 +164,20 @@ def gen_bookkeeping(ref):
                     sigs[fn.name] = {"params": [a.arg for a in fn.args.args if a.arg != "self"],
                                      "coroutine": isinstance(fn, ast.AsyncFunctionDef)}
     out["worker_signatures"] = sigs
+    # --- the status record the engine polls: get_worker_state run on stand-in workers with a fixed clock ---------
+    clock = _NS(perf_counter=lambda: 1000.0)
+    state_fn, _ = lift(os.path.join(ref, "hetu_dit/worker/worker.py"), "get_worker_state", cls="Worker",
+                       namespace={"time": clock, "torch": _NS(cuda=_NS(memory_allocated=lambda: 0))})
+    out["worker_state"] = []
+    for states in ({}, {"running_task": "t1", "task_start_time": 990.0},
+                   {"running_task": "t2", "task_start_time": 990.0, "stage_name": "diffusion",
+                    "diffusion_start_time": 995.5, "estimated_running_time": 25.0},
+                   {"running_task": "t3", "task_start_time": 990.0, "stage_name": "diffusion",
+                    "diffusion_start_time": 995.5, "estimated_running_time": 4.0},
+                   {"running_task": "t4", "task_start_time": 990.0, "stage_name": "vae", "estimated_running_time": 10.0},
+                   {"stage_name": "diffusion", "diffusion_start_time": 1000.0, "estimated_running_time": 3.0}):
+        out["worker_state"].append({"now": 1000.0, "rank": 3, "states": states,
+                                    "result": state_fn(_NS(rank=3, states=dict(states)))})
     # --- operator / coordinator / cache surface: parameter names and literal defaults, as written in the source --
     def surface(rel, wanted):
         with open(os.path.join(ref, rel)) as f:

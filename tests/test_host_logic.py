@@ -801,3 +801,21 @@ def test_stage_forward_matches_reference_transformer_wrappers(model, stages, mon
         if c["text_out"]:
             want_c = torch.from_numpy(z[c["key"] + "/out_c"])
             assert torch.allclose(text, want_c, rtol=1e-12, atol=1e-12), c
+
+
+def test_worker_state_record_matches_reference(book, monkeypatch):
+    """get_worker_state against the reference's method (worker/worker.py:1527-1563) run on stand-in workers with a
+    fixed clock (tests/golden/make_golden.py): every key of the reference's record with the same value; this
+    repository's extra keys come on top."""
+    from hetu_dit_b200.worker import worker as wmod
+    cases = book["worker_state"]
+    assert len(cases) == 6
+    for c in cases:
+        w = wmod.Worker.__new__(wmod.Worker)
+        w.rank, w.states, w.device = c["rank"], dict(c["states"]), torch.device("cpu")
+        w.plan_ranks, w.cache, w.arena = [c["rank"]], None, None
+        monkeypatch.setattr(wmod.time, "perf_counter", lambda now=c["now"]: now)
+        got = w.get_worker_state()
+        for key, want in c["result"].items():
+            assert got[key] == want and type(got[key]) is type(want), (key, got[key], want, c["states"])
+        assert {"plan", "cached_blocks", "arena_bytes"} <= set(got)
