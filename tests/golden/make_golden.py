@@ -12,8 +12,8 @@ inputs and outputs are written out:
   bookkeeping.json   integer bookkeeping (patch metadata, rank groups, slice
                      ranges, migration plans, TP split table)
   rope.npz           apply_rotary_emb on seeded inputs
-  usp_<case>.npz     hetuDiT*LongContextAttention / ring attention / KV cache on
-                     CPU `gloo` ranks, fp32
+  usp_<case>.npz     hetuDiT*LongContextAttention / hetuDiTUlyssesAttention / ring attention / KV cache on
+                     CPU `gloo` ranks, fp32 (--only usp, or --only usp:<name prefix> for some of them)
   attn_processors.npz  the attention processors' __call__ (SD3, Flux double / single, CogVideoX,
                      HunyuanVideo double / single) on a stand-in Attention module, fp32
                      (--only attn_processors)
@@ -544,6 +544,10 @@ def _install_stub_packages(ref, state):
     sys.modules["hetu_dit.core.parallel.ring"].ring_flash_attn_func = ring.ring_flash_attn_func
     load("hetu_dit.core.parallel.hybrid.utils", "hetu_dit/core/parallel/hybrid/utils.py")
     hyb = load("hetu_dit.core.parallel.hybrid.attn_layer", "hetu_dit/core/parallel/hybrid/attn_layer.py")
+    # the Ulysses-only operator asks for the GPU's name when it is built (to rule out flash-attn on old parts)
+    torch.cuda.get_device_name = lambda *a, **k: "stand-in"
+    uly = load("hetu_dit.core.parallel.ulysses.attn_layer", "hetu_dit/core/parallel/ulysses/attn_layer.py")
+    hyb.hetuDiTUlyssesAttention = uly.hetuDiTUlyssesAttention
     return _PG, cm, ring, hyb
 
 
@@ -556,6 +560,13 @@ USP_CASES = {
     "joint_rear_u4": (4, 4, 1, "hetuDiTJointLongContextAttention", "rear", 16, 7, 8, 64, False),
     "joint_rear_r4": (4, 1, 4, "hetuDiTJointLongContextAttention", "rear", 20, 5, 2, 64, False),
     "kvcache_rear_u2": (2, 2, 1, "hetuDiTJointLongContextAttention", "rear", 32, 11, 4, 64, True),
+    # the Ulysses-only operator (ulysses/attn_layer.py), built the way the processors build it without flash-attn
+    "ulysses_plain_u2": (2, 2, 1, "hetuDiTUlyssesAttention", "none", 40, 0, 4, 64, False,
+                         {"use_fa": False, "use_kv_cache": False}),
+    "ulysses_rear_u2": (2, 2, 1, "hetuDiTUlyssesAttention", "rear", 36, 10, 4, 128, False,
+                        {"use_fa": False, "use_kv_cache": False}),
+    "ulysses_kvcache_front_u2": (2, 2, 1, "hetuDiTUlyssesAttention", "front", 32, 9, 4, 64, True,
+                                 {"use_fa": False, "use_kv_cache": True}),
 }
 
 
@@ -564,7 +575,8 @@ def _usp_worker(rank, world, ref, name, port, outdir):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    _, U, R, cls_name, strategy, S_loc, S_txt, H, D, kv_cache = USP_CASES[name]
+    _, U, R, cls_name, strategy, S_loc, S_txt, H, D, kv_cache = USP_CASES[name][:10]
+    init_kw = USP_CASES[name][10] if len(USP_CASES[name]) > 10 else {}
     state = _NS(sp_world=U * R, ulysses=U, runtime=None)
     PG, cm, ring_mod, hyb = _install_stub_packages(ref, state)
     # Ulysses groups: consecutive ranks; ring groups: stride U (parallel_state.py:679-712).
@@ -584,7 +596,7 @@ def _usp_worker(rank, world, ref, name, port, outdir):
     joint = {k: torch.randn(B, S_txt, H, D, generator=gen) for k in ("jq", "jk", "jv")} if S_txt else {}
     sl = slice(rank * S_loc, (rank + 1) * S_loc)
     q, k, v = (full[n][:, sl].contiguous() for n in ("q", "k", "v"))
-    layer = getattr(hyb, cls_name)()
+    layer = getattr(hyb, cls_name)(**init_kw)
     kwargs = {}
     if strategy != "none":
         kwargs = dict(joint_tensor_query=joint["jq"], joint_tensor_key=joint["jk"], joint_tensor_value=joint["jv"],
@@ -623,11 +635,13 @@ def _usp_worker(rank, world, ref, name, port, outdir):
     dist.destroy_process_group()
 
 
-def gen_usp(ref):
+def gen_usp(ref, only=None):
     import tempfile
     import torch.multiprocessing as mp
     port = 29611
     for name, spec in USP_CASES.items():
+        if only and not name.startswith(only):
+            continue
         world = spec[0]
         with tempfile.TemporaryDirectory() as tmp:
             mp.spawn(_usp_worker, args=(world, ref, name, port, tmp), nprocs=world, join=True)
@@ -1219,6 +1233,8 @@ if __name__ == "__main__":
         gen_rope(a.reference)
     if a.only in ("", "usp"):
         gen_usp(a.reference)
+    if a.only.startswith("usp:"):                       # e.g. --only usp:ulysses_
+        gen_usp(a.reference, a.only[4:])
     if a.only in ("", "scheduler_step"):
         gen_scheduler_step(a.reference)
     if a.only in ("", "stage_forward"):

@@ -280,3 +280,33 @@ def test_result_scatter_from_the_epilogue(kv_split, kv_interleave):
         assert torch.equal(bufs[u][:, J:, H:], plain[:, J + u * S:J + (u + 1) * S])
         assert bufs[u][:, :, :H].abs().max().item() == 0
     _check(plain, None, [jq.cpu(), iq.cpu()], [k.cpu()], [v.cpu()])
+
+
+@pytest.mark.parametrize("strategy", ["none", "rear", "front"])
+def test_ulysses_only_operator_on_one_rank(strategy):
+    """hetuDiTUlyssesAttention (the reference's core/parallel/ulysses/attn_layer.py:12-155) with an Ulysses group of
+    one rank: the text rows join the image rows behind ("rear") or in front ("front") in Q, K and V, no exchange."""
+    from hetu_dit_b200 import _C
+    from hetu_dit_b200.core.parallel import hetuDiTUlyssesAttention
+    gen = torch.Generator().manual_seed(31)
+    dev = torch.device("cuda:0")
+    q, k, v = (_mk((1, 200, 4, 64), torch.bfloat16, gen) for _ in range(3))
+    jq, jk, jv = (_mk((1, 24, 4, 64), torch.bfloat16, gen) for _ in range(3))
+    layer = hetuDiTUlyssesAttention(use_fa=False, use_kv_cache=False)
+    kw = {}
+    if strategy != "none":
+        kw = dict(joint_tensor_query=jq.to(dev), joint_tensor_key=jk.to(dev), joint_tensor_value=jv.to(dev),
+                  joint_strategy=strategy)
+    out = layer(None, q.to(dev), k.to(dev), v.to(dev), **kw)
+    torch.cuda.synchronize()
+    assert _C.device_status(0, clear=True)[0] == 0
+
+    def join(x, j):
+        return x if strategy == "none" else torch.cat([x, j] if strategy == "rear" else [j, x], dim=1)
+
+    want, _ = oa.attention_with_lse(join(q, jq), join(k, jk), join(v, jv), None)
+    cos, rel = oa.cosine_and_max_rel(out.cpu(), want)
+    assert out.shape == want.shape and cos >= COS_MIN and rel <= MAX_REL, (cos, rel)
+    with pytest.raises(ValueError):
+        layer(None, q.to(dev), k.to(dev), v.to(dev), joint_tensor_query=jq.to(dev), joint_tensor_key=jk.to(dev),
+              joint_tensor_value=jv.to(dev), joint_strategy="none")

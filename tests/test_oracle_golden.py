@@ -142,10 +142,13 @@ def test_usp_attention(path):
             kv = oa.kv_cache_update(cache, new_kv, True, n_patch, 1, tok_start, slice_dim=1, ulysses_world=U,
                                     sequence_parallel=True)
             k_all, v_all = torch.chunk(kv, 2, dim=-1)
-            q_loc = torch.cat([fq[:, r * tok:(r + 1) * tok], d["jq"]], dim=1)  # rear
-            q_g = torch.cat([torch.cat([fq[:, s * tok:(s + 1) * tok], d["jq"]], dim=1) for s in range(P)], dim=1)[:, :, hs]
-            k_g = torch.cat([k_all, d["jk"][:, :, hs]], dim=1)
-            v_g = torch.cat([v_all, d["jv"][:, :, hs]], dim=1)
+            def join(x, j):                      # text rows behind ("rear") or in front of the image rows
+                return torch.cat([x, j] if strategy == "rear" else [j, x], dim=1)
+
+            q_loc = join(fq[:, r * tok:(r + 1) * tok], d["jq"])
+            q_g = torch.cat([join(fq[:, s * tok:(s + 1) * tok], d["jq"]) for s in range(P)], dim=1)[:, :, hs]
+            k_g = join(k_all, d["jk"][:, :, hs])
+            v_g = join(v_all, d["jv"][:, :, hs])
             ctx = oa.sdpa(q_g, k_g, v_g)  # (B, P*(tok+S_t), hpr, D): this rank's head slice, all ranks' rows
             rows = tok + spec["s_txt"]
             for dst in range(P):
