@@ -3,10 +3,14 @@ with stale K/V), fp32, one process.
 
 TEST INFRASTRUCTURE ONLY. Nothing under hetu_dit_b200/ may import this module.
 
-Parity unpinned for the step and patch loops: the reference's pipelines subclass diffusers classes and
-diffusers is not installed, so they cannot be run to record fixtures. Pinned underneath: the patch index
-lists and the stale-KV update order (fixtures recorded from the reference's own runtime_state and
-CacheManager), attention and the rotary embedding.
+Parity unpinned for the numbers this file's step and patch loops produce: the reference's pipelines subclass
+diffusers classes and diffusers is not installed, so a whole denoising run cannot be recorded. Pinned underneath:
+the patch index lists and the stale-KV update order (fixtures recorded from the reference's own runtime_state and
+CacheManager), attention and the rotary embedding, the scheduler step. The ORDER of events of the loops
+(receives, forwards, scheduler steps, sends per stage) and the stage forward of the transformer wrappers are
+pinned separately, product against the reference's own loops run on recording stand-ins
+(tests/golden/pipefusion_order.json, stage_forward.npz); this file is the sequential model those pipelined
+runs must agree with numerically.
 
 Restates the schedule of the reference's SD3 pipeline
 (hetu_dit/model_executor/pipelines/pipeline_stable_diffusion_3.py: _sync_pipeline :1352-1467,

@@ -15,8 +15,11 @@ rotate the video rows only (:1075-1082, :1410-1434).
 Also the timed CPU baseline of bench.py.
 
 Parity unpinned for the block wiring (adaLN order, residuals, MLP): it restates diffusers' MMDiT / Flux
-blocks from the architecture description, and diffusers is not installed to record fixtures from. Pinned
-underneath: attention, RMSNorm + rotary embedding (fixtures recorded from the reference's own code).
+blocks from the architecture description, and diffusers is not installed to record fixtures from. Pinned:
+joint_attention / single_attention / cogvideox_attention against the __call__ of the reference's five
+attention processors run on a stand-in Attention module (tests/golden/attn_processors.npz: row order of
+text and image / video rows, which rows are rotated, RMSNorm or LayerNorm QK norm), and underneath them
+attention, RMSNorm + rotary embedding (fixtures recorded from the reference's own code).
 """
 import math
 
