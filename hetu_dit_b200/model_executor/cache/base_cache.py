@@ -342,9 +342,34 @@ class BaseBlockCache:
             self._release(self.cache.pop(victim)[0])
 
     # ---- the plan switch -----------------------------------------------------------------------------------
-    def adjust_pipeline(self, transformer: nn.Module, cpu_full_transformer: nn.Module, old_pp_range, new_pp_range,
-                        old_tp_range, new_tp_range=None, slice_bias: bool = True, peer_directories=None,
-                        resolve_ptr=None, component_name=None) -> nn.Module:
+    async def adjust_pipeline(self, transformer: Optional[nn.Module] = None,
+                              cpu_full_transformer: Optional[nn.Module] = None, old_pp_range: tuple = None,
+                              new_pp_range: tuple = None, old_tp_range: tuple = None, new_tp_range: tuple = None,
+                              slice_bias: bool = True, text_encoder: Optional[nn.Module] = None,
+                              cpu_full_text_encoder: Optional[nn.Module] = None, model: Optional[nn.Module] = None,
+                              cpu_full_model: Optional[nn.Module] = None, peer_directories=None, resolve_ptr=None,
+                              **kwargs) -> nn.Module:
+        """The reference's entry point (model_executor/cache/base_cache.py:243-282): a coroutine taking the model as
+        (transformer, cpu_full_transformer), (text_encoder, cpu_full_text_encoder) or (model, cpu_full_model), by
+        keyword or in this order. `peer_directories` and `resolve_ptr` are this repository's additions (where the
+        reference asks its peers over RPC, the caller passes what the peers published). The work is synchronous
+        GPU / host work: adjust_pipeline_sync()."""
+        component_name = kwargs.pop("component_name", None)
+        if model is None or cpu_full_model is None:
+            if transformer is not None and cpu_full_transformer is not None:
+                model, cpu_full_model, component_name = transformer, cpu_full_transformer, "Transformer"
+            elif text_encoder is not None and cpu_full_text_encoder is not None:
+                model, cpu_full_model, component_name = text_encoder, cpu_full_text_encoder, "TextEncoder"
+            else:
+                raise TypeError("adjust_pipeline requires either (transformer, cpu_full_transformer) or "
+                                "(text_encoder, cpu_full_text_encoder) or (model, cpu_full_model)")
+        return self.adjust_pipeline_sync(model, cpu_full_model, old_pp_range, new_pp_range, old_tp_range,
+                                         new_tp_range, slice_bias=slice_bias, peer_directories=peer_directories,
+                                         resolve_ptr=resolve_ptr, component_name=component_name)
+
+    def adjust_pipeline_sync(self, transformer: nn.Module, cpu_full_transformer: nn.Module, old_pp_range,
+                             new_pp_range, old_tp_range, new_tp_range=None, slice_bias: bool = True,
+                             peer_directories=None, resolve_ptr=None, component_name=None) -> nn.Module:
         """Brings `transformer`'s block lists to the new (PP, TP) ranges: reuse what is cached, pull what peers
         hold, read the rest from the CPU master copy. `peer_directories` = {rank: directory()} of the peers."""
         total = self.get_total_blocks(cpu_full_transformer)

@@ -164,9 +164,9 @@ class Worker:
         # memory released during the switch is parked and only handed back once every rank's pulls are done.
         self.cache.defer_release = self.world_size > 1
         try:
-            self.cache.adjust_pipeline(self.transformer, self.cpu_full_transformer, old["pipeline_parallel"],
-                                       new["pipeline_parallel"], old["tensor_parallel"], new["tensor_parallel"],
-                                       slice_bias=True, peer_directories=peer_dirs)
+            self.cache.adjust_pipeline_sync(self.transformer, self.cpu_full_transformer, old["pipeline_parallel"],
+                                            new["pipeline_parallel"], old["tensor_parallel"],
+                                            new["tensor_parallel"], slice_bias=True, peer_directories=peer_dirs)
             if self.world_size > 1:
                 torch.cuda.synchronize(self.device)
                 self.exchange(None)

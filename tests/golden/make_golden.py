@@ -201,7 +201,8 @@ def gen_bookkeeping(ref):
                                     defaults[a] = ast.literal_eval(d)
                                 except ValueError:
                                     defaults[a] = "<expression>"
-                        got[f"{node.name}.{fn.name}"] = {"params": args + kwonly, "defaults": defaults}
+                        got[f"{node.name}.{fn.name}"] = {"params": args + kwonly, "defaults": defaults,
+                                                         "coroutine": isinstance(fn, ast.AsyncFunctionDef)}
         return got
     api = {}
     api.update(surface("hetu_dit/core/parallel/hybrid/attn_layer.py", {
@@ -211,7 +212,19 @@ def gen_bookkeeping(ref):
     api.update(surface("hetu_dit/core/distributed/group_coordinator.py", {"PipelineGroupCoordinator": [
         "pipeline_send", "pipeline_isend", "pipeline_recv", "add_pipeline_recv_task", "recv_next",
         "get_pipeline_recv_data", "reset_buffer"]}))
-    api.update(surface("hetu_dit/core/resource_manager/cache_manager.py", {"CacheManager": ["update_and_get_kv_cache"]}))
+    api.update(surface("hetu_dit/core/resource_manager/cache_manager.py", {"CacheManager": [
+        "update_and_get_kv_cache", "register_cache_entry"]}))
+    api.update(surface("hetu_dit/model_executor/cache/base_cache.py", {"BaseBlockCache": ["adjust_pipeline"]}))
+    api.update(surface("hetu_dit/core/distributed/runtime_state.py", {"DiTRuntimeState": [
+        "set_input_parameters", "set_video_input_parameters", "set_patched_mode", "next_patch"]}))
+    api.update(surface("hetu_dit/core/distributed/group_coordinator.py", {"GroupCoordinator": ["all_gather"],
+                                                                          "PipelineGroupCoordinator": ["set_config"]}))
+    # module-level: the ring attention entry point
+    with open(os.path.join(ref, "hetu_dit/core/parallel/ring/ring_flash_attn.py")) as f:
+        fn = _find(ast.parse(f.read()), "ring_flash_attn_func")
+    names = [a.arg for a in fn.args.args]
+    api["ring_flash_attn_func"] = {"params": names, "coroutine": False, "defaults": {
+        a: ast.literal_eval(d) for a, d in zip(names[len(names) - len(fn.args.defaults):], fn.args.defaults)}}
     out["api_surface"] = api
     out["masked_orthogonal"] = [
         {"world": 24, "sizes": [2, 3, 4], "mask": m, "groups": mo(24, [2, 3, 4], m)}

@@ -704,12 +704,22 @@ def test_operator_coordinator_and_cache_surface_matches_reference():
     from hetu_dit_b200.core.resource_manager.cache_manager import CacheManager
     with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "bookkeeping.json")) as f:
         want = json.load(f)["api_surface"]
-    assert len(want) == 14
-    owners = {"PipelineGroupCoordinator": PipelineGroupCoordinator, "CacheManager": CacheManager}
+    assert len(want) == 23
+    from hetu_dit_b200.core.distributed.peer import PeerGroup
+    from hetu_dit_b200.core.distributed.runtime_state import DiTRuntimeState
+    from hetu_dit_b200.core.parallel.ring.ring_flash_attn import ring_flash_attn_func
+    from hetu_dit_b200.model_executor.cache.base_cache import BaseBlockCache
+    owners = {"PipelineGroupCoordinator": PipelineGroupCoordinator, "CacheManager": CacheManager,
+              "GroupCoordinator": PeerGroup,          # the groups the getters return here
+              "DiTRuntimeState": DiTRuntimeState, "BaseBlockCache": BaseBlockCache}
     for key, sig in want.items():
-        cls_name, meth = key.split(".")
-        cls = owners.get(cls_name) or getattr(P, cls_name)
-        params = [p for p in inspect.signature(getattr(cls, meth)).parameters.values() if p.name != "self"]
+        if "." in key:
+            cls_name, meth = key.split(".")
+            fn = getattr(owners.get(cls_name) or getattr(P, cls_name), meth)
+        else:
+            fn = {"ring_flash_attn_func": ring_flash_attn_func}[key]
+        assert inspect.iscoroutinefunction(fn) == sig["coroutine"], key
+        params = [p for p in inspect.signature(fn).parameters.values() if p.name != "self"]
         positional = [p for p in params if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD, p.KEYWORD_ONLY)]
         names = [p.name for p in positional]
         assert names[:len(sig["params"])] == sig["params"], (key, names)
@@ -819,3 +829,35 @@ def test_worker_state_record_matches_reference(book, monkeypatch):
         for key, want in c["result"].items():
             assert got[key] == want and type(got[key]) is type(want), (key, got[key], want, c["states"])
         assert {"plan", "cached_blocks", "arena_bytes"} <= set(got)
+
+
+def test_adjust_pipeline_coroutine_takes_the_reference_argument_forms():
+    """BaseBlockCache.adjust_pipeline (base_cache.py:243-282 of the reference): a coroutine that takes the model as
+    (transformer, cpu_full_transformer), (text_encoder, cpu_full_text_encoder) or (model, cpu_full_model), by keyword
+    or position, and raises TypeError without any of them."""
+    import asyncio
+    from hetu_dit_b200.model_executor.cache.base_cache import BaseBlockCache
+
+    class Recorder(BaseBlockCache):
+        def __init__(self):
+            self.calls = []
+
+        def adjust_pipeline_sync(self, *args, **kwargs):
+            self.calls.append((args, kwargs))
+            return args[0]
+
+    c = Recorder()
+    gpu, cpu = object(), object()
+    ranges = dict(old_pp_range=(0, 0), new_pp_range=(0.0, 0.5), old_tp_range=(0.0, 1.0), new_tp_range=(0.0, 0.5))
+    assert asyncio.run(c.adjust_pipeline(transformer=gpu, cpu_full_transformer=cpu, slice_bias=True, **ranges)) is gpu
+    assert asyncio.run(c.adjust_pipeline(text_encoder=gpu, cpu_full_text_encoder=cpu, **ranges)) is gpu
+    assert asyncio.run(c.adjust_pipeline(model=gpu, cpu_full_model=cpu, **ranges)) is gpu
+    assert asyncio.run(c.adjust_pipeline(gpu, cpu, (0, 0), (0.0, 0.5), (0.0, 1.0), (0.0, 0.5),
+                                         peer_directories={1: {}})) is gpu
+    labels = [kw["component_name"] for _, kw in c.calls]
+    assert labels == ["Transformer", "TextEncoder", None, "Transformer"]
+    for args, kw in c.calls:
+        assert args == (gpu, cpu, (0, 0), (0.0, 0.5), (0.0, 1.0), (0.0, 0.5)) and kw["slice_bias"] is True
+    assert c.calls[3][1]["peer_directories"] == {1: {}} and c.calls[0][1]["peer_directories"] is None
+    with pytest.raises(TypeError):
+        asyncio.run(c.adjust_pipeline(transformer=gpu, **ranges))

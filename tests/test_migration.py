@@ -101,6 +101,12 @@ def _tiny_block(hidden, seed):
     return blk.to(torch.bfloat16)
 
 
+def _adjust(cache, *args, **kwargs):
+    """The cache's public entry point is a coroutine, as in the reference (base_cache.py:243)."""
+    import asyncio
+    return asyncio.run(cache.adjust_pipeline(*args, **kwargs))
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("hidden", [128, 200])
 def test_migration_pull_and_backfill_bit_exact(hidden):
@@ -111,15 +117,15 @@ def test_migration_pull_and_backfill_bit_exact(hidden):
     master = _Model([_tiny_block(hidden, s) for s in range(4)])
     peer = TransformerBlockCache(device=dev)
     peer_model = _Model([])
-    peer.adjust_pipeline(peer_model, master, (0, 0), (0.0, 0.75), (0.0, 1.0), (0.0, 1.0))  # holds blocks 0-2 fully
+    _adjust(peer, peer_model, master, (0, 0), (0.0, 0.75), (0.0, 1.0), (0.0, 1.0))  # holds blocks 0-2 fully
     assert peer.active_block_indices == [0, 1, 2]
     me = TransformerBlockCache(device=dev)
     my_model = _Model([])
-    me.adjust_pipeline(my_model, master, (0, 0), (0.0, 0.5), (0.0, 0.5), (0.0, 0.5))  # blocks 0-1, lower half
+    _adjust(me, my_model, master, (0, 0), (0.0, 0.5), (0.0, 0.5), (0.0, 0.5))  # blocks 0-1, lower half
     torch.cuda.synchronize()
     # switch: all four blocks, TP range (0.25, 1.0): overlap reused, rest pulled from the peer, block 3 from CPU
     dirs = {1: peer.directory()}
-    me.adjust_pipeline(my_model, master, (0.0, 0.5), (0.0, 1.0), (0.0, 0.5), (0.25, 1.0), peer_directories=dirs)
+    _adjust(me, my_model, master, (0.0, 0.5), (0.0, 1.0), (0.0, 0.5), (0.25, 1.0), peer_directories=dirs)
     torch.cuda.synchronize()
     pieces = me._last_p2p_all_pieces
     assert {p.source_rank for p in pieces if p.block_index < 3} == {1}
@@ -145,6 +151,6 @@ def test_migration_pull_and_backfill_bit_exact(hidden):
                 assert torch.equal(sub.bias.cpu(), r.bias)
     # an unchanged plan is a no-op; the LRU keeps what the plan needs
     before = [id(b) for b in my_model.transformer_blocks]
-    me.adjust_pipeline(my_model, master, (0.0, 1.0), (0.0, 1.0), (0.25, 1.0), (0.25, 1.0))
+    _adjust(me, my_model, master, (0.0, 1.0), (0.0, 1.0), (0.25, 1.0), (0.25, 1.0))
     assert [id(b) for b in my_model.transformer_blocks] == before
     assert peer.find_sources(pieces) and set(peer.find_sources(pieces)) <= {p.uid for p in pieces if p.block_index < 3}
