@@ -56,6 +56,9 @@ class DiTShape:
     temb_dim: Optional[int] = None       # width of the timestep embedding; None = hidden
     stale_kv: bool = True                # attention layers keep a PipeFusion stale-KV buffer (image models); the
                                          # reference's video processors pass attn=None and never do
+    out_norm_scale_first: bool = True    # the output norm's projection splits into (scale, shift), as diffusers'
+                                         # AdaLayerNormContinuous does (SD3, Flux, HunyuanVideo); False: (shift,
+                                         # scale), as its AdaLayerNorm with chunk_dim=1 does (CogVideoX)
 
     def __post_init__(self):
         if self.text_first is None:
@@ -78,7 +81,7 @@ FLUX_DEV = DiTShape("flux.1-dev", 19, 38, 3072, 24, 128, 64, 4096, 768, True, (1
 # embedding on the video rows only, no pooled text vector, 512-wide timestep embedding
 COGVIDEOX_5B = DiTShape("cogvideox-1.5-5b", 42, 0, 3072, 48, 64, 128, 4096, 0, True, (16, 24, 24), False,
                         text_first=True, rope_on_text=False, qk_norm_kind="layer", block_kind="cogvideox", temb_dim=512,
-                        stale_kv=False)
+                        stale_kv=False, out_norm_scale_first=False)
 # 20 double + 40 single blocks, 24 x 128 heads, patch 1x2x2 (64 features per token), text rear
 HUNYUAN_VIDEO = DiTShape("hunyuanvideo", 20, 40, 3072, 24, 128, 64, 4096, 768, True, (16, 56, 56), True,
                          text_first=False, rope_on_text=False, stale_kv=False)
@@ -530,10 +533,11 @@ class ShapedDiT(nn.Module):
                 x = blk(x, temb, rope, S_txt, token_offset, text_offset, text_total, mods_of(n_double + i))
             hidden = x[:, S_txt:] if shp.text_first else x[:, :S_img]
         if ahead is not None:
-            shift, scale = mods_of(len(ahead) - 1)
+            first, second = mods_of(len(ahead) - 1)
             main.wait_stream(self._mod_stream[temb.device])
         else:
-            shift, scale = self.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
+            first, second = self.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
+        scale, shift = (first, second) if shp.out_norm_scale_first else (second, first)
         return self.proj_out(kernels.ln_modulate(hidden.contiguous(), shift, scale))
 
     def forward_graphed(self, latent_tokens, text_embeds, pooled, timestep, guidance=None, grid=None,

@@ -88,7 +88,8 @@ class FluxShapedPipeline(SD3ShapedPipeline):
                 x = block(x, temb, rope, s_txt, tok0)
             encoder_hidden_states, hidden_states = x[:, :s_txt], x[:, s_txt:]
         if ps.is_pipeline_last_stage():
-            shift, scale = m.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
+            first, second = m.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
+            scale, shift = (first, second) if self.shape.out_norm_scale_first else (second, first)
             hidden_states = m.proj_out(kernels.ln_modulate(hidden_states.contiguous(), shift, scale))
         return hidden_states, encoder_hidden_states
 

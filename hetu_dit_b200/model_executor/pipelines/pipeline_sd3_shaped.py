@@ -116,7 +116,8 @@ class SD3ShapedPipeline:
             else:
                 hidden_states, encoder_hidden_states = block(hidden_states, encoder_hidden_states, temb, None)
         if ps.is_pipeline_last_stage():
-            shift, scale = m.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
+            first, second = m.norm_out.linear(F.silu(temb)).chunk(2, dim=-1)
+            scale, shift = (first, second) if self.shape.out_norm_scale_first else (second, first)
             hidden_states = m.proj_out(_modulate(F.layer_norm(hidden_states, (d,), eps=1e-6), shift, scale))
         return hidden_states, encoder_hidden_states
 

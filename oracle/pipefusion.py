@@ -106,7 +106,8 @@ def denoise(sd, shape, latents, prompt_embeds, pooled, num_steps, guidance_scale
             else:
                 hidden, _ = osd.joint_block(sd, f"transformer_blocks.{l}", hidden, text_cache[l], temb, None, H, D,
                                             "rear", kv_hook=hook)
-        shift, scale = osd._lin(sd, "norm_out.linear", F.silu(temb)).chunk(2, dim=-1)
+        first, second = osd._lin(sd, "norm_out.linear", F.silu(temb)).chunk(2, dim=-1)
+        scale, shift = (first, second) if shape.out_norm_scale_first else (second, first)
         out = osd._lin(sd, "proj_out", osd._mod(F.layer_norm(hidden, (d,), eps=1e-6), shift, scale))
         uncond, cond = out.chunk(2)
         return uncond + guidance_scale * (cond - uncond)
@@ -183,7 +184,8 @@ def denoise_flux(sd, shape, latents, prompt_embeds, pooled, num_steps, guidance,
                 xs = osd.single_block(sd, f"single_transformer_blocks.{g - n_double}", torch.cat([context, hidden], 1),
                                       temb, rope, H, D, text_len=S_txt, row0=S_txt + lo, kv_hook=hook)
                 context, hidden = xs[:, :S_txt], xs[:, S_txt:]
-        shift, scale = osd._lin(sd, "norm_out.linear", F.silu(temb)).chunk(2, dim=-1)
+        first, second = osd._lin(sd, "norm_out.linear", F.silu(temb)).chunk(2, dim=-1)
+        scale, shift = (first, second) if shape.out_norm_scale_first else (second, first)
         return osd._lin(sd, "proj_out", osd._mod(F.layer_norm(hidden, (d,), eps=1e-6), shift, scale))
 
     for i in range(num_steps):

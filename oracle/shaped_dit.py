@@ -298,6 +298,9 @@ def denoise_step(sd, shape, latent_tokens, text_embeds, pooled, timestep, guidan
                 block_outputs.append(xs[:, S_txt:] if shape.text_first else xs[:, :S_img])
             n += 1
         hidden = xs[:, S_txt:] if shape.text_first else xs[:, :S_img]
-    shift, scale = _lin(sd, "norm_out.linear", F.silu(temb)).chunk(2, dim=-1)
+    # the output norm's projection splits into (scale, shift) in diffusers' AdaLayerNormContinuous (SD3, Flux,
+    # HunyuanVideo) and into (shift, scale) in its AdaLayerNorm with chunk_dim=1 (CogVideoX)
+    first, second = _lin(sd, "norm_out.linear", F.silu(temb)).chunk(2, dim=-1)
+    scale, shift = (first, second) if shape.out_norm_scale_first else (second, first)
     hidden = _mod(F.layer_norm(hidden, (d,), eps=1e-6), shift, scale)
     return _lin(sd, "proj_out", hidden)

@@ -779,12 +779,12 @@ def test_stage_forward_matches_reference_transformer_wrappers(model, stages, mon
         x_embedder=lambda h: h * 2.0 + 1.0, context_embedder=lambda c: c * 3.0 - 1.0,
         transformer_blocks=[double(i) for i in range(n_double)],
         single_transformer_blocks=[single(j) for j in range(n_single)],
-        norm_out=types.SimpleNamespace(linear=lambda x: torch.cat([0.2 * x, 0.1 * x], dim=-1)),
+        norm_out=types.SimpleNamespace(linear=lambda x: torch.cat([0.1 * x, 0.2 * x], dim=-1)),    # (scale, shift)
         proj_out=lambda h: h * 7.0)
     cls = smod.SD3ShapedPipeline if model == "sd3" else fmod.FluxShapedPipeline
     pipe = cls.__new__(cls)
     pipe.model, pipe.stage_sliced, pipe.guidance_scale = m, False, 3.5
-    pipe.shape = types.SimpleNamespace(hidden=d)
+    pipe.shape = types.SimpleNamespace(hidden=d, out_norm_scale_first=True)
     pipe._positions = lambda n, device, dtype: 0.0
     pipe._rope_and_first_token = lambda s_txt, device: (None, 0)
     rt = types.SimpleNamespace(parallel_config=types.SimpleNamespace(pp_config=types.SimpleNamespace(
