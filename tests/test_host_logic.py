@@ -220,6 +220,14 @@ def test_operator_argument_errors():
         ring_flash_attn_func(q, q, q, joint_strategy="rear")
     with pytest.raises(AssertionError):
         ring_flash_attn_func(q, q, q, alibi_slopes=torch.zeros(2))
+    # the Ulysses-only operator (ulysses/attn_layer.py:69-83 of the reference): same two ValueErrors
+    from hetu_dit_b200.core.parallel import hetuDiTUlyssesAttention
+    uly = hetuDiTUlyssesAttention(use_fa=False, use_kv_cache=False)
+    for bad in ("none", "middle"):
+        with pytest.raises(ValueError):
+            uly(None, q, q, q, joint_tensor_query=q, joint_tensor_key=q, joint_tensor_value=q, joint_strategy=bad)
+    with pytest.raises(ValueError):
+        hetuDiTUlyssesAttention(scatter_idx=1, gather_idx=2)
 
 
 def _gloo_worker(rank, world, port, errq):
